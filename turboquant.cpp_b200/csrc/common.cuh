@@ -1,0 +1,98 @@
+// Shared helpers of the sm_100a kernels: element types, reductions, error reporting.
+//
+// Every kernel file exports plain C launchers (extern "C", called through ctypes with raw
+// device pointers and the caller's stream).  A launcher returns 0, or a negative code after
+// storing a message that tq_last_error() of the same library returns; it never falls back to
+// another implementation and never returns a result for sizes it cannot handle.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define TQ_EXPORT extern "C" __attribute__((visibility("default")))
+
+// element type codes shared with the Python side
+#define TQ_F32 0
+#define TQ_BF16 1
+
+static thread_local char tq_error_message[512] = "";
+
+#define TQ_FAIL(code, ...)                                                   \
+    do {                                                                     \
+        snprintf(tq_error_message, sizeof(tq_error_message), __VA_ARGS__);   \
+        return (code);                                                       \
+    } while (0)
+
+#define TQ_REQUIRE(cond, ...)                                                \
+    do {                                                                     \
+        if (!(cond)) TQ_FAIL(-2, __VA_ARGS__);                               \
+    } while (0)
+
+#define TQ_CHECK_LAUNCH(name)                                                \
+    do {                                                                     \
+        cudaError_t e__ = cudaGetLastError();                                \
+        if (e__ != cudaSuccess)                                              \
+            TQ_FAIL(-1, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define TQ_DEFINE_LAST_ERROR                                                 \
+    TQ_EXPORT const char* tq_last_error() { return tq_error_message; }
+
+__device__ __forceinline__ float tq_to_float(float v) { return v; }
+__device__ __forceinline__ float tq_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T tq_from_float(float v);
+template <> __device__ __forceinline__ float tq_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 tq_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float tq_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float tq_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float tq_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = tq_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = tq_warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float tq_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = tq_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = tq_warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Dispatch on an element type code: TQ_F32 -> float, TQ_BF16 -> __nv_bfloat16.
+#define TQ_DISPATCH(code, T, ...)                                            \
+    do {                                                                     \
+        if ((code) == TQ_F32) { using T = float; __VA_ARGS__; }              \
+        else if ((code) == TQ_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else TQ_FAIL(-2, "unknown element type code %d", (int)(code));       \
+    } while (0)

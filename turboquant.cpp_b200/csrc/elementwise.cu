@@ -1,0 +1,142 @@
+// Row-wise kernels: embedding rows, RMSNorm (with the residual sum and a row gather fused in),
+// SiLU(gate)*up, row gather.  All statistics and the residual sum are computed in fp32.
+//
+// Formulas as the reference computes them on the CPU:
+//   embedding  x = table[token]                       src/engine/tq_transformer.c:2298-2329
+//   rmsnorm    ss = sum(x^2)/n + eps; y = x*(1/sqrt(ss))*w   src/engine/tq_ops.c:1373-1410
+//   silu       x/(1+exp(-x))                          src/engine/tq_ops.c:1454-1478
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+// ---------------------------------------------------------------------------------------
+// x[t, :] = table[tokens[t], :]  (fp32 residual stream out)
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                  float* __restrict__ x, int H) {
+    const int t = blockIdx.x;
+    const TW* row = table + (size_t)tokens[t] * H;
+    float* out = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = tq_to_float(row[i]);
+}
+
+TQ_EXPORT int tq_embed_rows(const int* tokens, const void* table, int table_dtype, float* x,
+                            int T, int H, cudaStream_t stream) {
+    if (T == 0) return 0;
+    TQ_REQUIRE(T > 0 && H > 0, "embed_rows: bad sizes T=%d H=%d", T, H);
+    const int threads = H >= 1024 ? 256 : 128;
+    TQ_DISPATCH(table_dtype, TW,
+        embed_rows_kernel<TW><<<T, threads, 0, stream>>>(tokens, (const TW*)table, x, H));
+    TQ_CHECK_LAUNCH("embed_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm over rows of the fp32 residual stream.
+//   y given:    the norm is taken of x + y (the residual sum, in fp32)
+//   rows given: the norm of row rows[r] is written to out[r] and x is not changed;
+//               otherwise row r goes to out[r] and, with y, the sum is written back into x
+// ---------------------------------------------------------------------------------------
+template <typename TY, typename TW, typename TO>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
+                               const TW* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + src * H;
+    const TY* yr = y ? y + src * H : nullptr;
+    const bool write_back = y && !rows;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (yr) v += tq_to_float(yr[i]);
+        if (write_back) xr[i] = v;
+        ss += v * v;
+    }
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (yr && !write_back) v += tq_to_float(yr[i]);
+        o[i] = tq_from_float<TO>(v * rs * tq_to_float(w[i]));
+    }
+}
+
+TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, const void* w, int w_dtype,
+                         void* out, int out_dtype, int R, int H, float eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+        (rmsnorm_kernel<TY, TW, TO><<<R, threads, 0, stream>>>(x, (const TY*)y, rows, (const TW*)w,
+                                                              (TO*)out, H, eps)))));
+    TQ_CHECK_LAUNCH("rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// x[r] += y[r]  (fp32 residual stream; used where no norm follows the sum)
+// ---------------------------------------------------------------------------------------
+template <typename TY>
+__global__ void residual_add_kernel(float* __restrict__ x, const TY* __restrict__ y, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] += tq_to_float(y[i]);
+}
+
+TQ_EXPORT int tq_residual_add(float* x, const void* y, int y_dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TQ_DISPATCH(y_dtype, TY,
+        residual_add_kernel<TY><<<(int)blocks, threads, 0, stream>>>(x, (const TY*)y, (size_t)n));
+    TQ_CHECK_LAUNCH("residual_add");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// h[t, i] = silu(gu[t, i]) * gu[t, I + i]   (gate rows first, then up rows)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int I) {
+    const int t = blockIdx.x;
+    const T* g = gu + (size_t)t * 2 * I;
+    T* o = h + (size_t)t * I;
+    for (int i = threadIdx.x; i < I; i += blockDim.x) {
+        const float a = tq_to_float(g[i]), b = tq_to_float(g[I + i]);
+        o[i] = tq_from_float<T>(a / (1.0f + expf(-a)) * b);
+    }
+}
+
+TQ_EXPORT int tq_silu_mul(const void* gu, void* h, int dtype, int T_, int I, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);
+    TQ_DISPATCH(dtype, T, silu_mul_kernel<T><<<T_, 256, 0, stream>>>((const T*)gu, (T*)h, I));
+    TQ_CHECK_LAUNCH("silu_mul");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[r, :] = in[idx[r] / divisor, :]   (expert-sorted copies of token rows: divisor = top-k)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ idx, int divisor,
+                                   T* __restrict__ out, int H) {
+    const int r = blockIdx.x;
+    const T* src = in + (size_t)(idx[r] / divisor) * H;
+    T* dst = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* out, int dtype, int R, int H,
+                             cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(R > 0 && H > 0 && divisor > 0, "gather_rows: bad sizes R=%d H=%d divisor=%d", R, H, divisor);
+    TQ_DISPATCH(dtype, T,
+        gather_rows_kernel<T><<<R, 256, 0, stream>>>((const T*)in, idx, divisor, (T*)out, H));
+    TQ_CHECK_LAUNCH("gather_rows");
+    return 0;
+}

@@ -1,0 +1,330 @@
+// Mixture-of-experts feed-forward: router, expert-sorted row layout, exact grouped GEMM, combine.
+//
+//   tq_router_topk    logits = Wr x (fp32), softmax over all experts, k largest (ties to the lowest
+//                     index), optional renormalisation; the shared expert's sigmoid gate in the
+//                     same pass
+//   tq_moe_align      stable counting sort of (token, choice) pairs by expert, and the list of row
+//                     tiles the grouped GEMMs walk
+//   tq_grouped_gemm   C[rows of expert e] = A[rows] W[e]^T, fp32 accumulation on CUDA cores (the
+//                     exact path; any sizes), optionally with SiLU(gate)*up fused in
+//   tq_moe_combine    y[t] = sum_j w[t,j] Y[row(t,j)] + s[t] Y_shared[t], in the order chosen
+//
+// Formulas as the reference computes them on the CPU (src/engine/tq_moe.c): router logits
+// :612-618; selection of k experts :630-646 (the reference takes a softmax over the k picked
+// logits :659-678, which is the renormalised case here, and breaks exact ties toward the highest
+// index); experts g = Wg x, u = Wu x, h = silu(g)*u, o = Wd h, out += w*o :975-999 (exact exp
+// here, a fast approximation there :42-92); shared expert scaled by sigmoid(w_sg . x) :1006-1058;
+// accumulation order: chosen experts first, shared expert last.
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+#define ROUTER_THREADS 128
+#define ROUTER_MAX_EXPERTS 4096
+
+// ---------------------------------------------------------------------------------------
+// Router: one block per token.
+// ---------------------------------------------------------------------------------------
+template <typename TA, typename TW>
+__global__ void router_topk_kernel(const TA* __restrict__ x, const TW* __restrict__ wr,
+                                   const TW* __restrict__ wsg, int* __restrict__ ids, float* __restrict__ wts,
+                                   float* __restrict__ shared_scale, int H, int E, int k, int renorm) {
+    extern __shared__ float s_logit[];          // E logits, 1 for the shared gate, k picked weights
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const TA* xr = x + (size_t)t * H;
+    const int rows = E + (wsg ? 1 : 0);
+    float* s_pick = s_logit + E + 1;
+    for (int e = warp; e < rows; e += nwarps) {
+        const TW* w = e < E ? wr + (size_t)e * H : wsg;
+        float s = 0.f;
+        for (int i = lane; i < H; i += 32) s += tq_to_float(xr[i]) * tq_to_float(w[i]);
+        s = tq_warp_sum(s);
+        if (lane == 0) s_logit[e] = s;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (wsg && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
+    mx = tq_warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
+    sum = tq_warp_sum(sum);
+    float picked_sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = s_logit[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }   // NaN never wins
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) best_e = j;   // every remaining logit is NaN: keep indices valid
+        const float p = expf(best - mx) / sum;
+        picked_sum += p;                        // identical in every lane
+        if (lane == 0) {
+            ids[(size_t)t * k + j] = best_e;
+            s_pick[j] = p;
+            s_logit[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int j = lane; j < k; j += 32)
+        wts[(size_t)t * k + j] = renorm ? s_pick[j] / picked_sum : s_pick[j];
+}
+
+TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
+                             int* ids, float* wts, float* shared_scale, int T_, int H, int E, int k,
+                             int renorm, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
+    TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
+    TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
+    const size_t smem = (size_t)(E + 1 + k) * sizeof(float);
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
+        (router_topk_kernel<TA, TW><<<T_, ROUTER_THREADS, smem, stream>>>(
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, ids, wts, shared_scale, H, E, k, renorm))));
+    TQ_CHECK_LAUNCH("router_topk");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Expert-sorted layout.  Pair p = t*k + j chose expert ids[p].  Rows of the sorted layout:
+// expert 0's pairs in pair order, then expert 1's, …  Outputs:
+//   sorted_pair[row] = p, row_of_pair[p] = row, expert_offset[e] (E+1 entries),
+//   tiles of at most tile_rows rows that never span two experts: tile_expert, tile_row0,
+//   tile_count, and n_tiles[0].
+// Two kernels, one block per expert each: count, then fill (each block sums the counts before it).
+// ---------------------------------------------------------------------------------------
+#define ALIGN_THREADS 256
+
+__global__ void moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
+    __shared__ int s_c[ALIGN_THREADS / 32];
+    const int e = blockIdx.x;
+    int c = 0;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) c += ids[p] == e;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) s_c[warp] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tot = 0;
+        for (int w = 0; w < ALIGN_THREADS / 32; ++w) tot += s_c[w];
+        counts[e] = tot;
+    }
+}
+
+__global__ void moe_fill_kernel(const int* __restrict__ ids, int P, int E, int tile_rows,
+                                const int* __restrict__ counts, int* __restrict__ sorted_pair,
+                                int* __restrict__ row_of_pair, int* __restrict__ expert_offset,
+                                int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                int* __restrict__ tile_count, int* __restrict__ n_tiles) {
+    __shared__ int s_warp[ALIGN_THREADS / 32];
+    __shared__ int s_base, s_row0, s_tile0;
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        int row0 = 0, tile0 = 0;
+        for (int i = 0; i < e; ++i) {
+            row0 += counts[i];
+            tile0 += (counts[i] + tile_rows - 1) / tile_rows;
+        }
+        s_row0 = row0;
+        s_tile0 = tile0;
+        s_base = 0;
+        expert_offset[e] = row0;
+        if (e == E - 1) expert_offset[E] = row0 + counts[e];
+    }
+    __syncthreads();
+    const int row0 = s_row0;
+    for (int p0 = 0; p0 < P; p0 += ALIGN_THREADS) {
+        const int p = p0 + threadIdx.x;
+        const bool mine = p < P && ids[p] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) s_warp[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += s_warp[w];
+        const int rank = s_base + before + __popc(ballot & ((1u << lane) - 1u));
+        if (mine) {
+            sorted_pair[row0 + rank] = p;
+            row_of_pair[p] = row0 + rank;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < ALIGN_THREADS / 32; ++w) tot += s_warp[w];
+            s_base += tot;
+        }
+        __syncthreads();
+    }
+    const int count = counts[e];
+    const int my_tiles = (count + tile_rows - 1) / tile_rows;
+    for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
+        tile_expert[s_tile0 + i] = e;
+        tile_row0[s_tile0 + i] = row0 + i * tile_rows;
+        tile_count[s_tile0 + i] = min(tile_rows, count - i * tile_rows);
+    }
+    if (e == E - 1 && threadIdx.x == 0) n_tiles[0] = s_tile0 + my_tiles;
+}
+
+TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int* counts, int* sorted_pair,
+                           int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0,
+                           int* tile_count, int* n_tiles, cudaStream_t stream) {
+    TQ_REQUIRE(P >= 0 && E >= 1 && tile_rows >= 1, "moe_align: bad sizes P=%d E=%d tile_rows=%d", P, E, tile_rows);
+    moe_count_kernel<<<E, ALIGN_THREADS, 0, stream>>>(ids, P, counts);
+    TQ_CHECK_LAUNCH("moe_count");
+    moe_fill_kernel<<<E, ALIGN_THREADS, 0, stream>>>(ids, P, E, tile_rows, counts, sorted_pair, row_of_pair,
+                                                     expert_offset, tile_expert, tile_row0, tile_count, n_tiles);
+    TQ_CHECK_LAUNCH("moe_fill");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Exact grouped GEMM on CUDA cores.  A [R, K]; W [G, Nw, K] with Nw = N (plain) or 2N (SwiGLU:
+// gate rows [0, N), up rows [N, 2N)); C [R, N].  Rows come in tiles (tile_expert/row0/count);
+// with tile_expert == null there is one group and tile b covers rows [b*64, b*64+64).
+// Every output element is one sequential fp32 sum over K, so it does not depend on the tile the
+// row falls in.
+// ---------------------------------------------------------------------------------------
+#define GG_BM 64
+#define GG_BN 64
+#define GG_BK 16
+
+template <typename TA, typename TW, typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ C,
+                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ tile_count, const int* __restrict__ n_tiles,
+                    int R, int N, int K) {
+    __shared__ float As[GG_BK][GG_BM + 4];
+    __shared__ float Ws[SWIGLU ? 2 : 1][GG_BK][GG_BN + 4];
+    int expert = 0, row0, rows;
+    if (tile_expert) {
+        if ((int)blockIdx.y >= n_tiles[0]) return;
+        expert = tile_expert[blockIdx.y];
+        row0 = tile_row0[blockIdx.y];
+        rows = tile_count[blockIdx.y];
+    } else {
+        row0 = blockIdx.y * GG_BM;
+        if (row0 >= R) return;
+        rows = min(GG_BM, R - row0);
+    }
+    const int n0 = blockIdx.x * GG_BN;
+    const int Nw = SWIGLU ? 2 * N : N;
+    const TW* Wg = W + (size_t)expert * Nw * K;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;     // 16 x 16 threads, 4 x 4 outputs each
+    float acc[SWIGLU ? 2 : 1][4][4];
+#pragma unroll
+    for (int s = 0; s < (SWIGLU ? 2 : 1); ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[s][i][j] = 0.f;
+
+    const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;  // loader: row 0..63, k 0,4,8,12
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int kk = k0 + lk + u;
+            float a = 0.f;
+            if (lr < rows && kk < K) a = tq_to_float(A[(size_t)(row0 + lr) * K + kk]);
+            As[lk + u][lr] = a;
+            const int n = n0 + lr;
+            float w0 = 0.f;
+            if (n < N && kk < K) w0 = tq_to_float(Wg[(size_t)n * K + kk]);
+            Ws[0][lk + u][lr] = w0;
+            if (SWIGLU) {
+                float w1 = 0.f;
+                if (n < N && kk < K) w1 = tq_to_float(Wg[(size_t)(N + n) * K + kk]);
+                Ws[SWIGLU ? 1 : 0][lk + u][lr] = w1;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int s = 0; s < (SWIGLU ? 2 : 1); ++s) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Ws[s][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[s][i][j] = fmaf(a[i], b[j], acc[s][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v;
+            if (SWIGLU) {
+                const float g = acc[0][i][j], u = acc[SWIGLU ? 1 : 0][i][j];
+                v = g / (1.0f + expf(-g)) * u;
+            } else {
+                v = acc[0][i][j];
+            }
+            C[(size_t)(row0 + r) * N + n] = tq_from_float<TO>(v);
+        }
+    }
+}
+
+TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                              const int* tile_expert, const int* tile_row0, const int* tile_count,
+                              const int* n_tiles, int max_tiles, int R, int N, int K, int swiglu,
+                              cudaStream_t stream) {
+    if (R == 0 || max_tiles == 0) return 0;
+    TQ_REQUIRE(R > 0 && N > 0 && K > 0, "grouped_gemm: bad sizes R=%d N=%d K=%d", R, N, K);
+    const int by = tile_expert ? max_tiles : (R + GG_BM - 1) / GG_BM;
+    TQ_REQUIRE(by <= 65535, "grouped_gemm: %d row tiles exceed the grid limit", by);
+    dim3 grid((N + GG_BN - 1) / GG_BN, by);
+#define GG_LAUNCH(SW)                                                                                   \
+    TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                          \
+        (grouped_gemm_kernel<TA, TW, TO, SW><<<grid, 256, 0, stream>>>(                                 \
+            (const TA*)A, (const TW*)W, (TO*)C, tile_expert, tile_row0, tile_count, n_tiles, R, N, K)))))
+    if (swiglu) { GG_LAUNCH(true); } else { GG_LAUNCH(false); }
+#undef GG_LAUNCH
+    TQ_CHECK_LAUNCH("grouped_gemm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// y[t] = sum_j wts[t,j] * Y[row_of_pair[t*k+j]] + shared_scale[t] * Ys[t]   (fp32)
+// ---------------------------------------------------------------------------------------
+__global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ wts, const float* __restrict__ Ys,
+                                   const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = 0.f;
+        for (int j = 0; j < k; ++j)
+            v += wts[(size_t)t * k + j] * Y[(size_t)row_of_pair[(size_t)t * k + j] * H + i];
+        if (Ys) v += (shared_scale ? shared_scale[t] : 1.0f) * Ys[(size_t)t * H + i];
+        y[(size_t)t * H + i] = v;
+    }
+}
+
+TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float* wts, const float* Ys,
+                             const float* shared_scale, float* y, int T_, int H, int k, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(H > 0 && k >= 0, "moe_combine: bad sizes H=%d k=%d", H, k);
+    moe_combine_kernel<<<T_, 256, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
+    TQ_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

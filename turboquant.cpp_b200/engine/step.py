@@ -1,0 +1,126 @@
+"""The step function: one batch of sequences, the tokens each brings, logits at the wanted places.
+
+A step runs only the tokens it is given, packed one sequence after another with no padding, on
+top of what earlier steps left in the cache.  Sequences of one batch usually start together with
+whole prompts of unequal lengths and then go on by one token each; the step itself accepts any
+cut (a prompt in pieces, one token at a time).  The logits at a position do not depend on the cut
+or on the batch beyond rounding.
+
+The reference's step is one token of one sequence (`tq_forward(model, state, token, pos)`,
+include/turboquant/tq_engine.h:529); its only multi-token path handles one sequence, dense layers
+only, and returns the last row's logits (src/engine/tq_transformer.c:3049-3592, MoE refused at
+:3066-3067).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import CacheFull, PagedCache, Sequence_
+from ..csrc.build import ensure_built
+from ..parts.base import StepContext
+
+
+class StepError(ValueError):
+    """A step that cannot run: bad token ids, places, or a sequence beyond the model's positions."""
+
+
+@dataclass
+class StepEntry:
+    seq: Sequence_
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # places among `tokens` whose logits are asked for
+
+
+class Engine:
+    """A model, its cache and the step function."""
+
+    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, device="cuda:0"):
+        self.model = model
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device; there is no CPU path")
+        self.act_dtype = model.dtype
+        ensure_built(model.kernels())
+        self.cache = PagedCache(model.cache_needs(), model.state_needs(), [e.cache_of for e in model.schedule],
+                                max_tokens, self.act_dtype, self.device, max_slots=max_slots)
+        self.debug: Optional[Dict[str, Any]] = None
+        self.steps_run = 0
+
+    # ---- sequences ------------------------------------------------------------------------------
+    def open(self) -> Sequence_:
+        return self.cache.open()
+
+    def close(self, seq: Sequence_) -> None:
+        self.cache.close(seq)
+
+    # ---- one step -------------------------------------------------------------------------------
+    def _check(self, entries: Sequence[StepEntry]) -> None:
+        V, maxpos = self.model.vocab_size, self.model.max_position
+        seen = set()
+        for e in entries:
+            if e.seq.id in seen:
+                raise StepError(f"sequence {e.seq.id} appears twice in one step")
+            seen.add(e.seq.id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"sequence {e.seq.id} brings no token to the step")
+            if e.seq.length + n > maxpos:
+                raise StepError(f"sequence {e.seq.id} would reach {e.seq.length + n} tokens; the model's "
+                                f"max_position_embeddings is {maxpos}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"sequence {e.seq.id}: wanted place {w} is outside its {n} tokens")
+
+    def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[torch.Tensor]]:
+        """Packs the step's metadata and sends it to the device in one copy."""
+        B = len(entries)
+        q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int64)
+        T = int(q_lens.sum())
+        starts = np.array([e.seq.length for e in entries], dtype=np.int64)
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu[1:])
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
+        V = self.model.vocab_size
+        if tokens.size and (tokens.min() < 0 or tokens.max() >= V):
+            bad = int(tokens[(tokens < 0) | (tokens >= V)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary (0..{V - 1})")
+        seq_of_token = np.repeat(np.arange(B, dtype=np.int64), q_lens)
+        positions = np.arange(T, dtype=np.int64) - cu[:-1][seq_of_token] + starts[seq_of_token]
+        want = np.array([cu[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
+        slots = np.array([e.seq.slot for e in entries], dtype=np.int64)
+        tables = self.cache.page_tables([e.seq for e in entries])
+        fields = [tokens, positions, seq_of_token, cu, starts, slots, want] + [t.reshape(-1) for t in tables]
+        sizes = [f.size for f in fields]
+        packed = torch.from_numpy(np.concatenate(fields).astype(np.int32))
+        if packed.numel():
+            packed = packed.pin_memory()
+        dev = packed.to(self.device, non_blocking=True)
+        parts = torch.split(dev, sizes)
+        dev_tables = [parts[7 + g].view(tables[g].shape) for g in range(len(tables))]
+        ctx = StepContext(
+            n_tokens=T, n_seqs=B, tokens=parts[0], positions=parts[1], seq_of_token=parts[2], cu_seqlens=parts[3],
+            seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=int(want.size),
+            max_q_len=int(q_lens.max()), max_kv_len=int((starts + q_lens).max()), act_dtype=self.act_dtype,
+            device=self.device, host_q_lens=[int(n) for n in q_lens], host_slots=[int(s) for s in slots],
+            debug=self.debug)
+        return ctx, dev_tables
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one step.  Returns float32 logits [number of wanted places, vocab] on the device, in
+        the order of the entries and of each entry's `want`; None if nothing is wanted."""
+        if not entries:
+            return None
+        self._check(entries)
+        seqs = [e.seq for e in entries]
+        n_new = [len(e.tokens) for e in entries]
+        self.cache.reserve(seqs, n_new)          # raises CacheFull before anything is written
+        ctx, dev_tables = self.build_context(entries)
+        with torch.cuda.device(self.device):
+            logits = self.model.forward(ctx, self.cache.layer_caches(dev_tables))
+        self.cache.commit(seqs, n_new)
+        self.steps_run += 1
+        return logits

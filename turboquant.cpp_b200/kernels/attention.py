@@ -1,0 +1,56 @@
+"""Attention kernels over the paged cache (csrc/attention.cu)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_kernel
+from ._call import KernelError, check, code, ptr, stream, want_f32, want_int32
+
+_LIB = "attention"
+MAX_HEAD_DIM = 256
+PAIRING = {"half": 0, "interleaved": 1}
+
+
+def check_head_dim(head_dim: int) -> None:
+    if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+        raise KernelError(f"attention kernels take head sizes 16, 32, …, {MAX_HEAD_DIM}; got {head_dim}")
+
+
+def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], pairing: str, positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
+                   q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
+                   n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Bias and rotary encoding on the fused projection qkv [T, (nh+2nkv)*hd]; queries to q_out
+    [T, nh, hd]; keys and values into cache_layer [pages, 2, nkv, page_size, hd] (None: the layer
+    reads another layer's cache, so only the queries are produced)."""
+    T = qkv.shape[0]
+    if cos is not None:
+        want_f32(cos, "cos table")
+        want_f32(sin, "sin table")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_qkv_rope_cache(
+        ptr(qkv), c_int(code(qkv.dtype)), ptr(bias), c_int(code(bias.dtype) if bias is not None else 0),
+        ptr(cos), ptr(sin), c_int(PAIRING[pairing]), ptr(positions), ptr(seq_of_token), ptr(page_table),
+        c_int(page_table.shape[1]), c_int(page_size), ptr(q_out), ptr(cache_layer),
+        c_int(0 if cache_layer is None else 1), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+        stream()))
+
+
+def attention(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+              page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
+              n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Exact attention of every token's queries over its sequence's cache (causal; window > 0
+    limits a query to the last `window` positions, itself included)."""
+    T = q.shape[0]
+    want_int32(positions, "positions")
+    want_int32(page_table, "page table")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_attention(ptr(q), ptr(cache_layer), c_int(code(q.dtype)), ptr(positions),
+                                 ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]), c_int(page_size),
+                                 c_int(window), c_float(scale), ptr(out), c_int(T), c_int(n_heads),
+                                 c_int(n_kv_heads), c_int(head_dim), stream()))
+    return out

@@ -1,0 +1,36 @@
+"""Sampling kernels (csrc/sampling.cu): argmax, temperature with a nucleus."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int
+
+import torch
+
+from ..csrc.build import load_kernel
+from ._call import check, ptr, stream, want_f32, want_int32
+
+_LIB = "sampling"
+
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = index of the first maximum of logits[r]."""
+    want_f32(logits, "logits")
+    want_int32(out, "tokens")
+    R, V = logits.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_argmax_rows(ptr(logits), c_int(R), c_int(V), ptr(out), stream()))
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_p: float, uniforms: torch.Tensor,
+                work: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Temperature / top-p draw per row from uniforms [R] in [0, 1); work holds R*V floats of scratch."""
+    want_f32(logits, "logits")
+    want_f32(uniforms, "uniforms")
+    want_f32(work, "work")
+    want_int32(out, "tokens")
+    R, V = logits.shape
+    assert work.numel() >= R * V
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_sample_rows(ptr(logits), c_int(R), c_int(V), c_float(temperature), c_float(top_p),
+                                   ptr(uniforms), ptr(work), ptr(out), stream()))
+    return out

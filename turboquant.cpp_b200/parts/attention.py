@@ -1,0 +1,84 @@
+"""Attention mixer: fused QKV projection with bias, position encoding, cache write, attention over
+the paged cache (grouped-query, causal, optional window), output projection.
+
+Order of the reference (src/engine/tq_transformer.c): projections :1027-1083, biases :1044-1047
+and :1086-1093, rotary :1343, cache write :1371 and :1452-1455, scores/softmax/PV :1909-2191 with
+head h reading KV head h/(nh/nkv) :1679 and scale 1/sqrt(hd) :1633, output projection :2231-2240.
+The window (a query sees the last `window` positions, itself included) follows the mask of the
+reference's Gemma branch :1646-1654."""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..kernels import attention as KA
+from ..kernels.linear import linear
+from ..weights.loader import WeightSpec, WeightStore
+from .base import KVNeed, LayerCache, Mixer, PositionEncoding, StepContext, register_mixer
+
+
+class AttentionMixer(Mixer):
+    def __init__(self, prefix: str, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, window: int = 0, position: Optional[PositionEncoding] = None,
+                 scale: Optional[float] = None):
+        if n_heads < 1 or n_kv_heads < 1 or n_heads % n_kv_heads:
+            raise ValueError(f"attention '{prefix}': {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+        KA.check_head_dim(head_dim)
+        if window < 0:
+            raise ValueError(f"attention '{prefix}': negative window {window}")
+        self.prefix, self.hidden = prefix, int(hidden)
+        self.n_heads, self.n_kv_heads, self.head_dim = int(n_heads), int(n_kv_heads), int(head_dim)
+        self.qkv_bias, self.window, self.position = bool(qkv_bias), int(window), position
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.q_size, self.kv_size = n_heads * head_dim, n_kv_heads * head_dim
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p, H = self.prefix, self.hidden
+        specs = [WeightSpec(p + "q_proj.weight", (self.q_size, H)), WeightSpec(p + "k_proj.weight", (self.kv_size, H)),
+                 WeightSpec(p + "v_proj.weight", (self.kv_size, H)), WeightSpec(p + "o_proj.weight", (H, self.q_size))]
+        if self.qkv_bias:
+            specs += [WeightSpec(p + "q_proj.bias", (self.q_size,)), WeightSpec(p + "k_proj.bias", (self.kv_size,)),
+                      WeightSpec(p + "v_proj.bias", (self.kv_size,))]
+        return specs
+
+    def bind(self, store: WeightStore) -> None:
+        p = self.prefix
+        ws = [store.take(p + n + "_proj.weight") for n in "qkv"]
+        dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()      # one product for q, k and v
+        if self.qkv_bias:
+            bs = [store.take(p + n + "_proj.bias") for n in "qkv"]
+            bdt = torch.float32 if any(b.dtype == torch.float32 for b in bs) else bs[0].dtype
+            self.b_qkv = torch.cat([b.to(bdt) for b in bs], dim=0).contiguous()
+        self.w_o = store.get(p + "o_proj.weight")
+        if self.position is not None:
+            self.position.prepare(store.device)
+
+    def kernels(self) -> List[str]:
+        return ["attention"]
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        T = xn.shape[0]
+        act = ctx.act_dtype
+        qkv = linear(xn, self.w_qkv, out_dtype=act)
+        q = torch.empty((T, self.n_heads, self.head_dim), dtype=act, device=xn.device)
+        tables = self.position.tables() if self.position is not None else None
+        if self.position is not None and tables is None:
+            raise NotImplementedError("attention: a position encoding without tables needs an unfused pass")
+        cos, sin, pairing = tables if tables is not None else (None, None, "half")
+        KA.qkv_rope_cache(qkv, self.b_qkv, cos, sin, pairing, ctx.positions, ctx.seq_of_token, cache.page_table,
+                          cache.page_size, q, cache.kv if cache.writes else None,
+                          self.n_heads, self.n_kv_heads, self.head_dim)
+        o = torch.empty((T, self.q_size), dtype=act, device=xn.device)
+        KA.attention(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
+                     self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
+        return linear(o, self.w_o, out_dtype=torch.float32)
+
+
+register_mixer("attention", AttentionMixer)

@@ -1,0 +1,108 @@
+"""Routed experts with a shared expert (src/engine/tq_moe.c:688-1059).
+
+  router   logits = Wr x in fp32; p = softmax over all experts; the k most probable (ties to the
+           lowest index); weights p[sel], divided by their sum if norm_topk.  The reference picks
+           the k largest logits and takes a softmax over them (:600-682), i.e. the norm_topk case.
+  experts  for each chosen e: o_e = Wd_e (silu(Wg_e x) * (Wu_e x)); y = sum w_e o_e (:864-1000)
+  shared   y += sigmoid(w_sg . x) * shared_expert(x) (:1006-1058)
+
+Tokens are copied into an expert-sorted layout, two grouped products run over it (gate|up with the
+SiLU product fused, then down), and one pass sums each token's k rows and the shared expert in the
+order above.  Router logits, softmax and the weighted sum are fp32 on both paths.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..kernels import elementwise as KE
+from ..kernels import moe as KM
+from ..weights.loader import WeightSpec, WeightStore
+from .base import FeedForward, StepContext, register_feed_forward
+
+
+class MoEFeedForward(FeedForward):
+    def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
+                 norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True):
+        if n_experts < 1 or not 1 <= top_k <= n_experts:
+            raise ValueError(f"experts '{prefix}': top-k {top_k} must be in 1..{n_experts}")
+        if hidden < 1 or intermediate < 1 or shared_intermediate < 0:
+            raise ValueError(f"experts '{prefix}': bad sizes {hidden}, {intermediate}, {shared_intermediate}")
+        self.prefix, self.hidden = prefix, int(hidden)
+        self.n_experts, self.top_k, self.intermediate = int(n_experts), int(top_k), int(intermediate)
+        self.norm_topk, self.shared_intermediate = bool(norm_topk), int(shared_intermediate)
+        self.shared_gate = bool(shared_gate) and shared_intermediate > 0
+        self.w_router = self.w_shared_gate = None
+        self.w13 = self.w2 = None            # [E, 2I, H] (gate rows, up rows), [E, H, I]
+        self.ws13 = self.ws2 = None          # shared expert [1, 2S, H], [1, H, S]
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p, H, I, S = self.prefix, self.hidden, self.intermediate, self.shared_intermediate
+        specs = [WeightSpec(p + "gate.weight", (self.n_experts, H))]
+        for e in range(self.n_experts):
+            q = f"{p}experts.{e}."
+            specs += [WeightSpec(q + "gate_proj.weight", (I, H)), WeightSpec(q + "up_proj.weight", (I, H)),
+                      WeightSpec(q + "down_proj.weight", (H, I))]
+        if S > 0:
+            q = p + "shared_expert."
+            specs += [WeightSpec(q + "gate_proj.weight", (S, H)), WeightSpec(q + "up_proj.weight", (S, H)),
+                      WeightSpec(q + "down_proj.weight", (H, S))]
+            if self.shared_gate:
+                specs.append(WeightSpec(p + "shared_expert_gate.weight", (1, H)))
+        return specs
+
+    def bind(self, store: WeightStore) -> None:
+        p, H, I, S, E = self.prefix, self.hidden, self.intermediate, self.shared_intermediate, self.n_experts
+        self.w_router = store.get(p + "gate.weight")
+        first = store.get(f"{p}experts.0.gate_proj.weight")
+        dt = first.dtype
+        self.w13 = torch.empty((E, 2 * I, H), dtype=dt, device=store.device)
+        self.w2 = torch.empty((E, H, I), dtype=dt, device=store.device)
+        for e in range(E):
+            q = f"{p}experts.{e}."
+            self.w13[e, :I].copy_(store.take(q + "gate_proj.weight"))
+            self.w13[e, I:].copy_(store.take(q + "up_proj.weight"))
+            self.w2[e].copy_(store.take(q + "down_proj.weight"))
+        if S > 0:
+            q = p + "shared_expert."
+            g, u, d = (store.take(q + n + "_proj.weight") for n in ("gate", "up", "down"))
+            sdt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+            self.ws13 = torch.cat([g.to(sdt), u.to(sdt)], dim=0).unsqueeze(0).contiguous()
+            self.ws2 = d.unsqueeze(0).contiguous()
+            if self.shared_gate:
+                self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
+
+    def kernels(self) -> List[str]:
+        return ["moe", "elementwise"]
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
+        act = ctx.act_dtype
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+        scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
+        KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
+        if ctx.debug is not None:
+            ctx.debug.setdefault("router_ids", []).append(ids.clone())
+            ctx.debug.setdefault("router_weights", []).append(wts.clone())
+        layout = KM.ExpertLayout(T * k, self.n_experts, KM.TILE_ROWS, dev)
+        KM.moe_align(ids, layout)
+        x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
+        KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
+        h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
+        KM.grouped_gemm(x_rows, self.w13, h_rows, layout, swiglu=True)
+        y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
+        KM.grouped_gemm(h_rows, self.w2, y_rows, layout, swiglu=False)
+        y_shared = None
+        if self.ws13 is not None:
+            hs = torch.empty((T, self.shared_intermediate), dtype=act, device=dev)
+            KM.grouped_gemm(xn, self.ws13, hs, None, swiglu=True)
+            y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
+            KM.grouped_gemm(hs, self.ws2, y_shared, None, swiglu=False)
+        y = torch.empty((T, H), dtype=torch.float32, device=dev)
+        KM.moe_combine(y_rows, layout.row_of_pair, wts, y_shared, scale, y, k)
+        return y
+
+
+register_feed_forward("moe", MoEFeedForward)
