@@ -1,25 +1,16 @@
-"""The engine against the plain implementation on the GPU: whole requests, the last tokens one by
-one, batches of unequal lengths with slots used again — in float32 and in bfloat16."""
+"""The engine against the plain implementation on the GPU, in float32 and in bfloat16: each
+request alone and whole; with the last 32 tokens one by one; in batches of unequal lengths whose
+shorter requests end earlier, one batch after another so that slots and pages are used again;
+long decoding; the first tokens of a sequence."""
 import numpy as np
 import pytest
-import torch
 
 from conftest import TINY
-from plain.qwen2_moe_plain import forward as plain_forward, round_bf16, no_round
+from replay_util import batched, check_against_plain, run_schedule, whole, with_tail
 
 pytestmark = pytest.mark.gpu
-
-# Tolerances, fixed from the arithmetic and not from what passes:
-#  float32: the engine sums in fp32 in another order than the float64 plain model; logits are O(1),
-#           sums run over <= a few hundred terms -> a few 1e-6 absolute at most.
-#  bfloat16: the plain model rounds activations to bfloat16 where the engine stores them, so what
-#           remains is fp32 summation order plus occasional 1-ulp flips of a bfloat16 value
-#           (2^-8 relative) that spread through later layers: a few 1e-3 of the logits' scale.
-TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
-
-
-def rel_err(a, b):
-    return float(np.abs(a - b).max() / max(1e-30, np.abs(b).max()))
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B", "C"]
 
 
 @pytest.fixture(scope="module")
@@ -30,7 +21,7 @@ def engines(tiny_folders):
     def get(name, dtype):
         if (name, dtype) not in cache:
             model = tq.load_model(tiny_folders[name], dtype, "cuda:0")
-            cache[(name, dtype)] = tq.Engine(model, max_tokens=2048)
+            cache[(name, dtype)] = tq.Engine(model, max_tokens=1024)
         return cache[(name, dtype)]
     return get
 
@@ -40,16 +31,84 @@ def tokens_for(name, n, seed):
     return np.random.default_rng(seed).integers(0, V, size=n).tolist()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+def max_len(name):
+    return TINY[name][0]["max_position_embeddings"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
 def test_whole_request(engines, plain_models, name, dtype):
-    import turboquant_cpp_b200 as tq
     eng = engines(name, dtype)
-    n = min(100, TINY[name][0]["max_position_embeddings"])
-    toks = tokens_for(name, n, 10)
+    toks = tokens_for(name, min(100, max_len(name)), 10)
+    logits, routing = run_schedule(eng, *whole("r", toks))
+    assert sorted(logits["r"]) == list(range(len(toks)))
+    check_against_plain(plain_models[name], toks, logits["r"], routing.get("r", {}), dtype, f"{name} whole")
+    eng.cache.book.check_invariants()
+    assert eng.cache.book.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(engines, plain_models, name, dtype):
+    eng = engines(name, dtype)
+    toks = tokens_for(name, min(100, max_len(name)), 11)
+    logits, routing = run_schedule(eng, *with_tail("r", toks, 32))
+    check_against_plain(plain_models[name], toks, logits["r"], routing.get("r", {}), dtype, f"{name} tail")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another(engines, plain_models, name, dtype):
+    """Batch 1: prompts 5/11/17 with 8, 3 and 8 further tokens; batch 2 on the same engine right
+    after it (its sequences get the slots and pages batch 1 gave back): prompts 1/9/40/70 with
+    16, 2, 16 and 5 further tokens (70 is longer than Tiny B's window and than one page)."""
+    eng = engines(name, dtype)
+    free_before = [p.n_free for p in eng.cache.book.pools]
+    plans = [({"a": (5, 8), "b": (11, 3), "c": (17, 8)}, 20),
+             ({"d": (1, 16), "e": (9, 2), "f": (40, 16), "g": (70, 5)}, 30)]
+    for batch, seed in plans:
+        reqs = {r: tokens_for(name, p + d, seed + i) for i, (r, (p, d)) in enumerate(batch.items())}
+        logits, routing = run_schedule(eng, *batched(reqs, {r: batch[r][0] for r in batch}))
+        for r, toks in reqs.items():
+            assert sorted(logits[r]) == list(range(len(toks)))
+            check_against_plain(plain_models[name], toks, logits[r], routing.get(r, {}), dtype, f"{name} batch {r}")
+        eng.cache.book.check_invariants()
+        assert [p.n_free for p in eng.cache.book.pools] == free_before      # everything was given back
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_long_decoding(engines, plain_models, name, dtype):
+    """A short prompt, then token by token up to the model's last position (several pages, and far
+    beyond the window of the windowed layers)."""
+    eng = engines(name, dtype)
+    n = max_len(name)
+    toks = tokens_for(name, n, 12)
+    logits, routing = run_schedule(eng, *with_tail("r", toks, n - 3))
+    assert len(logits["r"]) == n
+    check_against_plain(plain_models[name], toks, logits["r"], routing.get("r", {}), dtype, f"{name} long")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens(engines, plain_models, name, dtype):
+    """Positions 0, 1, 2: a prompt of one token, then single tokens."""
+    eng = engines(name, dtype)
+    toks = tokens_for(name, 4, 13)
+    logits, routing = run_schedule(eng, *with_tail("r", toks, 3))
+    check_against_plain(plain_models[name], toks, logits["r"], routing.get("r", {}), dtype, f"{name} first")
+
+
+def test_step_refuses_bad_input(engines):
+    import turboquant_cpp_b200 as tq
+    eng = engines("A", "float32")
     seq = eng.open()
-    logits = eng.step([tq.StepEntry(seq, toks, list(range(n)))]).cpu().numpy()
+    with pytest.raises(tq.StepError):
+        eng.step([tq.StepEntry(seq, [256], [0])])                 # token outside the vocabulary
+    with pytest.raises(tq.StepError):
+        eng.step([tq.StepEntry(seq, [1, 2], [2])])                # wanted place outside the tokens
+    with pytest.raises(tq.StepError):
+        eng.step([tq.StepEntry(seq, list(range(129)), [])])       # beyond max_position_embeddings
+    assert seq.length == 0
     eng.close(seq)
-    ref = plain_forward(plain_models[name], toks, rnd=round_bf16 if dtype == "bfloat16" else no_round)
-    assert logits.shape == ref.shape
-    assert rel_err(logits, ref) < TOL[dtype]
+    eng.cache.book.check_invariants()

@@ -1,0 +1,364 @@
+"""Each kernel alone against the plain implementation's function for the same part, at sizes other
+than the engine's tiny models (odd widths, head sizes in steps of 16, one or many KV heads)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_moe_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device=DEV).contiguous()
+
+
+def bf16_values(a):
+    """Round a float64 array to bfloat16 values, so that both sides start from the same numbers."""
+    return P.round_bf16(a)
+
+
+def close(got, want, tol):
+    got = got.detach().float().cpu().numpy().astype(np.float64)
+    err = np.abs(got - want).max() / max(1e-30, np.abs(want).max())
+    assert err < tol, f"relative error {err:.3e} exceeds {tol:.1e}"
+
+
+DTYPES = [(torch.float32, 3e-6), (torch.bfloat16, 6e-3)]   # fp32 sums; one bfloat16 rounding of the result
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(wdtype):
+    from turboquant_cpp_b200.kernels import elementwise as K
+    rng = np.random.default_rng(0)
+    table = bf16_values(rng.normal(size=(37, 50)))
+    toks = rng.integers(0, 37, size=23)
+    out = torch.empty((23, 50), dtype=torch.float32, device=DEV)
+    K.embed_rows(dev(toks, torch.int32), dev(table, wdtype), out)
+    close(out, P.embedding(table, toks), 1e-7)
+
+
+@pytest.mark.parametrize("H", [50, 192, 2048, 3000])
+@pytest.mark.parametrize("odtype,tol", DTYPES)
+def test_rmsnorm(H, odtype, tol):
+    from turboquant_cpp_b200.kernels import elementwise as K
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(7, H)) * 3
+    w = bf16_values(1 + 0.1 * rng.normal(size=H))
+    y = rng.normal(size=(7, H))
+    eps = 1e-5
+    # plain norm
+    out = torch.empty((7, H), dtype=odtype, device=DEV)
+    xd = dev(x)
+    K.rmsnorm(xd, dev(w, torch.bfloat16), eps, out)
+    close(out, P.rmsnorm(x.astype(np.float32).astype(np.float64), w, eps), tol)
+    close(xd, x, 1e-7)                                    # x untouched
+    # residual sum fused in: x += y, then the norm
+    yd = dev(y)
+    K.rmsnorm(xd, dev(w), eps, out, add=yd)
+    xs = x.astype(np.float32).astype(np.float64) + y.astype(np.float32).astype(np.float64)
+    close(out, P.rmsnorm(xs, w, eps), tol)
+    close(xd, xs, 1e-6)                                   # the sum was written back
+    # gather of rows, with a pending sum that is not written back
+    rows = np.array([5, 0, 5, 3])
+    out2 = torch.empty((4, H), dtype=odtype, device=DEV)
+    before = xd.clone()
+    K.rmsnorm(xd, dev(w), eps, out2, add=yd, rows=dev(rows, torch.int32))
+    close(out2, P.rmsnorm((xs + y.astype(np.float32))[rows], w, eps), tol)
+    assert torch.equal(before, xd)
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_silu_mul(dtype, tol):
+    from turboquant_cpp_b200.kernels import elementwise as K
+    rng = np.random.default_rng(2)
+    gu = bf16_values(rng.normal(size=(5, 2 * 70)) * 4)
+    out = torch.empty((5, 70), dtype=dtype, device=DEV)
+    K.silu_mul(dev(gu, dtype), out)
+    close(out, P.silu(gu[:, :70]) * gu[:, 70:], tol)
+
+
+# ---------------------------------------------------------------------------------------------
+def paged_inputs(rng, seq_lens, q_lens, nkv, hd, page_size, dtype, n_pages=64):
+    """A batch whose sequences already hold (seq_len - q_len) tokens: K/V of all positions, shuffled
+    pages, and the packed description of the step's new tokens."""
+    B = len(seq_lens)
+    perm = rng.permutation(n_pages)
+    tables, used = [], 0
+    for L in seq_lens:
+        n = -(-L // page_size)
+        tables.append(perm[used:used + n])
+        used += n
+    width = max(len(t) for t in tables)
+    table = np.full((B, width), -1, dtype=np.int32)
+    for i, t in enumerate(tables):
+        table[i, :len(t)] = t
+    k_all = [bf16_values(rng.normal(size=(L, nkv, hd))) for L in seq_lens]
+    v_all = [bf16_values(rng.normal(size=(L, nkv, hd))) for L in seq_lens]
+    cache = np.zeros((n_pages, 2, nkv, page_size, hd))
+    for i, L in enumerate(seq_lens):
+        for p in range(L):
+            pg = table[i, p // page_size]
+            cache[pg, 0, :, p % page_size] = k_all[i][p]
+            cache[pg, 1, :, p % page_size] = v_all[i][p]
+    positions = np.concatenate([np.arange(L - q, L) for L, q in zip(seq_lens, q_lens)])
+    seq_of = np.concatenate([np.full(q, i) for i, q in enumerate(q_lens)])
+    return dict(table=table, k=k_all, v=v_all, cache=cache, positions=positions, seq_of=seq_of)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (5, 1, 48), (8, 2, 128), (3, 3, 80), (2, 1, 256)])
+@pytest.mark.parametrize("window", [0, 7])
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_attention(nh, nkv, hd, window, dtype, tol):
+    from turboquant_cpp_b200.kernels import attention as KA
+    rng = np.random.default_rng(nh * 100 + hd + window)
+    seq_lens, q_lens, page = [70, 1, 130, 9], [70, 1, 3, 1], 64
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, dtype)
+    T = sum(q_lens)
+    q = bf16_values(rng.normal(size=(T, nh, hd)))
+    out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    KA.attention(dev(q, dtype), dev(d["cache"], dtype), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
+                 dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd), out, nh, nkv, hd)
+    want = np.zeros((T, nh * hd))
+    t0 = 0
+    for i, (L, ql) in enumerate(zip(seq_lens, q_lens)):
+        qfull = np.zeros((L, nh, hd))
+        qfull[L - ql:] = q[t0:t0 + ql]
+        want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
+        t0 += ql
+    close(out, want, tol)
+
+
+def test_attention_far_key_stands_out():
+    """One key far back gets a large score: the output must be (almost) that key's value, which a
+    kernel that skips or misplaces distant pages would miss."""
+    from turboquant_cpp_b200.kernels import attention as KA
+    rng = np.random.default_rng(5)
+    nh = nkv = 2
+    hd, page, L, far = 32, 64, 700, 3
+    d = paged_inputs(rng, [L], [1], nkv, hd, page, torch.float32)
+    q = rng.normal(size=(1, nh, hd))
+    k = d["k"][0]
+    k[far] = 0
+    k[far, :, 0] = 40.0
+    q[0, :, 0] = 40.0
+    pg = d["table"][0, far // page]
+    d["cache"][pg, 0, :, far % page] = k[far]
+    out = torch.empty((1, nh * hd), dtype=torch.float32, device=DEV)
+    KA.attention(dev(q), dev(d["cache"]), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
+                 dev(d["table"], torch.int32), page, 0, 1 / math.sqrt(hd), out, nh, nkv, hd)
+    qfull = np.zeros((L, nh, hd))
+    qfull[-1] = q[0]
+    want = P.attention(qfull, k, d["v"][0], 0)[-1:]
+    close(out, want, 3e-6)
+    close(out, d["v"][0][far].reshape(1, -1), 1e-3)      # it is that value
+    # with a window that excludes it, the far key must not be seen
+    KA.attention(dev(q), dev(d["cache"]), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
+                 dev(d["table"], torch.int32), page, L - far - 1, 1 / math.sqrt(hd), out, nh, nkv, hd)
+    close(out, P.attention(qfull, k, d["v"][0], L - far - 1)[-1:], 3e-6)
+    KA.attention(dev(q), dev(d["cache"]), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
+                 dev(d["table"], torch.int32), page, L - far, 1 / math.sqrt(hd), out, nh, nkv, hd)
+    close(out, d["v"][0][far].reshape(1, -1), 1e-3)      # the window's edge includes it again
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (5, 1, 48), (2, 2, 128)])
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_qkv_rope_cache(nh, nkv, hd, pairing, dtype, tol):
+    from turboquant_cpp_b200.kernels import attention as KA
+    from turboquant_cpp_b200.parts.rotary import RotaryEncoding
+    rng = np.random.default_rng(7)
+    seq_lens, q_lens, page = [70, 130, 5], [70, 2, 1], 64
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, dtype)
+    T = sum(q_lens)
+    width = (nh + 2 * nkv) * hd
+    qkv = bf16_values(rng.normal(size=(T, width)))
+    bias = bf16_values(rng.normal(size=width))
+    theta = 12345.0
+    rot = RotaryEncoding(hd, theta, 256, pairing)
+    rot.prepare(DEV)
+    cos, sin, _ = rot.tables()
+    cache = torch.zeros((64, 2, nkv, page, hd), dtype=dtype, device=DEV)
+    q_out = torch.empty((T, nh, hd), dtype=dtype, device=DEV)
+    KA.qkv_rope_cache(dev(qkv, dtype), dev(bias, dtype), cos, sin, pairing, dev(d["positions"], torch.int32),
+                      dev(d["seq_of"], torch.int32), dev(d["table"], torch.int32), page, q_out, cache, nh, nkv, hd)
+    x = qkv + bias
+    pos = d["positions"]
+    q = P.rotary(x[:, :nh * hd].reshape(T, nh, hd), pos, theta, pairing)
+    k = P.rotary(x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd), pos, theta, pairing)
+    v = x[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    close(q_out, q, tol)
+    c = cache.float().cpu().numpy()
+    for t in range(T):
+        pg = d["table"][d["seq_of"][t], pos[t] // page]
+        np.testing.assert_allclose(c[pg, 0, :, pos[t] % page], k[t], atol=tol * 8, rtol=0)
+        np.testing.assert_allclose(c[pg, 1, :, pos[t] % page], v[t], atol=tol * 8, rtol=0)
+    # nothing else was written
+    written = np.zeros(c.shape, dtype=bool)
+    for t in range(T):
+        written[d["table"][d["seq_of"][t], pos[t] // page], :, :, pos[t] % page] = True
+    assert np.all(c[~written] == 0)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("E,k,H,renorm,shared", [(8, 2, 64, False, True), (6, 3, 192, True, True), (5, 1, 120, False, False),
+                                                  (60, 4, 200, False, True), (130, 8, 96, True, False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_router(E, k, H, renorm, shared, dtype):
+    from turboquant_cpp_b200.kernels import moe as KM
+    rng = np.random.default_rng(E + 1000)
+    T = 33
+    x = bf16_values(rng.normal(size=(T, H)))
+    wr = bf16_values(rng.normal(size=(E, H)) * 0.3)
+    wsg = bf16_values(rng.normal(size=(1, H)) * 0.3)
+    ids = torch.empty((T, k), dtype=torch.int32, device=DEV)
+    wts = torch.empty((T, k), dtype=torch.float32, device=DEV)
+    sc = torch.empty((T,), dtype=torch.float32, device=DEV) if shared else None
+    KM.router_topk(dev(x, dtype), dev(wr, dtype), dev(wsg, dtype) if shared else None, k, renorm, ids, wts, sc)
+    rid, rw, margin = P.router(x, wr, k, renorm)
+    assert margin.min() > 1e-4, "test data has a near-tie"
+    assert np.array_equal(ids.cpu().numpy(), rid)
+    close(wts, rw, 1e-5)
+    if shared:
+        close(sc, 1 / (1 + np.exp(-(x @ wsg.T)[:, 0])), 1e-5)
+
+
+def test_router_ties_go_to_the_lowest_index():
+    from turboquant_cpp_b200.kernels import moe as KM
+    x = np.ones((1, 16))
+    wr = np.zeros((7, 16))
+    wr[2] = wr[5] = 0.25          # two equal maxima, the rest equal and lower
+    ids = torch.empty((1, 3), dtype=torch.int32, device=DEV)
+    wts = torch.empty((1, 3), dtype=torch.float32, device=DEV)
+    KM.router_topk(dev(x), dev(wr), None, 3, False, ids, wts, None)
+    assert ids.cpu().tolist() == [[2, 5, 0]]
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (50, 6, 3), (300, 5, 1), (1000, 60, 4), (7, 64, 8)])
+def test_moe_align(T, E, k):
+    from turboquant_cpp_b200.kernels import moe as KM
+    rng = np.random.default_rng(T)
+    ids = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    if T > 10:
+        ids[ids == 1] = 0 if E > 2 and k == 1 else ids[ids == 1]     # may leave expert 1 without rows
+    lay = KM.ExpertLayout(T * k, E, 64, DEV)
+    KM.moe_align(dev(ids, torch.int32), lay)
+    flat = ids.reshape(-1)
+    counts = np.bincount(flat, minlength=E)
+    assert np.array_equal(lay.counts.cpu().numpy(), counts)
+    off = np.concatenate([[0], np.cumsum(counts)])
+    assert np.array_equal(lay.expert_offset.cpu().numpy(), off)
+    order = np.argsort(flat, kind="stable")
+    assert np.array_equal(lay.sorted_pair.cpu().numpy()[:T * k], order)
+    inv = np.empty(T * k, dtype=np.int64)
+    inv[order] = np.arange(T * k)
+    assert np.array_equal(lay.row_of_pair.cpu().numpy()[:T * k], inv)
+    n = int(lay.n_tiles.item())
+    assert n == sum(-(-c // 64) for c in counts) <= lay.max_tiles
+    te, t0, tc = (a.cpu().numpy()[:n] for a in (lay.tile_expert, lay.tile_row0, lay.tile_count))
+    covered = np.zeros(T * k, dtype=int)
+    for e, r0, c in zip(te, t0, tc):
+        assert 1 <= c <= 64 and off[e] <= r0 and r0 + c <= off[e + 1]
+        covered[r0:r0 + c] += 1
+    assert np.all(covered == 1)
+
+
+@pytest.mark.parametrize("R,N,K,G", [(1, 32, 64, 8), (130, 48, 192, 6), (77, 100, 50, 3), (200, 70, 130, 5)])
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_grouped_gemm(R, N, K, G, swiglu, dtype, tol):
+    from turboquant_cpp_b200.kernels import moe as KM
+    rng = np.random.default_rng(R + N)
+    a = bf16_values(rng.normal(size=(R, K)))
+    w = bf16_values(rng.normal(size=(G, 2 * N if swiglu else N, K)) / math.sqrt(K))
+    ids = rng.integers(0, G, size=(R, 1)).astype(np.int32)
+    if G > 2:
+        ids[ids == 1] = 2                      # an expert without rows
+    lay = KM.ExpertLayout(R, G, 64, DEV)
+    KM.moe_align(dev(ids, torch.int32), lay)
+    order = lay.sorted_pair.cpu().numpy()[:R]
+    a_sorted = a[order]
+    out = torch.full((R, N), float("nan"), dtype=dtype, device=DEV)
+    KM.grouped_gemm(dev(a_sorted, dtype), dev(w, dtype), out, lay, swiglu)
+    want = np.zeros((R, N))
+    for r in range(R):
+        e = ids[order[r], 0]
+        if swiglu:
+            want[r] = P.silu(w[e, :N] @ a_sorted[r]) * (w[e, N:] @ a_sorted[r])
+        else:
+            want[r] = w[e] @ a_sorted[r]
+    close(out, want, tol)
+    # one group, no layout (the shared expert's products)
+    out1 = torch.full((R, N), float("nan"), dtype=dtype, device=DEV)
+    KM.grouped_gemm(dev(a, dtype), dev(w[:1], dtype), out1, None, swiglu)
+    w0 = w[0]
+    want1 = P.silu(a @ w0[:N].T) * (a @ w0[N:].T) if swiglu else a @ w0.T
+    close(out1, want1, tol)
+
+
+def test_moe_combine():
+    from turboquant_cpp_b200.kernels import moe as KM
+    rng = np.random.default_rng(9)
+    T, k, H = 21, 3, 70
+    Y = rng.normal(size=(T * k, H))
+    Ys = rng.normal(size=(T, H))
+    inv = rng.permutation(T * k).astype(np.int32)
+    w = rng.random(size=(T, k))
+    s = rng.random(size=T)
+    out = torch.empty((T, H), dtype=torch.float32, device=DEV)
+    KM.moe_combine(dev(Y), dev(inv, torch.int32), dev(w), dev(Ys), dev(s), out, k)
+    want = np.einsum("tk,tkh->th", w, Y[inv].reshape(T, k, H)) + s[:, None] * Ys
+    close(out, want, 2e-6)
+    KM.moe_combine(dev(Y), dev(inv, torch.int32), dev(w), None, None, out, k)
+    close(out, np.einsum("tk,tkh->th", w, Y[inv].reshape(T, k, H)), 2e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [257, 5000, 151936])
+def test_argmax_first_maximum(V):
+    from turboquant_cpp_b200.kernels import sampling as KS
+    rng = np.random.default_rng(V)
+    l = rng.normal(size=(5, V)).astype(np.float32)
+    l[1, [V - 1, 7, V // 2]] = 9.0          # equal maxima: the first wins
+    l[2, 0] = 9.0
+    l[3, V - 1] = 9.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    KS.argmax_rows(dev(l), out)
+    assert out.cpu().tolist() == [P.sample_argmax(r) for r in l]
+    assert out.cpu().tolist()[1] == 7
+
+
+@pytest.mark.parametrize("V,temp,top_p", [(257, 0.8, 1.0), (320, 0.7, 0.9), (5000, 1.5, 0.5), (151936, 0.8, 0.95)])
+def test_sample_rows_matches_plain(V, temp, top_p):
+    from turboquant_cpp_b200.kernels import sampling as KS
+    rng = np.random.default_rng(V)
+    R = 24
+    l = (rng.normal(size=(R, V)) * 2).astype(np.float32)
+    u = rng.random(size=R).astype(np.float32)
+    u[0], u[1] = 0.0, 0.99999994
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    work = torch.empty(R * V, dtype=torch.float32, device=DEV)
+    KS.sample_rows(dev(l), temp, top_p, dev(u), work, out)
+    want = [P.sample_top_p(l[r], temp, top_p, float(u[r])) for r in range(R)]
+    got = out.cpu().tolist()
+    # a draw within float rounding of a boundary of the cumulative sum may fall either side
+    same = sum(g == w for g, w in zip(got, want))
+    assert same >= R - 1, (got, want)
+
+
+def test_sample_rows_distribution():
+    """Four equal logits: each token near a quarter of many draws (the reference's own check,
+    tests/test_ops.cpp:528-571, asks for 10-50 % of 1000 draws)."""
+    from turboquant_cpp_b200.kernels import sampling as KS
+    R, V = 2000, 4
+    l = np.zeros((R, V), dtype=np.float32)
+    u = np.random.default_rng(3).random(size=R).astype(np.float32)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    work = torch.empty(R * V, dtype=torch.float32, device=DEV)
+    KS.sample_rows(dev(l), 1.0, 1.0, dev(u), work, out)
+    counts = np.bincount(out.cpu().numpy(), minlength=V)
+    assert counts.min() > 0.2 * R and counts.max() < 0.3 * R

@@ -100,21 +100,22 @@ TQ_EXPORT int tq_residual_add(float* x, const void* y, int y_dtype, long long n,
 // ---------------------------------------------------------------------------------------
 // h[t, i] = silu(gu[t, i]) * gu[t, I + i]   (gate rows first, then up rows)
 // ---------------------------------------------------------------------------------------
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int I) {
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, int I) {
     const int t = blockIdx.x;
-    const T* g = gu + (size_t)t * 2 * I;
-    T* o = h + (size_t)t * I;
+    const TI* g = gu + (size_t)t * 2 * I;
+    TO* o = h + (size_t)t * I;
     for (int i = threadIdx.x; i < I; i += blockDim.x) {
         const float a = tq_to_float(g[i]), b = tq_to_float(g[I + i]);
-        o[i] = tq_from_float<T>(a / (1.0f + expf(-a)) * b);
+        o[i] = tq_from_float<TO>(a / (1.0f + expf(-a)) * b);
     }
 }
 
-TQ_EXPORT int tq_silu_mul(const void* gu, void* h, int dtype, int T_, int I, cudaStream_t stream) {
+TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, int T_, int I, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);
-    TQ_DISPATCH(dtype, T, silu_mul_kernel<T><<<T_, 256, 0, stream>>>((const T*)gu, (T*)h, I));
+    TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
+        (silu_mul_kernel<TI, TO><<<T_, 256, 0, stream>>>((const TI*)gu, (TO*)h, I))));
     TQ_CHECK_LAUNCH("silu_mul");
     return 0;
 }

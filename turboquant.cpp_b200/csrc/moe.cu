@@ -289,7 +289,7 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
                               const int* tile_expert, const int* tile_row0, const int* tile_count,
                               const int* n_tiles, int max_tiles, int R, int N, int K, int swiglu,
                               cudaStream_t stream) {
-    if (R == 0 || max_tiles == 0) return 0;
+    if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
     TQ_REQUIRE(R > 0 && N > 0 && K > 0, "grouped_gemm: bad sizes R=%d N=%d K=%d", R, N, K);
     const int by = tile_expert ? max_tiles : (R + GG_BM - 1) / GG_BM;
     TQ_REQUIRE(by <= 65535, "grouped_gemm: %d row tiles exceed the grid limit", by);

@@ -53,7 +53,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     T, I = out.shape
     lib = load_kernel(_LIB)
-    check(_LIB, lib.tq_silu_mul(ptr(gate_up), ptr(out), c_int(code(out.dtype)), c_int(T), c_int(I), stream()))
+    check(_LIB, lib.tq_silu_mul(ptr(gate_up), c_int(code(gate_up.dtype)), ptr(out), c_int(code(out.dtype)),
+                                c_int(T), c_int(I), stream()))
     return out
 
 

@@ -35,7 +35,7 @@ class SwiGLUFeedForward(FeedForward):
         return ["elementwise"]
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = linear(xn, self.w_gate_up, out_dtype=ctx.act_dtype)
+        gu = linear(xn, self.w_gate_up, out_dtype=torch.float32)     # gate and up stay fp32 until the product
         h = torch.empty((xn.shape[0], self.intermediate), dtype=ctx.act_dtype, device=xn.device)
         K.silu_mul(gu, h)
         return linear(h, self.w_down, out_dtype=torch.float32)
