@@ -1,0 +1,135 @@
+"""The generation loop's decisions with a stand-in engine (CPU): batching, stop tokens, sequences
+that end earlier, one batch after another, slots given back."""
+import numpy as np
+import pytest
+
+from turboquant_cpp_b200.cache import CacheBook, CacheFull
+from turboquant_cpp_b200.engine.generate import GenParams, GenStats, generate, plan_batches
+from turboquant_cpp_b200.sampling import uniforms_for
+from plain.qwen2_moe_plain import uniform_for
+
+
+class FakeEngine:
+    """Next token = (sum of the sequence's tokens) % vocab; the bookkeeping is the real CacheBook."""
+    page_size, max_position = 64, 300
+
+    def __init__(self, capacity_tokens=64 * 64, max_slots=8, vocab=50):
+        self.book = CacheBook([capacity_tokens // 64], [0], 64, max_slots)
+        self.capacity_tokens, self.max_slots, self.vocab = capacity_tokens, max_slots, vocab
+        self.sums, self.step_sizes, self.max_live = {}, [], 0
+
+    def open(self):
+        s = self.book.open()
+        self.sums[s.id] = 0
+        self.max_live = max(self.max_live, len(self.book.live))
+        return s
+
+    def close(self, seq):
+        self.book.close(seq)
+
+    @staticmethod
+    def make_entry(seq, tokens, want=()):
+        return (seq, list(tokens), list(want))
+
+    def step(self, entries):
+        self.book.reserve_all([e[0] for e in entries], [len(e[1]) for e in entries])
+        rows = []
+        for seq, toks, want in entries:
+            self.sums[seq.id] += sum(toks)
+            self.book.commit(seq, len(toks))
+            assert want in ([len(toks) - 1], [0])
+            row = np.zeros(self.vocab)
+            row[self.sums[seq.id] % self.vocab] = 1.0
+            rows.append(row)
+        self.step_sizes.append(len(entries))
+        self.book.check_invariants()
+        return np.stack(rows)
+
+
+class ArgmaxSampler:
+    def __init__(self):
+        self.calls = []
+
+    def sample(self, logits, requests, steps):
+        self.calls.append((list(requests), list(steps)))
+        return np.argmax(logits, axis=1)
+
+
+def expected(prompt, n, vocab=50, stop=()):
+    out, s = [], sum(prompt)
+    for _ in range(n):
+        t = s % vocab
+        out.append(t)
+        s += t
+        if t in stop:
+            break
+    return out
+
+
+def test_batches_of_unequal_prompts_and_early_ends():
+    eng, smp = FakeEngine(), ArgmaxSampler()
+    prompts = [[1, 2, 3], [4] * 11, [5] * 17, [7], [9, 9]]
+    stats = GenStats()
+    res = generate(eng, smp, prompts, GenParams(max_new_tokens=6, stop_token_ids=(24,)), max_batch=3, stats=stats)
+    for p, r in zip(prompts, res):
+        assert r.tokens == expected(p, 6, stop=(24,))
+        assert r.finish_reason == ("stop" if r.tokens[-1] == 24 else "length")
+    assert any(r.finish_reason == "stop" and len(r.tokens) < 6 for r in res)      # one ended earlier
+    assert stats.batches == 2 and eng.max_live == 3
+    assert eng.step_sizes[0] == 3 and min(eng.step_sizes) < 3                     # the batch shrank
+    assert not eng.book.live and eng.book.pools[0].n_free == eng.book.pools[0].n  # everything was given back
+    # the sampler saw each request under its own index and its own token count
+    for reqs, steps in smp.calls:
+        for i, s in zip(reqs, steps):
+            assert 0 <= s < 6 and 0 <= i < len(prompts)
+    assert stats.generated_tokens == sum(len(r.tokens) for r in res)
+    assert stats.prompt_tokens == sum(len(p) for p in prompts)
+
+
+def test_streaming_callback_gets_every_token_once():
+    eng = FakeEngine()
+    seen = {}
+    prompts = [[1], [2, 2], [3, 3, 3]]
+    res = generate(eng, ArgmaxSampler(), prompts, GenParams(max_new_tokens=4), max_batch=8,
+                   on_tokens=lambda idx, toks: [seen.setdefault(i, []).append(t) for i, t in zip(idx, toks)])
+    assert [seen[i] for i in range(3)] == [r.tokens for r in res]
+
+
+def test_context_and_cache_limits_end_a_sequence():
+    eng = FakeEngine()
+    res = generate(eng, ArgmaxSampler(), [[1] * 298], GenParams(max_new_tokens=10))
+    assert res[0].finish_reason == "context" and len(res[0].tokens) == 3         # 298 + 2 fed back = 300 positions
+    small = FakeEngine(capacity_tokens=128, max_slots=4)
+    res = generate(small, ArgmaxSampler(), [[1] * 60, [2] * 60], GenParams(max_new_tokens=200), max_batch=4)
+    assert [r.finish_reason for r in res] == ["context", "context"]             # each alone, until the cache is full
+    assert all(len(r.tokens) == 128 - 60 + 1 for r in res)
+    assert not small.book.live
+    with pytest.raises(CacheFull):
+        generate(small, ArgmaxSampler(), [[1] * 200], GenParams(max_new_tokens=1))
+    with pytest.raises(ValueError):
+        generate(eng, ArgmaxSampler(), [[]], GenParams(max_new_tokens=1))
+    assert generate(eng, ArgmaxSampler(), [[1]], GenParams(max_new_tokens=0))[0].tokens == []
+
+
+def test_plan_batches_respects_slots_pages_and_order():
+    plan = plan_batches([10, 100, 20, 64, 5], max_new_tokens=30, max_batch=8, capacity_tokens=256, max_slots=8,
+                        page_size=64, max_position=1000)
+    assert plan == [[0], [1, 2], [3], [4]] or sum(plan, []) == [0, 1, 2, 3, 4]
+    assert sum(plan, []) == [0, 1, 2, 3, 4]
+    for b in plan:
+        assert sum(-(-(n + 30) // 64) for n in ([10, 100, 20, 64, 5][i] for i in b)) <= 4
+    assert plan_batches([1] * 5, 1, max_batch=2, capacity_tokens=6400, max_slots=8, page_size=64, max_position=100) == \
+        [[0, 1], [2, 3], [4]]
+    assert plan_batches([1] * 5, 1, max_batch=8, capacity_tokens=6400, max_slots=3, page_size=64, max_position=100) == \
+        [[0, 1, 2], [3, 4]]
+
+
+def test_uniforms_do_not_depend_on_the_batch_and_match_the_plain_stream():
+    a = uniforms_for(7, [0, 1, 2, 3], [5, 5, 5, 5])
+    b = uniforms_for(7, [2], [5])
+    assert a[2] == b[0] and len(set(a.tolist())) == 4
+    assert all(0.0 <= u < 1.0 for u in a)
+    for seed, r, s in [(7, 2, 5), (0, 0, 0), (42, 63, 4095), (2 ** 40 + 3, 9, 1)]:
+        assert float(uniforms_for(seed, [r], [s])[0]) == pytest.approx(uniform_for(seed, r, s), abs=0)
+    many = uniforms_for(1, np.arange(20000) % 64, np.arange(20000) // 64)
+    assert abs(many.mean() - 0.5) < 0.01 and abs(np.mean(many < 0.1) - 0.1) < 0.01

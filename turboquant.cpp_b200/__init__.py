@@ -9,5 +9,8 @@ from .config import ConfigError, Qwen2MoeConfig, register_architecture, register
 from .weights import WeightError, WeightSpec
 from . import models  # registers the built-in architectures
 from .engine import Engine, StepEntry, StepError, build_model, load_model, random_model, write_random_folder
+from .engine.generate import GenParams, GenResult, GenStats, generate, plan_batches
+from .sampling import Sampler
+from .model import Model
 
 __version__ = "0.1.0"

@@ -1,0 +1,96 @@
+"""Command line in the manner of the reference's `quant` tool (tools/quant.c:126-163, 241-346).
+
+    quant <model folder> [-p "ids"]… [-n max_tokens] [-T temperature] [-P top_p] [-s seed]
+          [--ctx N] [--dtype bfloat16|float32] [--batch N] [--stop id]… [--info] [--profile]
+          [--bench-prefill] [--bench-memory]
+
+Names and meanings follow the reference where it has them: -p prompt (default "Hello" there; here
+a prompt is a list of token ids, "1,2,3" or "1 2 3", default "0"), -n max tokens (256), -T
+temperature (0.7), -P top-p (0.9), -s seed (42; 0 means the default), --ctx context length, --info
+print the model and exit, --profile time the kernels' groups, --bench-prefill and --bench-memory
+(decode speed at growing context).  -j (threads) is accepted and ignored.  -p may be given several
+times: the prompts run as batches.  Token ids go to stdout, one line per prompt; the summary
+"N tokens in X s (Y tok/s)" goes to stderr as the reference prints it (tools/quant.c:1371-1376).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+from typing import List
+
+
+def parse_ids(text: str) -> List[int]:
+    parts = text.replace(",", " ").split()
+    try:
+        return [int(p) for p in parts]
+    except ValueError:
+        raise SystemExit(f"quant: a prompt is a list of token ids (\"1,2,3\"), got {text!r}") from None
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="quant", description="Generate tokens with a model folder on one B200.")
+    ap.add_argument("model", help="folder with config.json and model.safetensors")
+    ap.add_argument("-p", dest="prompts", action="append", help="prompt as token ids; may repeat")
+    ap.add_argument("-n", dest="max_tokens", type=int, default=256)
+    ap.add_argument("-T", dest="temperature", type=float, default=0.7)
+    ap.add_argument("-P", dest="top_p", type=float, default=0.9)
+    ap.add_argument("-s", dest="seed", type=int, default=42)
+    ap.add_argument("-j", dest="threads", type=int, default=0, help="accepted for compatibility; ignored")
+    ap.add_argument("--ctx", type=int, default=0, help="context length per request (default: model's, at most 4096)")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    ap.add_argument("--batch", type=int, default=8, help="most requests in one batch")
+    ap.add_argument("--stop", type=int, action="append", help="stop token id; may repeat (default: the model's eos)")
+    ap.add_argument("--info", action="store_true")
+    ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--bench-prefill", action="store_true")
+    ap.add_argument("--bench-memory", action="store_true")
+    ap.add_argument("--device", default="cuda:0")
+    args = ap.parse_args(argv)
+
+    from .config.registry import load_config
+    from . import models  # noqa: F401
+    if args.info:
+        arch, cfg = load_config(args.model)
+        print(f"architecture: {arch.name}")
+        for k, v in sorted(cfg.to_dict().items()):
+            print(f"  {k}: {v}")
+        return 0
+
+    import torch
+    from .model import Model
+    seed = args.seed if args.seed != 0 else 42
+    m = Model(args.model, temperature=args.temperature, top_p=args.top_p, max_tokens=args.max_tokens,
+              context_length=args.ctx, seed=seed, dtype=args.dtype, device=args.device, max_batch=args.batch,
+              stop_token_ids=args.stop)
+    if args.bench_prefill or args.bench_memory:
+        from .engine.bench_tools import bench_memory, bench_prefill
+        if args.bench_prefill:
+            bench_prefill(m, file=sys.stderr)
+        if args.bench_memory:
+            bench_memory(m, file=sys.stderr)
+        return 0
+    prompts = [parse_ids(p) for p in (args.prompts or ["0"])]
+    prof = None
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+        prof = profile(activities=[ProfilerActivity.CUDA])
+        prof.__enter__()
+    t0 = time.perf_counter()
+    outs = m.generate_batch(prompts)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    if prof is not None:
+        prof.__exit__(None, None, None)
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12), file=sys.stderr)
+    for o in outs:
+        print(" ".join(str(t) for t in o))
+    n = sum(len(o) for o in outs)
+    st = m.last_stats
+    print(f"{n} tokens in {dt:.2f} s ({n / dt:.1f} tok/s; prefill {st.prompt_tokens} tokens in "
+          f"{st.prefill_seconds:.3f} s, decode {st.decode_seconds:.3f} s, {st.batches} batches)", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

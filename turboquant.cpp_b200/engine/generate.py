@@ -1,0 +1,144 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences that end earlier, and
+as many batches one after another as there are requests.
+
+The reference generates one sequence per call: prompt, first sample, then a loop of
+{stop check, forward, sample} until max_tokens (src/engine/tq_generate.c:167-643; end-of-sequence
+ids at :426-438, the loop at :441-605).  Its repetition penalty, loop detector and text stops are
+not carried over: stop tokens are a set the caller gives (the configuration's eos ids by default).
+
+The decisions — which requests share a batch, when a sequence ends, when a batch ends — are host
+code over an engine-like object, so they are tested on a CPU with a stand-in engine.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+from ..cache.allocator import CacheFull
+
+
+@dataclass
+class GenParams:
+    max_new_tokens: int = 256
+    temperature: float = 0.0
+    top_p: float = 1.0
+    seed: int = 42
+    stop_token_ids: Tuple[int, ...] = ()
+
+
+@dataclass
+class GenResult:
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = ""          # 'stop' | 'length' | 'context'
+
+
+@dataclass
+class GenStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    batches: int = 0
+    steps: int = 0
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int, capacity_tokens: int,
+                 max_slots: int, page_size: int, max_position: int) -> List[List[int]]:
+    """Splits requests, in order, into batches that fit the cache: a request is counted with the
+    most tokens it can come to hold, rounded up to whole pages."""
+    if max_batch < 1:
+        raise ValueError("max_batch must be at least 1")
+    budget = capacity_tokens // page_size
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, n in enumerate(prompt_lens):
+        if n < 1:
+            raise ValueError(f"request {i} has an empty prompt")
+        if n > max_position:
+            raise ValueError(f"request {i}: prompt of {n} tokens exceeds the model's {max_position} positions")
+        need = -(-min(n + max_new_tokens, max_position) // page_size)
+        if -(-n // page_size) > budget:
+            raise CacheFull(f"request {i}: prompt of {n} tokens does not fit a cache of {capacity_tokens} tokens")
+        need = min(need, budget)     # alone it may run until the cache is full
+        if cur and (len(cur) >= min(max_batch, max_slots) or used + need > budget):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParams, max_batch: int = 64,
+             on_tokens: Optional[Callable[[List[int], List[int]], None]] = None,
+             stats: Optional[GenStats] = None, sync: Optional[Callable[[], None]] = None) -> List[GenResult]:
+    """Generates a continuation for every prompt.
+
+    engine:   open(), close(seq), step(entries) -> logits rows, make_entry(seq, tokens, want),
+              capacity_tokens, max_slots, page_size, max_position
+    sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist())
+    on_tokens(request indices, tokens) is called after every step with that step's new tokens.
+    A stop token ends its sequence and is part of the output."""
+    stats = stats if stats is not None else GenStats()
+    sync = sync or (lambda: None)
+    results = [GenResult() for _ in prompts]
+    stop = set(int(t) for t in params.stop_token_ids)
+    if params.max_new_tokens <= 0:
+        for r in results:
+            r.finish_reason = "length"
+        return results
+    batches = plan_batches([len(p) for p in prompts], params.max_new_tokens, max_batch, engine.capacity_tokens,
+                           engine.max_slots, engine.page_size, engine.max_position)
+    for batch in batches:
+        stats.batches += 1
+        live = {i: engine.open() for i in batch}
+        try:
+            # the prompts, whole, in one step; logits at each prompt's last token
+            t0 = time.perf_counter()
+            order = list(batch)
+            logits = engine.step([engine.make_entry(live[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in order])
+            new = sampler.sample(logits, order, [0] * len(order)).tolist()
+            sync()
+            stats.prefill_seconds += time.perf_counter() - t0
+            stats.prompt_tokens += sum(len(prompts[i]) for i in order)
+            stats.steps += 1
+            t0 = time.perf_counter()
+            while True:
+                nxt: List[Tuple[int, int]] = []
+                for i, tok in zip(order, new):
+                    res = results[i]
+                    res.tokens.append(int(tok))
+                    stats.generated_tokens += 1
+                    if int(tok) in stop:
+                        res.finish_reason = "stop"
+                    elif len(res.tokens) >= params.max_new_tokens:
+                        res.finish_reason = "length"
+                    elif live[i].length + 1 > engine.max_position:
+                        res.finish_reason = "context"
+                    else:
+                        nxt.append((i, int(tok)))
+                        continue
+                    engine.close(live.pop(i))            # the sequence ends: its slot and pages go back
+                if on_tokens is not None:
+                    on_tokens(list(order), [int(t) for t in new])
+                if not nxt:
+                    break
+                order = [i for i, _ in nxt]
+                try:
+                    logits = engine.step([engine.make_entry(live[i], [tok], [0]) for i, tok in nxt])
+                except CacheFull:
+                    for i in order:                      # no room for one more token each
+                        results[i].finish_reason = "context"
+                        engine.close(live.pop(i))
+                    break
+                new = sampler.sample(logits, order, [len(results[i].tokens) for i in order]).tolist()
+                stats.steps += 1
+            sync()
+            stats.decode_seconds += time.perf_counter() - t0
+        finally:
+            for seq in live.values():
+                engine.close(seq)
+    return results

@@ -50,6 +50,27 @@ class Engine:
         self.debug: Optional[Dict[str, Any]] = None
         self.steps_run = 0
 
+    # ---- what the generation loop asks -----------------------------------------------------------
+    @property
+    def capacity_tokens(self) -> int:
+        return min(p.n for p in self.cache.book.pools) * self.cache.page_size if self.cache.book.pools else 1 << 30
+
+    @property
+    def max_slots(self) -> int:
+        return self.cache.max_slots
+
+    @property
+    def page_size(self) -> int:
+        return self.cache.page_size
+
+    @property
+    def max_position(self) -> int:
+        return self.model.max_position
+
+    @staticmethod
+    def make_entry(seq: Sequence_, tokens: Sequence[int], want: Sequence[int] = ()) -> "StepEntry":
+        return StepEntry(seq, tokens, want)
+
     # ---- sequences ------------------------------------------------------------------------------
     def open(self) -> Sequence_:
         return self.cache.open()

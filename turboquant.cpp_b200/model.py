@@ -1,0 +1,128 @@
+"""The Python entry point: a model folder in, generated token ids out.
+
+In the manner of the reference's binding (bindings/python/quantcpp/__init__.py:220-676):
+``Model(path, temperature=…, top_p=…, max_tokens=…, context_length=…)`` with ``ask`` for one
+answer, ``generate`` as an iterator of pieces, ``close`` and use as a context manager, and
+``FileNotFoundError`` for a path that does not exist.  The reference's methods take and return
+text through its tokenizer; this library's unit is the token id, so prompts are lists of ids and
+answers are lists of ids.  ``generate_batch`` is this library's addition: several prompts of
+unequal lengths as batches.
+"""
+from __future__ import annotations
+
+import os
+from typing import Iterator, List, Optional, Sequence, Union
+
+import torch
+
+from .engine.generate import GenParams, GenResult, GenStats, generate as _generate
+from .engine.loading import load_model
+from .engine.step import Engine
+from .sampling import Sampler
+
+
+class Model:
+    def __init__(self, path: str, *, temperature: float = 0.7, top_p: float = 0.9, max_tokens: int = 256,
+                 context_length: int = 0, seed: int = 42, dtype: str = "bfloat16", device: str = "cuda:0",
+                 max_batch: int = 8, stop_token_ids: Optional[Sequence[int]] = None):
+        """path: folder with config.json and safetensors.  context_length: most tokens one request
+        may hold (0: the model's max_position_embeddings, capped at 4096 as the reference caps its
+        default context, src/engine/tq_model.c:2951).  The cache is sized for max_batch such requests."""
+        if not os.path.isdir(path):
+            raise FileNotFoundError(f"model folder '{path}' does not exist")
+        self._path = path
+        self.temperature, self.top_p, self.max_tokens, self.seed = temperature, top_p, max_tokens, seed
+        self.max_batch = int(max_batch)
+        self._model = load_model(path, dtype, device)
+        ctx = int(context_length) if context_length and context_length > 0 else min(self._model.max_position, 4096)
+        self.context_length = min(ctx, self._model.max_position)
+        page = 64
+        per_request = -(-self.context_length // page) * page
+        self._engine = Engine(self._model, max_tokens=per_request * self.max_batch, max_slots=max(self.max_batch, 1),
+                              device=device)
+        eos = getattr(self._model.config, "eos_token_ids", ())
+        self.stop_token_ids = tuple(stop_token_ids) if stop_token_ids is not None else tuple(eos)
+        self.last_stats: Optional[GenStats] = None
+
+    # ---- properties ---------------------------------------------------------------------------
+    @property
+    def path(self) -> str:
+        return self._path
+
+    @property
+    def config(self):
+        return self._model.config
+
+    @property
+    def engine(self) -> Engine:
+        return self._engine
+
+    # ---- generation ---------------------------------------------------------------------------
+    def _params(self, max_tokens, temperature, top_p, seed, stop_token_ids) -> GenParams:
+        return GenParams(
+            max_new_tokens=self.max_tokens if max_tokens is None else int(max_tokens),
+            temperature=self.temperature if temperature is None else float(temperature),
+            top_p=self.top_p if top_p is None else float(top_p),
+            seed=self.seed if seed is None else int(seed),
+            stop_token_ids=self.stop_token_ids if stop_token_ids is None else tuple(stop_token_ids))
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]], *, max_tokens: Optional[int] = None,
+                       temperature: Optional[float] = None, top_p: Optional[float] = None,
+                       seed: Optional[int] = None, stop_token_ids: Optional[Sequence[int]] = None,
+                       on_tokens=None) -> List[List[int]]:
+        """Continuations of several prompts (token ids in, token ids out, on the host)."""
+        self._check_open()
+        p = self._params(max_tokens, temperature, top_p, seed, stop_token_ids)
+        stats = GenStats()
+        results = _generate(self._engine, Sampler(p.temperature, p.top_p, p.seed), prompts, p, self.max_batch,
+                            on_tokens=on_tokens, stats=stats, sync=torch.cuda.synchronize)
+        self.last_stats = stats
+        self.last_results = results
+        return [r.tokens for r in results]
+
+    def ask(self, prompt: Sequence[int], **kw) -> List[int]:
+        """The whole continuation of one prompt."""
+        return self.generate_batch([prompt], **kw)[0]
+
+    def generate(self, prompt: Sequence[int], **kw) -> Iterator[int]:
+        """Yields the continuation's tokens one by one as they are sampled."""
+        self._check_open()
+        import queue
+        import threading
+        q: "queue.Queue" = queue.Queue()
+        done = object()
+
+        def run():
+            try:
+                self.generate_batch([prompt], on_tokens=lambda idx, toks: [q.put(t) for t in toks], **kw)
+                q.put(done)
+            except BaseException as e:  # noqa: BLE001 - handed to the consumer
+                q.put(e)
+
+        t = threading.Thread(target=run, daemon=True)
+        t.start()
+        while True:
+            item = q.get()
+            if item is done:
+                break
+            if isinstance(item, BaseException):
+                raise item
+            yield item
+        t.join()
+
+    # ---- lifetime -----------------------------------------------------------------------------
+    def _check_open(self) -> None:
+        if self._engine is None:
+            raise RuntimeError("the model is closed")
+
+    def close(self) -> None:
+        self._engine = None
+        self._model = None
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def __enter__(self) -> "Model":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()

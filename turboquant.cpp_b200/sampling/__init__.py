@@ -1,0 +1,2 @@
+"""Sampling: greedy, temperature, top-p."""
+from .sampler import Sampler, uniforms_for
