@@ -1,0 +1,264 @@
+#!/usr/bin/env python3
+"""Decode and prefill speed of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference]
+
+The model has the layer sizes of Qwen1.5-MoE-A2.7B with seeded random weights in bfloat16; token ids
+are synthetic (uniform).  A "step" is one decode step of a batch of 8 sequences that start from
+2,048-token prompts (context 4,096).  One JSON line is printed:
+  value     decoded tokens per second, timed on the device with CUDA events over exactly K steps
+            (every step reads far more weight and cache bytes than the L2 holds, so no flush)
+  e2e       the same through the Python entry point (Model.generate_batch): host token ids in,
+            host token ids out, every step's host-to-device and device-to-host copies included
+  prefill   one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak
+  roofline  bytes the decode step has to read (each weight it uses once, and the cache of the live
+            requests) / its time, against the measured copy bandwidth
+  points    decode tokens per second at batch 1 and batch 64
+Only one GPU is supported: for --gpus N > 1 a line says so and the exit code is 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Layer sizes of the benchmark model (Qwen1.5-MoE-A2.7B); weights are random.
+A27B = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 24, "hidden_size": 2048, "num_attention_heads": 16, "num_key_value_heads": 16,
+    "num_experts": 60, "num_experts_per_tok": 4, "moe_intermediate_size": 1408, "norm_topk_prob": False,
+    "shared_expert_intermediate_size": 5632, "intermediate_size": 5632, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "use_sliding_window": False,
+    "sliding_window": 0, "max_window_layers": 24, "tie_word_embeddings": False, "decoder_sparse_step": 1,
+    "mlp_only_layers": [], "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 24
+PROMPT, CONTEXT = 2048, 4096
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured"}
+        except Exception:  # noqa: BLE001 - fall through to the stated fallback
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--id=0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = max((int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()), default=0)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else 0, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    """Parameter and flop counts from the configuration."""
+    H, nh, nkv = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = H // nh
+    E, k, I, S, V = (cfg["num_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"],
+                     cfg["shared_expert_intermediate_size"], cfg["vocab_size"])
+    attn = H * (nh + 2 * nkv) * hd + (nh + 2 * nkv) * hd + nh * hd * H
+    expert = 3 * H * I
+    shared = 3 * H * S + H
+    router = E * H
+    return dict(attn=attn, expert=expert, shared=shared, router=router, norms=2 * H, head=V * H, embed=V * H,
+                layers=layers, kv_per_token=layers * 2 * nkv * hd, H=H, E=E, k=k, V=V, nh=nh, hd=hd)
+
+
+def decode_bytes(n, distinct_experts_per_layer, batch, context_tokens_total, el=2):
+    """Bytes one decode step has to read: every weight it uses once and the live requests' cache."""
+    per_layer = n["attn"] + n["shared"] + n["router"] + n["norms"]
+    w = n["layers"] * per_layer + sum(distinct_experts_per_layer) * n["expert"] + n["head"] + batch * n["H"] + n["H"]
+    return w * el + context_tokens_total * n["kv_per_token"] * el
+
+
+def prefill_flops(n, T):
+    per_tok = 2 * (n["attn"] + n["k"] * n["expert"] + n["shared"] + n["router"])
+    attn = 4 * n["nh"] * n["hd"] * T * (T + 1) / 2
+    return n["layers"] * (T * per_tok + attn) + 2 * n["head"]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C project without setup.py/pyproject.toml at its root (pip install fails), "
+                          "and its engine runs this architecture from GGUF on the CPU only: no safetensors MoE, no "
+                          "random-weights mode, no CUDA forward"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": f"this library runs on one GPU; --gpus {args.gpus} is not supported", "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    import turboquant_cpp_b200 as tq
+    from turboquant_cpp_b200.kernels import _call
+
+    pk = peaks()
+    cfg = dict(A27B)
+    cfg["num_hidden_layers"] = args.layers
+    cfg["max_window_layers"] = args.layers
+    n = model_numbers(cfg, args.layers)
+    torch.cuda.set_device(0)
+    t_load = time.time()
+    model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    print(f"[bench] model with {args.layers} layers ready in {time.time() - t_load:.1f} s", file=sys.stderr, flush=True)
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+
+    def run_decode(batch, steps, warmup, want_experts=False):
+        """Prefill `batch` prompts of PROMPT tokens, then time `steps` decode steps on the device."""
+        eng = tq.Engine(model, max_tokens=batch * CONTEXT, max_slots=batch)
+        seqs = [eng.open() for _ in range(batch)]
+        group = 8
+        for g0 in range(0, batch, group):
+            eng.step([tq.StepEntry(s, rng.integers(0, V, size=PROMPT).tolist(), []) for s in seqs[g0:g0 + group]])
+        smp = tq.Sampler(0.0)
+        toks = rng.integers(0, V, size=(warmup + steps + 1, batch))
+
+        def one(i):
+            logits = eng.step([tq.StepEntry(s, [int(toks[i, j])], [0]) for j, s in enumerate(seqs)])
+            return smp.sample(logits, list(range(batch)), [i] * batch)
+
+        distinct = None
+        if want_experts:
+            eng.debug = {}
+            one(0)
+            distinct = [int(torch.unique(a).numel()) for a in eng.debug["router_ids"]]
+            eng.debug = None
+        else:
+            one(0)
+        for i in range(1, warmup):
+            one(i)
+        ctx_tokens = sum(s.length for s in seqs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = _call.LAUNCHES
+        torch.cuda.synchronize()
+        a.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        launches = _call.LAUNCHES - launches0
+        ctx_mid = ctx_tokens + batch * steps // 2
+        for s in seqs:
+            eng.close(s)
+        del eng
+        torch.cuda.empty_cache()
+        return dict(ms_per_step=ms / steps, tok_s=batch * steps / ms * 1e3, launches=launches, distinct=distinct,
+                    ctx_tokens=ctx_mid)
+
+    # ---- the headline: decode at the default batch ------------------------------------------------
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = run_decode(args.batch, args.steps, args.warmup, want_experts=True)
+    clock_rec = clocks.stop()
+    dbytes = decode_bytes(n, main_run["distinct"], args.batch, main_run["ctx_tokens"])
+    achieved = dbytes / (main_run["ms_per_step"] * 1e-3) / 1e9
+
+    # ---- end to end through the Python entry point ---------------------------------------------------
+    m = tq.Model.from_model(model, temperature=0.0, max_tokens=args.steps + 1, context_length=CONTEXT, max_batch=args.batch)
+    prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(args.batch)]
+    m.generate_batch([p[:64] for p in prompts], max_tokens=4)          # warm-up
+    m.generate_batch(prompts)
+    st = m.last_stats
+    e2e_tok_s = (st.generated_tokens - args.batch) / st.decode_seconds if st.decode_seconds > 0 else 0.0
+    h2d = 4 * (7 * args.batch + 1 + args.batch * (CONTEXT // 64))       # packed int32 metadata of a decode step
+    d2h = 4 * args.batch
+    m.close()
+
+    out = {
+        "metric": "decode tok/s @ batch 8 (Qwen1.5-MoE-A2.7B sizes, random weights)", "value": round(main_run["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": {"model": "Qwen1.5-MoE-A2.7B sizes", "layers": args.layers, "layers_of_model": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "experts": cfg["num_experts"],
+                   "top_k": cfg["num_experts_per_tok"], "moe_inter": cfg["moe_intermediate_size"],
+                   "shared_inter": cfg["shared_expert_intermediate_size"], "vocab": V, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights and cache read per step)"},
+        "clocks": clock_rec,
+        "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"],
+                     "bytes_per_step": int(dbytes)},
+    }
+    if not args.no_points:
+        # ---- prefill of one 2,048-token prompt --------------------------------------------------------
+        eng = tq.Engine(model, max_tokens=PROMPT, max_slots=1)
+        toks = rng.integers(0, V, size=PROMPT).tolist()
+        best = float("inf")
+        for i in range(4):
+            s = eng.open()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            eng.step([tq.StepEntry(s, toks, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            if i > 0:
+                best = min(best, a.elapsed_time(b))
+            eng.close(s)
+        del eng
+        torch.cuda.empty_cache()
+        fl = prefill_flops(n, PROMPT)
+        out["prefill"] = {"value": round(PROMPT / best * 1e3, 1), "tokens": PROMPT, "ms": round(best, 3),
+                          "frac": round(fl / (best * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        k_pts = max(8, min(args.steps, 32))
+        out["points"] = {"decode_b1": round(run_decode(1, k_pts, 3)["tok_s"], 1),
+                         "decode_b64": round(run_decode(64, k_pts, 3)["tok_s"], 1)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

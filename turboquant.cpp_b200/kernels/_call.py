@@ -37,7 +37,12 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def check(lib_name: str, rc: int) -> None:
+LAUNCHES = 0     # kernels of this library launched so far (counted by the wrappers)
+
+
+def check(lib_name: str, rc: int, kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += kernels
     if rc != 0:
         lib = load_kernel(lib_name)
         raise KernelError(lib.tq_last_error().decode("utf-8", "replace") or f"{lib_name}: error {rc}")

@@ -59,7 +59,7 @@ def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:
     check(_LIB, lib.tq_moe_align(ptr(ids), c_int(P), c_int(layout.n_experts), c_int(layout.tile_rows),
                                  ptr(layout.counts), ptr(layout.sorted_pair), ptr(layout.row_of_pair),
                                  ptr(layout.expert_offset), ptr(layout.tile_expert), ptr(layout.tile_row0),
-                                 ptr(layout.tile_count), ptr(layout.n_tiles), stream()))
+                                 ptr(layout.tile_count), ptr(layout.n_tiles), stream()), kernels=2)
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Optional[ExpertLayout],

@@ -30,10 +30,24 @@ class Model:
         default context, src/engine/tq_model.c:2951).  The cache is sized for max_batch such requests."""
         if not os.path.isdir(path):
             raise FileNotFoundError(f"model folder '{path}' does not exist")
+        self._setup(load_model(path, dtype, device), path, temperature, top_p, max_tokens, context_length, seed,
+                    device, max_batch, stop_token_ids)
+
+    @classmethod
+    def from_model(cls, model, *, temperature: float = 0.7, top_p: float = 0.9, max_tokens: int = 256,
+                   context_length: int = 0, seed: int = 42, device: str = "cuda:0", max_batch: int = 8,
+                   stop_token_ids: Optional[Sequence[int]] = None) -> "Model":
+        """Wraps a model that is already on the device (for instance one with random weights)."""
+        self = cls.__new__(cls)
+        self._setup(model, "", temperature, top_p, max_tokens, context_length, seed, device, max_batch, stop_token_ids)
+        return self
+
+    def _setup(self, model, path, temperature, top_p, max_tokens, context_length, seed, device, max_batch,
+               stop_token_ids) -> None:
         self._path = path
         self.temperature, self.top_p, self.max_tokens, self.seed = temperature, top_p, max_tokens, seed
         self.max_batch = int(max_batch)
-        self._model = load_model(path, dtype, device)
+        self._model = model
         ctx = int(context_length) if context_length and context_length > 0 else min(self._model.max_position, 4096)
         self.context_length = min(ctx, self._model.max_position)
         page = 64
@@ -43,6 +57,7 @@ class Model:
         eos = getattr(self._model.config, "eos_token_ids", ())
         self.stop_token_ids = tuple(stop_token_ids) if stop_token_ids is not None else tuple(eos)
         self.last_stats: Optional[GenStats] = None
+        self.last_results: List[GenResult] = []
 
     # ---- properties ---------------------------------------------------------------------------
     @property
