@@ -1,0 +1,87 @@
+"""The tensor-core grouped GEMM against numpy and against the exact CUDA-core kernel."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_moe_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype):
+    return torch.tensor(np.asarray(a), dtype=dtype, device=DEV).contiguous()
+
+
+def rel(got, want):
+    got = got.detach().float().cpu().numpy().astype(np.float64)
+    return np.abs(got - want).max() / max(1e-30, np.abs(want).max())
+
+
+@pytest.mark.parametrize("R,N,K,G", [(1, 128, 64, 1), (5, 128, 256, 3), (40, 200, 136, 6), (300, 1408, 2048, 8),
+                                      (77, 96, 72, 5), (1000, 256, 512, 4)])
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("bn", [16, 32, 64, 128])
+@pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
+def test_grouped(R, N, K, G, swiglu, bn, odtype):
+    from turboquant_cpp_b200.kernels import gemm_tc as KT, moe as KM
+    rng = np.random.default_rng(R * 7 + N + bn)
+    a = P.round_bf16(rng.normal(size=(R, K)))
+    w = P.round_bf16(rng.normal(size=(G, 2 * N if swiglu else N, K)) / math.sqrt(K))
+    ids = rng.integers(0, G, size=(R, 1)).astype(np.int32)
+    if G > 2:
+        ids[ids == 1] = 2                                   # a group without rows
+    lay = KM.ExpertLayout(R, G, bn, DEV)
+    KM.moe_align(dev(ids, torch.int32), lay)
+    order = lay.sorted_pair.cpu().numpy()[:R]
+    a_sorted = a[order]
+    out = torch.full((R, N), float("nan"), dtype=odtype, device=DEV)
+    KT.gemm_tc(dev(a_sorted, torch.bfloat16), dev(w, torch.bfloat16), out, lay, swiglu, bn)
+    KT.check_status()
+    want = np.zeros((R, N))
+    for g in range(G):
+        sel = np.nonzero(ids[order, 0] == g)[0]
+        if len(sel):
+            x = a_sorted[sel]
+            want[sel] = P.silu(x @ w[g, :N].T) * (x @ w[g, N:].T) if swiglu else x @ w[g].T
+    tol = 2e-5 if odtype == torch.float32 else 6e-3         # fp32 accumulation; one bfloat16 rounding of the result
+    assert rel(out, want) < tol
+    # the exact kernel on the same data
+    ref = torch.empty((R, N), dtype=torch.float32, device=DEV)
+    lay64 = KM.ExpertLayout(R, G, 64, DEV)
+    KM.moe_align(dev(ids, torch.int32), lay64)
+    KM.grouped_gemm(dev(a_sorted, torch.bfloat16), dev(w, torch.bfloat16), ref, lay64, swiglu)
+    assert rel(out, ref.double().cpu().numpy()) < tol
+
+
+@pytest.mark.parametrize("R,N,K", [(3, 5632, 2048), (130, 300, 1408), (2048, 384, 256)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_one_group(R, N, K, swiglu):
+    from turboquant_cpp_b200.kernels import gemm_tc as KT
+    rng = np.random.default_rng(R + N)
+    a = P.round_bf16(rng.normal(size=(R, K)))
+    w = P.round_bf16(rng.normal(size=(1, 2 * N if swiglu else N, K)) / math.sqrt(K))
+    bn = KT.token_tile_for(R, 1)
+    out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
+    KT.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out, None, swiglu, bn)
+    KT.check_status()
+    want = P.silu(a @ w[0, :N].T) * (a @ w[0, N:].T) if swiglu else a @ w[0].T
+    assert rel(out, want) < 2e-5
+
+
+def test_refuses_what_it_cannot_do():
+    from turboquant_cpp_b200.kernels import KernelError, gemm_tc as KT
+    x = torch.zeros((4, 20), dtype=torch.bfloat16, device=DEV)        # K not a multiple of 8
+    w = torch.zeros((1, 16, 20), dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros((4, 16), dtype=torch.float32, device=DEV)
+    assert not KT.usable(x, w)
+    with pytest.raises(KernelError):
+        KT.gemm_tc(x, w, out, None, False, 16)
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((1, 16, 64), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError):
+        KT.gemm_tc(x, w, out, None, False, 48)                         # not a token tile the kernel has
+    with pytest.raises(KernelError):
+        KT.gemm_tc(x.float(), w, out, None, False, 16)

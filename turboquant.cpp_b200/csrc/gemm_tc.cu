@@ -1,0 +1,348 @@
+// Grouped bf16 GEMM on the 5th-generation tensor cores (tcgen05) with TMA-fed shared memory and
+// the accumulator in tensor memory: the expert products of the mixture-of-experts feed-forward
+// (routed experts and the shared expert), for prompts and for decoding.
+//
+//   out[row, n] = sum_k X[row, k] * W[g(row), n, k]          (plain)
+//   out[row, n] = silu(X.Wg[n]) * (X.Wu[n])                   (SwiGLU: W holds gate rows [0, N) and
+//                                                              up rows [N, 2N) of each group)
+// as the reference's expert loop computes them on the CPU (src/engine/tq_moe.c:975-999: g = Wg x,
+// u = Wu x, h = silu(g)*u, o = Wd h), with exact expf in the SiLU.
+//
+// Orientation: the WEIGHT rows are the M side of the MMA (128 rows per tile), the token rows are
+// the N side (16..128 per tile).  One kernel therefore serves a 2,048-token prompt and a decode
+// step of a few tokens per expert without padding the tensor core's M dimension with empty rows:
+// at decode the kernel is a weight stream (each CTA pulls a [128 x K] slab through a multi-stage
+// TMA pipeline) and the tokens ride along as a narrow N.
+//
+// One CTA per (weight-row tile, token tile).  Warp 0 issues TMA loads, warp 1 owns the tensor
+// memory and issues tcgen05.mma, warps 2..5 read the accumulator back (tcgen05.ld), apply the
+// epilogue and store.  All waits on mbarriers are bounded: a wait that runs out sets a flag, every
+// role leaves its loop, copies in flight are waited for (bounded again), tensor memory is freed and
+// the kernel returns with *status != 0; nothing spins forever.
+#include <cuda.h>
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+namespace {
+
+constexpr int BM = 128;          // weight rows per tile (MMA M)
+constexpr int BK = 64;           // K elements per stage: 128 bytes of bf16 = one swizzle row
+constexpr int UMMA_K = 16;       // K of one tcgen05.mma for 16-bit inputs
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;     // polls of an mbarrier before a wait gives up
+constexpr uint64_t WAIT_NS = 2000000000ull;   // ... or two seconds, whichever comes first
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (and raises the CTA's abort flag) or when another
+// role already gave up.
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_NS) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address >> 4, leading byte offset 1 (unused for swizzled K-major), stride byte offset
+// 1024 >> 4 (eight rows), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+// Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+template <int BN, bool SWIGLU>
+struct Tile {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "token tile must be 16..128 in steps of 16");
+    static_assert(STAGES >= 2, "pipeline needs at least two stages");
+};
+
+template <int BN, bool SWIGLU, typename TO>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TO* __restrict__ out, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+               const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
+               int* __restrict__ status) {
+    using T = Tile<BN, SWIGLU>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_abort;
+    __shared__ uint32_t s_tmem_base;
+
+    int expert = 0, row0, count;
+    if (tile_expert) {
+        if ((int)blockIdx.y >= n_tiles[0]) return;
+        expert = tile_expert[blockIdx.y];
+        row0 = tile_row0[blockIdx.y];
+        count = tile_count[blockIdx.y];
+    } else {
+        row0 = blockIdx.y * BN;
+        if (row0 >= R) return;
+        count = min(BN, R - row0);
+    }
+    const int m0 = blockIdx.x * BM;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (K + BK - 1) / BK;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
+    const uint32_t bars = base + T::STAGES * T::STAGE_BYTES;         // full[STAGES], empty[STAGES], accum
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (T::STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * T::STAGES);
+    auto a_tile = [&](int s) { return base + s * T::STAGE_BYTES; };
+    auto a2_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES; };
+    auto b_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES * (SWIGLU ? 2 : 1); };
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < T::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = s_tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % T::STAGES;
+                const uint32_t ph = (uint32_t)(kb / T::STAGES) & 1u;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) break;
+                mbar_expect_tx(full_bar(s), (uint32_t)T::STAGE_BYTES);
+                tma_load_3d(a_tile(s), &map_w, kb * BK, m0, expert, full_bar(s));
+                if (SWIGLU) tma_load_3d(a2_tile(s), &map_w, kb * BK, N + m0, expert, full_bar(s));
+                tma_load_2d(b_tile(s), &map_x, kb * BK, row0, full_bar(s));
+                issued = kb + 1;
+            }
+            if (s_abort) {
+                // wait (bounded) for the copies this thread started, so none lands after the CTA is gone
+                const int first = issued > T::STAGES ? issued - T::STAGES : 0;
+                for (int kb = first; kb < issued; ++kb) {
+                    const uint32_t bar = full_bar(kb % T::STAGES), ph = (uint32_t)(kb / T::STAGES) & 1u;
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(bar, ph); ++i) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % T::STAGES;
+                const uint32_t ph = (uint32_t)(kb / T::STAGES) & 1u;
+                ok = mbar_wait(full_bar(s), ph, &s_abort);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    const uint64_t bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
+                    umma(tmem_d, umma_desc(a_tile(s) + k * UMMA_K * 2), bd, idesc, acc);
+                    if (SWIGLU) umma(tmem_d + BN, umma_desc(a2_tile(s) + k * UMMA_K * 2), bd, idesc, acc);
+                }
+                umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(accum_bar);         // the accumulator is complete once all MMAs are done
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                 // weight row within the tile
+        const int n = m0 + r;                              // output column
+        if (mbar_wait(accum_bar, 0u, &s_abort)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem_d + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= count) break;                    // uniform across the warp
+                uint32_t g[16], u[16];
+                tmem_ld16(lane_addr + c0, g);
+                if (SWIGLU) tmem_ld16(lane_addr + BN + c0, u);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < count) {
+                            float v = __uint_as_float(g[j]);
+                            if (SWIGLU) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
+                            out[(size_t)(row0 + c0 + j) * N + n] = tq_from_float<TO>(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)T::TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && s_abort) atomicExch(status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// bf16 tensor [d2][d1][d0 = K] (row-major, d0 contiguous); box [1][box_rows][64], 128-byte swizzle
+int make_map(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {k, rows, groups};
+    cuuint64_t strides[2] = {k * 2, rows * k * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    const cuuint32_t rank = groups > 0 ? 3 : 2;
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int BN, bool SWIGLU, typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* te, const int* tr, const int* tc,
+           const int* nt, int grid_y, int R, int N, int K, int* status, cudaStream_t stream) {
+    using T = Tile<BN, SWIGLU>;
+    auto kern = gemm_tc_kernel<BN, SWIGLU, TO>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (e != cudaSuccess) TQ_FAIL(-1, "gemm_tc: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((N + BM - 1) / BM, grid_y);
+    kern<<<grid, THREADS, T::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, te, tr, tc, nt, R, N, K, status);
+    TQ_CHECK_LAUNCH("gemm_tc");
+    return 0;
+}
+
+}  // namespace
+
+// X [R, K] bf16; W [G, Nw, K] bf16 with Nw = N (plain) or 2N (swiglu); out [R, N] in bf16 or fp32.
+// tile_* describe token tiles of at most `bn` rows that never span two groups (null: one group, tiles
+// of bn consecutive rows).  status: one int in device memory, set to 1 if a bounded wait ran out.
+TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
+                         const int* tile_row0, const int* tile_count, const int* n_tiles, int max_tiles, int bn,
+                         int R, int N, int K, int G, int swiglu, int* status, cudaStream_t stream) {
+    if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
+    TQ_REQUIRE(R > 0 && N > 0 && K > 0 && G > 0, "gemm_tc: bad sizes R=%d N=%d K=%d G=%d", R, N, K, G);
+    TQ_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    TQ_REQUIRE(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
+    TQ_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128, "gemm_tc: token tile %d is not one of 16, 32, 64, 128", bn);
+    TQ_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
+    const int grid_y = tile_expert ? max_tiles : (R + bn - 1) / bn;
+    TQ_REQUIRE(grid_y <= 65535, "gemm_tc: %d token tiles exceed the grid limit", grid_y);
+    CUtensorMap mw, mx;
+    const int Nw = swiglu ? 2 * N : N;
+    int rc = make_map(&mw, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)G, BM);
+    if (rc) return rc;
+    rc = make_map(&mx, X, (uint64_t)K, (uint64_t)R, 0, (uint32_t)bn);
+    if (rc) return rc;
+#define TC_CASE(BN_)                                                                                                  \
+    if (bn == BN_) {                                                                                                  \
+        if (swiglu) {                                                                                                 \
+            if (out_dtype == TQ_BF16) return launch<BN_, true, __nv_bfloat16>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
+            return launch<BN_, true, float>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
+        }                                                                                                             \
+        if (out_dtype == TQ_BF16) return launch<BN_, false, __nv_bfloat16>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
+        return launch<BN_, false, float>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
+    }
+    TQ_REQUIRE(out_dtype == TQ_BF16 || out_dtype == TQ_F32, "gemm_tc: unknown output type %d", out_dtype);
+    TC_CASE(16) TC_CASE(32) TC_CASE(64) TC_CASE(128)
+#undef TC_CASE
+    TQ_FAIL(-2, "gemm_tc: unreachable");
+}
