@@ -73,6 +73,9 @@ class DecoderModel:
         self.config, self.dtype = config, dtype
         self.embedding, self.blocks, self.schedule = embedding, list(blocks), list(schedule)
         self.final_norm, self.head = final_norm, head
+        for part in self.parts():            # parts may ask which dtype the run keeps activations in
+            for sub in (part.parts() if hasattr(part, "parts") else [part]):
+                sub.run_dtype = dtype
         for i, e in enumerate(self.schedule):
             if not 0 <= e.block < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names block {e.block}, but there are {len(self.blocks)} blocks")

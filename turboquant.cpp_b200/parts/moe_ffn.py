@@ -17,6 +17,7 @@ from typing import List, Optional
 import torch
 
 from ..kernels import elementwise as KE
+from ..kernels import gemm_tc as KT
 from ..kernels import moe as KM
 from ..weights.loader import WeightSpec, WeightStore
 from .base import FeedForward, StepContext, register_feed_forward
@@ -74,7 +75,17 @@ class MoEFeedForward(FeedForward):
                 self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
 
     def kernels(self) -> List[str]:
-        return ["moe", "elementwise"]
+        names = ["moe", "elementwise"]
+        dt = self.w13.dtype if self.w13 is not None else getattr(self, "run_dtype", torch.bfloat16)
+        if dt == torch.bfloat16:
+            names.append("gemm_tc")       # float32 runs never launch the tensor-core kernel
+        return names
+
+    def _product(self, x, w, out, layout, swiglu, token_tile):
+        """Tensor cores for bfloat16 operands with 16-byte rows, the exact CUDA-core kernel otherwise."""
+        if token_tile and KT.usable(x, w):
+            return KT.gemm_tc(x, w, out, layout, swiglu, token_tile)
+        return KM.grouped_gemm(x, w, out, layout, swiglu)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
@@ -86,20 +97,25 @@ class MoEFeedForward(FeedForward):
         if ctx.debug is not None:
             ctx.debug.setdefault("router_ids", []).append(ids.clone())
             ctx.debug.setdefault("router_weights", []).append(wts.clone())
-        layout = KM.ExpertLayout(T * k, self.n_experts, KM.TILE_ROWS, dev)
+        tc = xn.dtype == torch.bfloat16 and self.w13.dtype == torch.bfloat16 and H % 8 == 0 and self.intermediate % 8 == 0
+        tile = KT.token_tile_for(T * k, self.n_experts) if tc else 0
+        layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         KM.moe_align(ids, layout)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
         KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
         h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
-        KM.grouped_gemm(x_rows, self.w13, h_rows, layout, swiglu=True)
+        self._product(x_rows, self.w13, h_rows, layout, True, tile)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
-        KM.grouped_gemm(h_rows, self.w2, y_rows, layout, swiglu=False)
+        self._product(h_rows, self.w2, y_rows, layout, False, tile)
         y_shared = None
         if self.ws13 is not None:
-            hs = torch.empty((T, self.shared_intermediate), dtype=act, device=dev)
-            KM.grouped_gemm(xn, self.ws13, hs, None, swiglu=True)
+            S = self.shared_intermediate
+            tcs = xn.dtype == torch.bfloat16 and self.ws13.dtype == torch.bfloat16 and H % 8 == 0 and S % 8 == 0
+            stile = KT.token_tile_for(T, 1) if tcs else 0
+            hs = torch.empty((T, S), dtype=act, device=dev)
+            self._product(xn, self.ws13, hs, None, True, stile)
             y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
-            KM.grouped_gemm(hs, self.ws2, y_shared, None, swiglu=False)
+            self._product(hs, self.ws2, y_shared, None, False, stile)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
         KM.moe_combine(y_rows, layout.row_of_pair, wts, y_shared, scale, y, k)
         return y
