@@ -120,6 +120,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
+                    "prefill to this file (torch profiler; not part of any timed number)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -256,8 +258,39 @@ def main() -> int:
         k_pts = max(8, min(args.steps, 32))
         out["points"] = {"decode_b1": round(run_decode(1, k_pts, 3)["tok_s"], 1),
                          "decode_b64": round(run_decode(64, k_pts, 3)["tok_s"], 1)}
+    if args.kernel_table:
+        kernel_table(tq, model, rng, V, args.batch, args.kernel_table)
     print(json.dumps(out))
     return 0
+
+
+def kernel_table(tq, model, rng, V, batch, path):
+    """Per-kernel device time of 4 decode steps at context 2,048 and of one 2,048-token prefill."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    eng = tq.Engine(model, max_tokens=batch * CONTEXT, max_slots=batch)
+    seqs = [eng.open() for _ in range(batch)]
+    eng.step([tq.StepEntry(s, rng.integers(0, V, size=PROMPT).tolist(), []) for s in seqs])
+    step = lambda: eng.step([tq.StepEntry(s, [1], [0]) for s in seqs])
+    step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(4):
+            step()
+        torch.cuda.synchronize()
+    text = "== 4 decode steps, batch %d, context %d ==\n" % (batch, PROMPT)
+    text += prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70)
+    for s in seqs:
+        eng.close(s)
+    s = eng.open()
+    toks = rng.integers(0, V, size=PROMPT).tolist()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        eng.step([tq.StepEntry(s, toks, [PROMPT - 1])])
+        torch.cuda.synchronize()
+    text += "\n== prefill of one %d-token prompt ==\n" % PROMPT
+    text += prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70)
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    open(path, "w").write(text)
 
 
 if __name__ == "__main__":

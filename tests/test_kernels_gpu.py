@@ -107,6 +107,7 @@ def paged_inputs(rng, seq_lens, q_lens, nkv, hd, page_size, dtype, n_pages=64):
             cache[pg, 1, :, p % page_size] = v_all[i][p]
     positions = np.concatenate([np.arange(L - q, L) for L, q in zip(seq_lens, q_lens)])
     seq_of = np.concatenate([np.full(q, i) for i, q in enumerate(q_lens)])
+    cache[np.setdiff1d(np.arange(n_pages), perm[:used])] = 1e30     # pages of no sequence: never to be read
     return dict(table=table, k=k_all, v=v_all, cache=cache, positions=positions, seq_of=seq_of)
 
 
@@ -123,6 +124,33 @@ def test_attention(nh, nkv, hd, window, dtype, tol):
     out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
     KA.attention(dev(q, dtype), dev(d["cache"], dtype), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
                  dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd), out, nh, nkv, hd)
+    want = np.zeros((T, nh * hd))
+    t0 = 0
+    for i, (L, ql) in enumerate(zip(seq_lens, q_lens)):
+        qfull = np.zeros((L, nh, hd))
+        qfull[L - ql:] = q[t0:t0 + ql]
+        want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
+        t0 += ql
+    close(out, want, tol)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (8, 1, 64), (16, 16, 128), (14, 2, 128), (3, 1, 256)])
+@pytest.mark.parametrize("window", [0, 7, 70])
+@pytest.mark.parametrize("n_splits", [1, 3, 16])
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_attention_split(nh, nkv, hd, window, n_splits, dtype, tol):
+    from turboquant_cpp_b200.kernels import attention as KA
+    rng = np.random.default_rng(nh * 100 + hd + window + n_splits)
+    seq_lens, q_lens, page = [70, 1, 130, 9, 300], [70, 1, 3, 1, 1], 64
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, dtype)
+    T = sum(q_lens)
+    q = bf16_values(rng.normal(size=(T, nh, hd)))
+    out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    partial = torch.full((T * nh * n_splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
+    assert KA.split_usable(nh, nkv, hd, page)
+    KA.attention_split(dev(q, dtype), dev(d["cache"], dtype), dev(d["positions"], torch.int32),
+                       dev(d["seq_of"], torch.int32), dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd),
+                       out, nh, nkv, hd, n_splits, partial)
     want = np.zeros((T, nh * hd))
     t0 = 0
     for i, (L, ql) in enumerate(zip(seq_lens, q_lens)):

@@ -177,3 +177,197 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
     TQ_CHECK_LAUNCH("attention");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Split attention for decoding (and any step with few tokens per sequence): the keys of one
+// (token, KV head) are cut into `n_splits` ranges, one CTA per range; a second kernel merges the
+// ranges' partial softmax states.  A key row is read by LPK = hd/8 lanes with one 16-byte load
+// each (two for fp32), so a warp covers 32/LPK keys per instruction and eight keys per iteration
+// with all loads in flight together; the G query heads that share the KV head are computed from
+// the same registers.  Partial state per (token, head, split): max, sum, hd weighted values (fp32).
+// ---------------------------------------------------------------------------------------
+#define SPLIT_WARPS 4
+
+template <typename T> struct Vec8 { };
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+
+template <typename TA, int LPK, int GC>
+__global__ void __launch_bounds__(SPLIT_WARPS * 32)
+attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ positions,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
+                       int page_size, int window, float scale, float* __restrict__ partial, int n_splits,
+                       int nh, int nkv) {
+    constexpr int HD = LPK * 8;
+    constexpr int KPI = 32 / LPK;            // keys per load instruction of a warp
+    constexpr int GS = KPI > 8 ? KPI : 8;    // keys per iteration of a warp (a group of absolute positions)
+    constexpr int LOADS = GS / KPI;          // load instructions per iteration
+    constexpr int NSTATE = SPLIT_WARPS * KPI; // partial states to merge inside the CTA
+    __shared__ float s_m[NSTATE][GC], s_l[NSTATE][GC];
+    __shared__ float s_acc[NSTATE][GC][HD];
+    const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+    const int G = nh / nkv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPK, part = lane / LPK;       // part: which of the KPI keys of a load
+    const int pos = positions[t];
+    const int start = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int* table = page_table + (size_t)seq_of_token[t] * table_stride;
+    // this split's keys: whole groups of GS absolute positions
+    const int first8 = start / GS, last8 = pos / GS;                   // inclusive groups
+    const int groups = last8 - first8 + 1;
+    const int per = (groups + n_splits - 1) / n_splits;
+    const int gb = first8 + split * per, ge = min(last8 + 1, gb + per);
+
+    float qv[GC][8], acc[GC][8], m[GC], l[GC];
+#pragma unroll
+    for (int h = 0; h < GC; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (h < G) Vec8<TA>::load(q + ((size_t)t * nh + (size_t)g * G + h) * HD + sub * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { qv[h][i] = f[i] * scale; acc[h][i] = 0.f; }
+    }
+    for (int grp = gb + warp; grp < ge; grp += SPLIT_WARPS) {
+        const int p0 = grp * GS;
+        const int page = table[p0 / page_size];
+        const TA* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
+        const TA* vbase = kbase + (size_t)nkv * page_size * HD;
+        float kf[LOADS][8], vf[LOADS][8];
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) Vec8<TA>::load(kbase + (size_t)(j * KPI + part) * HD + sub * 8, kf[j]);
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) Vec8<TA>::load(vbase + (size_t)(j * KPI + part) * HD + sub * 8, vf[j]);
+        float s[LOADS][GC];
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j)
+#pragma unroll
+            for (int h = 0; h < GC; ++h) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d = fmaf(qv[h][i], kf[j][i], d);
+                s[j][h] = d;
+            }
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j)
+#pragma unroll
+                for (int h = 0; h < GC; ++h) s[j][h] += __shfl_xor_sync(0xffffffffu, s[j][h], o);
+#pragma unroll
+        for (int h = 0; h < GC; ++h) {
+            float mx = m[h];
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) {
+                const int p = p0 + j * KPI + part;
+                if (p < start || p > pos) s[j][h] = -INFINITY;
+                mx = fmaxf(mx, s[j][h]);
+            }
+            if (mx == -INFINITY) continue;                 // nothing visible yet for this lane group
+            const float corr = expf(m[h] - mx);
+            float lsum = l[h] * corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[h][i] *= corr;
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) {
+                const float pe = expf(s[j][h] - mx);       // exp(-inf) = 0 for masked keys
+                lsum += pe;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(pe, vf[j][i], acc[h][i]);
+            }
+            m[h] = mx; l[h] = lsum;
+        }
+    }
+    // merge the CTA's NSTATE partial states
+    const int st = warp * KPI + part;
+#pragma unroll
+    for (int h = 0; h < GC; ++h) {
+        if (sub == 0) { s_m[st][h] = m[h]; s_l[st][h] = l[h]; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s_acc[st][h][sub * 8 + i] = acc[h][i];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NSTATE; ++w) M = fmaxf(M, s_m[w][h]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < NSTATE; ++w) {
+            const float f = s_m[w][h] == -INFINITY ? 0.f : expf(s_m[w][h] - M);
+            L += s_l[w][h] * f;
+            a += s_acc[w][h][d] * f;
+        }
+        float* dst = partial + (((size_t)t * nh + (size_t)g * G + h) * n_splits + split) * (HD + 2);
+        dst[2 + d] = a;
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+    }
+}
+
+template <typename TA>
+__global__ void attention_merge_kernel(const float* __restrict__ partial, int n_splits, int hd, TA* __restrict__ out) {
+    const size_t th = blockIdx.x;                        // token * nh + head
+    const float* p = partial + th * n_splits * (hd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[(size_t)s * (hd + 2)]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = p[(size_t)s * (hd + 2)];
+        if (ms != -INFINITY) L += p[(size_t)s * (hd + 2) + 1] * expf(ms - M);
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = p[(size_t)s * (hd + 2)];
+            if (ms != -INFINITY) a += p[(size_t)s * (hd + 2) + 2 + d] * expf(ms - M);
+        }
+        out[th * hd + d] = tq_from_float<TA>(a / L);
+    }
+}
+
+// partial: T * nh * n_splits * (hd + 2) floats of scratch.
+TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype, const int* positions,
+                                 const int* seq_of_token, const int* page_table, int table_stride, int page_size,
+                                 int window, float scale, float* partial, int n_splits, void* out, int T_, int nh,
+                                 int nkv, int hd, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256,
+               "attention_split: head size %d is not 16, 32, 64, 128 or 256", hd);
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "attention_split: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    const int G = nh / nkv;
+    TQ_REQUIRE(G <= 8, "attention_split: %d query heads per key/value head exceed 8", G);
+    TQ_REQUIRE(page_size % 16 == 0, "attention_split: page size %d must be a multiple of 16", page_size);
+    TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_split: bad grid (%d splits, %d KV heads)", n_splits, nkv);
+    TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
+    dim3 grid(T_, nkv, n_splits);
+#define SPLIT_LAUNCH(TA, LPK, GC)                                                                               \
+    attention_split_kernel<TA, LPK, GC><<<grid, SPLIT_WARPS * 32, 0, stream>>>(                                 \
+        (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window,   \
+        scale, partial, n_splits, nh, nkv)
+#define SPLIT_GC(TA, LPK)                                                                                       \
+    do { if (G == 1) SPLIT_LAUNCH(TA, LPK, 1); else if (G == 2) SPLIT_LAUNCH(TA, LPK, 2);                       \
+         else if (G <= 4) SPLIT_LAUNCH(TA, LPK, 4); else SPLIT_LAUNCH(TA, LPK, 8); } while (0)
+#define SPLIT_HD(TA)                                                                                            \
+    do { if (hd == 16) SPLIT_GC(TA, 2); else if (hd == 32) SPLIT_GC(TA, 4); else if (hd == 64) SPLIT_GC(TA, 8);         \
+         else if (hd == 128) SPLIT_GC(TA, 16); else SPLIT_GC(TA, 32); } while (0)
+    if (act_dtype == TQ_BF16) SPLIT_HD(__nv_bfloat16);
+    else if (act_dtype == TQ_F32) SPLIT_HD(float);
+    else TQ_FAIL(-2, "attention_split: unknown element type %d", act_dtype);
+    TQ_CHECK_LAUNCH("attention_split");
+    TQ_DISPATCH(act_dtype, TA,
+        (attention_merge_kernel<TA><<<T_ * nh, hd >= 128 ? 128 : 64, 0, stream>>>(partial, n_splits, hd, (TA*)out)));
+    TQ_CHECK_LAUNCH("attention_merge");
+    return 0;
+}

@@ -54,3 +54,36 @@ def attention(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tenso
                                  c_int(window), c_float(scale), ptr(out), c_int(T), c_int(n_heads),
                                  c_int(n_kv_heads), c_int(head_dim), stream()))
     return out
+
+
+SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
+
+
+def split_usable(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return head_dim in SPLIT_HEAD_DIMS and n_heads // n_kv_heads <= 8 and page_size % 16 == 0
+
+
+def splits_for(n_tokens: int, n_kv_heads: int) -> int:
+    """Ranges the keys of one (token, KV head) are cut into: enough CTAs to fill the GPU a few times
+    over when a step has few tokens, one range when it has many."""
+    return max(1, min(64, -(-592 // max(1, n_tokens * n_kv_heads))))
+
+
+def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                    page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
+                    n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, partial: torch.Tensor) -> torch.Tensor:
+    """Attention with the keys of each (token, KV head) cut into n_splits ranges and merged; `partial`
+    holds T * n_heads * n_splits * (head_dim + 2) floats of scratch."""
+    T = q.shape[0]
+    want_int32(positions, "positions")
+    want_int32(page_table, "page table")
+    want_f32(partial, "partial states")
+    if partial.numel() < T * n_heads * n_splits * (head_dim + 2):
+        raise KernelError("attention_split: the scratch for partial states is too small")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_attention_split(ptr(q), ptr(cache_layer), c_int(code(q.dtype)), ptr(positions),
+                                       ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]),
+                                       c_int(page_size), c_int(window), c_float(scale), ptr(partial), c_int(n_splits),
+                                       ptr(out), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                                       stream()), kernels=2)
+    return out

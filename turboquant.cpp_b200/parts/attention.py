@@ -76,8 +76,14 @@ class AttentionMixer(Mixer):
                           cache.page_size, q, cache.kv if cache.writes else None,
                           self.n_heads, self.n_kv_heads, self.head_dim)
         o = torch.empty((T, self.q_size), dtype=act, device=xn.device)
-        KA.attention(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
-                     self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
+        if KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
+            n_splits = KA.splits_for(T, self.n_kv_heads)
+            partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32, device=xn.device)
+            KA.attention_split(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
+                               self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim, n_splits, partial)
+        else:
+            KA.attention(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
+                         self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
 
