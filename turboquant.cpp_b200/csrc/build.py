@@ -131,6 +131,12 @@ def compile_kernel(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise KernelBuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
+    for old in os.listdir(os.path.dirname(out)):          # libraries of earlier versions of this file
+        if old.startswith(f"tq_{name}_") and old.endswith(".so") and os.path.join(os.path.dirname(out), old) != out:
+            try:
+                os.remove(os.path.join(os.path.dirname(out), old))
+            except OSError:
+                pass
     if verbose:
         _say(f"compiled {name}.cu in {time.time() - t0:.1f} s -> {out}")
     return out

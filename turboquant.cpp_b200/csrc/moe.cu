@@ -19,26 +19,57 @@
 
 TQ_DEFINE_LAST_ERROR
 
-#define ROUTER_THREADS 128
 #define ROUTER_MAX_EXPERTS 4096
+#define ROUTER_MAX_STAGED_H 8192      // widths up to this are staged in shared memory as fp32
 
 // ---------------------------------------------------------------------------------------
-// Router: one block per token.
+// Router: one block per token.  The token's row is staged in shared memory as fp32; each warp
+// takes whole rows of the router matrix (and the shared expert's gate row) and reads them with
+// 16-byte loads, eight elements per lane per step, in a fixed order; warp 0 then does the softmax
+// and the selection.
 // ---------------------------------------------------------------------------------------
-template <typename TA, typename TW>
+template <typename TW> struct RowVec { };
+template <> struct RowVec<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+};
+template <> struct RowVec<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+
+template <typename TA, typename TW, bool STAGED>
 __global__ void router_topk_kernel(const TA* __restrict__ x, const TW* __restrict__ wr,
                                    const TW* __restrict__ wsg, int* __restrict__ ids, float* __restrict__ wts,
-                                   float* __restrict__ shared_scale, int H, int E, int k, int renorm) {
-    extern __shared__ float s_logit[];          // E logits, 1 for the shared gate, k picked weights
+                                   float* __restrict__ shared_scale, int H, int E, int k, int renorm, int vec_ok) {
+    extern __shared__ float s_logit[];          // E logits, 1 for the shared gate, k picked weights, [H staged x]
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const TA* xr = x + (size_t)t * H;
     const int rows = E + (wsg ? 1 : 0);
     float* s_pick = s_logit + E + 1;
+    float* s_x = s_pick + k;
+    if (STAGED) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) s_x[i] = tq_to_float(xr[i]);
+        __syncthreads();
+    }
+    const int Hv = vec_ok ? (H / 8) * 8 : 0;    // part of the row read with 16-byte loads
     for (int e = warp; e < rows; e += nwarps) {
         const TW* w = e < E ? wr + (size_t)e * H : wsg;
         float s = 0.f;
-        for (int i = lane; i < H; i += 32) s += tq_to_float(xr[i]) * tq_to_float(w[i]);
+        for (int i = lane * 8; i < Hv; i += 256) {
+            float f[8];
+            RowVec<TW>::load(w + i, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = fmaf(STAGED ? s_x[i + j] : tq_to_float(xr[i + j]), f[j], s);
+        }
+        for (int i = Hv + lane; i < H; i += 32) s = fmaf(STAGED ? s_x[i] : tq_to_float(xr[i]), tq_to_float(w[i]), s);
         s = tq_warp_sum(s);
         if (lane == 0) s_logit[e] = s;
     }
@@ -86,10 +117,18 @@ TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const
     TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
     TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
     TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
-    const size_t smem = (size_t)(E + 1 + k) * sizeof(float);
-    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
-        (router_topk_kernel<TA, TW><<<T_, ROUTER_THREADS, smem, stream>>>(
-            (const TA*)x, (const TW*)wr, (const TW*)wsg, ids, wts, shared_scale, H, E, k, renorm))));
+    const bool staged = H <= ROUTER_MAX_STAGED_H && (size_t)(E + 1 + k + H) * sizeof(float) <= 48 * 1024;
+    const size_t smem = (size_t)(E + 1 + k + (staged ? H : 0)) * sizeof(float);
+    const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
+    const int vec_ok = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
+    const int rows = E + (wsg ? 1 : 0);
+    const int threads = rows >= 32 ? 1024 : (rows >= 16 ? 512 : (rows >= 8 ? 256 : 128));
+#define ROUTER_LAUNCH(ST)                                                                              \
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
+        (router_topk_kernel<TA, TW, ST><<<T_, threads, smem, stream>>>(                                \
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, ids, wts, shared_scale, H, E, k, renorm, vec_ok))))
+    if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
+#undef ROUTER_LAUNCH
     TQ_CHECK_LAUNCH("router_topk");
     return 0;
 }

@@ -16,12 +16,15 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
 from ..cache import CacheFull, PagedCache, Sequence_
 from ..csrc.build import ensure_built
 from ..parts.base import StepContext
+from .graph import DecodeGraphs
 
 
 class StepError(ValueError):
@@ -38,7 +41,8 @@ class StepEntry:
 class Engine:
     """A model, its cache and the step function."""
 
-    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, device="cuda:0"):
+    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, device="cuda:0",
+                 use_graphs: Optional[bool] = None):
         self.model = model
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -49,6 +53,13 @@ class Engine:
                                 max_tokens, self.act_dtype, self.device, max_slots=max_slots)
         self.debug: Optional[Dict[str, Any]] = None
         self.steps_run = 0
+        # widest page table a sequence can need; decode graphs keep tables of this width
+        longest = min(self.model.max_position, max(self.capacity_tokens, self.cache.page_size))
+        self.table_width = -(-longest // self.cache.page_size)
+        if use_graphs is None:
+            use_graphs = os.environ.get("TQ_NO_GRAPHS", "") in ("", "0")
+        stateless = all(n is None for n in model.state_needs())      # a mixer with state of its own walks the
+        self.graphs = DecodeGraphs(self) if use_graphs and stateless else None   # batch on the host: no graph
 
     # ---- what the generation loop asks -----------------------------------------------------------
     @property
@@ -96,6 +107,12 @@ class Engine:
                 if not 0 <= w < n:
                     raise StepError(f"sequence {e.seq.id}: wanted place {w} is outside its {n} tokens")
 
+    def _check_tokens(self, tokens: np.ndarray) -> None:
+        V = self.model.vocab_size
+        if tokens.size and (tokens.min() < 0 or tokens.max() >= V):
+            bad = int(tokens[(tokens < 0) | (tokens >= V)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary (0..{V - 1})")
+
     def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[torch.Tensor]]:
         """Packs the step's metadata and sends it to the device in one copy."""
         B = len(entries)
@@ -105,10 +122,7 @@ class Engine:
         cu = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(q_lens, out=cu[1:])
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
-        V = self.model.vocab_size
-        if tokens.size and (tokens.min() < 0 or tokens.max() >= V):
-            bad = int(tokens[(tokens < 0) | (tokens >= V)][0])
-            raise StepError(f"token id {bad} is outside the vocabulary (0..{V - 1})")
+        self._check_tokens(tokens)
         seq_of_token = np.repeat(np.arange(B, dtype=np.int64), q_lens)
         positions = np.arange(T, dtype=np.int64) - cu[:-1][seq_of_token] + starts[seq_of_token]
         want = np.array([cu[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
@@ -139,9 +153,14 @@ class Engine:
         seqs = [e.seq for e in entries]
         n_new = [len(e.tokens) for e in entries]
         self.cache.reserve(seqs, n_new)          # raises CacheFull before anything is written
-        ctx, dev_tables = self.build_context(entries)
+        decode = all(n == 1 and len(e.want) == 1 for n, e in zip(n_new, entries))
         with torch.cuda.device(self.device):
-            logits = self.model.forward(ctx, self.cache.layer_caches(dev_tables))
+            if decode and self.graphs is not None and self.debug is None:
+                self._check_tokens(np.asarray([e.tokens[0] for e in entries], dtype=np.int64))
+                logits = self.graphs.step(entries)
+            else:
+                ctx, dev_tables = self.build_context(entries)
+                logits = self.model.forward(ctx, self.cache.layer_caches(dev_tables))
         self.cache.commit(seqs, n_new)
         self.steps_run += 1
         return logits
