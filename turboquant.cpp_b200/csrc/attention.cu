@@ -371,3 +371,42 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_CHECK_LAUNCH("attention_merge");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// The same split attention with its scratch inside the library (see attention_no_alloc.h): for
+// callers that cannot allocate device memory.  In host code `tq_static_partial` is only a stand-in
+// for the symbol; its device address comes from cudaGetSymbolAddress, once per device.
+// ---------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+
+static __device__ __align__(256) float tq_static_partial[TQ_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+#define TQ_MAX_DEVICES 64
+static float* tq_static_partial_addr[TQ_MAX_DEVICES];      // device address of the array, per device
+
+TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int act_dtype, const int* positions,
+                                        const int* seq_of_token, const int* page_table, int table_stride,
+                                        int page_size, int window, float scale, int n_splits, void* out, int T_,
+                                        int nh, int nkv, int hd, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && nh > 0 && n_splits > 0 && hd > 0, "attention_split_static: bad sizes T=%d nh=%d splits=%d hd=%d",
+               T_, nh, n_splits, hd);
+    const unsigned long long need = (unsigned long long)T_ * nh * n_splits * (hd + 2);
+    TQ_REQUIRE(need <= (unsigned long long)TQ_ATTENTION_STATIC_SCRATCH_FLOATS,
+               "attention_split_static: %llu floats of scratch needed (T=%d, heads=%d, splits=%d, head size=%d) but the "
+               "built-in array holds %d; use tq_attention_split with a buffer of your own",
+               need, T_, nh, n_splits, hd, TQ_ATTENTION_STATIC_SCRATCH_FLOATS);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) TQ_FAIL(-1, "attention_split_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    TQ_REQUIRE(device >= 0 && device < TQ_MAX_DEVICES, "attention_split_static: device %d is beyond %d", device, TQ_MAX_DEVICES);
+    if (tq_static_partial_addr[device] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, tq_static_partial);
+        if (e != cudaSuccess || p == nullptr)
+            TQ_FAIL(-1, "attention_split_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+        tq_static_partial_addr[device] = p;
+    }
+    return tq_attention_split(q, cache, act_dtype, positions, seq_of_token, page_table, table_stride, page_size, window,
+                              scale, tq_static_partial_addr[device], n_splits, out, T_, nh, nkv, hd, stream);
+}
