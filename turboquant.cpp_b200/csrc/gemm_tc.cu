@@ -117,7 +117,11 @@ struct Tile {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    // narrow token tiles (decoding) leave room for two CTAs per SM: one CTA's start-up and epilogue
+    // overlap the other's weight stream; wide tiles take the whole SM
+    static constexpr int CTAS_PER_SM = BN <= 32 ? 2 : 1;
+    static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -126,7 +130,7 @@ struct Tile {
 };
 
 template <int BN, bool SWIGLU, typename TO>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, Tile<BN, SWIGLU>::CTAS_PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ out, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,

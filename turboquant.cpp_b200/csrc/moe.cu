@@ -20,7 +20,7 @@
 TQ_DEFINE_LAST_ERROR
 
 #define ROUTER_MAX_EXPERTS 4096
-#define ROUTER_MAX_STAGED_H 8192      // widths up to this are staged in shared memory as fp32
+#define ROUTER_MAX_STAGED_H 12288     // widths up to this are staged in shared memory as fp32 (48 KiB)
 
 // ---------------------------------------------------------------------------------------
 // Router: one block per token.  The token's row is staged in shared memory as fp32; each warp
@@ -44,23 +44,22 @@ template <> struct RowVec<float> {
     }
 };
 
+// Kernel 1: logits[t, e] = x[t] . w[e] for a chunk of rows (grid: tokens x row chunks).
 template <typename TA, typename TW, bool STAGED>
-__global__ void router_topk_kernel(const TA* __restrict__ x, const TW* __restrict__ wr,
-                                   const TW* __restrict__ wsg, int* __restrict__ ids, float* __restrict__ wts,
-                                   float* __restrict__ shared_scale, int H, int E, int k, int renorm, int vec_ok) {
-    extern __shared__ float s_logit[];          // E logits, 1 for the shared gate, k picked weights, [H staged x]
+__global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
+                                     float* __restrict__ logits, int H, int E, int rows_per_cta, int vec_ok) {
+    extern __shared__ float s_x[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const TA* xr = x + (size_t)t * H;
     const int rows = E + (wsg ? 1 : 0);
-    float* s_pick = s_logit + E + 1;
-    float* s_x = s_pick + k;
     if (STAGED) {
         for (int i = threadIdx.x; i < H; i += blockDim.x) s_x[i] = tq_to_float(xr[i]);
         __syncthreads();
     }
     const int Hv = vec_ok ? (H / 8) * 8 : 0;    // part of the row read with 16-byte loads
-    for (int e = warp; e < rows; e += nwarps) {
+    const int e0 = blockIdx.y * rows_per_cta, e1 = min(rows, e0 + rows_per_cta);
+    for (int e = e0 + warp; e < e1; e += nwarps) {
         const TW* w = e < E ? wr + (size_t)e * H : wsg;
         float s = 0.f;
         for (int i = lane * 8; i < Hv; i += 256) {
@@ -71,18 +70,25 @@ __global__ void router_topk_kernel(const TA* __restrict__ x, const TW* __restric
         }
         for (int i = Hv + lane; i < H; i += 32) s = fmaf(STAGED ? s_x[i] : tq_to_float(xr[i]), tq_to_float(w[i]), s);
         s = tq_warp_sum(s);
-        if (lane == 0) s_logit[e] = s;
+        if (lane == 0) logits[(size_t)t * (E + 1) + e] = s;
     }
-    __syncthreads();
-    if (warp != 0) return;
-    if (wsg && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
+}
+
+// Kernel 2: one warp per token: softmax over the E logits, k largest, weights, shared gate.
+__global__ void router_select_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
+                                     float* __restrict__ shared_scale, int T_, int E, int k, int renorm) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T_) return;
+    float* s_logit = logits + (size_t)t * (E + 1);      // this warp's row; chosen entries are overwritten
+    if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
     mx = tq_warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
     sum = tq_warp_sum(sum);
-    float picked_sum = 0.f;
+    float picked_sum = 0.f, mine = 0.f;                 // lane j keeps the weight of choice j, j + 32, ...
     for (int j = 0; j < k; ++j) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -101,35 +107,49 @@ __global__ void router_topk_kernel(const TA* __restrict__ x, const TW* __restric
         picked_sum += p;                        // identical in every lane
         if (lane == 0) {
             ids[(size_t)t * k + j] = best_e;
-            s_pick[j] = p;
+            wts[(size_t)t * k + j] = p;
             s_logit[best_e] = -INFINITY;
         }
         __syncwarp();
     }
-    for (int j = lane; j < k; j += 32)
-        wts[(size_t)t * k + j] = renorm ? s_pick[j] / picked_sum : s_pick[j];
+    (void)mine;
+    if (renorm) {
+        __syncwarp();
+        for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
+    }
 }
 
+// logits: T * (E + 1) floats of scratch.
 TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
-                             int* ids, float* wts, float* shared_scale, int T_, int H, int E, int k,
+                             float* logits, int* ids, float* wts, float* shared_scale, int T_, int H, int E, int k,
                              int renorm, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
     TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
     TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
-    const bool staged = H <= ROUTER_MAX_STAGED_H && (size_t)(E + 1 + k + H) * sizeof(float) <= 48 * 1024;
-    const size_t smem = (size_t)(E + 1 + k + (staged ? H : 0)) * sizeof(float);
+    TQ_REQUIRE(logits != nullptr, "router: scratch for the logits is required");
+    const bool staged = H <= ROUTER_MAX_STAGED_H;
+    const size_t smem = staged ? (size_t)H * sizeof(float) : 0;
     const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
     const int vec_ok = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
     const int rows = E + (wsg ? 1 : 0);
-    const int threads = rows >= 32 ? 1024 : (rows >= 16 ? 512 : (rows >= 8 ? 256 : 128));
+    // few tokens: cut the rows into chunks so that the step still fills the GPU; many tokens: one chunk
+    int chunks = T_ >= 256 ? 1 : (512 + T_ - 1) / T_;
+    if (chunks > (rows + 3) / 4) chunks = (rows + 3) / 4;
+    if (chunks < 1) chunks = 1;
+    const int rows_per_cta = (rows + chunks - 1) / chunks;
+    chunks = (rows + rows_per_cta - 1) / rows_per_cta;
+    const int threads = rows_per_cta >= 32 ? 1024 : (rows_per_cta >= 16 ? 512 : (rows_per_cta >= 8 ? 256 : 128));
+    dim3 grid(T_, chunks);
 #define ROUTER_LAUNCH(ST)                                                                              \
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
-        (router_topk_kernel<TA, TW, ST><<<T_, threads, smem, stream>>>(                                \
-            (const TA*)x, (const TW*)wr, (const TW*)wsg, ids, wts, shared_scale, H, E, k, renorm, vec_ok))))
+        (router_logits_kernel<TA, TW, ST><<<grid, threads, smem, stream>>>(                            \
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
     if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
 #undef ROUTER_LAUNCH
-    TQ_CHECK_LAUNCH("router_topk");
+    TQ_CHECK_LAUNCH("router_logits");
+    router_select_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(logits, ids, wts, shared_scale, T_, E, k, renorm);
+    TQ_CHECK_LAUNCH("router_select");
     return 0;
 }
 
@@ -350,7 +370,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
                                    const float* __restrict__ wts, const float* __restrict__ Ys,
                                    const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k) {
     const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
         float v = 0.f;
         for (int j = 0; j < k; ++j)
             v += wts[(size_t)t * k + j] * Y[(size_t)row_of_pair[(size_t)t * k + j] * H + i];
@@ -363,7 +383,9 @@ TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float
                              const float* shared_scale, float* y, int T_, int H, int k, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(H > 0 && k >= 0, "moe_combine: bad sizes H=%d k=%d", H, k);
-    moe_combine_kernel<<<T_, 256, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
+    int cols = T_ >= 512 ? 1 : (H + 255) / 256;          // few tokens: spread a row over several CTAs
+    if (cols > 64) cols = 64;
+    moe_combine_kernel<<<dim3(T_, cols), 256, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
     TQ_CHECK_LAUNCH("moe_combine");
     return 0;
 }

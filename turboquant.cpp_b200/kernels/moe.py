@@ -24,10 +24,12 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional
     want_f32(weights, "expert weights")
     if w_shared_gate is not None and w_shared_gate.dtype != w_router.dtype:
         w_shared_gate = w_shared_gate.to(w_router.dtype)
+    logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)      # scratch of the two-kernel router
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_router_topk(ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate),
-                                   c_int(code(w_router.dtype)), ptr(ids), ptr(weights), ptr(shared_scale),
-                                   c_int(T), c_int(H), c_int(E), c_int(top_k), c_int(1 if renorm else 0), stream()))
+                                   c_int(code(w_router.dtype)), ptr(logits), ptr(ids), ptr(weights), ptr(shared_scale),
+                                   c_int(T), c_int(H), c_int(E), c_int(top_k), c_int(1 if renorm else 0), stream()),
+          kernels=2)
 
 
 def max_tiles(n_pairs: int, n_experts: int, tile_rows: int) -> int:

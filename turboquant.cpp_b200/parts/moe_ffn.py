@@ -81,6 +81,15 @@ class MoEFeedForward(FeedForward):
             names.append("gemm_tc")       # float32 runs never launch the tensor-core kernel
         return names
 
+    _side_streams = {}
+
+    @classmethod
+    def _side_stream(cls, device):
+        key = torch.device(device).index
+        if key not in cls._side_streams:
+            cls._side_streams[key] = torch.cuda.Stream(device=device)
+        return cls._side_streams[key]
+
     def _product(self, x, w, out, layout, swiglu, token_tile):
         """Tensor cores for bfloat16 operands with 16-byte rows, the exact CUDA-core kernel otherwise."""
         if token_tile and KT.usable(x, w):
@@ -97,6 +106,25 @@ class MoEFeedForward(FeedForward):
         if ctx.debug is not None:
             ctx.debug.setdefault("router_ids", []).append(ids.clone())
             ctx.debug.setdefault("router_weights", []).append(wts.clone())
+        # the shared expert does not depend on the routing: it runs on a second stream next to the
+        # routed experts (its few CTAs would leave most of the GPU idle on their own)
+        y_shared = None
+        side = None
+        if self.ws13 is not None:
+            S = self.shared_intermediate
+            tcs = xn.dtype == torch.bfloat16 and self.ws13.dtype == torch.bfloat16 and H % 8 == 0 and S % 8 == 0
+            stile = KT.token_tile_for(T, 1) if tcs else 0
+            main = torch.cuda.current_stream()
+            side = self._side_stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                hs = torch.empty((T, S), dtype=act, device=dev)
+                self._product(xn, self.ws13, hs, None, True, stile)
+                y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
+                self._product(hs, self.ws2, y_shared, None, False, stile)
+            # hs and y_shared were allocated on the side stream; both live until this function returns,
+            # after the main stream has joined the side stream again, and the side stream's next use
+            # starts with a wait on the main stream: no cross-stream reuse hazard
         tc = xn.dtype == torch.bfloat16 and self.w13.dtype == torch.bfloat16 and H % 8 == 0 and self.intermediate % 8 == 0
         tile = KT.token_tile_for(T * k, self.n_experts) if tc else 0
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
@@ -107,15 +135,8 @@ class MoEFeedForward(FeedForward):
         self._product(x_rows, self.w13, h_rows, layout, True, tile)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
         self._product(h_rows, self.w2, y_rows, layout, False, tile)
-        y_shared = None
-        if self.ws13 is not None:
-            S = self.shared_intermediate
-            tcs = xn.dtype == torch.bfloat16 and self.ws13.dtype == torch.bfloat16 and H % 8 == 0 and S % 8 == 0
-            stile = KT.token_tile_for(T, 1) if tcs else 0
-            hs = torch.empty((T, S), dtype=act, device=dev)
-            self._product(xn, self.ws13, hs, None, True, stile)
-            y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
-            self._product(hs, self.ws2, y_shared, None, False, stile)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
         KM.moe_combine(y_rows, layout.row_of_pair, wts, y_shared, scale, y, k)
         return y
