@@ -161,6 +161,67 @@ def test_attention_split(nh, nkv, hd, window, n_splits, dtype, tol):
     close(out, want, tol)
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(2, 2, 128), (6, 2, 128), (4, 1, 64), (3, 3, 64)])
+@pytest.mark.parametrize("window", [0, 40, 200])
+def test_attention_prefill(nh, nkv, hd, window):
+    """Runs of new tokens of unequal lengths; some sequences already hold earlier tokens."""
+    from turboquant_cpp_b200.kernels import attention as KA, gemm_tc as KT
+    rng = np.random.default_rng(nh * 10 + hd + window)
+    seq_lens, q_lens, page = [300, 130, 64, 1, 513], [300, 70, 64, 1, 257], 64
+    dtype = torch.bfloat16
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, dtype, n_pages=40)
+    T = sum(q_lens)
+    q = bf16_values(rng.normal(size=(T, nh, hd)))
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)])
+    starts = np.array(seq_lens) - np.array(q_lens)
+    KA.attention_prefill(dev(q, dtype), dev(d["cache"], dtype), dev(cu, torch.int32), dev(starts, torch.int32),
+                         dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd), out, len(seq_lens), max(q_lens),
+                         nh, nkv, hd)
+    KT.check_status()
+    want = np.zeros((T, nh * hd))
+    t0 = 0
+    for i, (L, ql) in enumerate(zip(seq_lens, q_lens)):
+        qfull = np.zeros((L, nh, hd))
+        qfull[L - ql:] = q[t0:t0 + ql]
+        want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
+        t0 += ql
+    close(out, want, 1e-2)      # P is rounded to bfloat16 before the second product, and so is the result
+
+
+def test_attention_prefill_far_key_and_window_edge():
+    """A key 600 positions back carries a huge score: every later query's output is that key's value;
+    a window that ends one short of it hides it, a window that just reaches it shows it again."""
+    from turboquant_cpp_b200.kernels import attention as KA, gemm_tc as KT
+    rng = np.random.default_rng(11)
+    nh = nkv = 2
+    hd, page, L, far = 128, 64, 700, 37
+    dtype = torch.bfloat16
+    d = paged_inputs(rng, [L], [L], nkv, hd, page, dtype, n_pages=16)
+    q = bf16_values(rng.normal(size=(L, nh, hd)))
+    k = d["k"][0]
+    k[far] = 0
+    k[far, :, 0] = 40.0
+    q[:, :, 0] = 40.0
+    d["cache"][d["table"][0, far // page], 0, :, far % page] = k[far]
+    args = lambda w, out: KA.attention_prefill(
+        dev(q, dtype), dev(d["cache"], dtype), dev([0, L], torch.int32), dev([0], torch.int32),
+        dev(d["table"], torch.int32), page, w, 1 / math.sqrt(hd), out, 1, L, nh, nkv, hd)
+    out = torch.empty((L, nh * hd), dtype=dtype, device=DEV)
+    args(0, out)
+    KT.check_status()
+    close(out, P.attention(q, k, d["v"][0], 0), 1e-2)
+    close(out[far:], np.tile(d["v"][0][far].reshape(1, -1), (L - far, 1)), 1e-2)
+    w = 100
+    args(w, out)
+    want = P.attention(q, k, d["v"][0], w)
+    close(out, want, 1e-2)
+    got = out.float().cpu().numpy()
+    edge = far + w - 1                                       # the last query that still sees the far key
+    assert np.abs(got[edge] - np.tile(d["v"][0][far].reshape(-1), 1)).max() < 0.05
+    assert np.abs(got[edge + 1] - d["v"][0][far].reshape(-1)).max() > 0.5
+
+
 def test_attention_far_key_stands_out():
     """One key far back gets a large score: the output must be (almost) that key's value, which a
     kernel that skips or misplaces distant pages would miss."""

@@ -1,0 +1,425 @@
+// Causal attention for prompts on the 5th-generation tensor cores: S = Q K^T and O = P V as
+// tcgen05.mma with the accumulators in tensor memory, Q/K/V tiles brought in by TMA straight from
+// the query buffer and the paged key/value cache, online softmax in fp32 registers.
+//
+// Same mathematics as the exact kernel (csrc/attention.cu) and as the reference's per-token loop
+// (src/engine/tq_transformer.c:1909-1936 scores with scale 1/sqrt(hd), :1960 softmax, :2183-2191
+// weighted sum of V, head h reading KV head h/(nh/nkv) :1679, window start :1646-1654): scores,
+// running maximum, sum and the output accumulator are fp32; only P is rounded to bf16 to feed the
+// second product.
+//
+// One CTA = 128 consecutive query tokens of one sequence x one query head; it walks the keys in
+// tiles of 64 (= one cache page):
+//   warp 0        TMA: Q once, then K and V pages through two-stage rings
+//   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 64, K hd)  and
+//                 O_tile = P V  (M 128, N hd, K 64; V is the MN-major operand, read as stored)
+//   warps 2..5    one thread per query row: read S from tensor memory, mask, online softmax, write
+//                 P (bf16, 128-byte swizzled) to shared memory, then add O_tile into the row's fp32
+//                 accumulator registers
+// The heaviest query tiles (the last ones of a sequence, which see the most keys) are scheduled
+// first.  Every wait on an mbarrier is bounded; a wait that runs out sets *status and the CTA
+// leaves cleanly.
+#include <cuda.h>
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+namespace {
+
+constexpr int BM = 128;      // query rows per CTA
+constexpr int BN = 64;       // keys per tile = tokens per cache page
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+constexpr uint64_t WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_NS) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand, rows of 128 bytes, 128-byte swizzle (see csrc/gemm_tc.cu)
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (V as stored: one key per 128-byte row of 64 head elements): leading byte offset =
+// distance between blocks of 64 head elements, stride byte offset = eight keys (1024 bytes)
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: D fp32, A/B bf16, M 128, N n; b_mn: B is MN-major
+__device__ __forceinline__ uint32_t idesc(int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t id, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(id), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
+template <int HD>
+struct Cfg {
+    static constexpr int HALVES = HD / 64;                 // 64-element (128-byte) column blocks of a head
+    static constexpr int Q_BYTES = BM * HD * 2;
+    static constexpr int KV_BYTES = BN * HD * 2;           // one page of K or of V for one KV head
+    static constexpr int P_BYTES = BM * BN * 2;
+    static constexpr int STAGES = 2;
+    static constexpr int TILE_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES;
+    static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 256;
+    static constexpr int TMEM_COLS = (BN + HD) <= 128 ? 128 : 256;
+    static_assert(HD == 64 || HD == 128, "head size 64 or 128");
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
+                         const int* __restrict__ page_table, int table_stride, int window, float scale_log2e,
+                         __nv_bfloat16* __restrict__ out, int nh, int nkv, int* __restrict__ status) {
+    using C = Cfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_abort;
+    __shared__ uint32_t s_tmem_base;
+
+    const int seq = blockIdx.y, h = blockIdx.z;
+    const int g = h / (nh / nkv);
+    const int t_begin = cu_seqlens[seq], t_end = cu_seqlens[seq + 1];
+    const int qt = gridDim.x - 1 - blockIdx.x;                     // later tiles see more keys: start them first
+    const int t0 = t_begin + qt * BM;
+    if (t0 >= t_end) return;
+    const int rows = min(BM, t_end - t0);
+    const int p_first = seq_start[seq] + qt * BM;                  // position of row 0
+    const int p_last = p_first + rows - 1;
+    const int lo = window > 0 ? max(0, p_first + 1 - window) : 0;
+    const int kb_first = lo / BN, kb_last = p_last / BN;
+    const int n_tiles = kb_last - kb_first + 1;
+    const int* table = page_table + (size_t)seq * table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = base;
+    auto k_smem = [&](int s) { return base + C::Q_BYTES + s * C::KV_BYTES; };
+    auto v_smem = [&](int s) { return base + C::Q_BYTES + (C::STAGES + s) * C::KV_BYTES; };
+    const uint32_t p_smem = base + C::Q_BYTES + 2 * C::STAGES * C::KV_BYTES;
+    const uint32_t bars = base + C::TILE_BYTES;
+    const uint32_t q_full = bars;
+    auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
+    auto v_full = [&](int s) { return bars + 8u * (5 + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
+    const uint32_t s_ready = bars + 8u * 9, p_ready = bars + 8u * 10, o_ready = bars + 8u * 11, o_free = bars + 8u * 12;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
+        mbar_init(s_ready, 1);
+        mbar_init(p_ready, 4);          // one arrival per softmax warp
+        mbar_init(o_ready, 1);
+        mbar_init(o_free, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_s = s_tmem_base;            // S: BN columns
+    const uint32_t tmem_o = s_tmem_base + BN;       // O_tile: HD columns
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (uint32_t)C::Q_BYTES);
+#pragma unroll
+            for (int c = 0; c < C::HALVES; ++c) tma_load_2d(q_smem + c * (BM * 128), &map_q, h * HD + c * 64, t0, q_full);
+            int issued = 0;
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+                const int page = table[kb_first + i];
+                const int krow = ((page * 2 + 0) * nkv + g) * BN, vrow = ((page * 2 + 1) * nkv + g) * BN;
+                if (!mbar_wait(k_empty(s), ph ^ 1u, &s_abort)) break;
+                mbar_expect_tx(k_full(s), (uint32_t)C::KV_BYTES);
+#pragma unroll
+                for (int c = 0; c < C::HALVES; ++c) tma_load_2d(k_smem(s) + c * (BN * 128), &map_kv, c * 64, krow, k_full(s));
+                if (!mbar_wait(v_empty(s), ph ^ 1u, &s_abort)) { issued = i + 1; break; }
+                mbar_expect_tx(v_full(s), (uint32_t)C::KV_BYTES);
+#pragma unroll
+                for (int c = 0; c < C::HALVES; ++c) tma_load_2d(v_smem(s) + c * (BN * 128), &map_kv, c * 64, vrow, v_full(s));
+                issued = i + 1;
+            }
+            if (s_abort) {      // let the copies this thread started land before the CTA goes away
+                for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(q_full, 0); ++i) {}
+                const int first = issued > C::STAGES ? issued - C::STAGES : 0;
+                for (int i = first; i < issued; ++i) {
+                    const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
+                    for (uint32_t j = 0; j < WAIT_LIMIT && !mbar_try_wait(k_full(i % C::STAGES), ph); ++j) {}
+                    for (uint32_t j = 0; j < WAIT_LIMIT && !mbar_try_wait(v_full(i % C::STAGES), ph); ++j) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t id_s = idesc(BN, 0), id_o = idesc(HD, 1);
+            bool ok = mbar_wait(q_full, 0u, &s_abort);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u, it = (uint32_t)i & 1u;
+                ok = mbar_wait(k_full(s), ph, &s_abort);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {         // S = Q K^T
+                    const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32, koff = (k / 4) * (BN * 128) + (k % 4) * 32;
+                    umma(tmem_s, desc_k_major(q_smem + off), desc_k_major(k_smem(s) + koff), id_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(s_ready);
+                umma_commit(k_empty(s));
+                ok = mbar_wait(p_ready, it, &s_abort) && mbar_wait(v_full(s), ph, &s_abort);
+                if (ok && i > 0) ok = mbar_wait(o_free, (uint32_t)(i - 1) & 1u, &s_abort);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k)            // O_tile = P V
+                    umma(tmem_o, desc_k_major(p_smem + k * 32), desc_mn_major(v_smem(s) + k * 2048, BN * 128), id_o,
+                         k > 0 ? 1u : 0u);
+                umma_commit(o_ready);
+                umma_commit(v_empty(s));
+            }
+        }
+    } else {
+        // ------------------------------ softmax and accumulation: one thread per query row ------------------------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int qpos = p_first + r;
+        const int start = window > 0 ? max(0, qpos + 1 - window) : 0;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const uint32_t it = (uint32_t)i & 1u;
+            const int k0 = (kb_first + i) * BN;
+            ok = mbar_wait(s_ready, it, &s_abort);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sv[2][32];
+            tmem_ld32(tmem_s + lane_addr, sv[0]);
+            tmem_ld32(tmem_s + lane_addr + 32, sv[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float mx = m;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                const int kp = k0 + c;
+                float s = __uint_as_float(sv[c / 32][c % 32]) * scale_log2e;
+                if (kp > qpos || kp < start) s = -INFINITY;
+                sv[c / 32][c % 32] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            const float corr = mx == -INFINITY ? 1.f : exp2f(m - mx);     // nothing visible yet: keep the zeros
+            float lsum = 0.f;
+            // P in bf16, 16-byte chunks of 8 keys, written with the 128-byte swizzle of a K-major operand
+            const uint32_t prow = p_smem + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
+#pragma unroll
+            for (int ch = 0; ch < BN / 8; ++ch) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = ch * 8 + 2 * e;
+                    const float a = mx == -INFINITY ? 0.f : exp2f(__uint_as_float(sv[c / 32][c % 32]) - mx);
+                    const float b = mx == -INFINITY ? 0.f : exp2f(__uint_as_float(sv[(c + 1) / 32][(c + 1) % 32]) - mx);
+                    lsum += a + b;
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
+                    packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+                const uint32_t dst = prow + (uint32_t)((ch ^ (r % 8)) * 16);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
+                             "r"(packed[2]), "r"(packed[3]) : "memory");
+            }
+            l = l * corr + lsum;
+            m = mx;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+            // meanwhile rescale the accumulator, then add this tile's P V
+#pragma unroll
+            for (int d = 0; d < HD; ++d) o[d] *= corr;
+            ok = mbar_wait(o_ready, it, &s_abort);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + lane_addr + c0, ov);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c0 + j] += __uint_as_float(ov[j]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_free);
+        }
+        if (ok && r < rows) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h) * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                    packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(s_tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && s_abort) atomicExch(status, 1);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// bf16 matrix [rows][cols] row-major; box [box_rows][64 columns], 128-byte swizzle
+int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) TQ_FAIL(-3, "attention_prefill: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TQ_FAIL(-3, "attention_prefill: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const int* cu, const int* starts, const int* table,
+           int table_stride, int window, float scale, void* out, int n_seqs, int max_q_len, int nh, int nkv, int* status,
+           cudaStream_t stream) {
+    using C = Cfg<HD>;
+    auto kern = attention_prefill_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) TQ_FAIL(-1, "attention_prefill: cannot reserve %d bytes of shared memory: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((max_q_len + BM - 1) / BM, n_seqs, nh);
+    kern<<<grid, THREADS, C::SMEM_BYTES, stream>>>(mq, mkv, cu, starts, table, table_stride, window,
+                                                   scale * 1.4426950408889634f, (__nv_bfloat16*)out, nh, nkv, status);
+    TQ_CHECK_LAUNCH("attention_prefill");
+    return 0;
+}
+
+}  // namespace
+
+// q [T, nh, hd] bf16; cache [n_pages, 2, nkv, 64, hd] bf16 (keys and values of this step already written);
+// out [T, nh*hd] bf16.  cu_seqlens [n_seqs+1]: rows of each sequence in q; seq_start [n_seqs]: position of
+// each sequence's first row.  status: one int in device memory, set to 1 if a bounded wait ran out.
+TQ_EXPORT int tq_attention_prefill(const void* q, const void* cache, const int* cu_seqlens, const int* seq_start,
+                                   const int* page_table, int table_stride, int page_size, int n_pages, int window,
+                                   float scale, void* out, int T_, int n_seqs, int max_q_len, int nh, int nkv, int hd,
+                                   int* status, cudaStream_t stream) {
+    if (T_ == 0 || n_seqs == 0) return 0;
+    TQ_REQUIRE(hd == 64 || hd == 128, "attention_prefill: head size %d is not 64 or 128", hd);
+    TQ_REQUIRE(page_size == BN, "attention_prefill: page size %d must be %d", page_size, BN);
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "attention_prefill: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    TQ_REQUIRE(n_seqs <= 65535 && nh <= 65535, "attention_prefill: grid too large (%d sequences, %d heads)", n_seqs, nh);
+    TQ_REQUIRE(window >= 0 && max_q_len >= 1, "attention_prefill: bad window %d or longest run %d", window, max_q_len);
+    TQ_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)out % 16) == 0,
+               "attention_prefill: q, cache and out must be 16-byte aligned");
+    TQ_REQUIRE(status != nullptr, "attention_prefill: a status word is required");
+    CUtensorMap mq, mkv;
+    int rc = make_map(&mq, q, (uint64_t)T_, (uint64_t)nh * hd, BM);
+    if (rc) return rc;
+    rc = make_map(&mkv, cache, (uint64_t)n_pages * 2 * nkv * BN, (uint64_t)hd, BN);
+    if (rc) return rc;
+    if (hd == 64)
+        return launch<64>(mq, mkv, cu_seqlens, seq_start, page_table, table_stride, window, scale, out, n_seqs, max_q_len,
+                          nh, nkv, status, stream);
+    return launch<128>(mq, mkv, cu_seqlens, seq_start, page_table, table_stride, window, scale, out, n_seqs, max_q_len,
+                       nh, nkv, status, stream);
+}

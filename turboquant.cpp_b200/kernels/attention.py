@@ -87,3 +87,30 @@ def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch
                                        ptr(out), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                                        stream()), kernels=2)
     return out
+
+
+def prefill_usable(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """The tensor-core prompt kernel takes bfloat16, head sizes 64 and 128 and pages of 64 tokens."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64
+
+
+def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, cu_seqlens: torch.Tensor, seq_start: torch.Tensor,
+                      page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
+                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Causal attention of whole runs of new tokens (prompts, or pieces of them) on tcgen05 tensor
+    cores (csrc/attention_prefill.cu).  Row t of q belongs to the sequence whose [cu_seqlens[i],
+    cu_seqlens[i+1]) holds t and sits at position seq_start[i] + (t - cu_seqlens[i]); the step's keys
+    and values are already in the cache."""
+    from .gemm_tc import status_word
+    T = q.shape[0]
+    want_int32(cu_seqlens, "cu_seqlens")
+    want_int32(seq_start, "seq_start")
+    want_int32(page_table, "page table")
+    if not prefill_usable(q.dtype, head_dim, page_size) or cache_layer.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: needs bfloat16, head size 64 or 128 and pages of 64 tokens")
+    lib = load_kernel("attention_prefill")
+    check("attention_prefill", lib.tq_attention_prefill(
+        ptr(q), ptr(cache_layer), ptr(cu_seqlens), ptr(seq_start), ptr(page_table), c_int(page_table.shape[1]),
+        c_int(page_size), c_int(cache_layer.shape[0]), c_int(window), c_float(scale), ptr(out), c_int(T), c_int(n_seqs),
+        c_int(max_q_len), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), ptr(status_word(q.device)), stream()))
+    return out

@@ -20,6 +20,8 @@ from .base import KVNeed, LayerCache, Mixer, PositionEncoding, StepContext, regi
 
 
 class AttentionMixer(Mixer):
+    PREFILL_MIN_RUN = 48      # steps whose longest run of new tokens is at least this use the prompt kernel
+
     def __init__(self, prefix: str, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  qkv_bias: bool, window: int = 0, position: Optional[PositionEncoding] = None,
                  scale: Optional[float] = None):
@@ -58,7 +60,10 @@ class AttentionMixer(Mixer):
             self.position.prepare(store.device)
 
     def kernels(self) -> List[str]:
-        return ["attention"]
+        names = ["attention"]
+        if getattr(self, "run_dtype", None) == torch.bfloat16 and self.head_dim in (64, 128):
+            names.append("attention_prefill")
+        return names
 
     def cache_need(self) -> KVNeed:
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
@@ -76,7 +81,12 @@ class AttentionMixer(Mixer):
                           cache.page_size, q, cache.kv if cache.writes else None,
                           self.n_heads, self.n_kv_heads, self.head_dim)
         o = torch.empty((T, self.q_size), dtype=act, device=xn.device)
-        if KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
+        if ctx.max_q_len >= self.PREFILL_MIN_RUN and KA.prefill_usable(act, self.head_dim, cache.page_size):
+            # long runs of new tokens (prompts): tensor cores
+            KA.attention_prefill(q, cache.kv, ctx.cu_seqlens, ctx.seq_start, cache.page_table, cache.page_size,
+                                 self.window, self.scale, o, ctx.n_seqs, ctx.max_q_len, self.n_heads, self.n_kv_heads,
+                                 self.head_dim)
+        elif KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
             n_splits = KA.splits_for(T, self.n_kv_heads)
             partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32, device=xn.device)
             KA.attention_split(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
