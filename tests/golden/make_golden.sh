@@ -1,0 +1,17 @@
+#!/bin/bash
+# Builds the reference's CPU sources (read-only checkout at $1, default /root/reference) and runs
+# ref_driver.c against them; writes logits.bin next to this script.  No network, no GPU.
+# The one flag the reference needs on x86-64 gcc is -D__fp16=_Float16 (src/engine/tq_transformer.c:3456).
+set -e
+R=${1:-/root/reference}
+HERE=$(cd "$(dirname "$0")" && pwd)
+W=$(mktemp -d)
+for f in $R/src/core/*.c $R/src/cache/*.c $R/src/backend/cpu/*.c $R/src/engine/*.c; do
+  gcc -O2 -std=c11 -D_GNU_SOURCE -D__fp16=_Float16 -I$R/include -c "$f" -o "$W/$(basename "$f" .c).o"
+done
+ar rcs "$W/libtq.a" "$W"/*.o
+gcc -O2 -std=c11 -I$R/include "$HERE/ref_driver.c" "$W/libtq.a" -lm -lpthread -o "$W/ref_driver"
+(cd "$W" && ./ref_driver)
+cp "$W/logits.bin" "$HERE/logits.bin"
+rm -rf "$W"
+echo "wrote $HERE/logits.bin"

@@ -190,10 +190,17 @@ def silu(x: np.ndarray) -> np.ndarray:
     return x / (1.0 + np.exp(-x))
 
 
-def swiglu(x: np.ndarray, wg: np.ndarray, wu: np.ndarray, wd: np.ndarray, rnd: Round = no_round) -> np.ndarray:
+# exp used by the experts' SiLU and the shared gate's sigmoid.  The library's formula is the exact
+# exponential; tests/test_golden.py swaps in the reference's fast approximation
+# (src/engine/tq_moe.c:42-48) to compare with the reference's own output.
+MOE_EXP = np.exp
+
+
+def swiglu(x: np.ndarray, wg: np.ndarray, wu: np.ndarray, wd: np.ndarray, rnd: Round = no_round, exp=np.exp) -> np.ndarray:
     """down(silu(gate x) * (up x)) (dense: src/engine/tq_transformer.c:2771-2806;
     experts: src/engine/tq_moe.c:975-999, with exact exp here)."""
-    h = rnd(silu(linear(x, wg)) * linear(x, wu))
+    g = linear(x, wg)
+    h = rnd(g / (1.0 + exp(-g)) * linear(x, wu))
     return linear(h, wd)
 
 
@@ -243,12 +250,12 @@ def moe_feed_forward(m: PlainModel, l: int, x: np.ndarray, rnd: Round = no_round
             e = int(ids[t, j])
             pe = f"{p}experts.{e}."
             o = swiglu(x[t:t + 1], w[pe + "gate_proj.weight"], w[pe + "up_proj.weight"],
-                       w[pe + "down_proj.weight"], rnd)
+                       w[pe + "down_proj.weight"], rnd, MOE_EXP)
             y[t] += wts[t, j] * o[0]
     if m.cfg.get("shared_expert_intermediate_size", 0) > 0:
-        s = 1.0 / (1.0 + np.exp(-linear(x, w[p + "shared_expert_gate.weight"])))      # [T,1]
+        s = 1.0 / (1.0 + MOE_EXP(-linear(x, w[p + "shared_expert_gate.weight"])))      # [T,1]
         o = swiglu(x, w[p + "shared_expert.gate_proj.weight"], w[p + "shared_expert.up_proj.weight"],
-                   w[p + "shared_expert.down_proj.weight"], rnd)
+                   w[p + "shared_expert.down_proj.weight"], rnd, MOE_EXP)
         y = y + s * o
     return y
 

@@ -1,0 +1,98 @@
+"""The plain implementation against the reference's own CPU code, once, on a tiny random model.
+
+tests/golden/logits.bin was written by tests/golden/make_golden.sh, which compiles the reference's
+C sources and runs tests/golden/ref_driver.c (7 tokens through tq_forward).  The weights are not
+stored: the driver draws them from a xorshift generator in creation order, and this test draws the
+same numbers.  The reference rotates interleaved pairs, always renormalises the chosen experts'
+weights, and uses a fast exp in the experts' SiLU and the shared gate's sigmoid
+(src/engine/tq_ops.c:1418-1448, src/engine/tq_moe.c:659-678, :42-48); with those three switches set
+the same way the plain model reproduces its logits to float32 rounding.  With the exact exp, which
+is the library's formula, the difference is the approximation's error (about 1e-2 of the logits).
+"""
+import os
+import types
+
+import numpy as np
+
+from plain import qwen2_moe_plain as P
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class XorShift:
+    def __init__(self):
+        self.s = 88172645463325252
+
+    def draw(self, n):
+        out = np.empty(n, dtype=np.float32)
+        s, M = self.s, (1 << 64) - 1
+        for i in range(n):
+            s ^= (s << 13) & M
+            s ^= s >> 7
+            s ^= (s << 17) & M
+            out[i] = s >> 40
+        self.s = s
+        return (out / np.float32(1 << 24) - np.float32(0.5)) * np.float32(0.2)
+
+    def fill(self, *shape):
+        return self.draw(int(np.prod(shape))).reshape(shape).astype(np.float64)
+
+    def ones(self, n):
+        return (np.float32(1.0) + self.draw(n) * np.float32(0.1)).astype(np.float64)
+
+
+def reference_fast_exp(x):
+    """exp as the reference's experts approximate it (src/engine/tq_moe.c:42-48)."""
+    x = np.asarray(x, dtype=np.float32)
+    bits = (np.float32(12102203.0) * x + np.float32(1065353216.0)).astype(np.int32)
+    y = bits.view(np.float32).astype(np.float64)
+    y = np.where(x < -20.0, 0.0, y)
+    return np.where(x > 20.0, np.exp(x.astype(np.float64)), y)
+
+
+def build_model():
+    L, D, NH, NKV, HD, E, K, I, S, V = 2, 64, 4, 2, 16, 8, 2, 32, 64, 256
+    g = XorShift()
+    w = {"model.embed_tokens.weight": g.fill(V, D), "lm_head.weight": g.fill(V, D), "model.norm.weight": g.ones(D)}
+    for l in range(L):
+        p = f"model.layers.{l}."
+        w[p + "input_layernorm.weight"] = g.ones(D)
+        w[p + "post_attention_layernorm.weight"] = g.ones(D)
+        w[p + "self_attn.q_proj.weight"] = g.fill(NH * HD, D)
+        w[p + "self_attn.k_proj.weight"] = g.fill(NKV * HD, D)
+        w[p + "self_attn.v_proj.weight"] = g.fill(NKV * HD, D)
+        w[p + "self_attn.o_proj.weight"] = g.fill(D, NH * HD)
+        w[p + "self_attn.q_proj.bias"] = g.fill(NH * HD)
+        w[p + "self_attn.k_proj.bias"] = g.fill(NKV * HD)
+        w[p + "self_attn.v_proj.bias"] = g.fill(NKV * HD)
+        w[p + "mlp.gate.weight"] = g.fill(E, D)
+        for e in range(E):
+            q = f"{p}mlp.experts.{e}."
+            w[q + "gate_proj.weight"] = g.fill(I, D)
+            w[q + "up_proj.weight"] = g.fill(I, D)
+            w[q + "down_proj.weight"] = g.fill(D, I)
+        w[p + "mlp.shared_expert.gate_proj.weight"] = g.fill(S, D)
+        w[p + "mlp.shared_expert.up_proj.weight"] = g.fill(S, D)
+        w[p + "mlp.shared_expert.down_proj.weight"] = g.fill(D, S)
+        w[p + "mlp.shared_expert_gate.weight"] = g.fill(1, D)
+    return types.SimpleNamespace(
+        w=w, L=L, H=D, nh=NH, nkv=NKV, hd=HD, eps=1e-6, theta=10000.0, E=E, k=K, norm_topk=True, tied=False,
+        cfg={"shared_expert_intermediate_size": S}, layer_is_sparse=lambda l: True, layer_window=lambda l: 0)
+
+
+def test_plain_model_reproduces_the_reference_build():
+    ref = np.fromfile(os.path.join(HERE, "golden", "logits.bin"), dtype="<f4").reshape(7, 256).astype(np.float64)
+    m = build_model()
+    toks = [3, 17, 200, 42, 9, 77, 255]
+    scale = np.abs(ref).max()
+    P.MOE_EXP = reference_fast_exp
+    try:
+        same = P.forward(m, toks, pairing="interleaved")
+    finally:
+        P.MOE_EXP = np.exp
+    assert np.abs(same - ref).max() / scale < 5e-6          # the reference's computation, to float32 rounding
+    exact = P.forward(m, toks, pairing="interleaved")
+    err = np.abs(exact - ref).max() / scale
+    assert 1e-4 < err < 3e-2                                  # the fast exp's own error, nothing else
+    other = P.forward(m, toks, pairing="half")
+    assert np.abs(other - ref).max() / scale > 3e-2           # the pairing matters and is not the reference's
