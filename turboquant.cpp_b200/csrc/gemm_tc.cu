@@ -14,9 +14,10 @@
 // at decode the kernel is a weight stream (each CTA pulls a [128 x K] slab through a multi-stage
 // TMA pipeline) and the tokens ride along as a narrow N.
 //
-// One CTA per (weight-row tile, token tile).  Warp 0 issues TMA loads, warp 1 owns the tensor
-// memory and issues tcgen05.mma, warps 2..5 read the accumulator back (tcgen05.ld), apply the
-// epilogue and store.  All waits on mbarriers are bounded: a wait that runs out sets a flag, every
+// Persistent CTAs (one or two per SM) each walk a strided list of (weight-row tile, token tile)
+// pairs.  Warp 0 issues TMA loads as one uninterrupted stream of k-blocks across tiles, warp 1 owns
+// the tensor memory and issues tcgen05.mma into one of two accumulators, warps 2..5 read the other
+// accumulator back (tcgen05.ld), apply the epilogue and store while the next tile is multiplied.  All waits on mbarriers are bounded: a wait that runs out sets a flag, every
 // role leaves its loop, copies in flight are waited for (bounded again), tensor memory is freed and
 // the kernel returns with *status != 0; nothing spins forever.
 #include <cuda.h>
@@ -40,6 +41,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -123,11 +127,35 @@ struct Tile {
     static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
-    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : 256));
+    // two accumulators in tensor memory: a tile's epilogue overlaps the next tile's products
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "token tile must be 16..128 in steps of 16");
     static_assert(STAGES >= 2, "pipeline needs at least two stages");
+    static_assert(TMEM_COLS * CTAS_PER_SM <= 512, "tensor memory holds 512 columns per SM");
 };
+
+// One tile of work: (weight-row tile, token tile).  Tiles are numbered with the token tile running
+// fastest, so CTAs that run side by side share a weight slab through the L2 when an expert has
+// several token tiles (prompts); a CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+struct TileInfo { int expert, row0, count, m0; };
+
+__device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int bn, const int* tile_expert, const int* tile_row0,
+                                              const int* tile_count, int R) {
+    TileInfo t;
+    const int mx = id / n_ty, ty = id % n_ty;
+    t.m0 = mx * BM;
+    if (tile_expert) {
+        t.expert = tile_expert[ty];
+        t.row0 = tile_row0[ty];
+        t.count = tile_count[ty];
+    } else {
+        t.expert = 0;
+        t.row0 = ty * bn;
+        t.count = min(bn, R - t.row0);
+    }
+    return t;
+}
 
 template <int BN, bool SWIGLU, typename TO>
 __global__ void __launch_bounds__(THREADS, Tile<BN, SWIGLU>::CTAS_PER_SM)
@@ -140,26 +168,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ int s_abort;
     __shared__ uint32_t s_tmem_base;
 
-    int expert = 0, row0, count;
-    if (tile_expert) {
-        if ((int)blockIdx.y >= n_tiles[0]) return;
-        expert = tile_expert[blockIdx.y];
-        row0 = tile_row0[blockIdx.y];
-        count = tile_count[blockIdx.y];
-    } else {
-        row0 = blockIdx.y * BN;
-        if (row0 >= R) return;
-        count = min(BN, R - row0);
-    }
-    const int m0 = blockIdx.x * BM;
+    const int n_ty = tile_expert ? n_tiles[0] : (R + BN - 1) / BN;       // token tiles
+    const int n_mx = (N + BM - 1) / BM;                                  // weight-row tiles
+    const int total = n_ty * n_mx;
+    if ((int)blockIdx.x >= total) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
-    const uint32_t bars = base + T::STAGES * T::STAGE_BYTES;         // full[STAGES], empty[STAGES], accum
+    const uint32_t bars = base + T::STAGES * T::STAGE_BYTES;         // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (T::STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * T::STAGES);
+    auto acc_full = [&](int b) { return bars + 8u * (2 * T::STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * T::STAGES + 2 + b); };
     auto a_tile = [&](int s) { return base + s * T::STAGE_BYTES; };
     auto a2_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES; };
     auto b_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES * (SWIGLU ? 2 : 1); };
@@ -167,7 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < T::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }   // 4 epilogue warps
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -178,27 +199,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = s_tmem_base;
+    const uint32_t tmem_base = s_tmem_base;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer: one stream of k-blocks across all of this CTA's tiles ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % T::STAGES;
-                const uint32_t ph = (uint32_t)(kb / T::STAGES) & 1u;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) break;
-                mbar_expect_tx(full_bar(s), (uint32_t)T::STAGE_BYTES);
-                tma_load_3d(a_tile(s), &map_w, kb * BK, m0, expert, full_bar(s));
-                if (SWIGLU) tma_load_3d(a2_tile(s), &map_w, kb * BK, N + m0, expert, full_bar(s));
-                tma_load_2d(b_tile(s), &map_x, kb * BK, row0, full_bar(s));
-                issued = kb + 1;
+            int issued = 0;          // k-blocks issued so far (stage = issued % STAGES)
+            bool ok = true;
+            for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+                const TileInfo t = tile_info(id, n_ty, BN, tile_expert, tile_row0, tile_count, R);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int s = issued % T::STAGES;
+                    const uint32_t ph = (uint32_t)(issued / T::STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), (uint32_t)T::STAGE_BYTES);
+                    tma_load_3d(a_tile(s), &map_w, kb * BK, t.m0, t.expert, full_bar(s));
+                    if (SWIGLU) tma_load_3d(a2_tile(s), &map_w, kb * BK, N + t.m0, t.expert, full_bar(s));
+                    tma_load_2d(b_tile(s), &map_x, kb * BK, t.row0, full_bar(s));
+                    ++issued;
+                }
             }
             if (s_abort) {
                 // wait (bounded) for the copies this thread started, so none lands after the CTA is gone
                 const int first = issued > T::STAGES ? issued - T::STAGES : 0;
-                for (int kb = first; kb < issued; ++kb) {
-                    const uint32_t bar = full_bar(kb % T::STAGES), ph = (uint32_t)(kb / T::STAGES) & 1u;
+                for (int j = first; j < issued; ++j) {
+                    const uint32_t bar = full_bar(j % T::STAGES), ph = (uint32_t)(j / T::STAGES) & 1u;
                     for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(bar, ph); ++i) {}
                 }
             }
@@ -207,35 +232,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BN);
+            int consumed = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % T::STAGES;
-                const uint32_t ph = (uint32_t)(kb / T::STAGES) & 1u;
-                ok = mbar_wait(full_bar(s), ph, &s_abort);
+            for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
+                const int b = it & 1;
+                const uint32_t acc = tmem_base + (uint32_t)(b * T::ACC_COLS);
+                // the epilogue must have drained this accumulator (two tiles ago)
+                if (it >= 2) ok = mbar_wait(acc_empty(b), (uint32_t)((it >> 1) - 1) & 1u, &s_abort);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int s = consumed % T::STAGES;
+                    const uint32_t ph = (uint32_t)(consumed / T::STAGES) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, &s_abort);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
-                    umma(tmem_d, umma_desc(a_tile(s) + k * UMMA_K * 2), bd, idesc, acc);
-                    if (SWIGLU) umma(tmem_d + BN, umma_desc(a2_tile(s) + k * UMMA_K * 2), bd, idesc, acc);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
+                        umma(acc, umma_desc(a_tile(s) + k * UMMA_K * 2), bd, idesc, accum);
+                        if (SWIGLU) umma(acc + BN, umma_desc(a2_tile(s) + k * UMMA_K * 2), bd, idesc, accum);
+                    }
+                    umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                    ++consumed;
                 }
-                umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                if (ok) umma_commit(acc_full(b));       // this tile's accumulator is complete once all MMAs are done
             }
-            if (ok) umma_commit(accum_bar);         // the accumulator is complete once all MMAs are done
         }
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                 // weight row within the tile
-        const int n = m0 + r;                              // output column
-        if (mbar_wait(accum_bar, 0u, &s_abort)) {
+        int it = 0;
+        bool ok = true;
+        for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
+            const TileInfo t = tile_info(id, n_ty, BN, tile_expert, tile_row0, tile_count, R);
+            const int b = it & 1;
+            const int n = t.m0 + r;                        // output column
+            ok = mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t lane_addr = tmem_d + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t lane_addr = tmem_base + (uint32_t)(b * T::ACC_COLS) + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (c0 >= count) break;                    // uniform across the warp
+                if (c0 >= t.count) break;                  // uniform across the warp
                 uint32_t g[16], u[16];
                 tmem_ld16(lane_addr + c0, g);
                 if (SWIGLU) tmem_ld16(lane_addr + BN + c0, u);
@@ -243,21 +284,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (n < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < count) {
+                        if (c0 + j < t.count) {
                             float v = __uint_as_float(g[j]);
                             if (SWIGLU) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
-                            out[(size_t)(row0 + c0 + j) * N + n] = tq_from_float<TO>(v);
+                            out[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(v);
                         }
                     }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));      // this warp has read its quarter of the accumulator
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && s_abort) atomicExch(status, 1);
 }
@@ -308,7 +352,16 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* t
         if (e != cudaSuccess) TQ_FAIL(-1, "gemm_tc: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((N + BM - 1) / BM, grid_y);
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    // persistent CTAs: at most what the GPU runs at once; each walks tiles blockIdx.x, + gridDim.x, ...
+    long long tiles = (long long)((N + BM - 1) / BM) * grid_y;
+    const long long resident = (long long)n_sm * T::CTAS_PER_SM;
+    const int grid = (int)(tiles < resident ? tiles : resident);
     kern<<<grid, THREADS, T::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, te, tr, tc, nt, R, N, K, status);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
@@ -329,7 +382,6 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     TQ_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128, "gemm_tc: token tile %d is not one of 16, 32, 64, 128", bn);
     TQ_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
     const int grid_y = tile_expert ? max_tiles : (R + bn - 1) / bn;
-    TQ_REQUIRE(grid_y <= 65535, "gemm_tc: %d token tiles exceed the grid limit", grid_y);
     CUtensorMap mw, mx;
     const int Nw = swiglu ? 2 * N : N;
     int rc = make_map(&mw, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)G, BM);
