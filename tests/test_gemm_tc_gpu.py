@@ -38,7 +38,7 @@ def test_grouped(R, N, K, G, swiglu, bn, odtype):
     order = lay.sorted_pair.cpu().numpy()[:R]
     a_sorted = a[order]
     out = torch.full((R, N), float("nan"), dtype=odtype, device=DEV)
-    KT.gemm_tc(dev(a_sorted, torch.bfloat16), dev(w, torch.bfloat16), out, lay, swiglu, bn)
+    KT.gemm_tc(dev(a_sorted, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, lay, bn)
     KT.check_status()
     want = np.zeros((R, N))
     for g in range(G):
@@ -65,7 +65,7 @@ def test_one_group(R, N, K, swiglu):
     w = P.round_bf16(rng.normal(size=(1, 2 * N if swiglu else N, K)) / math.sqrt(K))
     bn = KT.token_tile_for(R, 1)
     out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
-    KT.gemm_tc(dev(a, torch.bfloat16), dev(w, torch.bfloat16), out, None, swiglu, bn)
+    KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, None, bn)
     KT.check_status()
     want = P.silu(a @ w[0, :N].T) * (a @ w[0, N:].T) if swiglu else a @ w[0].T
     assert rel(out, want) < 2e-5
@@ -73,15 +73,30 @@ def test_one_group(R, N, K, swiglu):
 
 def test_refuses_what_it_cannot_do():
     from turboquant_cpp_b200.kernels import KernelError, gemm_tc as KT
-    x = torch.zeros((4, 20), dtype=torch.bfloat16, device=DEV)        # K not a multiple of 8
-    w = torch.zeros((1, 16, 20), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((1, 16, 20), dtype=torch.bfloat16, device=DEV)    # K not a multiple of 8
+    assert not KT.packable(w)
+    with pytest.raises(KernelError):
+        KT.pack_weights(w, False)
     out = torch.zeros((4, 16), dtype=torch.float32, device=DEV)
-    assert not KT.usable(x, w)
-    with pytest.raises(KernelError):
-        KT.gemm_tc(x, w, out, None, False, 16)
     x = torch.zeros((4, 64), dtype=torch.bfloat16, device=DEV)
-    w = torch.zeros((1, 16, 64), dtype=torch.bfloat16, device=DEV)
+    pw = KT.pack_weights(torch.zeros((1, 16, 64), dtype=torch.bfloat16, device=DEV), False)
     with pytest.raises(KernelError):
-        KT.gemm_tc(x, w, out, None, False, 48)                         # not a token tile the kernel has
+        KT.gemm_tc(x, pw, out, None, 48)                               # not a token tile the kernel has
     with pytest.raises(KernelError):
-        KT.gemm_tc(x.float(), w, out, None, False, 16)
+        KT.gemm_tc(x.float(), pw, out, None, 16)                       # activations must be bfloat16
+    with pytest.raises(KernelError):
+        KT.gemm_tc(x[:, :32].contiguous(), pw, out, None, 16)          # packed for another K
+    with pytest.raises(KernelError):
+        KT.gemm_tc(x, pw, torch.zeros((4, 24), dtype=torch.float32, device=DEV), None, 16)
+
+
+def test_packing_layout():
+    from turboquant_cpp_b200.kernels import gemm_tc as KT
+    w = torch.arange(2 * 2 * 130 * 72, dtype=torch.float32, device=DEV).reshape(2, 260, 72).to(torch.bfloat16)
+    pw = KT.pack_weights(w, True)                                      # N = 130 -> 2 tiles, K = 72 -> 2 k-blocks
+    assert pw.data.shape == (2 * 2 * 2, 2, 128, 64) and pw.n == 130 and pw.k == 72 and pw.groups == 2
+    d = pw.data.view(2, 2, 2, 2, 128, 64)                               # group, gate/up, tile, k-block, row, col
+    assert torch.equal(d[1, 0, 1, 1, 1, :8], w[1, 129, 64:72])          # gate row 129 = tile 1 row 1, k-block 1
+    assert torch.equal(d[1, 1, 0, 0, 5, :], w[1, 130 + 5, :64])         # up row 5
+    assert float(d[0, 0, 1, 0, 2:, :].abs().sum()) == 0.0               # rows beyond N are zero
+    assert float(d[0, 0, 0, 1, :, 8:].abs().sum()) == 0.0               # columns beyond K are zero

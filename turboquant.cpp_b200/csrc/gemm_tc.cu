@@ -8,6 +8,10 @@
 // as the reference's expert loop computes them on the CPU (src/engine/tq_moe.c:975-999: g = Wg x,
 // u = Wu x, h = silu(g)*u, o = Wd h), with exact expf in the SiLU.
 //
+// The weights are packed once at load time into [128 rows x 64 elements] blocks of 16 KiB, so a
+// stage of the pipeline is one contiguous read and a CTA's stream walks memory sequentially instead
+// of touching 128 rows 4 KiB apart (which thrashes DRAM row buffers when hundreds of CTAs stream).
+//
 // Orientation: the WEIGHT rows are the M side of the MMA (128 rows per tile), the token rows are
 // the N side (16..128 per tile).  One kernel therefore serves a 2,048-token prompt and a decode
 // step of a few tokens per expert without padding the tensor core's M dimension with empty rows:
@@ -81,10 +85,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+// one [128 rows x 64 elements] block of the packed weights: (k-block, tile) select the block
+__device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t bar) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(0), "r"(0), "r"(kb), "r"(tile) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
@@ -213,8 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint32_t ph = (uint32_t)(issued / T::STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), (uint32_t)T::STAGE_BYTES);
-                    tma_load_3d(a_tile(s), &map_w, kb * BK, t.m0, t.expert, full_bar(s));
-                    if (SWIGLU) tma_load_3d(a2_tile(s), &map_w, kb * BK, N + t.m0, t.expert, full_bar(s));
+                    const int wt = t.expert * (SWIGLU ? 2 * n_mx : n_mx) + t.m0 / BM;     // packed weight tile
+                    tma_load_block(a_tile(s), &map_w, kb, wt, full_bar(s));
+                    if (SWIGLU) tma_load_block(a2_tile(s), &map_w, kb, wt + n_mx, full_bar(s));
                     tma_load_2d(b_tile(s), &map_x, kb * BK, t.row0, full_bar(s));
                     ++issued;
                 }
@@ -325,19 +331,33 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// bf16 tensor [d2][d1][d0 = K] (row-major, d0 contiguous); box [1][box_rows][64], 128-byte swizzle
-int make_map(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+// activations: bf16 matrix [rows][K] row-major; box [box_rows][64], 128-byte swizzle
+int make_map_x(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint32_t box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[3] = {k, rows, groups};
-    cuuint64_t strides[2] = {k * 2, rows * k * 2};
-    cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
-    cuuint32_t elem[3] = {1, 1, 1};
-    const cuuint32_t rank = groups > 0 ? 3 : 2;
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, elem,
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (r != CUDA_SUCCESS) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled (activations) failed with code %d", (int)r);
+    return 0;
+}
+
+// packed weights: [tiles][k-blocks][128 rows][64 elements], every [128 x 64] block contiguous (16 KiB)
+int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t tiles) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[4] = {(cuuint64_t)BK, (cuuint64_t)BM, k_blocks, tiles};
+    cuuint64_t strides[3] = {(cuuint64_t)BK * 2, (cuuint64_t)BK * BM * 2, k_blocks * BK * BM * 2};
+    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)BM, 1, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) TQ_FAIL(-3, "gemm_tc: cuTensorMapEncodeTiled (weights) failed with code %d", (int)r);
     return 0;
 }
 
@@ -369,7 +389,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* t
 
 }  // namespace
 
-// X [R, K] bf16; W [G, Nw, K] bf16 with Nw = N (plain) or 2N (swiglu); out [R, N] in bf16 or fp32.
+// X [R, K] bf16; W: the [G, Nw, K] weights (Nw = N, or 2N with swiglu: gate rows then up rows) PACKED into
+// [G * tiles][ceil(K/64)][128][64] blocks, zero-padded, where tiles = ceil(N/128) (plain) or 2*ceil(N/128)
+// (swiglu: the gate's tiles, then the up's); out [R, N] in bf16 or fp32.
 // tile_* describe token tiles of at most `bn` rows that never span two groups (null: one group, tiles
 // of bn consecutive rows).  status: one int in device memory, set to 1 if a bounded wait ran out.
 TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
@@ -383,10 +405,10 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     TQ_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
     const int grid_y = tile_expert ? max_tiles : (R + bn - 1) / bn;
     CUtensorMap mw, mx;
-    const int Nw = swiglu ? 2 * N : N;
-    int rc = make_map(&mw, W, (uint64_t)K, (uint64_t)Nw, (uint64_t)G, BM);
+    const int n_mx = (N + BM - 1) / BM;
+    int rc = make_map_w(&mw, W, (uint64_t)((K + BK - 1) / BK), (uint64_t)G * (swiglu ? 2 * n_mx : n_mx));
     if (rc) return rc;
-    rc = make_map(&mx, X, (uint64_t)K, (uint64_t)R, 0, (uint32_t)bn);
+    rc = make_map_x(&mx, X, (uint64_t)K, (uint64_t)R, (uint32_t)bn);
     if (rc) return rc;
 #define TC_CASE(BN_)                                                                                                  \
     if (bn == BN_) {                                                                                                  \

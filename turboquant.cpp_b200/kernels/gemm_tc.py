@@ -33,10 +33,52 @@ def check_status(device=None) -> None:
             raise KernelError("gemm_tc: a wait inside a tensor-core kernel ran out; its output is not valid")
 
 
-def usable(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """The tensor-core kernel takes bfloat16 operands whose rows are a multiple of 16 bytes."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+BLOCK_ROWS, BLOCK_K = 128, 64
+
+
+class PackedWeights:
+    """Weights [G, Nw, K] re-laid for the tensor-core kernel: [G * tiles, ceil(K/64), 128, 64] bf16, every
+    [128 x 64] block contiguous and zero-padded; with swiglu the gate's tiles come first, then the up's."""
+
+    def __init__(self, data: torch.Tensor, groups: int, n: int, k: int, swiglu: bool):
+        self.data, self.groups, self.n, self.k, self.swiglu = data, groups, n, k, swiglu
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size()
+
+
+def packable(w: torch.Tensor) -> bool:
+    """bfloat16 weights whose K gives the activations 16-byte rows."""
+    return w.dtype == torch.bfloat16 and w.shape[-1] % 8 == 0
+
+
+def pack_weights(w: torch.Tensor, swiglu: bool) -> PackedWeights:
+    """w [G, Nw, K] (or [Nw, K]) bf16 with Nw = N, or 2N with swiglu (gate rows, then up rows)."""
+    if w.dim() == 2:
+        w = w.unsqueeze(0)
+    if not packable(w):
+        raise KernelError("gemm_tc: weights must be bfloat16 with K a multiple of 8")
+    G, Nw, K = w.shape
+    N = Nw // 2 if swiglu else Nw
+    n_t, n_k = -(-N // BLOCK_ROWS), -(-K // BLOCK_K)
+    parts = [w[:, :N], w[:, N:]] if swiglu else [w]
+    out = torch.zeros((G, len(parts) * n_t, n_k, BLOCK_ROWS, BLOCK_K), dtype=w.dtype, device=w.device)
+    for i, part in enumerate(parts):
+        padded = torch.zeros((G, n_t * BLOCK_ROWS, n_k * BLOCK_K), dtype=w.dtype, device=w.device)
+        padded[:, :N, :K] = part
+        out[:, i * n_t:(i + 1) * n_t] = padded.view(G, n_t, BLOCK_ROWS, n_k, BLOCK_K).permute(0, 1, 3, 2, 4)
+        del padded
+    return PackedWeights(out.view(G * len(parts) * n_t, n_k, BLOCK_ROWS, BLOCK_K), G, N, K, swiglu)
+
+
+def usable(x: torch.Tensor, w) -> bool:
+    """The tensor-core kernel takes bfloat16 activations with 16-byte rows and packed weights."""
+    return (isinstance(w, PackedWeights) and x.dtype == torch.bfloat16 and x.shape[-1] == w.k
+            and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
 def token_tile_for(rows: int, groups: int) -> int:
@@ -48,28 +90,25 @@ def token_tile_for(rows: int, groups: int) -> int:
     return TOKEN_TILES[-1]
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Optional[ExpertLayout], swiglu: bool,
+def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
             token_tile: int) -> torch.Tensor:
-    """x [R, K] bf16; w [G, Nw, K] bf16 (Nw = N, or 2N with swiglu: gate rows then up rows); out [R, N]
-    bf16 or fp32.  layout: expert-sorted tiles of `token_tile` rows (None: one group)."""
+    """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
+    silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group)."""
     if not usable(x, w):
-        raise KernelError("gemm_tc: needs bfloat16 operands with K a multiple of 8 and 16-byte aligned storage")
+        raise KernelError("gemm_tc: needs bfloat16 activations with K a multiple of 8 and weights packed for this K")
     R, K = x.shape
     N = out.shape[1]
-    if w.dim() == 2:
-        w = w.unsqueeze(0)
-    G = w.shape[0]
-    if w.shape[2] != K or w.shape[1] != (2 * N if swiglu else N):
-        raise KernelError(f"gemm_tc: weight {tuple(w.shape)} does not fit x {tuple(x.shape)} -> out {tuple(out.shape)}")
+    if N != w.n:
+        raise KernelError(f"gemm_tc: weights give {w.n} columns, out has {N}")
     if layout is not None and layout.tile_rows != token_tile:
         raise KernelError(f"gemm_tc: the layout has tiles of {layout.tile_rows} rows, the kernel was asked for {token_tile}")
-    if layout is None and G != 1:
+    if layout is None and w.groups != 1:
         raise KernelError("gemm_tc: several groups need a layout")
     lib = load_kernel(_LIB)
     lo = layout
     check(_LIB, lib.tq_gemm_tc(
-        ptr(x), ptr(w), ptr(out), c_int(code(out.dtype)),
+        ptr(x), ptr(w.data), ptr(out), c_int(code(out.dtype)),
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None, ptr(lo.tile_count) if lo else None,
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
-        c_int(R), c_int(N), c_int(K), c_int(G), c_int(1 if swiglu else 0), ptr(status_word(x.device)), stream()))
+        c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), ptr(status_word(x.device)), stream()))
     return out

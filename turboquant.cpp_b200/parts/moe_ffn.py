@@ -73,6 +73,15 @@ class MoEFeedForward(FeedForward):
             self.ws2 = d.unsqueeze(0).contiguous()
             if self.shared_gate:
                 self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
+        # bfloat16 runs whose sizes give 16-byte rows keep the expert weights only in the packed layout
+        # of the tensor-core kernel
+        if store.run_dtype == torch.bfloat16 and H % 8 == 0 and I % 8 == 0 and KT.packable(self.w13) and KT.packable(self.w2):
+            self.w13 = KT.pack_weights(self.w13, True)
+            self.w2 = KT.pack_weights(self.w2, False)
+        if self.ws13 is not None and store.run_dtype == torch.bfloat16 and H % 8 == 0 and S % 8 == 0 \
+                and KT.packable(self.ws13) and KT.packable(self.ws2):
+            self.ws13 = KT.pack_weights(self.ws13, True)
+            self.ws2 = KT.pack_weights(self.ws2, False)
 
     def kernels(self) -> List[str]:
         names = ["moe", "elementwise"]
@@ -91,9 +100,10 @@ class MoEFeedForward(FeedForward):
         return cls._side_streams[key]
 
     def _product(self, x, w, out, layout, swiglu, token_tile):
-        """Tensor cores for bfloat16 operands with 16-byte rows, the exact CUDA-core kernel otherwise."""
-        if token_tile and KT.usable(x, w):
-            return KT.gemm_tc(x, w, out, layout, swiglu, token_tile)
+        """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
+        kernel otherwise."""
+        if isinstance(w, KT.PackedWeights):
+            return KT.gemm_tc(x, w, out, layout, token_tile)
         return KM.grouped_gemm(x, w, out, layout, swiglu)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
@@ -112,8 +122,7 @@ class MoEFeedForward(FeedForward):
         side = None
         if self.ws13 is not None:
             S = self.shared_intermediate
-            tcs = xn.dtype == torch.bfloat16 and self.ws13.dtype == torch.bfloat16 and H % 8 == 0 and S % 8 == 0
-            stile = KT.token_tile_for(T, 1) if tcs else 0
+            stile = KT.token_tile_for(T, 1) if isinstance(self.ws13, KT.PackedWeights) else 0
             main = torch.cuda.current_stream()
             side = self._side_stream(dev)
             side.wait_stream(main)
@@ -125,8 +134,7 @@ class MoEFeedForward(FeedForward):
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
-        tc = xn.dtype == torch.bfloat16 and self.w13.dtype == torch.bfloat16 and H % 8 == 0 and self.intermediate % 8 == 0
-        tile = KT.token_tile_for(T * k, self.n_experts) if tc else 0
+        tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         KM.moe_align(ids, layout)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
