@@ -22,7 +22,7 @@ TQ_DEFINE_LAST_ERROR
 #define TQ_MAX_HEAD_DIM 256
 
 // ---------------------------------------------------------------------------------------
-// grid (T, nh + 2*nkv) [or (T, nh) when keys/values are not written]; one pair per thread
+// A block walks (head, pair) indices of one token's fused QKV row; with few tokens several blocks share a row.
 // ---------------------------------------------------------------------------------------
 template <typename TA, typename TB>
 __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __restrict__ bias,
@@ -30,34 +30,42 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
                                       int pairing, const int* __restrict__ positions,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
                                       int table_stride, int page_size, TA* __restrict__ q_out,
-                                      TA* __restrict__ cache, int nh, int nkv, int hd) {
-    const int t = blockIdx.x, j = blockIdx.y, i = threadIdx.x;
+                                      TA* __restrict__ cache, int heads, int nh, int nkv, int hd) {
+    const int t = blockIdx.x;
     const int half = hd >> 1;
-    if (i >= half) return;
     const int width = (nh + 2 * nkv) * hd;
-    const TA* src = qkv + (size_t)t * width + (size_t)j * hd;
-    const TB* b = bias ? bias + (size_t)j * hd : nullptr;
+    const TA* row = qkv + (size_t)t * width;
     const int pos = positions[t];
-    int ia, ib;
-    if (pairing == 0) { ia = i; ib = i + half; } else { ia = 2 * i; ib = 2 * i + 1; }
-    float a = tq_to_float(src[ia]), c = tq_to_float(src[ib]);
-    if (b) { a += tq_to_float(b[ia]); c += tq_to_float(b[ib]); }
-    const bool is_v = j >= nh + nkv;
-    if (!is_v && cos_t) {
-        const float cs = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
-        const float ra = a * cs - c * sn, rc = a * sn + c * cs;
-        a = ra; c = rc;
-    }
-    TA* dst;
-    if (j < nh) {
-        dst = q_out + ((size_t)t * nh + j) * hd;
-    } else {
-        const int kvh = is_v ? j - nh - nkv : j - nh;
+    const float* cs_row = cos_t ? cos_t + (size_t)pos * half : nullptr;
+    const float* sn_row = sin_t ? sin_t + (size_t)pos * half : nullptr;
+    size_t page_base = 0;
+    if (heads > nh) {
         const int page = page_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
-        dst = cache + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + pos % page_size) * hd;
+        page_base = (size_t)page * 2 * nkv * page_size * hd + (size_t)(pos % page_size) * hd;
     }
-    dst[ia] = tq_from_float<TA>(a);
-    dst[ib] = tq_from_float<TA>(c);
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < heads * half; idx += gridDim.y * blockDim.x) {
+        const int j = idx / half, i = idx - j * half;
+        const TA* src = row + (size_t)j * hd;
+        int ia, ib;
+        if (pairing == 0) { ia = i; ib = i + half; } else { ia = 2 * i; ib = 2 * i + 1; }
+        float a = tq_to_float(src[ia]), c = tq_to_float(src[ib]);
+        if (bias) { a += tq_to_float(bias[(size_t)j * hd + ia]); c += tq_to_float(bias[(size_t)j * hd + ib]); }
+        const bool is_v = j >= nh + nkv;
+        if (!is_v && cs_row) {
+            const float cs = cs_row[i], sn = sn_row[i];
+            const float ra = a * cs - c * sn, rc = a * sn + c * cs;
+            a = ra; c = rc;
+        }
+        TA* dst;
+        if (j < nh) {
+            dst = q_out + ((size_t)t * nh + j) * hd;
+        } else {
+            const int kvh = is_v ? j - nh - nkv : j - nh;
+            dst = cache + page_base + ((size_t)(is_v ? 1 : 0) * nkv + kvh) * page_size * hd;
+        }
+        dst[ia] = tq_from_float<TA>(a);
+        dst[ib] = tq_from_float<TA>(c);
+    }
 }
 
 TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias, int bias_dtype,
@@ -70,13 +78,15 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     TQ_REQUIRE(pairing == 0 || pairing == 1, "qkv_rope_cache: pairing %d is neither half (0) nor interleaved (1)", pairing);
     TQ_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_rope_cache: cos and sin tables must come together");
     const int heads = write_kv ? nh + 2 * nkv : nh;
-    TQ_REQUIRE(heads <= 65535, "qkv_rope_cache: %d heads exceed the grid limit", heads);
-    dim3 grid(T_, heads);
-    const int threads = ((hd / 2 + 31) / 32) * 32;
+    const int pairs = heads * (hd / 2);
+    const int threads = pairs >= 1024 ? 256 : (pairs >= 256 ? 128 : 64);
+    // few tokens: several blocks share a token's row, so that the step still fills the GPU
+    int chunks = T_ >= 512 ? 1 : (pairs + threads - 1) / threads;
+    if (chunks > 64) chunks = 64;
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
-        (qkv_rope_cache_kernel<TA, TB><<<grid, threads, 0, stream>>>(
+        (qkv_rope_cache_kernel<TA, TB><<<dim3(T_, chunks), threads, 0, stream>>>(
             (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
-            table_stride, page_size, (TA*)q_out, (TA*)cache, nh, nkv, hd))));
+            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd))));
     TQ_CHECK_LAUNCH("qkv_rope_cache");
     return 0;
 }

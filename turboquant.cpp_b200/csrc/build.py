@@ -132,7 +132,8 @@ def compile_kernel(name: str, verbose: bool = True) -> str:
         raise KernelBuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
     for old in os.listdir(os.path.dirname(out)):          # libraries of earlier versions of this file
-        if old.startswith(f"tq_{name}_") and old.endswith(".so") and os.path.join(os.path.dirname(out), old) != out:
+        stem = old[len(f"tq_{name}_"):-3] if old.startswith(f"tq_{name}_") and old.endswith(".so") else ""
+        if len(stem) == 16 and all(ch in "0123456789abcdef" for ch in stem) and os.path.join(os.path.dirname(out), old) != out:
             try:
                 os.remove(os.path.join(os.path.dirname(out), old))
             except OSError:

@@ -64,10 +64,80 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__ y, 
     }
 }
 
+// The same with 16-byte accesses: a thread keeps up to 8 groups of 4 elements of its row in registers
+// between the two passes (H a multiple of 4, at most 32 * blockDim elements).
+template <typename T> __device__ __forceinline__ float4 tq_load4(const T* p);
+template <> __device__ __forceinline__ float4 tq_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 tq_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void tq_store4(T* p, float4 v);
+template <> __device__ __forceinline__ void tq_store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void tq_store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+#define RMS_VEC_GROUPS 8
+template <typename TY, typename TW, typename TO>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
+                                   const TW* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + src * H;
+    const TY* yr = y ? y + src * H : nullptr;
+    const bool write_back = y && !rows;
+    const int nvec = H >> 2;
+    float4 v[RMS_VEC_GROUPS];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            float4 a = tq_load4<float>(xr + 4 * i);
+            if (yr) { const float4 b = tq_load4<TY>(yr + 4 * i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+            if (write_back) tq_store4<float>(xr + 4 * i, a);
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            v[c] = a;
+        }
+    }
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+#pragma unroll
+    for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            const float4 g = tq_load4<TW>(w + 4 * i);
+            tq_store4<TO>(o + 4 * i, make_float4(v[c].x * rs * g.x, v[c].y * rs * g.y, v[c].z * rs * g.z, v[c].w * rs * g.w));
+        }
+    }
+}
+
 TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, const void* w, int w_dtype,
                          void* out, int out_dtype, int R, int H, float eps, cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
+    if (H % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0) {
+        int vthreads = ((H / 4 + 31) / 32) * 32;
+        if (vthreads > 256 && H / 4 <= 256 * RMS_VEC_GROUPS) vthreads = ((H / 4 + 255) / 256 <= 4) ? 256 : 512;
+        if (vthreads > 1024) vthreads = 1024;
+        if (H / 4 <= vthreads * RMS_VEC_GROUPS) {
+            TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+                (rmsnorm_vec_kernel<TY, TW, TO><<<R, vthreads, 0, stream>>>(x, (const TY*)y, rows, (const TW*)w,
+                                                                            (TO*)out, H, eps)))));
+            TQ_CHECK_LAUNCH("rmsnorm");
+            return 0;
+        }
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (rmsnorm_kernel<TY, TW, TO><<<R, threads, 0, stream>>>(x, (const TY*)y, rows, (const TW*)w,
@@ -125,19 +195,28 @@ TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, 
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ idx, int divisor,
-                                   T* __restrict__ out, int H) {
+                                   T* __restrict__ out, int H, int vec) {
     const int r = blockIdx.x;
     const T* src = in + (size_t)(idx[r] / divisor) * H;
     T* dst = out + (size_t)r * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    if (vec) {          // rows are a multiple of 16 bytes and 16-byte aligned
+        const int n16 = (int)((size_t)H * sizeof(T) / 16);
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    }
 }
 
 TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* out, int dtype, int R, int H,
                              cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0 && divisor > 0, "gather_rows: bad sizes R=%d H=%d divisor=%d", R, H, divisor);
+    const int esize = dtype == TQ_F32 ? 4 : 2;
+    const int vec = ((size_t)H * esize) % 16 == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0;
     TQ_DISPATCH(dtype, T,
-        gather_rows_kernel<T><<<R, 256, 0, stream>>>((const T*)in, idx, divisor, (T*)out, H));
+        gather_rows_kernel<T><<<R, 256, 0, stream>>>((const T*)in, idx, divisor, (T*)out, H, vec));
     TQ_CHECK_LAUNCH("gather_rows");
     return 0;
 }

@@ -153,6 +153,17 @@ TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const
     return 0;
 }
 
+// Selection alone, for logits [T, E + 1] computed elsewhere (the tensor-core GEMM on long prompts).
+TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* shared_scale, int T_, int E, int k,
+                               int renorm, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
+    TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
+    router_select_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(logits, ids, wts, shared_scale, T_, E, k, renorm);
+    TQ_CHECK_LAUNCH("router_select");
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // Expert-sorted layout.  Pair p = t*k + j chose expert ids[p].  Rows of the sorted layout:
 // expert 0's pairs in pair order, then expert 1's, …  Outputs:
@@ -370,6 +381,23 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
                                    const float* __restrict__ wts, const float* __restrict__ Ys,
                                    const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k) {
     const int t = blockIdx.x;
+    if ((H & 3) == 0) {          // four columns per thread, 16-byte accesses (rows of fp32 are 16-byte aligned)
+        const float sc = Ys ? (shared_scale ? shared_scale[t] : 1.0f) : 0.f;
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < H; i += gridDim.y * blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < k; ++j) {
+                const float wj = wts[(size_t)t * k + j];
+                const float4 a = *reinterpret_cast<const float4*>(Y + (size_t)row_of_pair[(size_t)t * k + j] * H + i);
+                v.x += wj * a.x; v.y += wj * a.y; v.z += wj * a.z; v.w += wj * a.w;
+            }
+            if (Ys) {
+                const float4 a = *reinterpret_cast<const float4*>(Ys + (size_t)t * H + i);
+                v.x += sc * a.x; v.y += sc * a.y; v.z += sc * a.z; v.w += sc * a.w;
+            }
+            *reinterpret_cast<float4*>(y + (size_t)t * H + i) = v;
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
         float v = 0.f;
         for (int j = 0; j < k; ++j)
@@ -383,9 +411,11 @@ TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float
                              const float* shared_scale, float* y, int T_, int H, int k, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(H > 0 && k >= 0, "moe_combine: bad sizes H=%d k=%d", H, k);
-    int cols = T_ >= 512 ? 1 : (H + 255) / 256;          // few tokens: spread a row over several CTAs
+    // few tokens: narrow blocks, several per row, so that the step still fills the GPU
+    const int threads = T_ >= 512 ? 256 : 64;
+    int cols = T_ >= 512 ? 1 : (H + threads * 4 - 1) / (threads * 4);
     if (cols > 64) cols = 64;
-    moe_combine_kernel<<<dim3(T_, cols), 256, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
+    moe_combine_kernel<<<dim3(T_, cols), threads, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
     TQ_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -32,6 +32,18 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional
           kernels=2)
 
 
+def router_select(logits: torch.Tensor, top_k: int, renorm: bool, ids: torch.Tensor, weights: torch.Tensor,
+                  shared_scale: Optional[torch.Tensor]) -> None:
+    """The selection step alone, on float32 logits [T, E + 1] (column E: the shared gate's logit).
+    The chosen entries of `logits` are overwritten."""
+    want_f32(logits, "router logits")
+    want_int32(ids, "expert ids")
+    T, E1 = logits.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_router_select(ptr(logits), ptr(ids), ptr(weights), ptr(shared_scale), c_int(T), c_int(E1 - 1),
+                                     c_int(top_k), c_int(1 if renorm else 0), stream()))
+
+
 def max_tiles(n_pairs: int, n_experts: int, tile_rows: int) -> int:
     """Upper bound of the number of row tiles for any routing of n_pairs pairs."""
     return min(n_pairs, n_pairs // tile_rows + n_experts)

@@ -24,6 +24,8 @@ from .base import FeedForward, StepContext, register_feed_forward
 
 
 class MoEFeedForward(FeedForward):
+    ROUTER_TC_MIN_TOKENS = 256     # steps with at least this many tokens compute router logits on tensor cores
+
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
                  norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True):
         if n_experts < 1 or not 1 <= top_k <= n_experts:
@@ -34,7 +36,7 @@ class MoEFeedForward(FeedForward):
         self.n_experts, self.top_k, self.intermediate = int(n_experts), int(top_k), int(intermediate)
         self.norm_topk, self.shared_intermediate = bool(norm_topk), int(shared_intermediate)
         self.shared_gate = bool(shared_gate) and shared_intermediate > 0
-        self.w_router = self.w_shared_gate = None
+        self.w_router = self.w_shared_gate = self.w_router_packed = None
         self.w13 = self.w2 = None            # [E, 2I, H] (gate rows, up rows), [E, H, I]
         self.ws13 = self.ws2 = None          # shared expert [1, 2S, H], [1, H, S]
 
@@ -73,6 +75,13 @@ class MoEFeedForward(FeedForward):
             self.ws2 = d.unsqueeze(0).contiguous()
             if self.shared_gate:
                 self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
+        if store.run_dtype == torch.bfloat16 and H % 8 == 0 and self.w_router.dtype == torch.bfloat16:
+            rows = [self.w_router]
+            if self.w_shared_gate is not None:
+                rows.append(self.w_shared_gate.to(torch.bfloat16).reshape(1, H))
+            else:
+                rows.append(torch.zeros((1, H), dtype=torch.bfloat16, device=store.device))
+            self.w_router_packed = KT.pack_weights(torch.cat(rows, dim=0).contiguous(), False)
         # bfloat16 runs whose sizes give 16-byte rows keep the expert weights only in the packed layout
         # of the tensor-core kernel
         if store.run_dtype == torch.bfloat16 and H % 8 == 0 and I % 8 == 0 and KT.packable(self.w13) and KT.packable(self.w2):
@@ -109,15 +118,9 @@ class MoEFeedForward(FeedForward):
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
         act = ctx.act_dtype
-        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
-        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
-        scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
-        KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
-        if ctx.debug is not None:
-            ctx.debug.setdefault("router_ids", []).append(ids.clone())
-            ctx.debug.setdefault("router_weights", []).append(wts.clone())
-        # the shared expert does not depend on the routing: it runs on a second stream next to the
-        # routed experts (its few CTAs would leave most of the GPU idle on their own)
+        # the shared expert does not depend on the routing: it starts first, on a second stream, and runs
+        # next to the router, the expert-sorted layout and the routed experts (its few CTAs would leave
+        # most of the GPU idle on their own, and the router's small kernels hide behind its weight stream)
         y_shared = None
         side = None
         if self.ws13 is not None:
@@ -134,6 +137,20 @@ class MoEFeedForward(FeedForward):
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+        scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
+        if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
+            # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products are
+            # exact in fp32 and the sum is fp32), then the selection kernel
+            logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
+            KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1))
+            KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
+        else:
+            KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
+        if ctx.debug is not None:
+            ctx.debug.setdefault("router_ids", []).append(ids.clone())
+            ctx.debug.setdefault("router_weights", []).append(wts.clone())
         tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         KM.moe_align(ids, layout)
