@@ -11,11 +11,13 @@
 // One CTA = 128 consecutive query tokens of one sequence x one query head; it walks the keys in
 // tiles of 64 (= one cache page):
 //   warp 0        TMA: Q once, then K and V pages through two-stage rings
-//   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 64, K hd)  and
-//                 O_tile = P V  (M 128, N hd, K 64; V is the MN-major operand, read as stored)
-//   warps 2..5    one thread per query row: read S from tensor memory, mask, online softmax, write
-//                 P (bf16, 128-byte swizzled) to shared memory, then add O_tile into the row's fp32
-//                 accumulator registers
+//   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 64, K hd) one tile ahead into one
+//                 of two S buffers, and  O_tile = P V  (M 128, N hd, K 64; V is the MN-major
+//                 operand, read as stored)
+//   warps 2..9    two threads per query row (each warp reads its quarter of the tensor-memory lanes;
+//                 the two threads of a row split the tile's 64 keys and the head's elements): read S,
+//                 mask, online softmax, write P (bf16, 128-byte swizzled) to shared memory, then add
+//                 their half of O_tile into fp32 accumulator registers
 // The heaviest query tiles (the last ones of a sequence, which see the most keys) are scheduled
 // first.  Every wait on an mbarrier is bounded; a wait that runs out sets *status and the CTA
 // leaves cleanly.
@@ -28,7 +30,7 @@ namespace {
 
 constexpr int BM = 128;      // query rows per CTA
 constexpr int BN = 64;       // keys per tile = tokens per cache page
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // TMA warp, MMA warp, eight softmax warps
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr uint64_t WAIT_NS = 2000000000ull;
 
@@ -99,6 +101,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// 2^x, one MUFU instruction; 2^-inf = 0
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -119,7 +127,7 @@ struct Cfg {
     static constexpr int STAGES = 2;
     static constexpr int TILE_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 256;
-    static constexpr int TMEM_COLS = (BN + HD) <= 128 ? 128 : 256;
+    static constexpr int TMEM_COLS = 256;                  // S twice (2 x 64 columns), O_tile (HD columns)
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
 };
 
@@ -160,16 +168,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
     auto v_full = [&](int s) { return bars + 8u * (5 + s); };
     auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
-    const uint32_t s_ready = bars + 8u * 9, p_ready = bars + 8u * 10, o_ready = bars + 8u * 11, o_free = bars + 8u * 12;
+    auto s_ready = [&](int b) { return bars + 8u * (9 + b); };
+    const uint32_t p_ready = bars + 8u * 11, o_ready = bars + 8u * 12, o_free = bars + 8u * 13;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         mbar_init(q_full, 1);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
-        mbar_init(s_ready, 1);
-        mbar_init(p_ready, 4);          // one arrival per softmax warp
+        mbar_init(s_ready(0), 1);
+        mbar_init(s_ready(1), 1);
+        mbar_init(p_ready, 8);          // one arrival per softmax warp
         mbar_init(o_ready, 1);
-        mbar_init(o_free, 4);
+        mbar_init(o_free, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -180,8 +190,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = s_tmem_base;            // S: BN columns
-    const uint32_t tmem_o = s_tmem_base + BN;       // O_tile: HD columns
+    auto tmem_s = [&](int b) { return s_tmem_base + (uint32_t)(b * BN); };    // S, twice: BN columns each
+    const uint32_t tmem_o = s_tmem_base + 2 * BN;                              // O_tile: HD columns
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -220,19 +230,27 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (lane == 0) {
             const uint32_t id_s = idesc(BN, 0), id_o = idesc(HD, 1);
             bool ok = mbar_wait(q_full, 0u, &s_abort);
+            // S = Q K^T of tile i into S buffer i & 1; issued one tile ahead of the P V product
+            auto issue_qk = [&](int i) -> bool {
+                const int s = i % C::STAGES;
+                if (!mbar_wait(k_full(s), (uint32_t)(i / C::STAGES) & 1u, &s_abort)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32, koff = (k / 4) * (BN * 128) + (k % 4) * 32;
+                    umma(tmem_s(i & 1), desc_k_major(q_smem + off), desc_k_major(k_smem(s) + koff), id_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(s_ready(i & 1));
+                umma_commit(k_empty(s));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u, it = (uint32_t)i & 1u;
-                ok = mbar_wait(k_full(s), ph, &s_abort);
+                // the other S buffer is free: its tile's P was complete before P V of tile i - 1 was issued
+                if (i + 1 < n_tiles) ok = issue_qk(i + 1);
                 if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {         // S = Q K^T
-                    const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32, koff = (k / 4) * (BN * 128) + (k % 4) * 32;
-                    umma(tmem_s, desc_k_major(q_smem + off), desc_k_major(k_smem(s) + koff), id_s, k > 0 ? 1u : 0u);
-                }
-                umma_commit(s_ready);
-                umma_commit(k_empty(s));
                 ok = mbar_wait(p_ready, it, &s_abort) && mbar_wait(v_full(s), ph, &s_abort);
                 if (ok && i > 0) ok = mbar_wait(o_free, (uint32_t)(i - 1) & 1u, &s_abort);
                 if (!ok) break;
@@ -246,53 +264,64 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        // ------------------------------ softmax and accumulation: one thread per query row ------------------------------
-        const int quarter = warp & 3;
+        // ------------------------------ softmax and accumulation: two threads per query row ------------------------------
+        constexpr int HK = BN / 2, HDH = HD / 2;      // keys and head elements of one thread
+        const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int qpos = p_first + r;
         const int start = window > 0 ? max(0, qpos + 1 - window) : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float o[HD];
+        float o[HDH];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        for (int d = 0; d < HDH; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;                 // l: this thread's keys only; the two halves are added at the end
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const uint32_t it = (uint32_t)i & 1u;
             const int k0 = (kb_first + i) * BN;
-            ok = mbar_wait(s_ready, it, &s_abort);
+            ok = __all_sync(0xffffffffu, mbar_wait(s_ready(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t sv[2][32];
-            tmem_ld32(tmem_s + lane_addr, sv[0]);
-            tmem_ld32(tmem_s + lane_addr + 32, sv[1]);
+            uint32_t sv[32], other[32];
+            tmem_ld32(tmem_s(i & 1) + lane_addr + part * HK, sv);
+            tmem_ld32(tmem_s(i & 1) + lane_addr + (1 - part) * HK, other);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // m is the running maximum of the raw scores; exponents are taken base 2 of (s - m) * scale * log2(e)
             float mx = m;
+            const bool visible = (k0 + BN - 1 <= p_first) && (window == 0 || k0 >= p_first + BM - window);
+            if (visible) {                             // every key of the tile is seen by every row: no masking
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                const int kp = k0 + c;
-                float s = __uint_as_float(sv[c / 32][c % 32]) * scale_log2e;
-                if (kp > qpos || kp < start) s = -INFINITY;
-                sv[c / 32][c % 32] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int c = 0; c < HK; ++c)
+                    mx = fmaxf(mx, fmaxf(__uint_as_float(sv[c]), __uint_as_float(other[c])));
+            } else {
+#pragma unroll
+                for (int c = 0; c < HK; ++c) {         // the row's maximum needs all 64 scores
+                    const int kp = k0 + part * HK + c, kq = k0 + (1 - part) * HK + c;
+                    float a = __uint_as_float(sv[c]), b = __uint_as_float(other[c]);
+                    if (kp > qpos || kp < start) a = -INFINITY;
+                    if (kq > qpos || kq < start) b = -INFINITY;
+                    sv[c] = __float_as_uint(a);
+                    mx = fmaxf(mx, fmaxf(a, b));
+                }
             }
-            const float corr = mx == -INFINITY ? 1.f : exp2f(m - mx);     // nothing visible yet: keep the zeros
+            const float mref = mx == -INFINITY ? 0.f : mx * scale_log2e;   // nothing visible yet: exponents of -inf
+            const float corr = mx == -INFINITY ? 1.f : ex2(m * scale_log2e - mref);
             float lsum = 0.f;
             // P in bf16, 16-byte chunks of 8 keys, written with the 128-byte swizzle of a K-major operand
             const uint32_t prow = p_smem + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
 #pragma unroll
-            for (int ch = 0; ch < BN / 8; ++ch) {
+            for (int ch = 0; ch < HK / 8; ++ch) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int c = ch * 8 + 2 * e;
-                    const float a = mx == -INFINITY ? 0.f : exp2f(__uint_as_float(sv[c / 32][c % 32]) - mx);
-                    const float b = mx == -INFINITY ? 0.f : exp2f(__uint_as_float(sv[(c + 1) / 32][(c + 1) % 32]) - mx);
+                    const float a = ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -mref));
+                    const float b = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, -mref));
                     lsum += a + b;
                     const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
                     packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
                 }
-                const uint32_t dst = prow + (uint32_t)((ch ^ (r % 8)) * 16);
+                const uint32_t dst = prow + (uint32_t)(((part * (HK / 8) + ch) ^ (r % 8)) * 16);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
                              "r"(packed[2]), "r"(packed[3]) : "memory");
             }
@@ -302,16 +331,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
-            // meanwhile rescale the accumulator, then add this tile's P V
+            // meanwhile rescale the accumulator (skipped when no row of the warp saw a new maximum), then
+            // add this tile's P V
+            if (!__all_sync(0xffffffffu, corr == 1.0f)) {
 #pragma unroll
-            for (int d = 0; d < HD; ++d) o[d] *= corr;
-            ok = mbar_wait(o_ready, it, &s_abort);
+                for (int d = 0; d < HDH; ++d) o[d] *= corr;
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(o_ready, it, &s_abort));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
+            for (int c0 = 0; c0 < HDH; c0 += 32) {
                 uint32_t ov[32];
-                tmem_ld32(tmem_o + lane_addr + c0, ov);
+                tmem_ld32(tmem_o + lane_addr + part * HDH + c0, ov);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o[c0 + j] += __uint_as_float(ov[j]);
@@ -320,11 +352,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(o_free);
         }
+        // the row's sum is the sum of its two threads' sums (same maximum m in both)
+        float* s_l = reinterpret_cast<float*>(smem_raw + (p_smem - smem_u32(smem_raw)));   // P's buffer is free now
+        asm volatile("bar.sync 1, 256;" ::: "memory");           // all softmax warps are past their last tile
+        s_l[part * BM + r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float lrow = s_l[r] + s_l[BM + r];
         if (ok && r < rows) {
-            const float inv = 1.0f / l;
-            __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h) * HD;
+            const float inv = 1.0f / lrow;
+            __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h) * HD + part * HDH;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
+            for (int d = 0; d < HDH; d += 8) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {

@@ -140,15 +140,28 @@ struct Tile {
     static_assert(TMEM_COLS * CTAS_PER_SM <= 512, "tensor memory holds 512 columns per SM");
 };
 
-// One tile of work: (weight-row tile, token tile).  Tiles are numbered with the token tile running
-// fastest, so CTAs that run side by side share a weight slab through the L2 when an expert has
-// several token tiles (prompts); a CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// One tile of work: (weight-row tile, token tile).  Tiles are numbered in bands of TILE_BAND token
+// tiles: inside a band the token tile runs fastest, then the weight-row tile, so the CTAs that run
+// side by side share both a few weight slabs and a few activation tiles through the L2 (prompts:
+// an expert has several token tiles, and every activation tile meets every weight-row tile).  A
+// CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 struct TileInfo { int expert, row0, count, m0; };
+constexpr int TILE_BAND = 8;
 
-__device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int bn, const int* tile_expert, const int* tile_row0,
-                                              const int* tile_count, int R) {
+__device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int n_mx, int bn, const int* tile_expert,
+                                              const int* tile_row0, const int* tile_count, int R) {
     TileInfo t;
-    const int mx = id / n_ty, ty = id % n_ty;
+    const int full = (n_ty / TILE_BAND) * TILE_BAND;          // token tiles in whole bands
+    int mx, ty;
+    if (id < full * n_mx) {
+        const int band = id / (TILE_BAND * n_mx), rem = id - band * (TILE_BAND * n_mx);
+        mx = rem / TILE_BAND;
+        ty = band * TILE_BAND + rem % TILE_BAND;
+    } else {
+        const int rem = id - full * n_mx, w = n_ty - full;    // the last, narrower band
+        mx = rem / w;
+        ty = full + rem % w;
+    }
     t.m0 = mx * BM;
     if (tile_expert) {
         t.expert = tile_expert[ty];
@@ -212,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int issued = 0;          // k-blocks issued so far (stage = issued % STAGES)
             bool ok = true;
             for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
-                const TileInfo t = tile_info(id, n_ty, BN, tile_expert, tile_row0, tile_count, R);
+                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int s = issued % T::STAGES;
                     const uint32_t ph = (uint32_t)(issued / T::STAGES) & 1u;
@@ -273,10 +286,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
-            const TileInfo t = tile_info(id, n_ty, BN, tile_expert, tile_row0, tile_count, R);
+            const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
             const int b = it & 1;
             const int n = t.m0 + r;                        // output column
-            ok = mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort);
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + (uint32_t)(b * T::ACC_COLS) + ((uint32_t)(quarter * 32) << 16);
