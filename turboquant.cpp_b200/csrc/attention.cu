@@ -198,20 +198,28 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
 // ---------------------------------------------------------------------------------------
 #define SPLIT_WARPS 4
 
+// eight consecutive elements: fetched raw (so that the next group's loads can be in flight while the
+// current group is computed), widened to fp32 when used
 template <typename T> struct Vec8 { };
 template <> struct Vec8<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    struct Raw { uint4 v; };
+    static __device__ __forceinline__ Raw fetch(const __nv_bfloat16* p) { Raw r; r.v = *reinterpret_cast<const uint4*>(p); return r; }
+    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
     }
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) { widen(fetch(p), f); }
 };
 template <> struct Vec8<float> {
-    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
-        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw fetch(const float* p) {
+        Raw r; r.a = *reinterpret_cast<const float4*>(p); r.b = *reinterpret_cast<const float4*>(p + 4); return r;
     }
+    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
+        f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
+    }
+    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) { widen(fetch(p), f); }
 };
 
 template <typename TA, int LPK, int GC>
@@ -249,16 +257,26 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
 #pragma unroll
         for (int i = 0; i < 8; ++i) { qv[h][i] = f[i] * scale; acc[h][i] = 0.f; }
     }
-    for (int grp = gb + warp; grp < ge; grp += SPLIT_WARPS) {
+    using Raw = typename Vec8<TA>::Raw;
+    // the keys and values of a group of GS positions, as this lane reads them
+    auto fetch_group = [&](int grp, Raw (&kr)[LOADS], Raw (&vr)[LOADS]) {
         const int p0 = grp * GS;
         const int page = table[p0 / page_size];
         const TA* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
         const TA* vbase = kbase + (size_t)nkv * page_size * HD;
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) kr[j] = Vec8<TA>::fetch(kbase + (size_t)(j * KPI + part) * HD + sub * 8);
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) vr[j] = Vec8<TA>::fetch(vbase + (size_t)(j * KPI + part) * HD + sub * 8);
+    };
+    Raw kr[LOADS], vr[LOADS];
+    if (gb + warp < ge) fetch_group(gb + warp, kr, vr);
+    for (int grp = gb + warp; grp < ge; grp += SPLIT_WARPS) {
+        const int p0 = grp * GS;
         float kf[LOADS][8], vf[LOADS][8];
 #pragma unroll
-        for (int j = 0; j < LOADS; ++j) Vec8<TA>::load(kbase + (size_t)(j * KPI + part) * HD + sub * 8, kf[j]);
-#pragma unroll
-        for (int j = 0; j < LOADS; ++j) Vec8<TA>::load(vbase + (size_t)(j * KPI + part) * HD + sub * 8, vf[j]);
+        for (int j = 0; j < LOADS; ++j) { Vec8<TA>::widen(kr[j], kf[j]); Vec8<TA>::widen(vr[j], vf[j]); }
+        if (grp + SPLIT_WARPS < ge) fetch_group(grp + SPLIT_WARPS, kr, vr);      // next group's loads fly during this one's math
         float s[LOADS][GC];
 #pragma unroll
         for (int j = 0; j < LOADS; ++j)

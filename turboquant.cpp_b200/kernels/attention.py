@@ -66,7 +66,9 @@ def split_usable(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -
 def splits_for(n_tokens: int, n_kv_heads: int) -> int:
     """Ranges the keys of one (token, KV head) are cut into: enough CTAs to fill the GPU a few times
     over when a step has few tokens, one range when it has many."""
-    return max(1, min(64, -(-592 // max(1, n_tokens * n_kv_heads))))
+    rows = max(1, n_tokens * n_kv_heads)
+    target = 592 if rows < 512 else 1184        # measured on B200: more, smaller CTAs only pay once rows alone fill the GPU
+    return max(1, min(64, -(-target // rows)))
 
 
 def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
