@@ -31,6 +31,8 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
                                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
                                       int table_stride, int page_size, TA* __restrict__ q_out,
                                       TA* __restrict__ cache, int heads, int nh, int nkv, int hd) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int width = (nh + 2 * nkv) * hd;
@@ -84,7 +86,7 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     int chunks = T_ >= 512 ? 1 : (pairs + threads - 1) / threads;
     if (chunks > 64) chunks = 64;
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
-        (qkv_rope_cache_kernel<TA, TB><<<dim3(T_, chunks), threads, 0, stream>>>(
+        (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB>, 
             (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
             table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd))));
     TQ_CHECK_LAUNCH("qkv_rope_cache");
@@ -104,6 +106,8 @@ __global__ void attention_kernel(const TA* __restrict__ q, const TA* __restrict_
                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                  const int* __restrict__ page_table, int table_stride, int page_size,
                                  int window, float scale, TA* __restrict__ out, int nh, int nkv, int hd) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
     __shared__ float s_acc[ATT_WARPS][TQ_MAX_HEAD_DIM];
     const int t = blockIdx.x, h = blockIdx.y;
@@ -181,7 +185,7 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
     TQ_REQUIRE(window >= 0, "attention: negative window %d", window);
     dim3 grid(T_, nh);
     TQ_DISPATCH(act_dtype, TA,
-        (attention_kernel<TA><<<grid, ATT_WARPS * 32, 0, stream>>>(
+        (tq_launch(grid, ATT_WARPS * 32, 0, stream)(attention_kernel<TA>, 
             (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size,
             window, scale, (TA*)out, nh, nkv, hd)));
     TQ_CHECK_LAUNCH("attention");
@@ -228,6 +232,8 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
                        const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
                        int page_size, int window, float scale, float* __restrict__ partial, int n_splits,
                        int nh, int nkv) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     constexpr int HD = LPK * 8;
     constexpr int KPI = 32 / LPK;            // keys per load instruction of a warp
     constexpr int GS = KPI > 8 ? KPI : 8;    // keys per iteration of a warp (a group of absolute positions)
@@ -346,6 +352,8 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
 
 template <typename TA>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, int n_splits, int hd, TA* __restrict__ out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const size_t th = blockIdx.x;                        // token * nh + head
     const float* p = partial + th * n_splits * (hd + 2);
     float M = -INFINITY;
@@ -381,7 +389,7 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
     dim3 grid(T_, nkv, n_splits);
 #define SPLIT_LAUNCH(TA, LPK, GC)                                                                               \
-    attention_split_kernel<TA, LPK, GC><<<grid, SPLIT_WARPS * 32, 0, stream>>>(                                 \
+    tq_launch(grid, SPLIT_WARPS * 32, 0, stream)(attention_split_kernel<TA, LPK, GC>,                                  \
         (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window,   \
         scale, partial, n_splits, nh, nkv)
 #define SPLIT_GC(TA, LPK)                                                                                       \
@@ -395,7 +403,7 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     else TQ_FAIL(-2, "attention_split: unknown element type %d", act_dtype);
     TQ_CHECK_LAUNCH("attention_split");
     TQ_DISPATCH(act_dtype, TA,
-        (attention_merge_kernel<TA><<<T_ * nh, hd >= 128 ? 128 : 64, 0, stream>>>(partial, n_splits, hd, (TA*)out)));
+        (tq_launch(T_ * nh, hd >= 128 ? 128 : 64, 0, stream)(attention_merge_kernel<TA>, partial, n_splits, hd, (TA*)out)));
     TQ_CHECK_LAUNCH("attention_merge");
     return 0;
 }

@@ -137,6 +137,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ page_table, int table_stride, int window, float scale_log2e,
                          __nv_bfloat16* __restrict__ out, int nh, int nkv, int* __restrict__ status) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
     using C = Cfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_abort;
@@ -190,6 +191,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // only now: a dependent kernel that took tensor memory first could starve a CTA of this grid that
+    // had not allocated yet, and then wait forever for this grid to finish
+    tq_grid_launch_dependents();
     auto tmem_s = [&](int b) { return s_tmem_base + (uint32_t)(b * BN); };    // S, twice: BN columns each
     const uint32_t tmem_o = s_tmem_base + 2 * BN;                              // O_tile: HD columns
 
@@ -426,7 +430,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const int* cu, const i
         configured = true;
     }
     dim3 grid((max_q_len + BM - 1) / BM, n_seqs, nh);
-    kern<<<grid, THREADS, C::SMEM_BYTES, stream>>>(mq, mkv, cu, starts, table, table_stride, window,
+    tq_launch(grid, THREADS, C::SMEM_BYTES, stream)(kern, mq, mkv, cu, starts, table, table_stride, window,
                                                    scale * 1.4426950408889634f, (__nv_bfloat16*)out, nh, nkv, status);
     TQ_CHECK_LAUNCH("attention_prefill");
     return 0;

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define TQ_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -88,6 +89,39 @@ __device__ __forceinline__ float tq_block_max(float v, float* scratch) {
     __syncthreads();
     return scratch[32];
 }
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels are launched so that their CTAs may become resident
+// while the previous kernel of the stream is still running; every kernel calls tq_grid_wait()
+// before it touches global memory (it returns once the previous kernel has completed and its
+// writes are visible) and tq_grid_launch_dependents() once it holds the resources it needs, so
+// the next kernel's CTAs can move in as SMs free up.  This removes most of the launch gap between
+// the many small kernels of a decode step, inside CUDA graphs too.  TQ_NO_PDL=1 switches it off.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tq_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void tq_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+struct TqLaunch {
+    dim3 grid, block;
+    size_t smem;
+    cudaStream_t stream;
+    template <typename... KArgs, typename... Args>
+    void operator()(void (*kernel)(KArgs...), Args&&... args) const {
+        static const bool pdl = [] { const char* e = getenv("TQ_NO_PDL"); return !(e && e[0] && e[0] != '0'); }();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in TQ_CHECK_LAUNCH
+    }
+};
+inline TqLaunch tq_launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream) { return TqLaunch{grid, block, smem, stream}; }
 
 // Dispatch on an element type code: TQ_F32 -> float, TQ_BF16 -> __nv_bfloat16.
 #define TQ_DISPATCH(code, T, ...)                                            \

@@ -15,6 +15,8 @@ TQ_DEFINE_LAST_ERROR
 template <typename TW>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                   float* __restrict__ x, int H) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
     const TW* row = table + (size_t)tokens[t] * H;
     float* out = x + (size_t)t * H;
@@ -27,7 +29,7 @@ TQ_EXPORT int tq_embed_rows(const int* tokens, const void* table, int table_dtyp
     TQ_REQUIRE(T > 0 && H > 0, "embed_rows: bad sizes T=%d H=%d", T, H);
     const int threads = H >= 1024 ? 256 : 128;
     TQ_DISPATCH(table_dtype, TW,
-        embed_rows_kernel<TW><<<T, threads, 0, stream>>>(tokens, (const TW*)table, x, H));
+        tq_launch(T, threads, 0, stream)(embed_rows_kernel<TW>, tokens, (const TW*)table, x, H));
     TQ_CHECK_LAUNCH("embed_rows");
     return 0;
 }
@@ -41,6 +43,8 @@ TQ_EXPORT int tq_embed_rows(const int* tokens, const void* table, int table_dtyp
 template <typename TY, typename TW, typename TO>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
                                const TW* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -88,6 +92,8 @@ template <> __device__ __forceinline__ void tq_store4<__nv_bfloat16>(__nv_bfloat
 template <typename TY, typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
                                    const TW* __restrict__ w, TO* __restrict__ out, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -132,7 +138,7 @@ TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, 
         if (vthreads > 1024) vthreads = 1024;
         if (H / 4 <= vthreads * RMS_VEC_GROUPS) {
             TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
-                (rmsnorm_vec_kernel<TY, TW, TO><<<R, vthreads, 0, stream>>>(x, (const TY*)y, rows, (const TW*)w,
+                (tq_launch(R, vthreads, 0, stream)(rmsnorm_vec_kernel<TY, TW, TO>, x, (const TY*)y, rows, (const TW*)w,
                                                                             (TO*)out, H, eps)))));
             TQ_CHECK_LAUNCH("rmsnorm");
             return 0;
@@ -140,7 +146,7 @@ TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, 
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
-        (rmsnorm_kernel<TY, TW, TO><<<R, threads, 0, stream>>>(x, (const TY*)y, rows, (const TW*)w,
+        (tq_launch(R, threads, 0, stream)(rmsnorm_kernel<TY, TW, TO>, x, (const TY*)y, rows, (const TW*)w,
                                                               (TO*)out, H, eps)))));
     TQ_CHECK_LAUNCH("rmsnorm");
     return 0;
@@ -151,6 +157,8 @@ TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, 
 // ---------------------------------------------------------------------------------------
 template <typename TY>
 __global__ void residual_add_kernel(float* __restrict__ x, const TY* __restrict__ y, size_t n) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) x[i] += tq_to_float(y[i]);
@@ -162,7 +170,7 @@ TQ_EXPORT int tq_residual_add(float* x, const void* y, int y_dtype, long long n,
     long long blocks = (n + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     TQ_DISPATCH(y_dtype, TY,
-        residual_add_kernel<TY><<<(int)blocks, threads, 0, stream>>>(x, (const TY*)y, (size_t)n));
+        tq_launch((int)blocks, threads, 0, stream)(residual_add_kernel<TY>, x, (const TY*)y, (size_t)n));
     TQ_CHECK_LAUNCH("residual_add");
     return 0;
 }
@@ -172,6 +180,8 @@ TQ_EXPORT int tq_residual_add(float* x, const void* y, int y_dtype, long long n,
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, int I) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
     const TI* g = gu + (size_t)t * 2 * I;
     TO* o = h + (size_t)t * I;
@@ -185,7 +195,7 @@ TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, 
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);
     TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
-        (silu_mul_kernel<TI, TO><<<T_, 256, 0, stream>>>((const TI*)gu, (TO*)h, I))));
+        (tq_launch(T_, 256, 0, stream)(silu_mul_kernel<TI, TO>, (const TI*)gu, (TO*)h, I))));
     TQ_CHECK_LAUNCH("silu_mul");
     return 0;
 }
@@ -196,6 +206,8 @@ TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, 
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ idx, int divisor,
                                    T* __restrict__ out, int H, int vec) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int r = blockIdx.x;
     const T* src = in + (size_t)(idx[r] / divisor) * H;
     T* dst = out + (size_t)r * H;
@@ -216,7 +228,7 @@ TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* 
     const int esize = dtype == TQ_F32 ? 4 : 2;
     const int vec = ((size_t)H * esize) % 16 == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0;
     TQ_DISPATCH(dtype, T,
-        gather_rows_kernel<T><<<R, 256, 0, stream>>>((const T*)in, idx, divisor, (T*)out, H, vec));
+        tq_launch(R, 256, 0, stream)(gather_rows_kernel<T>, (const T*)in, idx, divisor, (T*)out, H, vec));
     TQ_CHECK_LAUNCH("gather_rows");
     return 0;
 }

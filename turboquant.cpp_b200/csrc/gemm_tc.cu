@@ -181,6 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                TO* __restrict__ out, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
                int* __restrict__ status) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
     using T = Tile<BN, SWIGLU>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_abort;
@@ -217,6 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // only now: a dependent kernel that took tensor memory first could starve a CTA of this grid that
+    // had not allocated yet, and then wait forever for this grid to finish
+    tq_grid_launch_dependents();
     const uint32_t tmem_base = s_tmem_base;
 
     if (warp == 0) {
@@ -395,7 +399,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* t
     long long tiles = (long long)((N + BM - 1) / BM) * grid_y;
     const long long resident = (long long)n_sm * T::CTAS_PER_SM;
     const int grid = (int)(tiles < resident ? tiles : resident);
-    kern<<<grid, THREADS, T::SMEM_BYTES, stream>>>(mw, mx, (TO*)out, te, tr, tc, nt, R, N, K, status);
+    tq_launch(grid, THREADS, T::SMEM_BYTES, stream)(kern, mw, mx, (TO*)out, te, tr, tc, nt, R, N, K, status);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }

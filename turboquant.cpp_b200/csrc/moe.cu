@@ -48,6 +48,8 @@ template <> struct RowVec<float> {
 template <typename TA, typename TW, bool STAGED>
 __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
                                      float* __restrict__ logits, int H, int E, int rows_per_cta, int vec_ok) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     extern __shared__ float s_x[];
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -77,6 +79,8 @@ __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restr
 // Kernel 2: one warp per token: softmax over the E logits, k largest, weights, shared gate.
 __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
                                      float* __restrict__ shared_scale, int T_, int E, int k, int renorm) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= T_) return;
@@ -143,12 +147,12 @@ TQ_EXPORT int tq_router_topk(const void* x, int act_dtype, const void* wr, const
     dim3 grid(T_, chunks);
 #define ROUTER_LAUNCH(ST)                                                                              \
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
-        (router_logits_kernel<TA, TW, ST><<<grid, threads, smem, stream>>>(                            \
+        (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                             \
             (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
     if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
 #undef ROUTER_LAUNCH
     TQ_CHECK_LAUNCH("router_logits");
-    router_select_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(logits, ids, wts, shared_scale, T_, E, k, renorm);
+    tq_launch((T_ + 3) / 4, 128, 0, stream)(router_select_kernel, logits, ids, wts, shared_scale, T_, E, k, renorm);
     TQ_CHECK_LAUNCH("router_select");
     return 0;
 }
@@ -159,7 +163,7 @@ TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* share
     if (T_ == 0) return 0;
     TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
     TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
-    router_select_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(logits, ids, wts, shared_scale, T_, E, k, renorm);
+    tq_launch((T_ + 3) / 4, 128, 0, stream)(router_select_kernel, logits, ids, wts, shared_scale, T_, E, k, renorm);
     TQ_CHECK_LAUNCH("router_select");
     return 0;
 }
@@ -175,6 +179,8 @@ TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* share
 #define ALIGN_THREADS 256
 
 __global__ void moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ int s_c[ALIGN_THREADS / 32];
     const int e = blockIdx.x;
     int c = 0;
@@ -196,6 +202,8 @@ __global__ void moe_fill_kernel(const int* __restrict__ ids, int P, int E, int t
                                 int* __restrict__ row_of_pair, int* __restrict__ expert_offset,
                                 int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                 int* __restrict__ tile_count, int* __restrict__ n_tiles) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ int s_warp[ALIGN_THREADS / 32];
     __shared__ int s_base, s_row0, s_tile0;
     const int e = blockIdx.x;
@@ -249,9 +257,9 @@ TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int* cou
                            int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0,
                            int* tile_count, int* n_tiles, cudaStream_t stream) {
     TQ_REQUIRE(P >= 0 && E >= 1 && tile_rows >= 1, "moe_align: bad sizes P=%d E=%d tile_rows=%d", P, E, tile_rows);
-    moe_count_kernel<<<E, ALIGN_THREADS, 0, stream>>>(ids, P, counts);
+    tq_launch(E, ALIGN_THREADS, 0, stream)(moe_count_kernel, ids, P, counts);
     TQ_CHECK_LAUNCH("moe_count");
-    moe_fill_kernel<<<E, ALIGN_THREADS, 0, stream>>>(ids, P, E, tile_rows, counts, sorted_pair, row_of_pair,
+    tq_launch(E, ALIGN_THREADS, 0, stream)(moe_fill_kernel, ids, P, E, tile_rows, counts, sorted_pair, row_of_pair,
                                                      expert_offset, tile_expert, tile_row0, tile_count, n_tiles);
     TQ_CHECK_LAUNCH("moe_fill");
     return 0;
@@ -274,6 +282,8 @@ grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ tile_count, const int* __restrict__ n_tiles,
                     int R, int N, int K) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float As[GG_BK][GG_BM + 4];
     __shared__ float Ws[SWIGLU ? 2 : 1][GG_BK][GG_BN + 4];
     int expert = 0, row0, rows;
@@ -366,7 +376,7 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
     dim3 grid((N + GG_BN - 1) / GG_BN, by);
 #define GG_LAUNCH(SW)                                                                                   \
     TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                          \
-        (grouped_gemm_kernel<TA, TW, TO, SW><<<grid, 256, 0, stream>>>(                                 \
+        (tq_launch(grid, 256, 0, stream)(grouped_gemm_kernel<TA, TW, TO, SW>,                                  \
             (const TA*)A, (const TW*)W, (TO*)C, tile_expert, tile_row0, tile_count, n_tiles, R, N, K)))))
     if (swiglu) { GG_LAUNCH(true); } else { GG_LAUNCH(false); }
 #undef GG_LAUNCH
@@ -380,6 +390,8 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
 __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ wts, const float* __restrict__ Ys,
                                    const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
     if ((H & 3) == 0) {          // four columns per thread, 16-byte accesses (rows of fp32 are 16-byte aligned)
         const float sc = Ys ? (shared_scale ? shared_scale[t] : 1.0f) : 0.f;
@@ -415,7 +427,7 @@ TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float
     const int threads = T_ >= 512 ? 256 : 64;
     int cols = T_ >= 512 ? 1 : (H + threads * 4 - 1) / (threads * 4);
     if (cols > 64) cols = 64;
-    moe_combine_kernel<<<dim3(T_, cols), threads, 0, stream>>>(Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
+    tq_launch(dim3(T_, cols), threads, 0, stream)(moe_combine_kernel, Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
     TQ_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -16,6 +16,8 @@ TQ_DEFINE_LAST_ERROR
 
 // ---------------------------------------------------------------------------------------
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const float* row = logits + (size_t)blockIdx.x * V;
@@ -50,7 +52,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int*
 TQ_EXPORT int tq_argmax_rows(const float* logits, int R, int V, int* out, cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && V > 0, "argmax_rows: bad sizes R=%d V=%d", R, V);
-    argmax_rows_kernel<<<R, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, V, out);
+    tq_launch(R, V >= 4096 ? 1024 : 256, 0, stream)(argmax_rows_kernel, logits, V, out);
     TQ_CHECK_LAUNCH("argmax_rows");
     return 0;
 }
@@ -88,6 +90,8 @@ __device__ PrefixPick find_crossing(const float* __restrict__ p, int V, float ta
 __global__ void sample_rows_kernel(const float* __restrict__ logits, int V, float temperature, float top_p,
                                    const float* __restrict__ uniforms, float* __restrict__ work,
                                    int* __restrict__ out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
     __shared__ int s_warp[SAMPLE_THREADS / 32];
     __shared__ int s_base, s_found;
@@ -149,7 +153,7 @@ TQ_EXPORT int tq_sample_rows(const float* logits, int R, int V, float temperatur
     TQ_REQUIRE(R > 0 && V > 0, "sample_rows: bad sizes R=%d V=%d", R, V);
     TQ_REQUIRE(temperature > 0.f && top_p > 0.f, "sample_rows: temperature %g and top_p %g must be positive "
                "(use argmax_rows otherwise)", (double)temperature, (double)top_p);
-    sample_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_p, uniforms, work, out);
+    tq_launch(R, SAMPLE_THREADS, 0, stream)(sample_rows_kernel, logits, V, temperature, top_p, uniforms, work, out);
     TQ_CHECK_LAUNCH("sample_rows");
     return 0;
 }
