@@ -319,3 +319,41 @@ def test_toy_architecture_registers_builds_loads_and_steps(tmp_path):
         assert all(sorted(logits[r]) == list(range(len(reqs[r]))) for r in reqs)
     eng.cache.book.check_invariants()
     tq.config.unregister_architecture("ToyStatefulLM")
+
+
+def test_block_embedding_and_head_alone():
+    """A whole pre-norm block (norm, attention, add, norm, experts, add), the embedding and the LM head."""
+    from turboquant_cpp_b200.cache import PagedCache
+    from turboquant_cpp_b200.models import Embedding, LMHead
+    from turboquant_cpp_b200.parts import (PreNormBlock, make_feed_forward, make_mixer, make_norm,
+                                           make_position_encoding)
+    H, nh, nkv, hd, E, k, I, S, V = 48, 3, 1, 16, 4, 2, 24, 40, 50
+    rot = make_position_encoding("rotary", head_dim=hd, theta=300.0, max_position=128, pairing="half")
+    p = "model.layers.0."
+    blk = PreNormBlock(
+        make_norm("rmsnorm", name=p + "input_layernorm.weight", size=H, eps=1e-5),
+        make_mixer("attention", prefix=p + "self_attn.", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                   qkv_bias=True, window=0, position=rot),
+        make_norm("rmsnorm", name=p + "post_attention_layernorm.weight", size=H, eps=1e-5),
+        make_feed_forward("moe", prefix=p + "mlp.", hidden=H, n_experts=E, top_k=k, intermediate=I, norm_topk=True,
+                          shared_intermediate=S))
+    emb, head = Embedding("model.embed_tokens.weight", V, H), LMHead("lm_head.weight", V, H)
+    from turboquant_cpp_b200.weights import RandomSource, WeightStore
+    specs = blk.weight_specs() + emb.weight_specs() + head.weight_specs()
+    store = WeightStore(RandomSource(specs, 9, std=0.1), specs, DEV, torch.float32)
+    w = plain_weights(store, specs)
+    for part in (blk, emb, head):
+        part.bind(store)
+    toks = np.random.default_rng(0).integers(0, V, size=20)
+    x = emb.forward(torch.tensor(toks, dtype=torch.int32, device=DEV))
+    close(x, P.embedding(w["model.embed_tokens.weight"], toks), 1e-7)
+    cache = PagedCache([blk.mixer.cache_need()], [None], [None], 256, torch.float32, DEV)
+    ctx, tables, seqs = context_for([20], [0], torch.float32, cache)
+    x0 = x.double().cpu().numpy()
+    xr, pending = blk.forward(x, None, ctx, cache.layer_caches(tables)[0])
+    m = types.SimpleNamespace(w=w, L=1, H=H, nh=nh, nkv=nkv, hd=hd, eps=1e-5, theta=300.0, E=E, k=k, norm_topk=True,
+                              cfg={"shared_expert_intermediate_size": S}, layer_is_sparse=lambda l: True,
+                              layer_window=lambda l: 0)
+    want = P.block(m, 0, x0, np.arange(20))
+    close(xr + pending, want, 1e-5)
+    close(head.forward(xr + pending), P.linear((xr + pending).double().cpu().numpy(), w["lm_head.weight"]), 1e-5)

@@ -82,6 +82,12 @@ class Engine:
     def make_entry(seq: Sequence_, tokens: Sequence[int], want: Sequence[int] = ()) -> "StepEntry":
         return StepEntry(seq, tokens, want)
 
+    def check_kernels(self) -> None:
+        """Raises if a tensor-core kernel gave up on one of its bounded waits since the last check
+        (it synchronises the device; call it where results are brought to the host anyway)."""
+        from ..kernels.gemm_tc import check_status
+        check_status(self.device)
+
     # ---- sequences ------------------------------------------------------------------------------
     def open(self) -> Sequence_:
         return self.cache.open()

@@ -91,6 +91,7 @@ class Model:
         stats = GenStats()
         results = _generate(self._engine, Sampler(p.temperature, p.top_p, p.seed), prompts, p, self.max_batch,
                             on_tokens=on_tokens, stats=stats, sync=torch.cuda.synchronize)
+        self._engine.check_kernels()
         self.last_stats = stats
         self.last_results = results
         return [r.tokens for r in results]
