@@ -451,3 +451,38 @@ def test_sample_rows_distribution():
     KS.sample_rows(dev(l), 1.0, 1.0, dev(u), work, out)
     counts = np.bincount(out.cpu().numpy(), minlength=V)
     assert counts.min() > 0.2 * R and counts.max() < 0.3 * R
+
+
+@pytest.mark.parametrize("T,E,k,H,renorm,shared", [(1, 8, 2, 64, False, True), (8, 60, 4, 2048, False, True),
+                                                    (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype):
+    """The two-launch decode path (logits, then one block for selection, layout and gathered rows)
+    gives exactly what the separate kernels give."""
+    from turboquant_cpp_b200.kernels import elementwise as KE, moe as KM
+    rng = np.random.default_rng(T + E)
+    x = dev(bf16_values(rng.normal(size=(T, H))), dtype)
+    wr = dev(bf16_values(rng.normal(size=(E, H)) * 0.3), dtype)
+    wsg = dev(bf16_values(rng.normal(size=(1, H)) * 0.3), dtype) if shared else None
+    assert KM.router_small_usable(T, k, E)
+
+    def buffers():
+        return (torch.empty((T, k), dtype=torch.int32, device=DEV), torch.empty((T, k), dtype=torch.float32, device=DEV),
+                torch.empty((T,), dtype=torch.float32, device=DEV) if shared else None, KM.ExpertLayout(T * k, E, 16, DEV),
+                torch.empty((T * k, H), dtype=dtype, device=DEV))
+    ids1, w1, s1, lay1, rows1 = buffers()
+    KM.router_topk(x, wr, wsg, k, renorm, ids1, w1, s1)
+    KM.moe_align(ids1, lay1)
+    KE.gather_rows(x, lay1.sorted_pair, k, rows1)
+    ids2, w2, s2, lay2, rows2 = buffers()
+    KM.router_small(x, wr, wsg, k, renorm, ids2, w2, s2, lay2, rows2)
+    assert torch.equal(ids1, ids2) and torch.equal(w1, w2) and torch.equal(rows1, rows2)
+    if shared:
+        assert torch.equal(s1, s2)
+    n = int(lay1.n_tiles.item())
+    assert n == int(lay2.n_tiles.item())
+    for a, b in ((lay1.counts, lay2.counts), (lay1.expert_offset, lay2.expert_offset),
+                 (lay1.sorted_pair[:T * k], lay2.sorted_pair[:T * k]), (lay1.row_of_pair[:T * k], lay2.row_of_pair[:T * k]),
+                 (lay1.tile_expert[:n], lay2.tile_expert[:n]), (lay1.tile_row0[:n], lay2.tile_row0[:n]),
+                 (lay1.tile_count[:n], lay2.tile_count[:n])):
+        assert torch.equal(a, b)

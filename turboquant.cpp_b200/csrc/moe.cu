@@ -266,6 +266,155 @@ TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int* cou
 }
 
 // ---------------------------------------------------------------------------------------
+// Steps with few tokens (decoding): everything between the router logits and the expert products in
+// ONE block — selection, counts, offsets, stable placement, tile list and the expert-sorted copies of
+// the token rows — instead of four launches that each do microseconds of work.
+// ---------------------------------------------------------------------------------------
+#define SMALL_MAX_PAIRS 512
+#define SMALL_MAX_EXPERTS 1024
+#define SMALL_THREADS 1024
+
+template <typename TA>
+__global__ void __launch_bounds__(SMALL_THREADS)
+router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
+                         float* __restrict__ shared_scale, int T_, int E, int k, int renorm, int tile_rows,
+                         int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                         int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                         int* __restrict__ tile_count, int* __restrict__ n_tiles, const TA* __restrict__ x,
+                         TA* __restrict__ x_rows, int H, int vec) {
+    tq_grid_wait();
+    tq_grid_launch_dependents();
+    __shared__ int s_ids[SMALL_MAX_PAIRS], s_row[SMALL_MAX_PAIRS];
+    __shared__ int s_count[SMALL_MAX_EXPERTS], s_off[SMALL_MAX_EXPERTS + 1], s_toff[SMALL_MAX_EXPERTS + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int P = T_ * k;
+    // selection: one warp per token (the same steps as router_select_kernel)
+    for (int t = warp; t < T_; t += nwarps) {
+        float* s_logit = logits + (size_t)t * (E + 1);
+        if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
+        mx = tq_warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
+        sum = tq_warp_sum(sum);
+        float picked_sum = 0.f;
+        for (int j = 0; j < k; ++j) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = s_logit[e];
+                if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (best_e == 0x7fffffff) best_e = j;
+            const float p = expf(best - mx) / sum;
+            picked_sum += p;
+            if (lane == 0) {
+                ids[(size_t)t * k + j] = best_e;
+                s_ids[t * k + j] = best_e;
+                wts[(size_t)t * k + j] = p;
+                s_logit[best_e] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        if (renorm) {
+            __syncwarp();
+            for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
+        }
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&s_count[s_ids[p]], 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {      // offsets of rows and of tiles before expert e
+        int rows = 0, tiles = 0;
+        for (int i = 0; i < e; ++i) { rows += s_count[i]; tiles += (s_count[i] + tile_rows - 1) / tile_rows; }
+        s_off[e] = rows;
+        s_toff[e] = tiles;
+        expert_offset[e] = rows;
+        if (e < E) counts[e] = s_count[e];
+        if (e == E) n_tiles[0] = tiles;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {       // stable: pairs of an expert keep their order
+        const int e = s_ids[p];
+        int rank = 0;
+        for (int q = 0; q < p; ++q) rank += s_ids[q] == e;
+        const int row = s_off[e] + rank;
+        s_row[row] = p;
+        sorted_pair[row] = p;
+        row_of_pair[p] = row;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = s_count[e];
+        for (int i = 0; i * tile_rows < c; ++i) {
+            tile_expert[s_toff[e] + i] = e;
+            tile_row0[s_toff[e] + i] = s_off[e] + i * tile_rows;
+            tile_count[s_toff[e] + i] = min(tile_rows, c - i * tile_rows);
+        }
+    }
+    __syncthreads();
+    for (int row = warp; row < P; row += nwarps) {            // expert-sorted copies of the token rows
+        const TA* src = x + (size_t)(s_row[row] / k) * H;
+        TA* dst = x_rows + (size_t)row * H;
+        if (vec) {
+            const int n16 = (int)((size_t)H * sizeof(TA) / 16);
+            const uint4* s4 = reinterpret_cast<const uint4*>(src);
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+            for (int i = lane; i < n16; i += 32) d4[i] = s4[i];
+        } else {
+            for (int i = lane; i < H; i += 32) dst[i] = src[i];
+        }
+    }
+}
+
+// Router, expert-sorted layout and gathered rows for a step of few tokens: two launches in all.
+// Needs T*k <= 512 pairs and E <= 1024 experts; logits: T * (E + 1) floats of scratch.
+TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype, float* logits,
+                              int* ids, float* wts, float* shared_scale, int tile_rows, int* counts, int* sorted_pair,
+                              int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0, int* tile_count,
+                              int* n_tiles, void* x_rows, int T_, int H, int E, int k, int renorm, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ * k <= SMALL_MAX_PAIRS && E <= SMALL_MAX_EXPERTS,
+               "router_small: %d pairs / %d experts exceed %d / %d", T_ * k, E, SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS);
+    TQ_REQUIRE(E >= 1 && k >= 1 && k <= E && tile_rows >= 1, "router_small: bad sizes E=%d k=%d tile_rows=%d", E, k, tile_rows);
+    TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
+    const bool staged = H <= ROUTER_MAX_STAGED_H;
+    const size_t smem = staged ? (size_t)H * sizeof(float) : 0;
+    const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
+    const int vec_ok = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
+    const int rows = E + (wsg ? 1 : 0);
+    int chunks = (512 + T_ - 1) / T_;
+    if (chunks > (rows + 3) / 4) chunks = (rows + 3) / 4;
+    if (chunks < 1) chunks = 1;
+    const int rows_per_cta = (rows + chunks - 1) / chunks;
+    chunks = (rows + rows_per_cta - 1) / rows_per_cta;
+    const int threads = rows_per_cta >= 32 ? 1024 : (rows_per_cta >= 16 ? 512 : (rows_per_cta >= 8 ? 256 : 128));
+    dim3 grid(T_, chunks);
+#define ROUTER_LAUNCH(ST)                                                                              \
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
+        (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                      \
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
+    if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
+#undef ROUTER_LAUNCH
+    TQ_CHECK_LAUNCH("router_logits");
+    const int abytes = act_dtype == TQ_F32 ? 4 : 2;
+    const int vec = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
+    TQ_DISPATCH(act_dtype, TA,
+        (tq_launch(1, SMALL_THREADS, 0, stream)(router_small_tail_kernel<TA>, logits, ids, wts, shared_scale, T_, E, k,
+            renorm, tile_rows, counts, sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0, tile_count,
+            n_tiles, (const TA*)x, (TA*)x_rows, H, vec)));
+    TQ_CHECK_LAUNCH("router_small_tail");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // Exact grouped GEMM on CUDA cores.  A [R, K]; W [G, Nw, K] with Nw = N (plain) or 2N (SwiGLU:
 // gate rows [0, N), up rows [N, 2N)); C [R, N].  Rows come in tiles (tile_expert/row0/count);
 // with tile_expert == null there is one group and tile b covers rows [b*64, b*64+64).

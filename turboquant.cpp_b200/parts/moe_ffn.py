@@ -140,22 +140,26 @@ class MoEFeedForward(FeedForward):
         ids = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
-        if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
-            # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products are
-            # exact in fp32 and the sum is fp32), then the selection kernel
-            logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
-            KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1))
-            KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
+        tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
+        layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
+        x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
+        if KM.router_small_pays(T, k, self.n_experts):
+            # few tokens (decoding): router, layout and the sorted copies of the rows in two launches
+            KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows)
         else:
-            KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
+            if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
+                # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products
+                # are exact in fp32 and the sum is fp32), then the selection kernel
+                logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
+                KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1))
+                KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
+            else:
+                KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
+            KM.moe_align(ids, layout)
+            KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
         if ctx.debug is not None:
             ctx.debug.setdefault("router_ids", []).append(ids.clone())
             ctx.debug.setdefault("router_weights", []).append(wts.clone())
-        tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
-        layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
-        KM.moe_align(ids, layout)
-        x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
-        KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
         h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
         self._product(x_rows, self.w13, h_rows, layout, True, tile)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
