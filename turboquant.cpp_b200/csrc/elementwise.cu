@@ -101,12 +101,13 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__
     const TY* yr = y ? y + src * H : nullptr;
     const bool write_back = y && !rows;
     const int nvec = H >> 2;
-    float4 v[RMS_VEC_GROUPS];
+    float4 v[RMS_VEC_GROUPS], g[RMS_VEC_GROUPS];
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
         if (i < nvec) {
+            g[c] = tq_load4<TW>(w + 4 * i);                 // fetched now, so that it arrives during the reduction
             float4 a = tq_load4<float>(xr + 4 * i);
             if (yr) { const float4 b = tq_load4<TY>(yr + 4 * i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
             if (write_back) tq_store4<float>(xr + 4 * i, a);
@@ -120,10 +121,9 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__
 #pragma unroll
     for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
-        if (i < nvec) {
-            const float4 g = tq_load4<TW>(w + 4 * i);
-            tq_store4<TO>(o + 4 * i, make_float4(v[c].x * rs * g.x, v[c].y * rs * g.y, v[c].z * rs * g.z, v[c].w * rs * g.w));
-        }
+        if (i < nvec)
+            tq_store4<TO>(o + 4 * i, make_float4(v[c].x * rs * g[c].x, v[c].y * rs * g[c].y, v[c].z * rs * g[c].z,
+                                                 v[c].w * rs * g[c].w));
     }
 }
 

@@ -64,7 +64,8 @@ __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restr
     for (int e = e0 + warp; e < e1; e += nwarps) {
         const TW* w = e < E ? wr + (size_t)e * H : wsg;
         float s = 0.f;
-        for (int i = lane * 8; i < Hv; i += 256) {
+#pragma unroll 4
+        for (int i = lane * 8; i < Hv; i += 256) {          // unrolled: four 16-byte loads in flight per lane
             float f[8];
             RowVec<TW>::load(w + i, f);
 #pragma unroll
@@ -406,8 +407,10 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
     TQ_CHECK_LAUNCH("router_logits");
     const int abytes = act_dtype == TQ_F32 ? 4 : 2;
     const int vec = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
+    int tail_threads = 32 * (T_ * k > T_ ? T_ * k : T_);      // a warp per (token, choice) row to copy, at least one per token
+    tail_threads = tail_threads < 128 ? 128 : (tail_threads > SMALL_THREADS ? SMALL_THREADS : tail_threads);
     TQ_DISPATCH(act_dtype, TA,
-        (tq_launch(1, SMALL_THREADS, 0, stream)(router_small_tail_kernel<TA>, logits, ids, wts, shared_scale, T_, E, k,
+        (tq_launch(1, tail_threads, 0, stream)(router_small_tail_kernel<TA>, logits, ids, wts, shared_scale, T_, E, k,
             renorm, tile_rows, counts, sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0, tile_count,
             n_tiles, (const TA*)x, (TA*)x_rows, H, vec)));
     TQ_CHECK_LAUNCH("router_small_tail");
@@ -546,7 +549,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
         const float sc = Ys ? (shared_scale ? shared_scale[t] : 1.0f) : 0.f;
         for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < H; i += gridDim.y * blockDim.x * 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int j = 0; j < k; ++j) {
+#pragma unroll 4
+            for (int j = 0; j < k; ++j) {                   // unrolled: the chosen experts' rows load side by side
                 const float wj = wts[(size_t)t * k + j];
                 const float4 a = *reinterpret_cast<const float4*>(Y + (size_t)row_of_pair[(size_t)t * k + j] * H + i);
                 v.x += wj * a.x; v.y += wj * a.y; v.z += wj * a.z; v.w += wj * a.w;
