@@ -211,7 +211,8 @@ def router(x: np.ndarray, wr: np.ndarray, k: int, norm_topk: bool):
     softmax over them (:630-678), which is the norm_topk=true case of this formula; it breaks
     exact ties toward the highest index, this library toward the lowest.
     Returns (ids [T,k], weights [T,k], margin [T]): margin is the gap between the k-th and the
-    (k+1)-th largest logit, the distance of the choice from a flip."""
+    (k+1)-th largest logit divided by the spread (standard deviation) of the token's logits: the
+    distance of the choice from a flip, in the unit in which rounding moves the logits."""
     logits = linear(x, wr)
     p = softmax(logits)
     order = np.argsort(-p, axis=-1, kind="stable")
@@ -219,7 +220,7 @@ def router(x: np.ndarray, wr: np.ndarray, k: int, norm_topk: bool):
     w = np.take_along_axis(p, ids, axis=-1)
     if p.shape[1] > k:
         margin = (np.take_along_axis(logits, order[:, k - 1:k], axis=-1)
-                  - np.take_along_axis(logits, order[:, k:k + 1], axis=-1))[:, 0]
+                  - np.take_along_axis(logits, order[:, k:k + 1], axis=-1))[:, 0] / (logits.std(axis=-1) + 1e-30)
     else:
         margin = np.full(p.shape[0], np.inf)
     if norm_topk:

@@ -4,9 +4,9 @@ and compare every wanted position with the plain implementation.
 Routing is discontinuous: when two experts' router logits are closer than the arithmetic's error,
 either choice is right, and a different choice changes the logits by far more than rounding.  So
 the comparison has two parts: (1) the engine's expert choices must equal the plain model's, except
-where the plain model's own margin (gap between the k-th and the next logit) is below `flip_margin`
-— and such places must be rare; (2) the logits must agree with the plain model run *with the
-engine's choices*, to the tolerance of the dtype.
+where the plain model's own margin (gap between the k-th and the next router logit, in units of the
+spread of that token's logits) is below `flip_margin` — and such places must be rare; (2) the
+logits must agree with the plain model run *with the engine's choices*, to the tolerance of the dtype.
 """
 from __future__ import annotations
 
@@ -17,11 +17,13 @@ import numpy as np
 from plain.qwen2_moe_plain import PlainModel, forward as plain_forward, no_round, round_bf16
 
 # (logit tolerance relative to the largest logit, margin below which a different expert is accepted)
-#  float32: fp32 sums of a few hundred terms in another order than float64: a few 1e-6.
+#  float32: fp32 sums of up to a few thousand terms in another order than float64: a few 1e-6 of the
+#            logits' scale, and 1e-5 of the spread of a token's router logits.
 #  bfloat16: the plain model rounds activations where the engine stores bfloat16, so what is left is
 #            summation order plus 1-ulp (2^-8) flips of single activations that spread through the
-#            layers; router logits move by about 1e-3 of their scale for the same reason.
-TOL = {"float32": (2e-5, 2e-6), "bfloat16": (1.5e-2, 4e-3)}
+#            layers (and P rounded to bfloat16 inside the prompt attention kernel): a few 1e-3 of the
+#            logits' scale; a token's router logits move by up to about 1e-2 of their spread.
+TOL = {"float32": (2e-5, 1e-5), "bfloat16": (1.5e-2, 2.5e-2)}
 
 
 def whole(rid: str, tokens: Sequence[int]):
@@ -115,7 +117,9 @@ def check_against_plain(plain: PlainModel, tokens: Sequence[int], logits: Dict[i
                 f"{what}: layer {l} position {p}: engine chose experts {forced[l][p].tolist()}, plain "
                 f"{rec['ids'][l][p].tolist()} with margin {rec['margin'][l][p]:.3e}")
         n_diff += len(differ)
-    assert n_diff <= max(1, (n * len(sparse)) // 50), f"{what}: {n_diff} expert choices differ"
+    # near-ties are a few per cent of all choices (the gap to the next expert is a fraction of the spread
+    # divided by the number of experts); more than that would be a fault, not rounding
+    assert n_diff <= max(2, (n * len(sparse)) // 20), f"{what}: {n_diff} expert choices differ"
     ref = plain_forward(plain, tokens, rnd, forced_ids=forced)
     scale = np.abs(ref).max()
     worst, worst_p = 0.0, -1

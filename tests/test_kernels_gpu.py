@@ -309,7 +309,7 @@ def test_router(E, k, H, renorm, shared, dtype):
     sc = torch.empty((T,), dtype=torch.float32, device=DEV) if shared else None
     KM.router_topk(dev(x, dtype), dev(wr, dtype), dev(wsg, dtype) if shared else None, k, renorm, ids, wts, sc)
     rid, rw, margin = P.router(x, wr, k, renorm)
-    assert margin.min() > 1e-4, "test data has a near-tie"
+    assert margin.min() > 1e-4, "test data has a near-tie"      # in units of the logits' spread
     assert np.array_equal(ids.cpu().numpy(), rid)
     close(wts, rw, 1e-5)
     if shared:

@@ -158,7 +158,7 @@ def test_moe_feed_forward_alone(E, k, I, S, norm):
     m = types.SimpleNamespace(w=w, k=k, norm_topk=norm, cfg={"shared_expert_intermediate_size": S})
     rec = {}
     want = P.moe_feed_forward(m, 0, x.double().cpu().numpy(), record=rec)
-    assert rec["margin"][0].min() > 1e-5
+    assert rec["margin"][0].min() > 1e-4
     assert np.array_equal(ctx.debug["router_ids"][0].cpu().numpy(), rec["ids"][0])
     close(y, want, 5e-6)
 

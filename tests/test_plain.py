@@ -50,7 +50,7 @@ def test_router_norm_and_ties():
     ids, w, margin = P.router(x[:1], wr, 2, False)
     assert ids.tolist() == [[0, 2]]                                         # equal logits: the lower index first
     p = np.exp([1, .5, 1, 0]) / np.exp([1, .5, 1, 0]).sum()
-    assert np.allclose(w, [[p[0], p[2]]]) and np.allclose(margin, [0.5])
+    assert np.allclose(w, [[p[0], p[2]]]) and np.allclose(margin, [0.5 / np.std([1, .5, 1, 0])])
     _, wn, _ = P.router(x[:1], wr, 2, True)
     assert np.allclose(wn.sum(), 1.0) and np.allclose(wn, [[0.5, 0.5]])
 
