@@ -21,6 +21,41 @@ TQ_DEFINE_LAST_ERROR
 
 #define TQ_MAX_HEAD_DIM 256
 
+// eight consecutive elements: fetched raw (so that the next group's loads can be in flight while the
+// current group is computed), widened to fp32 when used
+template <typename T> struct Vec8 { };
+template <> struct Vec8<__nv_bfloat16> {
+    struct Raw { uint4 v; };
+    static __device__ __forceinline__ Raw fetch(const __nv_bfloat16* p) { Raw r; r.v = *reinterpret_cast<const uint4*>(p); return r; }
+    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) { widen(fetch(p), f); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+        uint4 v;
+        uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); u[i] = *reinterpret_cast<const uint32_t*>(&h); }
+        *reinterpret_cast<uint4*>(p) = v;
+    }
+};
+template <> struct Vec8<float> {
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw fetch(const float* p) {
+        Raw r; r.a = *reinterpret_cast<const float4*>(p); r.b = *reinterpret_cast<const float4*>(p + 4); return r;
+    }
+    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
+        f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
+    }
+    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) { widen(fetch(p), f); }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+};
+
 // ---------------------------------------------------------------------------------------
 // A block walks (head, pair) indices of one token's fused QKV row; with few tokens several blocks share a row.
 // ---------------------------------------------------------------------------------------
@@ -30,7 +65,7 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
                                       int pairing, const int* __restrict__ positions,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
                                       int table_stride, int page_size, TA* __restrict__ q_out,
-                                      TA* __restrict__ cache, int heads, int nh, int nkv, int hd) {
+                                      TA* __restrict__ cache, int heads, int nh, int nkv, int hd, int vec8) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
@@ -44,6 +79,44 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
     if (heads > nh) {
         const int page = page_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         page_base = (size_t)page * 2 * nkv * page_size * hd + (size_t)(pos % page_size) * hd;
+    }
+    if (vec8) {
+        // half pairing, head size a multiple of 16, 16-byte aligned rows: a thread takes eight pairs,
+        // elements i..i+7 of the first half of a head and the same of the second half
+        const int groups = half >> 3;
+        for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < heads * groups; idx += gridDim.y * blockDim.x) {
+            const int j = idx / groups, i = (idx - j * groups) * 8;
+            const TA* src = row + (size_t)j * hd;
+            float a[8], c[8];
+            Vec8<TA>::load(src + i, a);
+            Vec8<TA>::load(src + half + i, c);
+            if (bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    a[e] += tq_to_float(bias[(size_t)j * hd + i + e]);
+                    c[e] += tq_to_float(bias[(size_t)j * hd + half + i + e]);
+                }
+            }
+            const bool is_v = j >= nh + nkv;
+            if (!is_v && cs_row) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float cs = cs_row[i + e], sn = sn_row[i + e];
+                    const float ra = a[e] * cs - c[e] * sn, rc = a[e] * sn + c[e] * cs;
+                    a[e] = ra; c[e] = rc;
+                }
+            }
+            TA* dst;
+            if (j < nh) {
+                dst = q_out + ((size_t)t * nh + j) * hd;
+            } else {
+                const int kvh = is_v ? j - nh - nkv : j - nh;
+                dst = cache + page_base + ((size_t)(is_v ? 1 : 0) * nkv + kvh) * page_size * hd;
+            }
+            Vec8<TA>::store(dst + i, a);
+            Vec8<TA>::store(dst + half + i, c);
+        }
+        return;
     }
     for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < heads * half; idx += gridDim.y * blockDim.x) {
         const int j = idx / half, i = idx - j * half;
@@ -80,7 +153,10 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     TQ_REQUIRE(pairing == 0 || pairing == 1, "qkv_rope_cache: pairing %d is neither half (0) nor interleaved (1)", pairing);
     TQ_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_rope_cache: cos and sin tables must come together");
     const int heads = write_kv ? nh + 2 * nkv : nh;
-    const int pairs = heads * (hd / 2);
+    const int esize = act_dtype == TQ_F32 ? 4 : 2;
+    const int vec8 = pairing == 0 && hd % 16 == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
+                     ((uintptr_t)cache % 16) == 0 && ((size_t)hd * esize) % 16 == 0;
+    const int pairs = vec8 ? heads * (hd / 16) : heads * (hd / 2);      // work items per token
     const int threads = pairs >= 1024 ? 256 : (pairs >= 256 ? 128 : 64);
     // few tokens: several blocks share a token's row, so that the step still fills the GPU
     int chunks = T_ >= 512 ? 1 : (pairs + threads - 1) / threads;
@@ -88,7 +164,7 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
         (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB>, 
             (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
-            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd))));
+            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8))));
     TQ_CHECK_LAUNCH("qkv_rope_cache");
     return 0;
 }
@@ -201,30 +277,6 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
 // the same registers.  Partial state per (token, head, split): max, sum, hd weighted values (fp32).
 // ---------------------------------------------------------------------------------------
 #define SPLIT_WARPS 4
-
-// eight consecutive elements: fetched raw (so that the next group's loads can be in flight while the
-// current group is computed), widened to fp32 when used
-template <typename T> struct Vec8 { };
-template <> struct Vec8<__nv_bfloat16> {
-    struct Raw { uint4 v; };
-    static __device__ __forceinline__ Raw fetch(const __nv_bfloat16* p) { Raw r; r.v = *reinterpret_cast<const uint4*>(p); return r; }
-    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.v);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
-    }
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) { widen(fetch(p), f); }
-};
-template <> struct Vec8<float> {
-    struct Raw { float4 a, b; };
-    static __device__ __forceinline__ Raw fetch(const float* p) {
-        Raw r; r.a = *reinterpret_cast<const float4*>(p); r.b = *reinterpret_cast<const float4*>(p + 4); return r;
-    }
-    static __device__ __forceinline__ void widen(const Raw& r, float (&f)[8]) {
-        f[0] = r.a.x; f[1] = r.a.y; f[2] = r.a.z; f[3] = r.a.w; f[4] = r.b.x; f[5] = r.b.y; f[6] = r.b.z; f[7] = r.b.w;
-    }
-    static __device__ __forceinline__ void load(const float* p, float (&f)[8]) { widen(fetch(p), f); }
-};
 
 template <typename TA, int LPK, int GC>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)

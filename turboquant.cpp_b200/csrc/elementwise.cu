@@ -203,21 +203,25 @@ TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, 
 // ---------------------------------------------------------------------------------------
 // out[r, :] = in[idx[r] / divisor, :]   (expert-sorted copies of token rows: divisor = top-k)
 // ---------------------------------------------------------------------------------------
+// A warp copies a row (16-byte accesses when rows allow it); a block takes several rows.
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ idx, int divisor,
-                                   T* __restrict__ out, int H, int vec) {
+                                   T* __restrict__ out, int R, int H, int vec) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    const int r = blockIdx.x;
-    const T* src = in + (size_t)(idx[r] / divisor) * H;
-    T* dst = out + (size_t)r * H;
-    if (vec) {          // rows are a multiple of 16 bytes and 16-byte aligned
-        const int n16 = (int)((size_t)H * sizeof(T) / 16);
-        const uint4* s4 = reinterpret_cast<const uint4*>(src);
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
-        for (int i = threadIdx.x; i < n16; i += blockDim.x) d4[i] = s4[i];
-    } else {
-        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+        const T* src = in + (size_t)(idx[r] / divisor) * H;
+        T* dst = out + (size_t)r * H;
+        if (vec) {          // rows are a multiple of 16 bytes and 16-byte aligned
+            const int n16 = (int)((size_t)H * sizeof(T) / 16);
+            const uint4* s4 = reinterpret_cast<const uint4*>(src);
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll 4
+            for (int i = lane; i < n16; i += 32) d4[i] = s4[i];
+        } else {
+            for (int i = lane; i < H; i += 32) dst[i] = src[i];
+        }
     }
 }
 
@@ -227,8 +231,10 @@ TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* 
     TQ_REQUIRE(R > 0 && H > 0 && divisor > 0, "gather_rows: bad sizes R=%d H=%d divisor=%d", R, H, divisor);
     const int esize = dtype == TQ_F32 ? 4 : 2;
     const int vec = ((size_t)H * esize) % 16 == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    int blocks = (R + 7) / 8;                     // eight warps, a row each, per block
+    if (blocks > 148 * 8) blocks = 148 * 8;
     TQ_DISPATCH(dtype, T,
-        tq_launch(R, 256, 0, stream)(gather_rows_kernel<T>, (const T*)in, idx, divisor, (T*)out, H, vec));
+        tq_launch(blocks, 256, 0, stream)(gather_rows_kernel<T>, (const T*)in, idx, divisor, (T*)out, R, H, vec));
     TQ_CHECK_LAUNCH("gather_rows");
     return 0;
 }
