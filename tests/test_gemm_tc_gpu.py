@@ -23,9 +23,9 @@ def rel(got, want):
 @pytest.mark.parametrize("R,N,K,G", [(1, 128, 64, 1), (5, 128, 256, 3), (40, 200, 136, 6), (300, 1408, 2048, 8),
                                       (77, 96, 72, 5), (1000, 256, 512, 4)])
 @pytest.mark.parametrize("swiglu", [False, True])
-@pytest.mark.parametrize("bn", [16, 32, 64, 128])
+@pytest.mark.parametrize("bn,pair", [(16, False), (32, False), (64, False), (128, False), (256, False), (128, True), (256, True)])
 @pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
-def test_grouped(R, N, K, G, swiglu, bn, odtype):
+def test_grouped(R, N, K, G, swiglu, bn, pair, odtype):
     from turboquant_cpp_b200.kernels import gemm_tc as KT, moe as KM
     rng = np.random.default_rng(R * 7 + N + bn)
     a = P.round_bf16(rng.normal(size=(R, K)))
@@ -38,7 +38,7 @@ def test_grouped(R, N, K, G, swiglu, bn, odtype):
     order = lay.sorted_pair.cpu().numpy()[:R]
     a_sorted = a[order]
     out = torch.full((R, N), float("nan"), dtype=odtype, device=DEV)
-    KT.gemm_tc(dev(a_sorted, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, lay, bn)
+    KT.gemm_tc(dev(a_sorted, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, lay, bn, pair)
     KT.check_status()
     want = np.zeros((R, N))
     for g in range(G):
@@ -58,14 +58,15 @@ def test_grouped(R, N, K, G, swiglu, bn, odtype):
 
 @pytest.mark.parametrize("R,N,K", [(3, 5632, 2048), (130, 300, 1408), (2048, 384, 256)])
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_one_group(R, N, K, swiglu):
+@pytest.mark.parametrize("pair", [False, True])
+def test_one_group(R, N, K, swiglu, pair):
     from turboquant_cpp_b200.kernels import gemm_tc as KT
     rng = np.random.default_rng(R + N)
     a = P.round_bf16(rng.normal(size=(R, K)))
     w = P.round_bf16(rng.normal(size=(1, 2 * N if swiglu else N, K)) / math.sqrt(K))
-    bn = KT.token_tile_for(R, 1)
+    bn = max(128, KT.token_tile_for(R, 1)) if pair else KT.token_tile_for(R, 1)
     out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
-    KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, None, bn)
+    KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, None, bn, pair)
     KT.check_status()
     want = P.silu(a @ w[0, :N].T) * (a @ w[0, N:].T) if swiglu else a @ w[0].T
     assert rel(out, want) < 2e-5
@@ -83,6 +84,8 @@ def test_refuses_what_it_cannot_do():
     with pytest.raises(KernelError):
         KT.gemm_tc(x, pw, out, None, 48)                               # not a token tile the kernel has
     with pytest.raises(KernelError):
+        KT.gemm_tc(x, pw, out, None, 64, True)                         # pairs of CTAs want wide token tiles
+    with pytest.raises(KernelError):
         KT.gemm_tc(x.float(), pw, out, None, 16)                       # activations must be bfloat16
     with pytest.raises(KernelError):
         KT.gemm_tc(x[:, :32].contiguous(), pw, out, None, 16)          # packed for another K
@@ -93,10 +96,18 @@ def test_refuses_what_it_cannot_do():
 def test_packing_layout():
     from turboquant_cpp_b200.kernels import gemm_tc as KT
     w = torch.arange(2 * 2 * 130 * 72, dtype=torch.float32, device=DEV).reshape(2, 260, 72).to(torch.bfloat16)
-    pw = KT.pack_weights(w, True)                                      # N = 130 -> 2 tiles, K = 72 -> 2 k-blocks
-    assert pw.data.shape == (2 * 2 * 2, 2, 128, 64) and pw.n == 130 and pw.k == 72 and pw.groups == 2
-    d = pw.data.view(2, 2, 2, 2, 128, 64)                               # group, gate/up, tile, k-block, row, col
-    assert torch.equal(d[1, 0, 1, 1, 1, :8], w[1, 129, 64:72])          # gate row 129 = tile 1 row 1, k-block 1
-    assert torch.equal(d[1, 1, 0, 0, 5, :], w[1, 130 + 5, :64])         # up row 5
-    assert float(d[0, 0, 1, 0, 2:, :].abs().sum()) == 0.0               # rows beyond N are zero
-    assert float(d[0, 0, 0, 1, :, 8:].abs().sum()) == 0.0               # columns beyond K are zero
+    pw = KT.pack_weights(w, True)                                      # N = 130 -> 3 tiles of 64 columns, K = 72 -> 2 k-blocks
+    assert pw.data.shape == (2 * 3, 2, 128, 64) and pw.n == 130 and pw.k == 72 and pw.groups == 2
+    d = pw.data.view(2, 3, 2, 128, 64)                                  # group, tile, k-block, row, col
+    # column 129 = tile 2, column 1 of the tile = quarter 0, i = 1: gate at row 1, up at row 17
+    assert torch.equal(d[1, 2, 1, 1, :8], w[1, 129, 64:72])
+    assert torch.equal(d[1, 2, 0, 17, :], w[1, 130 + 129, :64])
+    # column 64 + 37 = tile 1, quarter 2, i = 5: gate at row 69, up at row 85
+    assert torch.equal(d[0, 1, 0, 69, :], w[0, 101, :64])
+    assert torch.equal(d[0, 1, 0, 85, :], w[0, 130 + 101, :64])
+    assert float(d[0, 2, 0, 2:16, :].abs().sum()) == 0.0                # columns beyond N are zero (gate ...
+    assert float(d[0, 2, 0, 18:, :].abs().sum()) == 0.0                 # ... and up)
+    assert float(d[0, 0, 1, :, 8:].abs().sum()) == 0.0                  # elements beyond K are zero
+    pp = KT.pack_weights(w, False)                                      # plain: 260 rows -> 3 tiles of 128
+    assert pp.data.shape == (2 * 3, 2, 128, 64)
+    assert torch.equal(pp.data.view(2, 3, 2, 128, 64)[1, 2, 1, 3, :8], w[1, 259, 64:72])

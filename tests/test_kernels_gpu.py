@@ -327,7 +327,8 @@ def test_router_ties_go_to_the_lowest_index():
     assert ids.cpu().tolist() == [[2, 5, 0]]
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (50, 6, 3), (300, 5, 1), (1000, 60, 4), (7, 64, 8)])
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (50, 6, 3), (300, 5, 1), (1000, 60, 4), (7, 64, 8),
+                                   (2048, 60, 4), (5000, 130, 5), (4097, 3, 1), (700, 1500, 6)])   # several chunks, a ragged last one
 def test_moe_align(T, E, k):
     from turboquant_cpp_b200.kernels import moe as KM
     rng = np.random.default_rng(T)

@@ -105,23 +105,41 @@ struct TqLaunch {
     dim3 grid, block;
     size_t smem;
     cudaStream_t stream;
-    template <typename... KArgs, typename... Args>
-    void operator()(void (*kernel)(KArgs...), Args&&... args) const {
+    unsigned cluster;          // CTAs per cluster along x (1: no clusters)
+    void config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr) const {
         static const bool pdl = [] { const char* e = getenv("TQ_NO_PDL"); return !(e && e[0] && e[0] != '0'); }();
-        cudaLaunchConfig_t cfg = {};
+        cfg = cudaLaunchConfig_t{};
         cfg.gridDim = grid;
         cfg.blockDim = block;
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        unsigned n = 0;
+        if (pdl) {
+            attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n].val.programmaticStreamSerializationAllowed = 1;
+            ++n;
+        }
+        if (cluster > 1) {
+            attr[n].id = cudaLaunchAttributeClusterDimension;
+            attr[n].val.clusterDim.x = cluster;
+            attr[n].val.clusterDim.y = 1;
+            attr[n].val.clusterDim.z = 1;
+            ++n;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = pdl ? 1 : 0;
+        cfg.numAttrs = n;
+    }
+    template <typename... KArgs, typename... Args>
+    void operator()(void (*kernel)(KArgs...), Args&&... args) const {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[2];
+        config(cfg, attr);
         cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // errors surface in TQ_CHECK_LAUNCH
     }
 };
-inline TqLaunch tq_launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream) { return TqLaunch{grid, block, smem, stream}; }
+inline TqLaunch tq_launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster = 1) {
+    return TqLaunch{grid, block, smem, stream, cluster};
+}
 
 // Dispatch on an element type code: TQ_F32 -> float, TQ_BF16 -> __nv_bfloat16.
 #define TQ_DISPATCH(code, T, ...)                                            \

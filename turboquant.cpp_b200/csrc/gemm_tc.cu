@@ -11,12 +11,17 @@
 // The weights are packed once at load time into [128 rows x 64 elements] blocks of 16 KiB, so a
 // stage of the pipeline is one contiguous read and a CTA's stream walks memory sequentially instead
 // of touching 128 rows 4 KiB apart (which thrashes DRAM row buffers when hundreds of CTAs stream).
+// With SwiGLU a block holds 64 gate rows and the 64 up rows of the same output columns, interleaved
+// in runs of 16 (rows 32q..32q+15: gate of columns 64j+16q.., rows 32q+16..32q+31: up of the same),
+// so one MMA yields both halves of 64 outputs and an epilogue warp pairs them with one shuffle.
 //
 // Orientation: the WEIGHT rows are the M side of the MMA (128 rows per tile), the token rows are
-// the N side (16..128 per tile).  One kernel therefore serves a 2,048-token prompt and a decode
-// step of a few tokens per expert without padding the tensor core's M dimension with empty rows:
-// at decode the kernel is a weight stream (each CTA pulls a [128 x K] slab through a multi-stage
-// TMA pipeline) and the tokens ride along as a narrow N.
+// the N side: a tile has up to BN (16..256) token rows and the MMA's N is the tile's own row count
+// rounded up to 16, so an expert with 136 rows costs one product of N = 144, not two of 128.  One
+// kernel therefore serves a 2,048-token prompt and a decode step of a few tokens per expert without
+// padding the tensor core's M dimension with empty rows: at decode the kernel is a weight stream
+// (each CTA pulls a [128 x K] slab through a multi-stage TMA pipeline) and the tokens ride along as
+// a narrow N.
 //
 // Persistent CTAs (one or two per SM) each walk a strided list of (weight-row tile, token tile)
 // pairs.  Warp 0 issues TMA loads as one uninterrupted stream of k-blocks across tiles, warp 1 owns
@@ -34,7 +39,6 @@ namespace {
 constexpr int BM = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // K elements per stage: 128 bytes of bf16 = one swizzle row
 constexpr int UMMA_K = 16;       // K of one tcgen05.mma for 16-bit inputs
-constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;     // polls of an mbarrier before a wait gives up
 constexpr uint64_t WAIT_NS = 2000000000ull;   // ... or two seconds, whichever comes first
 
@@ -121,21 +125,82 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr));
 }
 
-template <int BN, bool SWIGLU>
+// ---- CTA pairs (cta_group::2) ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// loads of a CTA pair: the data lands in this CTA, the bytes are counted on the barrier of the pair's first CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_block_pair(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(0), "r"(0), "r"(kb), "r"(tile) : "memory");
+}
+// one product of the pair: M = 256 (128 weight rows from each CTA), the token rows half from each CTA
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this address in both CTAs of the pair once the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+// silu(gate) * up.  A bfloat16 result keeps 8 bits, so the fast exponential and division (a few units in
+// the last place of fp32) do; an fp32 result gets the exact ones.
+template <typename TO> __device__ __forceinline__ float silu_mul(float gate, float up) {
+    return gate / (1.0f + expf(-gate)) * up;
+}
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float gate, float up) {
+    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
+
+template <int BN, bool PAIR>
 struct Tile {
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;       // token rows this CTA holds of a tile
+    static constexpr int B_BYTES = B_ROWS * BK * 2;
+    static constexpr int BOX_ROWS = B_ROWS < 64 ? B_ROWS : 64;   // token rows of one TMA box; the tail comes in boxes of 16
+    static constexpr int BOX_BYTES = BOX_ROWS * BK * 2;
+    static constexpr int TAIL_ROWS = 16, TAIL_BYTES = TAIL_ROWS * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // narrow token tiles (decoding) leave room for two CTAs per SM: one CTA's start-up and epilogue
     // overlap the other's weight stream; wide tiles take the whole SM
     static constexpr int CTAS_PER_SM = BN <= 32 ? 2 : 1;
     static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
-    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
+    // epilogue warps: one per quarter of the accumulator's lanes, two for wide tiles (each takes every other
+    // group of 16 token rows), so that reading a tile back never takes longer than multiplying the next
+    static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int ACC_COLS = BN;
     // two accumulators in tensor memory: a tile's epilogue overlaps the next tile's products
     static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 128, "token tile must be 16..128 in steps of 16");
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "token tile must be 16..256 in steps of 16");
+    static_assert(!PAIR || BN >= 128, "pairs are for wide token tiles");
     static_assert(STAGES >= 2, "pipeline needs at least two stages");
     static_assert(TMEM_COLS * CTAS_PER_SM <= 512, "tensor memory holds 512 columns per SM");
 };
@@ -144,25 +209,24 @@ struct Tile {
 // tiles: inside a band the token tile runs fastest, then the weight-row tile, so the CTAs that run
 // side by side share both a few weight slabs and a few activation tiles through the L2 (prompts:
 // an expert has several token tiles, and every activation tile meets every weight-row tile).  A
-// CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-struct TileInfo { int expert, row0, count, m0; };
+// CTA (or pair) takes tiles w, w + workers, ...; a pair's weight-row tile is two adjacent ones.
+struct TileInfo { int expert, row0, count, mx; };
 constexpr int TILE_BAND = 8;
 
 __device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int n_mx, int bn, const int* tile_expert,
                                               const int* tile_row0, const int* tile_count, int R) {
     TileInfo t;
     const int full = (n_ty / TILE_BAND) * TILE_BAND;          // token tiles in whole bands
-    int mx, ty;
+    int ty;
     if (id < full * n_mx) {
         const int band = id / (TILE_BAND * n_mx), rem = id - band * (TILE_BAND * n_mx);
-        mx = rem / TILE_BAND;
+        t.mx = rem / TILE_BAND;
         ty = band * TILE_BAND + rem % TILE_BAND;
     } else {
         const int rem = id - full * n_mx, w = n_ty - full;    // the last, narrower band
-        mx = rem / w;
+        t.mx = rem / w;
         ty = full + rem % w;
     }
-    t.m0 = mx * BM;
     if (tile_expert) {
         t.expert = tile_expert[ty];
         t.row0 = tile_row0[ty];
@@ -175,22 +239,28 @@ __device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int n_mx, int bn
     return t;
 }
 
-template <int BN, bool SWIGLU, typename TO>
-__global__ void __launch_bounds__(THREADS, Tile<BN, SWIGLU>::CTAS_PER_SM)
+template <int BN, bool SWIGLU, typename TO, bool PAIR>
+__global__ void __launch_bounds__((Tile<BN, PAIR>::THREADS), (Tile<BN, PAIR>::CTAS_PER_SM))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TO* __restrict__ out, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+               const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
+               const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
                int* __restrict__ status) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    using T = Tile<BN, SWIGLU>;
+    using T = Tile<BN, PAIR>;
+    constexpr int COLS = SWIGLU ? BM / 2 : BM;         // output columns of a weight-row tile
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_abort;
     __shared__ uint32_t s_tmem_base;
 
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                 // place in the pair; 0 issues the products
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int n_ty = tile_expert ? n_tiles[0] : (R + BN - 1) / BN;       // token tiles
-    const int n_mx = (N + BM - 1) / BM;                                  // weight-row tiles
+    const int n_m1 = (N + COLS - 1) / COLS;                              // weight-row tiles
+    const int n_mx = PAIR ? (n_m1 + 1) / 2 : n_m1;                       // ... as units of work
     const int total = n_ty * n_mx;
-    if ((int)blockIdx.x >= total) return;
+    if (worker >= total) return;                                         // both CTAs of a pair leave together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
 
@@ -201,22 +271,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     auto acc_full = [&](int b) { return bars + 8u * (2 * T::STAGES + b); };
     auto acc_empty = [&](int b) { return bars + 8u * (2 * T::STAGES + 2 + b); };
     auto a_tile = [&](int s) { return base + s * T::STAGE_BYTES; };
-    auto a2_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES; };
-    auto b_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES * (SWIGLU ? 2 : 1); };
+    auto b_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES; };
 
     if (threadIdx.x == 0) {
         s_abort = 0;
+        // pairs: the stage barriers that count bytes (of both CTAs' loads) and the accumulator-drained barriers
+        // live in the first CTA; the others are signalled in both CTAs at once by the products' commits
         for (int s = 0; s < T::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }   // 4 epilogue warps
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), (PAIR ? 2 : 1) * T::EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)T::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if (PAIR) cluster_sync_all(); else __syncthreads();     // barriers are ready in both CTAs before either signals the other
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     // only now: a dependent kernel that took tensor memory first could starve a CTA of this grid that
     // had not allocated yet, and then wait forever for this grid to finish
@@ -228,21 +305,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             int issued = 0;          // k-blocks issued so far (stage = issued % STAGES)
             bool ok = true;
-            for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+            for (int id = worker; id < total && ok; id += workers) {
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                const int n_mma = (t.count + 15) & ~15;                                   // N of the products
+                const int rows = PAIR ? n_mma / 2 : t.count;                              // token rows this CTA loads ...
+                const int row0 = t.row0 + (PAIR ? (int)rank * (n_mma / 2) : 0);           // ... from here
+                const int boxes = rows / T::BOX_ROWS;
+                const int tails = (rows - boxes * T::BOX_ROWS + T::TAIL_ROWS - 1) / T::TAIL_ROWS;
+                const uint32_t bytes = (uint32_t)(T::A_BYTES + boxes * T::BOX_BYTES + tails * T::TAIL_BYTES);
+                const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int s = issued % T::STAGES;
                     const uint32_t ph = (uint32_t)(issued / T::STAGES) & 1u;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), (uint32_t)T::STAGE_BYTES);
-                    const int wt = t.expert * (SWIGLU ? 2 * n_mx : n_mx) + t.m0 / BM;     // packed weight tile
-                    tma_load_block(a_tile(s), &map_w, kb, wt, full_bar(s));
-                    if (SWIGLU) tma_load_block(a2_tile(s), &map_w, kb, wt + n_mx, full_bar(s));
-                    tma_load_2d(b_tile(s), &map_x, kb * BK, t.row0, full_bar(s));
+                    if (PAIR) {
+                        // the first CTA expects the bytes of both (the halves are equal); the second only loads
+                        const uint32_t bar = rank == 0 ? full_bar(s) : map_to_cta(full_bar(s), 0);
+                        if (rank == 0) mbar_expect_tx(full_bar(s), 2u * bytes);
+                        tma_load_block_pair(a_tile(s), &map_w, kb, wt, bar);
+                        for (int bx = 0; bx < boxes; ++bx)
+                            tma_load_2d_pair(b_tile(s) + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, bar);
+                        for (int bx = 0; bx < tails; ++bx)
+                            tma_load_2d_pair(b_tile(s) + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                                             row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, bar);
+                    } else {
+                        mbar_expect_tx(full_bar(s), bytes);
+                        tma_load_block(a_tile(s), &map_w, kb, wt, full_bar(s));
+                        for (int bx = 0; bx < boxes; ++bx)
+                            tma_load_2d(b_tile(s) + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, full_bar(s));
+                        for (int bx = 0; bx < tails; ++bx)
+                            tma_load_2d(b_tile(s) + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                                        row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, full_bar(s));
+                    }
                     ++issued;
                 }
             }
-            if (s_abort) {
+            if (s_abort && rank == 0) {
                 // wait (bounded) for the copies this thread started, so none lands after the CTA is gone
                 const int first = issued > T::STAGES ? issued - T::STAGES : 0;
                 for (int j = first; j < issued; ++j) {
@@ -252,12 +350,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(BN);
+        // ---------------- MMA issuer (the pair's first CTA issues for both) ----------------
+        if (lane == 0 && rank == 0) {
             int consumed = 0, it = 0;
             bool ok = true;
-            for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
+            for (int id = worker; id < total && ok; id += workers, ++it) {
+                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                // N of the products: this tile's rows; pairs: M = 256, 128 weight rows from each CTA
+                const uint32_t idesc = umma_idesc((t.count + 15) & ~15) + (PAIR ? ((uint32_t)(BM >> 4) << 24) : 0u);
                 const int b = it & 1;
                 const uint32_t acc = tmem_base + (uint32_t)(b * T::ACC_COLS);
                 // the epilogue must have drained this accumulator (two tiles ago)
@@ -273,58 +373,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-                        const uint64_t bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
-                        umma(acc, umma_desc(a_tile(s) + k * UMMA_K * 2), bd, idesc, accum);
-                        if (SWIGLU) umma(acc + BN, umma_desc(a2_tile(s) + k * UMMA_K * 2), bd, idesc, accum);
+                        const uint64_t ad = umma_desc(a_tile(s) + k * UMMA_K * 2), bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
+                        if (PAIR) umma_pair(acc, ad, bd, idesc, accum); else umma(acc, ad, bd, idesc, accum);
                     }
-                    umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                    // the stage is free (in both CTAs) once these MMAs have read it
+                    if (PAIR) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
                     ++consumed;
                 }
-                if (ok) umma_commit(acc_full(b));       // this tile's accumulator is complete once all MMAs are done
+                // this tile's accumulator is complete once all MMAs are done
+                if (ok) { if (PAIR) umma_commit_pair(acc_full(b)); else umma_commit(acc_full(b)); }
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+        // ---------------- epilogue: warps 2.., TMEM lane quarter = warp % 4 ----------------
         const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;                 // weight row within the tile
+        const int group0 = (warp - 2) >> 2;                // wide tiles: which groups of 16 token rows (even or odd)
+        constexpr int GROUP_STEP = T::EPI_WARPS / 4;
+        // plain: lane = weight row = output column.  SwiGLU: lanes 0..15 hold the gate of 16 columns, lanes
+        // 16..31 the up of the same columns; after the exchange the low half writes token rows 0..7 of each
+        // group of 16 and the high half rows 8..15.
+        const bool high = SWIGLU && lane >= 16;
+        const int r = SWIGLU ? quarter * 16 + (lane & 15) : quarter * 32 + lane;     // output column within the tile
         int it = 0;
         bool ok = true;
-        for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
+        for (int id = worker; id < total && ok; id += workers, ++it) {
             const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
             const int b = it & 1;
-            const int n = t.m0 + r;                        // output column
+            const int n = (PAIR ? 2 * t.mx + (int)rank : t.mx) * COLS + r;           // output column
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t lane_addr = tmem_base + (uint32_t)(b * T::ACC_COLS) + ((uint32_t)(quarter * 32) << 16);
+            uint32_t buf[2][16];                           // the loop is unrolled: both are registers
+            if (group0 * 16 < t.count) tmem_ld16(lane_addr + group0 * 16, buf[0]);
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int i = 0; i < BN / (16 * GROUP_STEP); ++i) {
+                const int c0 = (group0 + i * GROUP_STEP) * 16;
                 if (c0 >= t.count) break;                  // uniform across the warp
-                uint32_t g[16], u[16];
-                tmem_ld16(lane_addr + c0, g);
-                if (SWIGLU) tmem_ld16(lane_addr + BN + c0, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < N) {
+                uint32_t (&g)[16] = buf[i & 1];
+                const int c_next = c0 + 16 * GROUP_STEP;   // the next group is on its way while this one is written out
+                if (i + 1 < BN / (16 * GROUP_STEP) && c_next < t.count) tmem_ld16(lane_addr + c_next, buf[(i + 1) & 1]);
+                if (SWIGLU) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < t.count) {
-                            float v = __uint_as_float(g[j]);
-                            if (SWIGLU) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
-                            out[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(v);
-                        }
+                    for (int j = 0; j < 8; ++j) {
+                        // low lanes keep rows 0..7 and send their gate of rows 8..15; high lanes the other way round
+                        const uint32_t got = __shfl_xor_sync(0xffffffffu, high ? g[j] : g[8 + j], 16);
+                        const float gate = __uint_as_float(high ? got : g[j]);
+                        const float up = __uint_as_float(high ? g[8 + j] : got);
+                        const int c = c0 + j + (high ? 8 : 0);
+                        if (n < N && c < t.count) out[(size_t)(t.row0 + c) * N + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
                     }
+                } else if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < t.count) out[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(__uint_as_float(g[j]));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(b));      // this warp has read its quarter of the accumulator
+            if (lane == 0) {                               // this warp has read its part of the accumulator
+                if (PAIR) mbar_arrive_cluster(map_to_cta(acc_empty(b), 0)); else mbar_arrive(acc_empty(b));
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    // pairs: neither CTA may leave (or free tensor memory) while the other can still signal it or read through it
+    if (PAIR) cluster_sync_all(); else __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && s_abort) atomicExch(status, 1);
 }
@@ -378,28 +499,41 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
     return 0;
 }
 
-template <int BN, bool SWIGLU, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* te, const int* tr, const int* tc,
-           const int* nt, int grid_y, int R, int N, int K, int* status, cudaStream_t stream) {
-    using T = Tile<BN, SWIGLU>;
-    auto kern = gemm_tc_kernel<BN, SWIGLU, TO>;
+template <int BN, bool SWIGLU, typename TO, bool PAIR>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
+           const int* tc, const int* nt, int grid_y, int R, int N, int K, int* status, cudaStream_t stream) {
+    using T = Tile<BN, PAIR>;
+    auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
         if (e != cudaSuccess) TQ_FAIL(-1, "gemm_tc: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES, cudaGetErrorString(e));
         configured = true;
     }
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
+    // persistent CTAs (or pairs): at most what the GPU runs at once; each walks tiles w, w + workers, ...
+    static int resident = 0;
+    if (resident == 0) {
+        int dev = 0, n_sm = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        resident = n_sm * T::CTAS_PER_SM;
+        if (PAIR) {
+            // pairs share a cluster of two SMs; the GPU may not pair up every SM
+            cudaLaunchConfig_t cfg;
+            cudaLaunchAttribute attr[2];
+            tq_launch(n_sm & ~1, T::THREADS, T::SMEM_BYTES, stream, 2).config(cfg, attr);
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) == cudaSuccess && clusters > 0) resident = 2 * clusters;
+            else { cudaGetLastError(); resident = (n_sm / 2) & ~1; }
+            if (getenv("TQ_DEBUG")) fprintf(stderr, "gemm_tc pair BN=%d: clusters=%d resident=%d\n", BN, clusters, resident);
+        }
     }
-    // persistent CTAs: at most what the GPU runs at once; each walks tiles blockIdx.x, + gridDim.x, ...
-    long long tiles = (long long)((N + BM - 1) / BM) * grid_y;
-    const long long resident = (long long)n_sm * T::CTAS_PER_SM;
-    const int grid = (int)(tiles < resident ? tiles : resident);
-    tq_launch(grid, THREADS, T::SMEM_BYTES, stream)(kern, mw, mx, (TO*)out, te, tr, tc, nt, R, N, K, status);
+    constexpr int COLS = SWIGLU ? BM / 2 : BM;
+    const long long n_m1 = (N + COLS - 1) / COLS;
+    const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y;      // units of work
+    const long long want = PAIR ? 2 * tiles : tiles;
+    const int grid = (int)(want < resident ? want : resident);
+    tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K, status);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -407,37 +541,46 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, const int* t
 }  // namespace
 
 // X [R, K] bf16; W: the [G, Nw, K] weights (Nw = N, or 2N with swiglu: gate rows then up rows) PACKED into
-// [G * tiles][ceil(K/64)][128][64] blocks, zero-padded, where tiles = ceil(N/128) (plain) or 2*ceil(N/128)
-// (swiglu: the gate's tiles, then the up's); out [R, N] in bf16 or fp32.
+// [G * tiles][ceil(K/64)][128][64] blocks, zero-padded, where tiles = ceil(N/128) (plain) or ceil(N/64)
+// (swiglu: a block's rows 32q+i are the gate and 32q+16+i the up of column 64*tile+16q+i, i < 16);
+// out [R, N] in bf16 or fp32.
 // tile_* describe token tiles of at most `bn` rows that never span two groups (null: one group, tiles
-// of bn consecutive rows).  status: one int in device memory, set to 1 if a bounded wait ran out.
+// of bn consecutive rows).  pair: token tiles of 128 or 256 rows run on pairs of CTAs (cta_group::2: each
+// CTA holds 128 weight rows and half of the token rows).  status: one int in device memory, set to 1 if
+// a bounded wait ran out.
 TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
                          const int* tile_row0, const int* tile_count, const int* n_tiles, int max_tiles, int bn,
-                         int R, int N, int K, int G, int swiglu, int* status, cudaStream_t stream) {
+                         int R, int N, int K, int G, int swiglu, int pair, int* status, cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
     TQ_REQUIRE(R > 0 && N > 0 && K > 0 && G > 0, "gemm_tc: bad sizes R=%d N=%d K=%d G=%d", R, N, K, G);
     TQ_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     TQ_REQUIRE(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
-    TQ_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128, "gemm_tc: token tile %d is not one of 16, 32, 64, 128", bn);
+    TQ_REQUIRE(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", bn);
+    TQ_REQUIRE(!pair || bn >= 128, "gemm_tc: pairs of CTAs take token tiles of 128 or 256 rows, not %d", bn);
     TQ_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
-    const int grid_y = tile_expert ? max_tiles : (R + bn - 1) / bn;
-    CUtensorMap mw, mx;
-    const int n_mx = (N + BM - 1) / BM;
-    int rc = make_map_w(&mw, W, (uint64_t)((K + BK - 1) / BK), (uint64_t)G * (swiglu ? 2 * n_mx : n_mx));
-    if (rc) return rc;
-    rc = make_map_x(&mx, X, (uint64_t)K, (uint64_t)R, (uint32_t)bn);
-    if (rc) return rc;
-#define TC_CASE(BN_)                                                                                                  \
-    if (bn == BN_) {                                                                                                  \
-        if (swiglu) {                                                                                                 \
-            if (out_dtype == TQ_BF16) return launch<BN_, true, __nv_bfloat16>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
-            return launch<BN_, true, float>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
-        }                                                                                                             \
-        if (out_dtype == TQ_BF16) return launch<BN_, false, __nv_bfloat16>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
-        return launch<BN_, false, float>(mw, mx, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream); \
-    }
     TQ_REQUIRE(out_dtype == TQ_BF16 || out_dtype == TQ_F32, "gemm_tc: unknown output type %d", out_dtype);
-    TC_CASE(16) TC_CASE(32) TC_CASE(64) TC_CASE(128)
+    const int grid_y = tile_expert ? max_tiles : (R + bn - 1) / bn;
+    CUtensorMap mw, mx, mxt;
+    const int n_mx = swiglu ? (N + BM / 2 - 1) / (BM / 2) : (N + BM - 1) / BM;
+    int rc = make_map_w(&mw, W, (uint64_t)((K + BK - 1) / BK), (uint64_t)G * n_mx);
+    if (rc) return rc;
+    rc = make_map_x(&mx, X, (uint64_t)K, (uint64_t)R, (uint32_t)(bn < 64 ? bn : 64));
+    if (rc) return rc;
+    rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u);
+    if (rc) return rc;
+#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream
+#define TC_CASE(BN_, PAIR_)                                                                          \
+    if (bn == BN_ && (pair != 0) == PAIR_) {                                                         \
+        if (swiglu) {                                                                                \
+            if (out_dtype == TQ_BF16) return launch<BN_, true, __nv_bfloat16, PAIR_>(TC_ARGS);        \
+            return launch<BN_, true, float, PAIR_>(TC_ARGS);                                          \
+        }                                                                                            \
+        if (out_dtype == TQ_BF16) return launch<BN_, false, __nv_bfloat16, PAIR_>(TC_ARGS);           \
+        return launch<BN_, false, float, PAIR_>(TC_ARGS);                                             \
+    }
+    TC_CASE(16, false) TC_CASE(32, false) TC_CASE(64, false) TC_CASE(128, false) TC_CASE(256, false)
+    TC_CASE(128, true) TC_CASE(256, true)
 #undef TC_CASE
+#undef TC_ARGS
     TQ_FAIL(-2, "gemm_tc: unreachable");
 }

@@ -175,94 +175,126 @@ TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* share
 //   sorted_pair[row] = p, row_of_pair[p] = row, expert_offset[e] (E+1 entries),
 //   tiles of at most tile_rows rows that never span two experts: tile_expert, tile_row0,
 //   tile_count, and n_tiles[0].
-// Two kernels, one block per expert each: count, then fill (each block sums the counts before it).
+// Two kernels over chunks of pairs (512 or more, 256 chunks at most): per-chunk histograms, then every chunk places its pairs.
 // ---------------------------------------------------------------------------------------
-#define ALIGN_THREADS 256
-
-__global__ void moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
+// Kernel 1: histogram of each chunk of `chunk` pairs.
+__global__ void moe_chunk_hist_kernel(const int* __restrict__ ids, int P, int E, int chunk, int* __restrict__ chunk_hist) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    __shared__ int s_c[ALIGN_THREADS / 32];
-    const int e = blockIdx.x;
-    int c = 0;
-    for (int p = threadIdx.x; p < P; p += blockDim.x) c += ids[p] == e;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if (lane == 0) s_c[warp] = c;
+    extern __shared__ int s_hist[];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+    __syncthreads();
+    const int p0 = blockIdx.x * chunk, p1 = min(P, p0 + chunk);
+    for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) atomicAdd(&s_hist[ids[p]], 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_hist[(size_t)blockIdx.x * E + e] = s_hist[e];
+}
+
+// Kernel 2: every block places its chunk.  The row of a pair = rows of the experts before its expert
+// + pairs of the same expert in earlier chunks + its rank among the same expert's pairs of this chunk
+// (in pair order: the sort is stable).  Block 0 also writes the per-expert tables and the tile list.
+__global__ void moe_chunk_place_kernel(const int* __restrict__ ids, int P, int E, int tile_rows, int chunk, int n_chunks,
+                                       const int* __restrict__ chunk_hist, int* __restrict__ counts,
+                                       int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                                       int* __restrict__ expert_offset, int* __restrict__ tile_expert,
+                                       int* __restrict__ tile_row0, int* __restrict__ tile_count,
+                                       int* __restrict__ n_tiles) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ int s_mem[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* s_total = s_mem;                      // [E]   pairs of each expert
+    int* s_run = s_mem + E;                    // [E]   next row of each expert for this block
+    int* s_off = s_mem + 2 * E;                // [E+1] first row of each expert
+    int* s_toff = s_mem + 3 * E + 1;           // [E+1] first tile of each expert
+    int* s_cnt = s_mem + 4 * E + 2;            // [warps][E] pairs of each expert per warp in the current round
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int total = 0, before = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int h = chunk_hist[(size_t)c * E + e];
+            total += h;
+            if (c < (int)blockIdx.x) before += h;
+        }
+        s_total[e] = total;
+        s_run[e] = before;
+        for (int w = 0; w < warps; ++w) s_cnt[w * E + e] = 0;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int tot = 0;
-        for (int w = 0; w < ALIGN_THREADS / 32; ++w) tot += s_c[w];
-        counts[e] = tot;
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            s_off[e] = rows;
+            s_toff[e] = tiles;
+            rows += s_total[e];
+            tiles += (s_total[e] + tile_rows - 1) / tile_rows;
+        }
+        s_off[E] = rows;
+        s_toff[E] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_run[e] += s_off[e];
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+            expert_offset[e] = s_off[e];
+            if (e < E) {
+                counts[e] = s_total[e];
+                // an expert's rows are split evenly over its tiles (136 rows in tiles of 128: 68 + 68, not 128 + 8)
+                const int nt = (s_total[e] + tile_rows - 1) / tile_rows;
+                for (int i = 0, t = s_toff[e]; i < nt; ++i, ++t) {
+                    const int r0 = (int)((long long)s_total[e] * i / nt), r1 = (int)((long long)s_total[e] * (i + 1) / nt);
+                    tile_expert[t] = e;
+                    tile_row0[t] = s_off[e] + r0;
+                    tile_count[t] = r1 - r0;
+                }
+            }
+        }
+        if (threadIdx.x == 0) n_tiles[0] = s_toff[E];
+    }
+    __syncthreads();
+    const int p0 = blockIdx.x * chunk, p1 = min(P, p0 + chunk);
+    for (int r0 = p0; r0 < p1; r0 += blockDim.x) {
+        const int p = r0 + threadIdx.x;
+        const int e = p < p1 ? ids[p] : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, e);        // lanes of this warp with the same expert
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const bool leader = rank == 0 && e >= 0;
+        if (leader) s_cnt[warp * E + e] = __popc(peers);
+        __syncthreads();
+        if (e >= 0) {
+            int row = s_run[e] + rank;
+            for (int w = 0; w < warp; ++w) row += s_cnt[w * E + e];
+            sorted_pair[row] = p;
+            row_of_pair[p] = row;
+        }
+        __syncthreads();
+        if (leader) {
+            atomicAdd(&s_run[e], __popc(peers));
+            s_cnt[warp * E + e] = 0;
+        }
+        __syncthreads();
     }
 }
 
-__global__ void moe_fill_kernel(const int* __restrict__ ids, int P, int E, int tile_rows,
-                                const int* __restrict__ counts, int* __restrict__ sorted_pair,
-                                int* __restrict__ row_of_pair, int* __restrict__ expert_offset,
-                                int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                int* __restrict__ tile_count, int* __restrict__ n_tiles) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    __shared__ int s_warp[ALIGN_THREADS / 32];
-    __shared__ int s_base, s_row0, s_tile0;
-    const int e = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) {
-        int row0 = 0, tile0 = 0;
-        for (int i = 0; i < e; ++i) {
-            row0 += counts[i];
-            tile0 += (counts[i] + tile_rows - 1) / tile_rows;
-        }
-        s_row0 = row0;
-        s_tile0 = tile0;
-        s_base = 0;
-        expert_offset[e] = row0;
-        if (e == E - 1) expert_offset[E] = row0 + counts[e];
-    }
-    __syncthreads();
-    const int row0 = s_row0;
-    for (int p0 = 0; p0 < P; p0 += ALIGN_THREADS) {
-        const int p = p0 + threadIdx.x;
-        const bool mine = p < P && ids[p] == e;
-        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-        if (lane == 0) s_warp[warp] = __popc(ballot);
-        __syncthreads();
-        int before = 0;
-        for (int w = 0; w < warp; ++w) before += s_warp[w];
-        const int rank = s_base + before + __popc(ballot & ((1u << lane) - 1u));
-        if (mine) {
-            sorted_pair[row0 + rank] = p;
-            row_of_pair[p] = row0 + rank;
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < ALIGN_THREADS / 32; ++w) tot += s_warp[w];
-            s_base += tot;
-        }
-        __syncthreads();
-    }
-    const int count = counts[e];
-    const int my_tiles = (count + tile_rows - 1) / tile_rows;
-    for (int i = threadIdx.x; i < my_tiles; i += blockDim.x) {
-        tile_expert[s_tile0 + i] = e;
-        tile_row0[s_tile0 + i] = row0 + i * tile_rows;
-        tile_count[s_tile0 + i] = min(tile_rows, count - i * tile_rows);
-    }
-    if (e == E - 1 && threadIdx.x == 0) n_tiles[0] = s_tile0 + my_tiles;
-}
-
-TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int* counts, int* sorted_pair,
+// chunk: pairs per block; chunk_hist: ceil(P / chunk) * E ints of scratch.
+TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int chunk, int* chunk_hist, int* counts, int* sorted_pair,
                            int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0,
                            int* tile_count, int* n_tiles, cudaStream_t stream) {
     TQ_REQUIRE(P >= 0 && E >= 1 && tile_rows >= 1, "moe_align: bad sizes P=%d E=%d tile_rows=%d", P, E, tile_rows);
-    tq_launch(E, ALIGN_THREADS, 0, stream)(moe_count_kernel, ids, P, counts);
-    TQ_CHECK_LAUNCH("moe_count");
-    tq_launch(E, ALIGN_THREADS, 0, stream)(moe_fill_kernel, ids, P, E, tile_rows, counts, sorted_pair, row_of_pair,
-                                                     expert_offset, tile_expert, tile_row0, tile_count, n_tiles);
-    TQ_CHECK_LAUNCH("moe_fill");
+    TQ_REQUIRE(E <= ROUTER_MAX_EXPERTS, "moe_align: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
+    TQ_REQUIRE(chunk >= 1 && chunk_hist != nullptr, "moe_align: a chunk size and scratch for the chunk histograms are required");
+    const int n_chunks = P > 0 ? (P + chunk - 1) / chunk : 1;
+    const int threads = E <= 1024 ? 256 : 64;                     // [warps][E] counters must fit shared memory
+    tq_launch(n_chunks, threads, (size_t)E * sizeof(int), stream)(moe_chunk_hist_kernel, ids, P, E, chunk, chunk_hist);
+    TQ_CHECK_LAUNCH("moe_chunk_hist");
+    const size_t smem = (size_t)(4 * E + 2 + (threads / 32) * E) * sizeof(int);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_chunk_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TQ_REQUIRE(e == cudaSuccess, "moe_align: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    }
+    tq_launch(n_chunks, threads, smem, stream)(moe_chunk_place_kernel, ids, P, E, tile_rows, chunk, n_chunks, chunk_hist, counts,
+                                               sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0, tile_count,
+                                               n_tiles);
+    TQ_CHECK_LAUNCH("moe_chunk_place");
     return 0;
 }
 
@@ -353,11 +385,12 @@ router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, floa
         row_of_pair[p] = row;
     }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const int c = s_count[e];
-        for (int i = 0; i * tile_rows < c; ++i) {
+        const int c = s_count[e], nt = (c + tile_rows - 1) / tile_rows;
+        for (int i = 0; i < nt; ++i) {                        // an expert's rows split evenly over its tiles
+            const int r0 = (int)((long long)c * i / nt), r1 = (int)((long long)c * (i + 1) / nt);
             tile_expert[s_toff[e] + i] = e;
-            tile_row0[s_toff[e] + i] = s_off[e] + i * tile_rows;
-            tile_count[s_toff[e] + i] = min(tile_rows, c - i * tile_rows);
+            tile_row0[s_toff[e] + i] = s_off[e] + r0;
+            tile_count[s_toff[e] + i] = r1 - r0;
         }
     }
     __syncthreads();

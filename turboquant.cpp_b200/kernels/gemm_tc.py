@@ -1,6 +1,7 @@
 """Grouped bf16 GEMM on tcgen05 tensor cores (csrc/gemm_tc.cu): the experts' products."""
 from __future__ import annotations
 
+import os
 from ctypes import c_int
 from typing import Dict, Optional
 
@@ -11,7 +12,7 @@ from ._call import KernelError, check, code, ptr, stream
 from .moe import ExpertLayout
 
 _LIB = "gemm_tc"
-TOKEN_TILES = (16, 32, 64, 128)
+TOKEN_TILES = (16, 32, 64, 128, 256)
 _status: Dict[int, torch.Tensor] = {}
 
 
@@ -38,7 +39,9 @@ BLOCK_ROWS, BLOCK_K = 128, 64
 
 class PackedWeights:
     """Weights [G, Nw, K] re-laid for the tensor-core kernel: [G * tiles, ceil(K/64), 128, 64] bf16, every
-    [128 x 64] block contiguous and zero-padded; with swiglu the gate's tiles come first, then the up's."""
+    [128 x 64] block contiguous and zero-padded.  Plain: a block holds 128 rows.  With swiglu a block holds
+    the gate rows and the up rows of 64 output columns, interleaved in runs of 16: block row 32q+i is the gate
+    and 32q+16+i the up of column 64*tile + 16q + i (q < 4, i < 16)."""
 
     def __init__(self, data: torch.Tensor, groups: int, n: int, k: int, swiglu: bool):
         self.data, self.groups, self.n, self.k, self.swiglu = data, groups, n, k, swiglu
@@ -64,15 +67,21 @@ def pack_weights(w: torch.Tensor, swiglu: bool) -> PackedWeights:
         raise KernelError("gemm_tc: weights must be bfloat16 with K a multiple of 8")
     G, Nw, K = w.shape
     N = Nw // 2 if swiglu else Nw
-    n_t, n_k = -(-N // BLOCK_ROWS), -(-K // BLOCK_K)
-    parts = [w[:, :N], w[:, N:]] if swiglu else [w]
-    out = torch.zeros((G, len(parts) * n_t, n_k, BLOCK_ROWS, BLOCK_K), dtype=w.dtype, device=w.device)
-    for i, part in enumerate(parts):
-        padded = torch.zeros((G, n_t * BLOCK_ROWS, n_k * BLOCK_K), dtype=w.dtype, device=w.device)
-        padded[:, :N, :K] = part
-        out[:, i * n_t:(i + 1) * n_t] = padded.view(G, n_t, BLOCK_ROWS, n_k, BLOCK_K).permute(0, 1, 3, 2, 4)
-        del padded
-    return PackedWeights(out.view(G * len(parts) * n_t, n_k, BLOCK_ROWS, BLOCK_K), G, N, K, swiglu)
+    cols = BLOCK_ROWS // 2 if swiglu else BLOCK_ROWS            # output columns of a block
+    n_t, n_k = -(-N // cols), -(-K // BLOCK_K)
+    rows = torch.zeros((G, n_t, BLOCK_ROWS, n_k * BLOCK_K), dtype=w.dtype, device=w.device)
+    if swiglu:
+        both = torch.zeros((G, 2, n_t * cols, K), dtype=w.dtype, device=w.device)
+        both[:, 0, :N] = w[:, :N]
+        both[:, 1, :N] = w[:, N:]
+        # [G, half, tile, q, i, K] -> [G, tile, q, half, i, K]
+        rows.view(G, n_t, 4, 2, 16, n_k * BLOCK_K)[..., :K] = both.view(G, 2, n_t, 4, 16, K).permute(0, 2, 3, 1, 4, 5)
+        del both
+    else:
+        rows.view(G, n_t * BLOCK_ROWS, n_k * BLOCK_K)[:, :N, :K] = w
+    out = rows.view(G, n_t, BLOCK_ROWS, n_k, BLOCK_K).permute(0, 1, 3, 2, 4).contiguous()
+    del rows
+    return PackedWeights(out.view(G * n_t, n_k, BLOCK_ROWS, BLOCK_K), G, N, K, swiglu)
 
 
 def usable(x: torch.Tensor, w) -> bool:
@@ -90,10 +99,17 @@ def token_tile_for(rows: int, groups: int) -> int:
     return TOKEN_TILES[-1]
 
 
+PAIR_MIN_TILE = 128      # token tiles from this width on run on pairs of CTAs (cta_group::2)
+_NO_PAIRS = os.environ.get("TQ_NO_PAIRS", "") not in ("", "0")
+
+
 def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
-            token_tile: int) -> torch.Tensor:
+            token_tile: int, pair: Optional[bool] = None) -> torch.Tensor:
     """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
-    silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group)."""
+    silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group).
+    pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1)."""
+    if pair is None:
+        pair = token_tile >= PAIR_MIN_TILE and not _NO_PAIRS
     if not usable(x, w):
         raise KernelError("gemm_tc: needs bfloat16 activations with K a multiple of 8 and weights packed for this K")
     R, K = x.shape
@@ -110,5 +126,6 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         ptr(x), ptr(w.data), ptr(out), c_int(code(out.dtype)),
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None, ptr(lo.tile_count) if lo else None,
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
-        c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), ptr(status_word(x.device)), stream()))
+        c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
+        ptr(status_word(x.device)), stream()))
     return out

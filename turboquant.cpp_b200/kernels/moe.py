@@ -13,6 +13,11 @@ _LIB = "moe"
 TILE_ROWS = 64     # rows of a tile of the exact grouped GEMM
 
 
+def align_chunk(n_pairs: int) -> int:
+    """Pairs per block of the layout kernels: 512 or more, and 256 chunks at most."""
+    return max(512, 256 * -(-n_pairs // (256 * 256)))
+
+
 def router_topk(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top_k: int,
                 renorm: bool, ids: torch.Tensor, weights: torch.Tensor,
                 shared_scale: Optional[torch.Tensor]) -> None:
@@ -64,6 +69,7 @@ class ExpertLayout:
         self.tile_row0 = torch.empty(self.max_tiles, **i32)
         self.tile_count = torch.empty(self.max_tiles, **i32)
         self.n_tiles = torch.empty(1, **i32)
+        self.chunk_hist = torch.empty(-(-max(1, n_pairs) // align_chunk(n_pairs)) * n_experts, **i32)     # scratch of moe_align
 
 
 SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS = 512, 1024      # what the kernel accepts
@@ -106,7 +112,7 @@ def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:
     P = ids.numel()
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_moe_align(ptr(ids), c_int(P), c_int(layout.n_experts), c_int(layout.tile_rows),
-                                 ptr(layout.counts), ptr(layout.sorted_pair), ptr(layout.row_of_pair),
+                                 c_int(align_chunk(layout.n_pairs)), ptr(layout.chunk_hist), ptr(layout.counts), ptr(layout.sorted_pair), ptr(layout.row_of_pair),
                                  ptr(layout.expert_offset), ptr(layout.tile_expert), ptr(layout.tile_row0),
                                  ptr(layout.tile_count), ptr(layout.n_tiles), stream()), kernels=2)
 
