@@ -24,9 +24,13 @@
 // a narrow N.
 //
 // Persistent CTAs (one or two per SM) each walk a strided list of (weight-row tile, token tile)
-// pairs.  Warp 0 issues TMA loads as one uninterrupted stream of k-blocks across tiles, warp 1 owns
-// the tensor memory and issues tcgen05.mma into one of two accumulators, warps 2..5 read the other
-// accumulator back (tcgen05.ld), apply the epilogue and store while the next tile is multiplied.  All waits on mbarriers are bounded: a wait that runs out sets a flag, every
+// pairs.  Warp 0 issues the TMA loads of the weight blocks as one uninterrupted stream of k-blocks
+// across tiles and warp 2 those of the token blocks (two rings of different depth), warp 1 owns
+// the tensor memory and issues tcgen05.mma into one of two accumulators, warps 3.. read the other
+// accumulator back (tcgen05.ld), apply the epilogue and store while the next tile is multiplied.
+// Token tiles of 128 or 256 rows run on pairs of CTAs (cta_group::2): each CTA holds 128 weight rows
+// and half of the token rows, the first CTA issues the products for both.
+// All waits on mbarriers are bounded: a wait that runs out sets a flag, every
 // role leaves its loop, copies in flight are waited for (bounded again), tensor memory is freed and
 // the kernel returns with *status != 0; nothing spins forever.
 #include <cuda.h>
@@ -84,16 +88,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+// L2 policies: weights of a prompt's or a step's experts are read once (evict first), token rows are read by
+// every weight-row tile of their expert (evict last), so the weight stream does not push them out of the L2.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
 }
 // one [128 rows x 64 elements] block of the packed weights: (k-block, tile) select the block
-__device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t bar) {
+__device__ __forceinline__ void tma_load_block(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t bar, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(0), "r"(0), "r"(kb), "r"(tile) : "memory");
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(0), "r"(0), "r"(kb), "r"(tile), "l"(policy) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
@@ -144,15 +160,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // loads of a CTA pair: the data lands in this CTA, the bytes are counted on the barrier of the pair's first CTA
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy) : "memory");
 }
-__device__ __forceinline__ void tma_load_block_pair(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t cluster_bar) {
+__device__ __forceinline__ void tma_load_block_pair(uint32_t dst, const CUtensorMap* map, int kb, int tile, uint32_t cluster_bar, uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(0), "r"(0), "r"(kb), "r"(tile) : "memory");
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(dst), "l"((uint64_t)map), "r"(cluster_bar), "r"(0), "r"(0), "r"(kb), "r"(tile), "l"(policy) : "memory");
 }
 // one product of the pair: M = 256 (128 weight rows from each CTA), the token rows half from each CTA
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
@@ -185,23 +201,31 @@ struct Tile {
     static constexpr int BOX_ROWS = B_ROWS < 64 ? B_ROWS : 64;   // token rows of one TMA box; the tail comes in boxes of 16
     static constexpr int BOX_BYTES = BOX_ROWS * BK * 2;
     static constexpr int TAIL_ROWS = 16, TAIL_BYTES = TAIL_ROWS * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+
     // narrow token tiles (decoding) leave room for two CTAs per SM: one CTA's start-up and epilogue
     // overlap the other's weight stream; wide tiles take the whole SM
     static constexpr int CTAS_PER_SM = BN <= 32 ? 2 : 1;
-    static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
-    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+    static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 208) * 1024;
+    // Two rings: weight blocks (16 KiB each) and token blocks.  Narrow token tiles: equally deep.  Wide ones:
+    // the token blocks come from the L2 and a few slots cover its latency, while the weights of a prompt's
+    // routed experts are read once from DRAM, whose latency under load (microseconds) needs as many
+    // blocks in flight as fit; their loads run ahead of the token blocks' by the difference in depth.
+    static constexpr int B_SLOTS = BN <= 64 ? ((BUDGET / (A_BYTES + B_BYTES)) > 8 ? 8 : BUDGET / (A_BYTES + B_BYTES))
+                                            : (B_BYTES > 16 * 1024 ? 3 : 6);
+    static constexpr int A_SLOTS = BN <= 64 ? B_SLOTS
+                                            : ((BUDGET - B_SLOTS * B_BYTES) / A_BYTES > 12 ? 12 : (BUDGET - B_SLOTS * B_BYTES) / A_BYTES);
     // epilogue warps: one per quarter of the accumulator's lanes, two for wide tiles (each takes every other
     // group of 16 token rows), so that reading a tile back never takes longer than multiplying the next
     static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;
-    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int THREADS = 96 + 32 * EPI_WARPS;        // two producers, the MMA issuer, the epilogue
     static constexpr int ACC_COLS = BN;
     // two accumulators in tensor memory: a tile's epilogue overlaps the next tile's products
     static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : (2 * ACC_COLS <= 64 ? 64 : (2 * ACC_COLS <= 128 ? 128 : (2 * ACC_COLS <= 256 ? 256 : 512)));
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SMEM_BYTES = A_SLOTS * A_BYTES + B_SLOTS * B_BYTES + 1024 /* alignment slack */ + 512 /* barriers */;
     static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "token tile must be 16..256 in steps of 16");
     static_assert(!PAIR || BN >= 128, "pairs are for wide token tiles");
-    static_assert(STAGES >= 2, "pipeline needs at least two stages");
+    static_assert(B_SLOTS >= 2 && A_SLOTS >= B_SLOTS, "pipeline needs at least two stages");
+    static_assert((2 * A_SLOTS + 4) * 8 <= 512, "barriers");
     static_assert(TMEM_COLS * CTAS_PER_SM <= 512, "tensor memory holds 512 columns per SM");
 };
 
@@ -265,19 +289,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int num_kb = (K + BK - 1) / BK;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
-    const uint32_t bars = base + T::STAGES * T::STAGE_BYTES;         // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    constexpr int SA = T::A_SLOTS, SB = T::B_SLOTS;
+    // One pair of barriers per k-block in flight (SA of them): `full` hears of the weight block and of the
+    // token block (two arrivals and their bytes), `done` of the products that read them.  Block i uses weight
+    // slot i % SA and token slot i % SB.
+    const uint32_t bars = base + SA * T::A_BYTES + SB * T::B_BYTES;  // full[SA], done[SA], acc_full[2], acc_empty[2]
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (T::STAGES + s); };
-    auto acc_full = [&](int b) { return bars + 8u * (2 * T::STAGES + b); };
-    auto acc_empty = [&](int b) { return bars + 8u * (2 * T::STAGES + 2 + b); };
-    auto a_tile = [&](int s) { return base + s * T::STAGE_BYTES; };
-    auto b_tile = [&](int s) { return base + s * T::STAGE_BYTES + T::A_BYTES; };
+    auto done_bar = [&](int s) { return bars + 8u * (SA + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (2 * SA + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * SA + 2 + b); };
+    auto a_tile = [&](int s) { return base + s * T::A_BYTES; };
+    auto b_tile = [&](int s) { return base + SA * T::A_BYTES + s * T::B_BYTES; };
 
     if (threadIdx.x == 0) {
         s_abort = 0;
         // pairs: the stage barriers that count bytes (of both CTAs' loads) and the accumulator-drained barriers
         // live in the first CTA; the others are signalled in both CTAs at once by the products' commits
-        for (int s = 0; s < T::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < SA; ++s) { mbar_init(full_bar(s), 2); mbar_init(done_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), (PAIR ? 2 : 1) * T::EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -300,10 +328,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tq_grid_launch_dependents();
     const uint32_t tmem_base = s_tmem_base;
 
+    // The two producers are one thread each and their loops are kept to a few instructions per block: a single
+    // thread runs one dependent instruction every few cycles, and a block lasts only some hundred cycles.
     if (warp == 0) {
-        // ---------------- TMA producer: one stream of k-blocks across all of this CTA's tiles ----------------
+        // ---------------- weight blocks: one stream of k-blocks across all of this CTA's tiles ----------------
         if (lane == 0) {
-            int issued = 0;          // k-blocks issued so far (stage = issued % STAGES)
+            // one group's weights are read by every token tile (keep them); several groups' are streamed once
+            const uint64_t policy = tile_expert ? policy_evict_first() : policy_evict_last();
+            int slot = 0, issued = 0;
+            uint32_t phase = 0;      // parity of the slot's current use
+            bool ok = true;
+            for (int id = worker; id < total && ok; id += workers) {
+                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    // the slot is free once the products of the block SA before this one are done
+                    if (!mbar_wait(done_bar(slot), phase ^ 1u, &s_abort)) { ok = false; break; }
+                    if (PAIR) {
+                        // the first CTA expects the bytes of both (the halves are equal); the second only loads
+                        if (rank == 0) mbar_expect_tx(full_bar(slot), 2u * T::A_BYTES);
+                        tma_load_block_pair(a_tile(slot), &map_w, kb, wt, rank == 0 ? full_bar(slot) : map_to_cta(full_bar(slot), 0), policy);
+                    } else {
+                        mbar_expect_tx(full_bar(slot), (uint32_t)T::A_BYTES);
+                        tma_load_block(a_tile(slot), &map_w, kb, wt, full_bar(slot), policy);
+                    }
+                    ++issued;
+                    if (++slot == SA) { slot = 0; phase ^= 1u; }
+                }
+            }
+            if (s_abort && rank == 0) {
+                // wait (bounded) for the copies this thread started, so none lands after the CTA is gone
+                // (a block whose token half was never issued stays incomplete: that wait runs out)
+                for (int j = issued > SA ? issued - SA : 0; j < issued; ++j)
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(full_bar(j % SA), (uint32_t)(j / SA) & 1u); ++i) {}
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- token blocks: block i goes to token slot i % SB and reports to full[i % SA] ----------------
+        if (lane == 0) {
+            const uint64_t policy = policy_evict_last();
+            int slot = 0, fb = 0, issued = 0;
+            int freed = 0;           // done[] index of the block SB before this one ...
+            uint32_t freed_phase = 0;   // ... and the parity of that block's use of it
             bool ok = true;
             for (int id = worker; id < total && ok; id += workers) {
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
@@ -312,47 +378,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int row0 = t.row0 + (PAIR ? (int)rank * (n_mma / 2) : 0);           // ... from here
                 const int boxes = rows / T::BOX_ROWS;
                 const int tails = (rows - boxes * T::BOX_ROWS + T::TAIL_ROWS - 1) / T::TAIL_ROWS;
-                const uint32_t bytes = (uint32_t)(T::A_BYTES + boxes * T::BOX_BYTES + tails * T::TAIL_BYTES);
-                const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
+                const uint32_t bytes = (uint32_t)(boxes * T::BOX_BYTES + tails * T::TAIL_BYTES);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    const int s = issued % T::STAGES;
-                    const uint32_t ph = (uint32_t)(issued / T::STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) { ok = false; break; }
+                    if (issued >= SB) {
+                        if (!mbar_wait(done_bar(freed), freed_phase, &s_abort)) { ok = false; break; }
+                        if (++freed == SA) { freed = 0; freed_phase ^= 1u; }
+                    }
+                    const uint32_t dst = b_tile(slot);
                     if (PAIR) {
-                        // the first CTA expects the bytes of both (the halves are equal); the second only loads
-                        const uint32_t bar = rank == 0 ? full_bar(s) : map_to_cta(full_bar(s), 0);
-                        if (rank == 0) mbar_expect_tx(full_bar(s), 2u * bytes);
-                        tma_load_block_pair(a_tile(s), &map_w, kb, wt, bar);
+                        const uint32_t bar = rank == 0 ? full_bar(fb) : map_to_cta(full_bar(fb), 0);
+                        if (rank == 0) mbar_expect_tx(full_bar(fb), 2u * bytes);
                         for (int bx = 0; bx < boxes; ++bx)
-                            tma_load_2d_pair(b_tile(s) + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, bar);
+                            tma_load_2d_pair(dst + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, bar, policy);
                         for (int bx = 0; bx < tails; ++bx)
-                            tma_load_2d_pair(b_tile(s) + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
-                                             row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, bar);
+                            tma_load_2d_pair(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                                             row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, bar, policy);
                     } else {
-                        mbar_expect_tx(full_bar(s), bytes);
-                        tma_load_block(a_tile(s), &map_w, kb, wt, full_bar(s));
+                        mbar_expect_tx(full_bar(fb), bytes);
                         for (int bx = 0; bx < boxes; ++bx)
-                            tma_load_2d(b_tile(s) + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, full_bar(s));
+                            tma_load_2d(dst + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, full_bar(fb), policy);
                         for (int bx = 0; bx < tails; ++bx)
-                            tma_load_2d(b_tile(s) + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
-                                        row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, full_bar(s));
+                            tma_load_2d(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                                        row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, full_bar(fb), policy);
                     }
                     ++issued;
-                }
-            }
-            if (s_abort && rank == 0) {
-                // wait (bounded) for the copies this thread started, so none lands after the CTA is gone
-                const int first = issued > T::STAGES ? issued - T::STAGES : 0;
-                for (int j = first; j < issued; ++j) {
-                    const uint32_t bar = full_bar(j % T::STAGES), ph = (uint32_t)(j / T::STAGES) & 1u;
-                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(bar, ph); ++i) {}
+                    if (++slot == SB) slot = 0;
+                    if (++fb == SA) fb = 0;
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (the pair's first CTA issues for both) ----------------
         if (lane == 0 && rank == 0) {
-            int consumed = 0, it = 0;
+            int sa = 0, sb = 0, it = 0;      // weight slot (and barrier) and token slot of the next block
+            uint32_t phase = 0;
             bool ok = true;
             for (int id = worker; id < total && ok; id += workers, ++it) {
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
@@ -365,29 +424,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    const int s = consumed % T::STAGES;
-                    const uint32_t ph = (uint32_t)(consumed / T::STAGES) & 1u;
-                    ok = mbar_wait(full_bar(s), ph, &s_abort);
+                    ok = mbar_wait(full_bar(sa), phase, &s_abort);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-                        const uint64_t ad = umma_desc(a_tile(s) + k * UMMA_K * 2), bd = umma_desc(b_tile(s) + k * UMMA_K * 2);
+                        const uint64_t ad = umma_desc(a_tile(sa) + k * UMMA_K * 2), bd = umma_desc(b_tile(sb) + k * UMMA_K * 2);
                         if (PAIR) umma_pair(acc, ad, bd, idesc, accum); else umma(acc, ad, bd, idesc, accum);
                     }
-                    // the stage is free (in both CTAs) once these MMAs have read it
-                    if (PAIR) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
-                    ++consumed;
+                    // the slots are free (in both CTAs) once these MMAs have read them
+                    if (PAIR) umma_commit_pair(done_bar(sa)); else umma_commit(done_bar(sa));
+                    if (++sa == SA) { sa = 0; phase ^= 1u; }
+                    if (++sb == SB) sb = 0;
                 }
                 // this tile's accumulator is complete once all MMAs are done
                 if (ok) { if (PAIR) umma_commit_pair(acc_full(b)); else umma_commit(acc_full(b)); }
             }
         }
     } else {
-        // ---------------- epilogue: warps 2.., TMEM lane quarter = warp % 4 ----------------
+        // ---------------- epilogue: warps 3.., TMEM lane quarter = warp % 4 ----------------
         const int quarter = warp & 3;
-        const int group0 = (warp - 2) >> 2;                // wide tiles: which groups of 16 token rows (even or odd)
+        const int group0 = (warp - 3) >> 2;                // wide tiles: which groups of 16 token rows (even or odd)
         constexpr int GROUP_STEP = T::EPI_WARPS / 4;
         // plain: lane = weight row = output column.  SwiGLU: lanes 0..15 hold the gate of 16 columns, lanes
         // 16..31 the up of the same columns; after the exchange the low half writes token rows 0..7 of each
