@@ -458,14 +458,14 @@ def test_sample_rows_distribution():
                                                     (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype):
-    """The two-launch decode path (logits, then one block for selection, layout and gathered rows)
-    gives exactly what the separate kernels give."""
+    """The one-launch decode path (a block per token for logits and selection; the block that finishes last
+    does the layout and the gathered rows) gives exactly what the separate kernels give, call after call."""
     from turboquant_cpp_b200.kernels import elementwise as KE, moe as KM
     rng = np.random.default_rng(T + E)
     x = dev(bf16_values(rng.normal(size=(T, H))), dtype)
     wr = dev(bf16_values(rng.normal(size=(E, H)) * 0.3), dtype)
     wsg = dev(bf16_values(rng.normal(size=(1, H)) * 0.3), dtype) if shared else None
-    assert KM.router_small_usable(T, k, E)
+    assert KM.router_small_usable(T, k, E, H)
 
     def buffers():
         return (torch.empty((T, k), dtype=torch.int32, device=DEV), torch.empty((T, k), dtype=torch.float32, device=DEV),
@@ -475,8 +475,10 @@ def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dt
     KM.router_topk(x, wr, wsg, k, renorm, ids1, w1, s1)
     KM.moe_align(ids1, lay1)
     KE.gather_rows(x, lay1.sorted_pair, k, rows1)
-    ids2, w2, s2, lay2, rows2 = buffers()
-    KM.router_small(x, wr, wsg, k, renorm, ids2, w2, s2, lay2, rows2)
+    for _ in range(3):                      # the counter that finds the last block is left ready for the next launch
+        ids2, w2, s2, lay2, rows2 = buffers()
+        rows2.fill_(float("nan"))
+        KM.router_small(x, wr, wsg, k, renorm, ids2, w2, s2, lay2, rows2)
     assert torch.equal(ids1, ids2) and torch.equal(w1, w2) and torch.equal(rows1, rows2)
     if shared:
         assert torch.equal(s1, s2)

@@ -299,31 +299,59 @@ TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int chun
 }
 
 // ---------------------------------------------------------------------------------------
-// Steps with few tokens (decoding): everything between the router logits and the expert products in
-// ONE block — selection, counts, offsets, stable placement, tile list and the expert-sorted copies of
-// the token rows — instead of four launches that each do microseconds of work.
+// Steps with few tokens (decoding): router logits, selection, expert-sorted layout, tile list and the
+// expert-sorted copies of the token rows in ONE launch instead of six that each do microseconds of
+// work.  One block per token computes that token's logits (its row staged in shared memory) and its
+// choices; the block that finishes last (a counter in global memory) lays out all pairs and copies the
+// rows.  The counter is zero between launches: the last block resets it.  Launches that share a counter
+// must not overlap.
 // ---------------------------------------------------------------------------------------
 #define SMALL_MAX_PAIRS 512
 #define SMALL_MAX_EXPERTS 1024
 #define SMALL_THREADS 1024
 
-template <typename TA>
+template <typename TA, typename TW>
 __global__ void __launch_bounds__(SMALL_THREADS)
-router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
-                         float* __restrict__ shared_scale, int T_, int E, int k, int renorm, int tile_rows,
-                         int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
-                         int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                         int* __restrict__ tile_count, int* __restrict__ n_tiles, const TA* __restrict__ x,
-                         TA* __restrict__ x_rows, int H, int vec) {
+router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
+                    int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_scale,
+                    int T_, int H, int E, int k, int renorm, int vec_w, int tile_rows,
+                    int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                    int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                    int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x,
+                    int* __restrict__ counter) {
     tq_grid_wait();
     tq_grid_launch_dependents();
+    extern __shared__ float s_dyn[];
+    float* s_x = s_dyn;               // [H] the token's row
+    float* s_logit = s_dyn + H;       // [E + 1] router logits, then the shared expert's gate logit
     __shared__ int s_ids[SMALL_MAX_PAIRS], s_row[SMALL_MAX_PAIRS];
     __shared__ int s_count[SMALL_MAX_EXPERTS], s_off[SMALL_MAX_EXPERTS + 1], s_toff[SMALL_MAX_EXPERTS + 1];
+    __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int P = T_ * k;
-    // selection: one warp per token (the same steps as router_select_kernel)
-    for (int t = warp; t < T_; t += nwarps) {
-        float* s_logit = logits + (size_t)t * (E + 1);
+    const int t = blockIdx.x;
+    const TA* xr = x + (size_t)t * H;
+    // ---- this token's logits (the same sums, in the same order, as router_logits_kernel) ----
+    for (int i = threadIdx.x; i < H; i += blockDim.x) s_x[i] = tq_to_float(xr[i]);
+    __syncthreads();
+    const int rows = E + (wsg ? 1 : 0);
+    const int Hv = vec_w ? (H / 8) * 8 : 0;
+    for (int e = warp; e < rows; e += nwarps) {
+        const TW* w = e < E ? wr + (size_t)e * H : wsg;
+        float s = 0.f;
+#pragma unroll 4
+        for (int i = lane * 8; i < Hv; i += 256) {
+            float f[8];
+            RowVec<TW>::load(w + i, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s = fmaf(s_x[i + j], f[j], s);
+        }
+        for (int i = Hv + lane; i < H; i += 32) s = fmaf(s_x[i], tq_to_float(w[i]), s);
+        s = tq_warp_sum(s);
+        if (lane == 0) s_logit[e] = s;
+    }
+    __syncthreads();
+    // ---- selection: warp 0 (the same steps as router_select_kernel) ----
+    if (warp == 0) {
         if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
@@ -350,7 +378,6 @@ router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, floa
             picked_sum += p;
             if (lane == 0) {
                 ids[(size_t)t * k + j] = best_e;
-                s_ids[t * k + j] = best_e;
                 wts[(size_t)t * k + j] = p;
                 s_logit[best_e] = -INFINITY;
             }
@@ -360,19 +387,52 @@ router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, floa
             __syncwarp();
             for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
         }
+        __threadfence();                                      // this token's choices are visible before the count
+        __syncwarp();
+        if (lane == 0) s_last = atomicAdd(counter, 1) == T_ - 1;
     }
+    __syncthreads();
+    if (!s_last) return;
+    // ---- the last block: layout of all pairs, tile list, expert-sorted copies of the rows ----
+    __threadfence();
+    const int P = T_ * k;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) s_ids[p] = __ldcg(ids + p);
     for (int e = threadIdx.x; e < E; e += blockDim.x) s_count[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&s_count[s_ids[p]], 1);
     __syncthreads();
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) {      // offsets of rows and of tiles before expert e
-        int rows = 0, tiles = 0;
-        for (int i = 0; i < e; ++i) { rows += s_count[i]; tiles += (s_count[i] + tile_rows - 1) / tile_rows; }
-        s_off[e] = rows;
-        s_toff[e] = tiles;
-        expert_offset[e] = rows;
-        if (e < E) counts[e] = s_count[e];
-        if (e == E) n_tiles[0] = tiles;
+    {   // offsets of rows and of tiles before expert e: a scan over the experts (E <= blockDim.x = 1024)
+        __shared__ int s_wrows[32], s_wtiles[32];
+        const int e = threadIdx.x;
+        const int c = e < E ? s_count[e] : 0, tl = (c + tile_rows - 1) / tile_rows;
+        int r_incl = c, t_incl = tl;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, r_incl, o), u = __shfl_up_sync(0xffffffffu, t_incl, o);
+            if (lane >= o) { r_incl += r; t_incl += u; }
+        }
+        if (lane == 31) { s_wrows[warp] = r_incl; s_wtiles[warp] = t_incl; }
+        __syncthreads();
+        if (warp == 0) {
+            int r = lane < nwarps ? s_wrows[lane] : 0, u = lane < nwarps ? s_wtiles[lane] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int r2 = __shfl_up_sync(0xffffffffu, r, o), u2 = __shfl_up_sync(0xffffffffu, u, o);
+                if (lane >= o) { r += r2; u += u2; }
+            }
+            s_wrows[lane] = r;                                // inclusive over warps
+            s_wtiles[lane] = u;
+        }
+        __syncthreads();
+        const int r_before = (warp > 0 ? s_wrows[warp - 1] : 0) + r_incl - c;
+        const int t_before = (warp > 0 ? s_wtiles[warp - 1] : 0) + t_incl - tl;
+        if (e <= E) {
+            s_off[e] = r_before;
+            s_toff[e] = t_before;
+            expert_offset[e] = r_before;
+            if (e < E) counts[e] = c;
+            if (e == E) n_tiles[0] = t_before;
+        }
     }
     __syncthreads();
     for (int p = threadIdx.x; p < P; p += blockDim.x) {       // stable: pairs of an expert keep their order
@@ -397,56 +457,49 @@ router_small_tail_kernel(float* __restrict__ logits, int* __restrict__ ids, floa
     for (int row = warp; row < P; row += nwarps) {            // expert-sorted copies of the token rows
         const TA* src = x + (size_t)(s_row[row] / k) * H;
         TA* dst = x_rows + (size_t)row * H;
-        if (vec) {
+        if (vec_x) {
             const int n16 = (int)((size_t)H * sizeof(TA) / 16);
             const uint4* s4 = reinterpret_cast<const uint4*>(src);
             uint4* d4 = reinterpret_cast<uint4*>(dst);
-            for (int i = lane; i < n16; i += 32) d4[i] = s4[i];
+            for (int i0 = lane; i0 < n16; i0 += 256) {          // eight 16-byte loads in flight per lane, then the stores
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (i0 + 32 * j < n16) v[j] = s4[i0 + 32 * j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (i0 + 32 * j < n16) d4[i0 + 32 * j] = v[j];
+            }
         } else {
             for (int i = lane; i < H; i += 32) dst[i] = src[i];
         }
     }
+    if (threadIdx.x == 0) *counter = 0;                       // ready for the next launch
 }
 
-// Router, expert-sorted layout and gathered rows for a step of few tokens: two launches in all.
-// Needs T*k <= 512 pairs and E <= 1024 experts; logits: T * (E + 1) floats of scratch.
-TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype, float* logits,
+// Router, expert-sorted layout and gathered rows for a step of few tokens, in one launch.
+// Needs T*k <= 512 pairs, E <= 1024 experts and (H + E + 1) floats of shared memory within 48 KiB;
+// counter: one int in device memory, zero before the first launch (the kernel leaves it zero).
+TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
                               int* ids, float* wts, float* shared_scale, int tile_rows, int* counts, int* sorted_pair,
                               int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0, int* tile_count,
-                              int* n_tiles, void* x_rows, int T_, int H, int E, int k, int renorm, cudaStream_t stream) {
+                              int* n_tiles, void* x_rows, int* counter, int T_, int H, int E, int k, int renorm,
+                              cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ * k <= SMALL_MAX_PAIRS && E <= SMALL_MAX_EXPERTS,
                "router_small: %d pairs / %d experts exceed %d / %d", T_ * k, E, SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS);
     TQ_REQUIRE(E >= 1 && k >= 1 && k <= E && tile_rows >= 1, "router_small: bad sizes E=%d k=%d tile_rows=%d", E, k, tile_rows);
     TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
-    const bool staged = H <= ROUTER_MAX_STAGED_H;
-    const size_t smem = staged ? (size_t)H * sizeof(float) : 0;
+    TQ_REQUIRE(counter != nullptr, "router_small: a counter is required");
+    const size_t smem = (size_t)(H + E + 1) * sizeof(float);
+    TQ_REQUIRE(smem <= 48 * 1024, "router_small: a row of %d values and %d logits do not fit 48 KiB of shared memory", H, E);
     const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
-    const int vec_ok = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
-    const int rows = E + (wsg ? 1 : 0);
-    int chunks = (512 + T_ - 1) / T_;
-    if (chunks > (rows + 3) / 4) chunks = (rows + 3) / 4;
-    if (chunks < 1) chunks = 1;
-    const int rows_per_cta = (rows + chunks - 1) / chunks;
-    chunks = (rows + rows_per_cta - 1) / rows_per_cta;
-    const int threads = rows_per_cta >= 32 ? 1024 : (rows_per_cta >= 16 ? 512 : (rows_per_cta >= 8 ? 256 : 128));
-    dim3 grid(T_, chunks);
-#define ROUTER_LAUNCH(ST)                                                                              \
-    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
-        (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                      \
-            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
-    if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
-#undef ROUTER_LAUNCH
-    TQ_CHECK_LAUNCH("router_logits");
+    const int vec_w = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
     const int abytes = act_dtype == TQ_F32 ? 4 : 2;
-    const int vec = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
-    int tail_threads = 32 * (T_ * k > T_ ? T_ * k : T_);      // a warp per (token, choice) row to copy, at least one per token
-    tail_threads = tail_threads < 128 ? 128 : (tail_threads > SMALL_THREADS ? SMALL_THREADS : tail_threads);
-    TQ_DISPATCH(act_dtype, TA,
-        (tq_launch(1, tail_threads, 0, stream)(router_small_tail_kernel<TA>, logits, ids, wts, shared_scale, T_, E, k,
-            renorm, tile_rows, counts, sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0, tile_count,
-            n_tiles, (const TA*)x, (TA*)x_rows, H, vec)));
-    TQ_CHECK_LAUNCH("router_small_tail");
+    const int vec_x = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
+        (tq_launch(T_, SMALL_THREADS, smem, stream)(router_small_kernel<TA, TW>, (const TA*)x, (const TW*)wr, (const TW*)wsg,
+            ids, wts, shared_scale, T_, H, E, k, renorm, vec_w, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
+            tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter))));
+    TQ_CHECK_LAUNCH("router_small");
     return 0;
 }
 

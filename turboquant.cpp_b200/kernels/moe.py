@@ -76,35 +76,47 @@ SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS = 512, 1024      # what the kernel accepts
 SMALL_PAIRS_WORTH_IT = 128                           # beyond this one block is slower than the separate kernels
 
 
-def router_small_usable(n_tokens: int, top_k: int, n_experts: int) -> bool:
-    return n_tokens * top_k <= SMALL_MAX_PAIRS and n_experts <= SMALL_MAX_EXPERTS
+def router_small_usable(n_tokens: int, top_k: int, n_experts: int, hidden: int) -> bool:
+    return (n_tokens * top_k <= SMALL_MAX_PAIRS and n_experts <= SMALL_MAX_EXPERTS
+            and (hidden + n_experts + 1) * 4 <= 48 * 1024)
 
 
-def router_small_pays(n_tokens: int, top_k: int, n_experts: int) -> bool:
+def router_small_pays(n_tokens: int, top_k: int, n_experts: int, hidden: int) -> bool:
     """Measured on B200: at 256 pairs (batch 64, top-4) the single block costs more than it saves."""
-    return n_tokens * top_k <= SMALL_PAIRS_WORTH_IT and n_experts <= SMALL_MAX_EXPERTS
+    return n_tokens * top_k <= SMALL_PAIRS_WORTH_IT and router_small_usable(n_tokens, top_k, n_experts, hidden)
+
+
+_counters = {}
+
+
+def _counter(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the last block of router_small finds its turn with; zero between launches."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _counters:
+        _counters[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _counters[idx]
 
 
 def router_small(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top_k: int,
                  renorm: bool, ids: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
                  layout: ExpertLayout, x_rows: torch.Tensor) -> None:
     """For steps of few tokens: router, expert-sorted layout and the sorted copies of the token rows
-    (x_rows[row] = x[token of that row]) in two launches."""
+    (x_rows[row] = x[token of that row]) in one launch.  Launches on one device must not overlap (they share
+    the counter that tells the last block its turn)."""
     T, H = x.shape
     E = w_router.shape[0]
     want_int32(ids, "expert ids")
     want_f32(weights, "expert weights")
     if w_shared_gate is not None and w_shared_gate.dtype != w_router.dtype:
         w_shared_gate = w_shared_gate.to(w_router.dtype)
-    logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
     lib = load_kernel(_LIB)
     lo = layout
     check(_LIB, lib.tq_router_small(
-        ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate), c_int(code(w_router.dtype)), ptr(logits),
+        ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate), c_int(code(w_router.dtype)),
         ptr(ids), ptr(weights), ptr(shared_scale), c_int(lo.tile_rows), ptr(lo.counts), ptr(lo.sorted_pair),
         ptr(lo.row_of_pair), ptr(lo.expert_offset), ptr(lo.tile_expert), ptr(lo.tile_row0), ptr(lo.tile_count),
-        ptr(lo.n_tiles), ptr(x_rows), c_int(T), c_int(H), c_int(E), c_int(top_k), c_int(1 if renorm else 0), stream()),
-          kernels=2)
+        ptr(lo.n_tiles), ptr(x_rows), ptr(_counter(x.device)), c_int(T), c_int(H), c_int(E), c_int(top_k),
+        c_int(1 if renorm else 0), stream()))
 
 
 def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:

@@ -143,7 +143,7 @@ class MoEFeedForward(FeedForward):
         tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
-        if KM.router_small_pays(T, k, self.n_experts):
+        if KM.router_small_pays(T, k, self.n_experts, H):
             # few tokens (decoding): router, layout and the sorted copies of the rows in two launches
             KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows)
         else:
