@@ -93,7 +93,7 @@ __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
     sum = tq_warp_sum(sum);
-    float picked_sum = 0.f, mine = 0.f;                 // lane j keeps the weight of choice j, j + 32, ...
+    float picked_sum = 0.f;
     for (int j = 0; j < k; ++j) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -117,7 +117,6 @@ __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict
         }
         __syncwarp();
     }
-    (void)mine;
     if (renorm) {
         __syncwarp();
         for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
@@ -335,22 +334,31 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     __syncthreads();
     const int rows = E + (wsg ? 1 : 0);
     const int Hv = vec_w ? (H / 8) * 8 : 0;
-    for (int e = warp; e < rows; e += nwarps) {
+    // two rows per warp at a time and the loop unrolled: all of a step's loads are in flight together (the
+    // work is a few hundred KB; what counts is the number of dependent trips to memory)
+    for (int e = warp; e < rows; e += 2 * nwarps) {
+        const int e2 = e + nwarps < rows ? e + nwarps : e;
         const TW* w = e < E ? wr + (size_t)e * H : wsg;
-        float s = 0.f;
-#pragma unroll 4
+        const TW* w2 = e2 < E ? wr + (size_t)e2 * H : wsg;
+        float s = 0.f, s2 = 0.f;
+#pragma unroll 8
         for (int i = lane * 8; i < Hv; i += 256) {
-            float f[8];
+            float f[8], f2[8];
             RowVec<TW>::load(w + i, f);
+            RowVec<TW>::load(w2 + i, f2);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s = fmaf(s_x[i + j], f[j], s);
+            for (int j = 0; j < 8; ++j) { s = fmaf(s_x[i + j], f[j], s); s2 = fmaf(s_x[i + j], f2[j], s2); }
         }
-        for (int i = Hv + lane; i < H; i += 32) s = fmaf(s_x[i], tq_to_float(w[i]), s);
+        for (int i = Hv + lane; i < H; i += 32) {
+            s = fmaf(s_x[i], tq_to_float(w[i]), s);
+            s2 = fmaf(s_x[i], tq_to_float(w2[i]), s2);
+        }
         s = tq_warp_sum(s);
-        if (lane == 0) s_logit[e] = s;
+        s2 = tq_warp_sum(s2);
+        if (lane == 0) { s_logit[e] = s; s_logit[e2] = s2; }      // e2 == e: the same value twice
     }
     __syncthreads();
-    // ---- selection: warp 0 (the same steps as router_select_kernel) ----
+    // ---- selection: warp 0 (the same choices and weights as router_select_kernel) ----
     if (warp == 0) {
         if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
         float mx = -INFINITY;
@@ -359,34 +367,34 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
         float sum = 0.f;
         for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
         sum = tq_warp_sum(sum);
-        float picked_sum = 0.f;
+        float* s_val = s_x;                                   // the row is no longer needed: its place holds the k picked logits
         for (int j = 0; j < k; ++j) {
-            float best = -INFINITY;
+            // largest remaining logit, ties to the lowest index; NaN and -inf (already picked) never win.
+            // Floats compare like these integers: sign-magnitude to offset binary.
+            unsigned best = 0;
             int best_e = 0x7fffffff;
             for (int e = lane; e < E; e += 32) {
                 const float v = s_logit[e];
-                if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+                const unsigned u = __float_as_uint(v);
+                const unsigned key = (v != v || v == -INFINITY) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+                if (key > best) { best = key; best_e = e; }   // lower e first within a lane
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
-            }
-            if (best_e == 0x7fffffff) best_e = j;
-            const float p = expf(best - mx) / sum;
-            picked_sum += p;
+            const unsigned top = __reduce_max_sync(0xffffffffu, best);
+            int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
+            if (pick == 0x7fffffff) pick = j;                 // nothing left to pick: keep indices valid
             if (lane == 0) {
-                ids[(size_t)t * k + j] = best_e;
-                wts[(size_t)t * k + j] = p;
-                s_logit[best_e] = -INFINITY;
+                ids[(size_t)t * k + j] = pick;
+                s_val[j] = top != 0u ? s_logit[pick] : -INFINITY;
+                s_logit[pick] = -INFINITY;
             }
             __syncwarp();
         }
-        if (renorm) {
-            __syncwarp();
-            for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
-        }
+        // weights: lanes take the exponentials, every lane adds them up in the order of the choices
+        for (int j = lane; j < k; j += 32) s_val[j] = expf(s_val[j] - mx) / sum;
+        __syncwarp();
+        float picked_sum = 0.f;
+        if (renorm) for (int j = 0; j < k; ++j) picked_sum += s_val[j];
+        for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = renorm ? s_val[j] / picked_sum : s_val[j];
         __threadfence();                                      // this token's choices are visible before the count
         __syncwarp();
         if (lane == 0) s_last = atomicAdd(counter, 1) == T_ - 1;
