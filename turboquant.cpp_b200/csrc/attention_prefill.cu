@@ -12,12 +12,15 @@
 // tiles of 64 (= one cache page):
 //   warp 0        TMA: Q once, then K and V pages through two-stage rings
 //   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 64, K hd) one tile ahead into one
-//                 of two S buffers, and  O_tile = P V  (M 128, N hd, K 64; V is the MN-major
-//                 operand, read as stored)
+//                 of two S buffers, and  O += P V  (M 128, N hd, K 64; V is the MN-major operand, read
+//                 as stored), accumulating in tensor memory over all key tiles
 //   warps 2..9    two threads per query row (each warp reads its quarter of the tensor-memory lanes;
 //                 the two threads of a row split the tile's 64 keys and the head's elements): read S,
-//                 mask, online softmax, write P (bf16, 128-byte swizzled) to shared memory, then add
-//                 their half of O_tile into fp32 accumulator registers
+//                 mask, online softmax, write P (bf16, 128-byte swizzled) to one of two buffers in
+//                 shared memory.  O stays in tensor memory: it is rescaled there only when a row's
+//                 maximum grows by more than 2^8 over the one its exponentials are taken against
+//                 (until then P is simply larger, at most 256, and the row's sum carries the same
+//                 factor), so a tile's softmax never waits for the products before it.
 // The heaviest query tiles (the last ones of a sequence, which see the most keys) are scheduled
 // first.  Every wait on an mbarrier is bounded; a wait that runs out sets *status and the CTA
 // leaves cleanly.
@@ -118,16 +121,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
 template <int HD>
 struct Cfg {
     static constexpr int HALVES = HD / 64;                 // 64-element (128-byte) column blocks of a head
     static constexpr int Q_BYTES = BM * HD * 2;
     static constexpr int KV_BYTES = BN * HD * 2;           // one page of K or of V for one KV head
     static constexpr int P_BYTES = BM * BN * 2;
-    static constexpr int STAGES = 2;
-    static constexpr int TILE_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES;
+    static constexpr int STAGES = 4;                       // K and V pages in flight: the loads' latency is several tiles long
+    static constexpr int TILE_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 2 * P_BYTES;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 256;
-    static constexpr int TMEM_COLS = 256;                  // S twice (2 x 64 columns), O_tile (HD columns)
+    static constexpr int TMEM_COLS = 256;                  // S twice (2 x 64 columns), O (HD columns)
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
 };
 
@@ -162,15 +176,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t q_smem = base;
     auto k_smem = [&](int s) { return base + C::Q_BYTES + s * C::KV_BYTES; };
     auto v_smem = [&](int s) { return base + C::Q_BYTES + (C::STAGES + s) * C::KV_BYTES; };
-    const uint32_t p_smem = base + C::Q_BYTES + 2 * C::STAGES * C::KV_BYTES;
+    auto p_smem = [&](int b) { return base + C::Q_BYTES + 2 * C::STAGES * C::KV_BYTES + b * C::P_BYTES; };
     const uint32_t bars = base + C::TILE_BYTES;
     const uint32_t q_full = bars;
+    constexpr int NS = C::STAGES;
     auto k_full = [&](int s) { return bars + 8u * (1 + s); };
-    auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
-    auto v_full = [&](int s) { return bars + 8u * (5 + s); };
-    auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
-    auto s_ready = [&](int b) { return bars + 8u * (9 + b); };
-    const uint32_t p_ready = bars + 8u * 11, o_ready = bars + 8u * 12, o_free = bars + 8u * 13;
+    auto k_empty = [&](int s) { return bars + 8u * (1 + NS + s); };
+    auto v_full = [&](int s) { return bars + 8u * (1 + 2 * NS + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * NS + s); };
+    auto s_ready = [&](int b) { return bars + 8u * (1 + 4 * NS + b); };
+    auto p_ready = [&](int b) { return bars + 8u * (3 + 4 * NS + b); };   // P of a tile is in its buffer (and S has been read)
+    auto pv_done = [&](int b) { return bars + 8u * (5 + 4 * NS + b); };   // the products that read P buffer b are done
+    static_assert((7 + 4 * NS) * 8 <= 256, "barriers");
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -178,9 +195,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
         mbar_init(s_ready(0), 1);
         mbar_init(s_ready(1), 1);
-        mbar_init(p_ready, 8);          // one arrival per softmax warp
-        mbar_init(o_ready, 1);
-        mbar_init(o_free, 8);
+        for (int b = 0; b < 2; ++b) { mbar_init(p_ready(b), 8); mbar_init(pv_done(b), 1); }   // 8: one arrival per softmax warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -195,7 +210,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // had not allocated yet, and then wait forever for this grid to finish
     tq_grid_launch_dependents();
     auto tmem_s = [&](int b) { return s_tmem_base + (uint32_t)(b * BN); };    // S, twice: BN columns each
-    const uint32_t tmem_o = s_tmem_base + 2 * BN;                              // O_tile: HD columns
+    const uint32_t tmem_o = s_tmem_base + 2 * BN;                              // O: HD columns
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -250,47 +265,45 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             };
             if (ok) ok = issue_qk(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
-                const int s = i % C::STAGES;
-                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u, it = (uint32_t)i & 1u;
+                const int s = i % C::STAGES, b = i & 1;
+                const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
                 // the other S buffer is free: its tile's P was complete before P V of tile i - 1 was issued
                 if (i + 1 < n_tiles) ok = issue_qk(i + 1);
                 if (!ok) break;
-                ok = mbar_wait(p_ready, it, &s_abort) && mbar_wait(v_full(s), ph, &s_abort);
-                if (ok && i > 0) ok = mbar_wait(o_free, (uint32_t)(i - 1) & 1u, &s_abort);
+                ok = mbar_wait(p_ready(b), (uint32_t)(i >> 1) & 1u, &s_abort) && mbar_wait(v_full(s), ph, &s_abort);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)            // O_tile = P V
-                    umma(tmem_o, desc_k_major(p_smem + k * 32), desc_mn_major(v_smem(s) + k * 2048, BN * 128), id_o,
-                         k > 0 ? 1u : 0u);
-                umma_commit(o_ready);
+                for (int k = 0; k < BN / 16; ++k)            // O += P V (the first tile starts the sum)
+                    umma(tmem_o, desc_k_major(p_smem(b) + k * 32), desc_mn_major(v_smem(s) + k * 2048, BN * 128), id_o,
+                         (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(pv_done(b));
                 umma_commit(v_empty(s));
             }
         }
     } else {
-        // ------------------------------ softmax and accumulation: two threads per query row ------------------------------
+        // ------------------------------ softmax: two threads per query row ------------------------------
         constexpr int HK = BN / 2, HDH = HD / 2;      // keys and head elements of one thread
+        constexpr float RESCALE_LOG2 = 8.0f;          // O is rescaled when a row's maximum has grown by more than 2^8
         const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int qpos = p_first + r;
         const int start = window > 0 ? max(0, qpos + 1 - window) : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        float o[HDH];
-#pragma unroll
-        for (int d = 0; d < HDH; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;                 // l: this thread's keys only; the two halves are added at the end
+        // m: the maximum the row's exponentials are taken against (both threads of a row hold the same);
+        // l: the sum of this thread's keys' exponentials
+        float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const uint32_t it = (uint32_t)i & 1u;
+            const int b = i & 1;
             const int k0 = (kb_first + i) * BN;
-            ok = __all_sync(0xffffffffu, mbar_wait(s_ready(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort));   // warp-uniform
+            ok = __all_sync(0xffffffffu, mbar_wait(s_ready(b), (uint32_t)(i >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[32], other[32];
-            tmem_ld32(tmem_s(i & 1) + lane_addr + part * HK, sv);
-            tmem_ld32(tmem_s(i & 1) + lane_addr + (1 - part) * HK, other);
+            tmem_ld32(tmem_s(b) + lane_addr + part * HK, sv);
+            tmem_ld32(tmem_s(b) + lane_addr + (1 - part) * HK, other);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            // m is the running maximum of the raw scores; exponents are taken base 2 of (s - m) * scale * log2(e)
             float mx = m;
             const bool visible = (k0 + BN - 1 <= p_first) && (window == 0 || k0 >= p_first + BM - window);
             if (visible) {                             // every key of the tile is seen by every row: no masking
@@ -301,18 +314,45 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                 for (int c = 0; c < HK; ++c) {         // the row's maximum needs all 64 scores
                     const int kp = k0 + part * HK + c, kq = k0 + (1 - part) * HK + c;
-                    float a = __uint_as_float(sv[c]), b = __uint_as_float(other[c]);
+                    float a = __uint_as_float(sv[c]), bq = __uint_as_float(other[c]);
                     if (kp > qpos || kp < start) a = -INFINITY;
-                    if (kq > qpos || kq < start) b = -INFINITY;
+                    if (kq > qpos || kq < start) bq = -INFINITY;
                     sv[c] = __float_as_uint(a);
-                    mx = fmaxf(mx, fmaxf(a, b));
+                    mx = fmaxf(mx, fmaxf(a, bq));
                 }
             }
-            const float mref = mx == -INFINITY ? 0.f : mx * scale_log2e;   // nothing visible yet: exponents of -inf
-            const float corr = mx == -INFINITY ? 1.f : ex2(m * scale_log2e - mref);
+            // keep m unless the maximum grew by more than 2^8 (or nothing had been seen yet)
+            float corr = 1.0f;
+            if (m == -INFINITY) {
+                m = mx;                                // l and O are still zero: nothing to rescale
+            } else if ((mx - m) * scale_log2e > RESCALE_LOG2) {
+                corr = ex2((m - mx) * scale_log2e);
+                l *= corr;
+                m = mx;
+            }
+            // the P buffer must be free (the products of two tiles ago are done), and O can only be rescaled
+            // between the previous tile's products and this tile's
+            if (i >= 2) ok = __all_sync(0xffffffffu, mbar_wait(pv_done(b), (uint32_t)((i >> 1) - 1) & 1u, &s_abort));
+            if (!ok) break;
+            if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(pv_done(b ^ 1), (uint32_t)((i - 1) >> 1) & 1u, &s_abort));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c0 = 0; c0 < HDH; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_o + lane_addr + part * HDH + c0, ov);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * corr);
+                    tmem_st32(tmem_o + lane_addr + part * HDH + c0, ov);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            const float mref = m == -INFINITY ? 0.f : m * scale_log2e;   // nothing visible yet: exponents of -inf
             float lsum = 0.f;
             // P in bf16, 16-byte chunks of 8 keys, written with the 128-byte swizzle of a K-major operand
-            const uint32_t prow = p_smem + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
+            const uint32_t prow = p_smem(b) + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
 #pragma unroll
             for (int ch = 0; ch < HK / 8; ++ch) {
                 uint32_t packed[4];
@@ -320,60 +360,50 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 for (int e = 0; e < 4; ++e) {
                     const int c = ch * 8 + 2 * e;
                     const float a = ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -mref));
-                    const float b = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, -mref));
-                    lsum += a + b;
-                    const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
+                    const float bq = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, -mref));
+                    lsum += a + bq;
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(a, bq);
                     packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
                 }
                 const uint32_t dst = prow + (uint32_t)(((part * (HK / 8) + ch) ^ (r % 8)) * 16);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
                              "r"(packed[2]), "r"(packed[3]) : "memory");
             }
-            l = l * corr + lsum;
-            m = mx;
+            l += lsum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready);
-            // meanwhile rescale the accumulator (skipped when no row of the warp saw a new maximum), then
-            // add this tile's P V
-            if (!__all_sync(0xffffffffu, corr == 1.0f)) {
-#pragma unroll
-                for (int d = 0; d < HDH; ++d) o[d] *= corr;
-            }
-            ok = __all_sync(0xffffffffu, mbar_wait(o_ready, it, &s_abort));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c0 = 0; c0 < HDH; c0 += 32) {
-                uint32_t ov[32];
-                tmem_ld32(tmem_o + lane_addr + part * HDH + c0, ov);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c0 + j] += __uint_as_float(ov[j]);
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_free);
+            if (lane == 0) mbar_arrive(p_ready(b));
         }
-        // the row's sum is the sum of its two threads' sums (same maximum m in both)
-        float* s_l = reinterpret_cast<float*>(smem_raw + (p_smem - smem_u32(smem_raw)));   // P's buffer is free now
+        // all products done: O / (the row's sum = the sum of its two threads' sums, same maximum m in both)
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, &s_abort));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float* s_l = reinterpret_cast<float*>(smem_raw + (p_smem(0) - smem_u32(smem_raw)));   // P's buffers are free now
         asm volatile("bar.sync 1, 256;" ::: "memory");           // all softmax warps are past their last tile
         s_l[part * BM + r] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const float lrow = s_l[r] + s_l[BM + r];
-        if (ok && r < rows) {
+        if (ok) {
             const float inv = 1.0f / lrow;
             __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h) * HD + part * HDH;
 #pragma unroll
-            for (int d = 0; d < HDH; d += 8) {
-                uint32_t packed[4];
+            for (int c0 = 0; c0 < HDH; c0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + lane_addr + part * HDH + c0, ov);      // every lane takes part: the load is warp-wide
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < rows) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const __nv_bfloat162 pk = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                    packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                    for (int d = 0; d < 32; d += 8) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(ov[d + 2 * e]) * inv,
+                                                                            __uint_as_float(ov[d + 2 * e + 1]) * inv);
+                            packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c0 + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
         }
     }
