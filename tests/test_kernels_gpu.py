@@ -222,6 +222,35 @@ def test_attention_prefill_far_key_and_window_edge():
     assert np.abs(got[edge + 1] - d["v"][0][far].reshape(-1)).max() > 0.5
 
 
+def test_attention_prefill_rising_scores_rescale_the_accumulator():
+    """Scores that grow with the key's position: the running maximum rises in every key tile, by more than
+    2^8 per tile for some query rows (the accumulator in tensor memory must be rescaled there) and by less
+    for others (their exponentials are taken against an older maximum and exceed 1)."""
+    from turboquant_cpp_b200.kernels import attention as KA, gemm_tc as KT
+    rng = np.random.default_rng(23)
+    nh = nkv = 2
+    hd, page, L = 128, 64, 640
+    dtype = torch.bfloat16
+    d = paged_inputs(rng, [L], [L], nkv, hd, page, dtype, n_pages=16)
+    q = bf16_values(rng.normal(size=(L, nh, hd)))
+    k = d["k"][0]
+    k[:, :, 0] = bf16_values(np.arange(L) / 16.0)[:, None]          # rises by 4 per tile of 64 keys
+    # per tile the score rises by 4 * q0 / sqrt(hd) nats: q0 = 2..60 gives 1..30 bits per tile
+    q[:, :, 0] = bf16_values(2.0 + 58.0 * rng.random(size=(L, nh)))
+    for p in range(L):
+        d["cache"][d["table"][0, p // page], 0, :, p % page] = k[p]
+    out = torch.empty((L, nh * hd), dtype=dtype, device=DEV)
+    KA.attention_prefill(dev(q, dtype), dev(d["cache"], dtype), dev([0, L], torch.int32), dev([0], torch.int32),
+                         dev(d["table"], torch.int32), page, 0, 1 / math.sqrt(hd), out, 1, L, nh, nkv, hd)
+    KT.check_status()
+    close(out, P.attention(q, k, d["v"][0], 0), 1e-2)
+    w = 150                                                          # and with a window that drops the early keys
+    KA.attention_prefill(dev(q, dtype), dev(d["cache"], dtype), dev([0, L], torch.int32), dev([0], torch.int32),
+                         dev(d["table"], torch.int32), page, w, 1 / math.sqrt(hd), out, 1, L, nh, nkv, hd)
+    KT.check_status()
+    close(out, P.attention(q, k, d["v"][0], w), 1e-2)
+
+
 def test_attention_far_key_stands_out():
     """One key far back gets a large score: the output must be (almost) that key's value, which a
     kernel that skips or misplaces distant pages would miss."""
