@@ -43,16 +43,17 @@ def test_embed_rows(wdtype):
 
 
 @pytest.mark.parametrize("H", [50, 192, 2048, 3000])
+@pytest.mark.parametrize("R", [7, 700])                   # few rows: a block per row; many: a warp per row
 @pytest.mark.parametrize("odtype,tol", DTYPES)
-def test_rmsnorm(H, odtype, tol):
+def test_rmsnorm(H, R, odtype, tol):
     from turboquant_cpp_b200.kernels import elementwise as K
     rng = np.random.default_rng(1)
-    x = rng.normal(size=(7, H)) * 3
+    x = rng.normal(size=(R, H)) * 3
     w = bf16_values(1 + 0.1 * rng.normal(size=H))
-    y = rng.normal(size=(7, H))
+    y = rng.normal(size=(R, H))
     eps = 1e-5
     # plain norm
-    out = torch.empty((7, H), dtype=odtype, device=DEV)
+    out = torch.empty((R, H), dtype=odtype, device=DEV)
     xd = dev(x)
     K.rmsnorm(xd, dev(w, torch.bfloat16), eps, out)
     close(out, P.rmsnorm(x.astype(np.float32).astype(np.float64), w, eps), tol)
@@ -64,8 +65,8 @@ def test_rmsnorm(H, odtype, tol):
     close(out, P.rmsnorm(xs, w, eps), tol)
     close(xd, xs, 1e-6)                                   # the sum was written back
     # gather of rows, with a pending sum that is not written back
-    rows = np.array([5, 0, 5, 3])
-    out2 = torch.empty((4, H), dtype=odtype, device=DEV)
+    rows = np.array([5, 0, 5, 3]) if R < 512 else rng.integers(0, R, size=600)
+    out2 = torch.empty((len(rows), H), dtype=odtype, device=DEV)
     before = xd.clone()
     K.rmsnorm(xd, dev(w), eps, out2, add=yd, rows=dev(rows, torch.int32))
     close(out2, P.rmsnorm((xs + y.astype(np.float32))[rows], w, eps), tol)

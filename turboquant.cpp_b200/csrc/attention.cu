@@ -91,18 +91,20 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
             Vec8<TA>::load(src + i, a);
             Vec8<TA>::load(src + half + i, c);
             if (bias) {
+                float ba[8], bc[8];
+                Vec8<TB>::load(bias + (size_t)j * hd + i, ba);
+                Vec8<TB>::load(bias + (size_t)j * hd + half + i, bc);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    a[e] += tq_to_float(bias[(size_t)j * hd + i + e]);
-                    c[e] += tq_to_float(bias[(size_t)j * hd + half + i + e]);
-                }
+                for (int e = 0; e < 8; ++e) { a[e] += ba[e]; c[e] += bc[e]; }
             }
             const bool is_v = j >= nh + nkv;
             if (!is_v && cs_row) {
+                float cs[8], sn[8];                        // i is a multiple of 8 and a table row of 4 floats: 16-byte loads
+                Vec8<float>::load(cs_row + i, cs);
+                Vec8<float>::load(sn_row + i, sn);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float cs = cs_row[i + e], sn = sn_row[i + e];
-                    const float ra = a[e] * cs - c[e] * sn, rc = a[e] * sn + c[e] * cs;
+                    const float ra = a[e] * cs[e] - c[e] * sn[e], rc = a[e] * sn[e] + c[e] * cs[e];
                     a[e] = ra; c[e] = rc;
                 }
             }
@@ -155,9 +157,13 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     const int heads = write_kv ? nh + 2 * nkv : nh;
     const int esize = act_dtype == TQ_F32 ? 4 : 2;
     const int vec8 = pairing == 0 && hd % 16 == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
-                     ((uintptr_t)cache % 16) == 0 && ((size_t)hd * esize) % 16 == 0;
+                     ((uintptr_t)cache % 16) == 0 && ((size_t)hd * esize) % 16 == 0 &&
+                     ((uintptr_t)cos_t % 16) == 0 && ((uintptr_t)sin_t % 16) == 0 &&
+                     ((uintptr_t)bias % 16) == 0 && ((size_t)hd * (bias_dtype == TQ_F32 ? 4 : 2)) % 16 == 0;
     const int pairs = vec8 ? heads * (hd / 16) : heads * (hd / 2);      // work items per token
-    const int threads = pairs >= 1024 ? 256 : (pairs >= 256 ? 128 : 64);
+    // long steps: one block per token whose threads cover the token's work items in whole rounds
+    const int threads = T_ >= 512 ? (pairs % 192 == 0 ? 192 : (pairs % 128 == 0 ? 128 : 256))
+                                  : (pairs >= 1024 ? 256 : (pairs >= 256 ? 128 : 64));
     // few tokens: several blocks share a token's row, so that the step still fills the GPU
     int chunks = T_ >= 512 ? 1 : (pairs + threads - 1) / threads;
     if (chunks > 64) chunks = 64;

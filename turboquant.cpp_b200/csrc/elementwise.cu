@@ -127,12 +127,72 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__
     }
 }
 
+// Many rows (prompts): a warp per row, the row in registers (up to 16 groups of 4 elements per lane: H <= 2048, a
+// multiple of 4), the sums by shuffles: no block-wide barrier, and a lane's loads are all in flight together.
+#define RMS_WARP_GROUPS 16
+#define RMS_WARP_ROWS 8          // warps (rows) per block
+template <typename TY, typename TW, typename TO>
+__global__ void __launch_bounds__(32 * RMS_WARP_ROWS)
+rmsnorm_warp_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
+                    const TW* __restrict__ w, TO* __restrict__ out, int R, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * RMS_WARP_ROWS + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + src * H;
+    const TY* yr = y ? y + src * H : nullptr;
+    const bool write_back = y && !rows;
+    const int nvec = H >> 2;
+    float4 v[RMS_WARP_GROUPS];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < RMS_WARP_GROUPS; ++c) {
+        const int i = lane + 32 * c;
+        if (i < nvec) v[c] = tq_load4<float>(xr + 4 * i);
+    }
+    if (yr) {
+#pragma unroll
+        for (int c = 0; c < RMS_WARP_GROUPS; ++c) {
+            const int i = lane + 32 * c;
+            if (i < nvec) { const float4 b = tq_load4<TY>(yr + 4 * i); v[c].x += b.x; v[c].y += b.y; v[c].z += b.z; v[c].w += b.w; }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < RMS_WARP_GROUPS; ++c) {
+        const int i = lane + 32 * c;
+        if (i < nvec) {
+            if (write_back) tq_store4<float>(xr + 4 * i, v[c]);
+            ss += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
+        }
+    }
+    ss = tq_warp_sum(ss);
+    const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+#pragma unroll
+    for (int c = 0; c < RMS_WARP_GROUPS; ++c) {
+        const int i = lane + 32 * c;
+        if (i < nvec) {
+            const float4 g = tq_load4<TW>(w + 4 * i);
+            tq_store4<TO>(o + 4 * i, make_float4(v[c].x * rs * g.x, v[c].y * rs * g.y, v[c].z * rs * g.z, v[c].w * rs * g.w));
+        }
+    }
+}
+
 TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, const void* w, int w_dtype,
                          void* out, int out_dtype, int R, int H, float eps, cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
     if (H % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
         ((uintptr_t)out % 16) == 0) {
+        if (R >= 512 && H / 4 <= 32 * RMS_WARP_GROUPS) {
+            TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+                (tq_launch((R + RMS_WARP_ROWS - 1) / RMS_WARP_ROWS, 32 * RMS_WARP_ROWS, 0, stream)(
+                    rmsnorm_warp_kernel<TY, TW, TO>, x, (const TY*)y, rows, (const TW*)w, (TO*)out, R, H, eps)))));
+            TQ_CHECK_LAUNCH("rmsnorm");
+            return 0;
+        }
         int vthreads = ((H / 4 + 31) / 32) * 32;
         if (vthreads > 256 && H / 4 <= 256 * RMS_VEC_GROUPS) vthreads = ((H / 4 + 255) / 256 <= 4) ? 256 : 512;
         if (vthreads > 1024) vthreads = 1024;

@@ -77,7 +77,19 @@ __global__ void router_logits_kernel(const TA* __restrict__ x, const TW* __restr
     }
 }
 
-// Kernel 2: one warp per token: softmax over the E logits, k largest, weights, shared gate.
+// Floats compare like these integers (sign-magnitude to offset binary); NaN and -inf map to 0, below all.
+__device__ __forceinline__ unsigned tq_order_key(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (v != v || v == -INFINITY) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+}
+__device__ __forceinline__ float tq_order_value(unsigned key) {      // the inverse, for key != 0
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// Kernel 2: one warp per token: softmax over the E logits, k largest (ties to the lowest index; NaN never
+// wins), weights, shared gate.  Up to 256 experts a lane keeps its logits in registers and a choice is two
+// warp-wide integer reductions; beyond that the row is re-read from memory and chosen entries overwritten.
+#define SELECT_REGS 8
 __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
                                      float* __restrict__ shared_scale, int T_, int E, int k, int renorm) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
@@ -85,8 +97,50 @@ __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= T_) return;
-    float* s_logit = logits + (size_t)t * (E + 1);      // this warp's row; chosen entries are overwritten
+    float* s_logit = logits + (size_t)t * (E + 1);      // this warp's row
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
+    if (E <= 32 * SELECT_REGS) {
+        float v[SELECT_REGS];
+        unsigned key[SELECT_REGS];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < SELECT_REGS; ++c) {
+            const int e = lane + 32 * c;
+            v[c] = e < E ? s_logit[e] : -INFINITY;
+            key[c] = e < E ? tq_order_key(v[c]) : 0u;
+            mx = fmaxf(mx, v[c]);
+        }
+        mx = tq_warp_max(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < SELECT_REGS; ++c) if (lane + 32 * c < E) sum += expf(v[c] - mx);
+        sum = tq_warp_sum(sum);
+        float picked_sum = 0.f, mine = 0.f;             // lane j % 32 keeps the weight of choice j
+        for (int j = 0; j < k; ++j) {
+            unsigned best = 0;
+            int best_e = 0x7fffffff;
+#pragma unroll
+            for (int c = 0; c < SELECT_REGS; ++c)
+                if (key[c] > best) { best = key[c]; best_e = lane + 32 * c; }      // lower e first within a lane
+            const unsigned top = __reduce_max_sync(0xffffffffu, best);
+            int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
+            const bool found = pick != 0x7fffffff;
+            if (!found) pick = j;                       // nothing left to pick: keep indices valid
+            const float p = expf((found ? tq_order_value(top) : -INFINITY) - mx) / sum;
+            picked_sum += p;                            // identical in every lane
+#pragma unroll
+            for (int c = 0; c < SELECT_REGS; ++c) if (found && lane + 32 * c == pick) key[c] = 0u;
+            if (lane == 0) ids[(size_t)t * k + j] = pick;
+            if (j < 32) { if (lane == j) mine = p; }
+            else if (lane == 0) wts[(size_t)t * k + j] = p;          // more than 32 choices: the rest go through memory
+        }
+        if (lane < k) wts[(size_t)t * k + lane] = renorm ? mine / picked_sum : mine;
+        if (k > 32 && renorm) {
+            __syncwarp();
+            for (int j = 32 + lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
+        }
+        return;
+    }
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
     mx = tq_warp_max(mx);
@@ -369,14 +423,11 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
         sum = tq_warp_sum(sum);
         float* s_val = s_x;                                   // the row is no longer needed: its place holds the k picked logits
         for (int j = 0; j < k; ++j) {
-            // largest remaining logit, ties to the lowest index; NaN and -inf (already picked) never win.
-            // Floats compare like these integers: sign-magnitude to offset binary.
+            // largest remaining logit, ties to the lowest index; NaN and -inf (already picked) never win
             unsigned best = 0;
             int best_e = 0x7fffffff;
             for (int e = lane; e < E; e += 32) {
-                const float v = s_logit[e];
-                const unsigned u = __float_as_uint(v);
-                const unsigned key = (v != v || v == -INFINITY) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+                const unsigned key = tq_order_key(s_logit[e]);
                 if (key > best) { best = key; best_e = e; }   // lower e first within a lane
             }
             const unsigned top = __reduce_max_sync(0xffffffffu, best);
