@@ -9,10 +9,10 @@
 // second product.
 //
 // One CTA = 128 consecutive query tokens of one sequence x one query head; it walks the keys in
-// tiles of 64 (= one cache page):
+// tiles of 128 (= two cache pages; the last tile may hold one):
 //   warp 0        TMA: Q once, then K and V pages through two-stage rings
-//   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 64, K hd) one tile ahead into one
-//                 of two S buffers, and  O += P V  (M 128, N hd, K 64; V is the MN-major operand, read
+//   warp 1        owns tensor memory, issues  S = Q K^T  (M 128, N 128, K hd) one tile ahead into one
+//                 of two S buffers, and  O += P V  (M 128, N hd, K 128; V is the MN-major operand, read
 //                 as stored), accumulating in tensor memory over all key tiles
 //   warps 2..9    two threads per query row (each warp reads its quarter of the tensor-memory lanes;
 //                 the two threads of a row split the tile's 64 keys and the head's elements): read S,
@@ -32,7 +32,6 @@ TQ_DEFINE_LAST_ERROR
 namespace {
 
 constexpr int BM = 128;      // query rows per CTA
-constexpr int BN = 64;       // keys per tile = tokens per cache page
 constexpr int THREADS = 320;   // TMA warp, MMA warp, eight softmax warps
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr uint64_t WAIT_NS = 2000000000ull;
@@ -132,17 +131,22 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         : "memory");
 }
 
+constexpr int PAGE = 64;     // tokens per cache page
+constexpr int BN = 128;      // keys per tile = two cache pages (the last tile of a CTA may hold one)
+
 template <int HD>
 struct Cfg {
     static constexpr int HALVES = HD / 64;                 // 64-element (128-byte) column blocks of a head
     static constexpr int Q_BYTES = BM * HD * 2;
-    static constexpr int KV_BYTES = BN * HD * 2;           // one page of K or of V for one KV head
+    static constexpr int PAGE_BYTES = PAGE * HD * 2;       // one page of K or of V for one KV head
+    static constexpr int KV_BYTES = BN * HD * 2;           // a tile of K or of V
     static constexpr int P_BYTES = BM * BN * 2;
-    static constexpr int STAGES = 4;                       // K and V pages in flight: the loads' latency is several tiles long
+    static constexpr int STAGES = 2;                       // K and V tiles in flight
     static constexpr int TILE_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 2 * P_BYTES;
     static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 256;
-    static constexpr int TMEM_COLS = 256;                  // S twice (2 x 64 columns), O (HD columns)
+    static constexpr int TMEM_COLS = 512;                  // S twice (2 x 128 columns), O (HD columns)
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 
 template <int HD>
@@ -167,8 +171,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int p_first = seq_start[seq] + qt * BM;                  // position of row 0
     const int p_last = p_first + rows - 1;
     const int lo = window > 0 ? max(0, p_first + 1 - window) : 0;
-    const int kb_first = lo / BN, kb_last = p_last / BN;
-    const int n_tiles = kb_last - kb_first + 1;
+    const int pg_first = lo / PAGE, pg_last = p_last / PAGE;       // cache pages this CTA reads
+    const int n_pages = pg_last - pg_first + 1;
+    const int n_tiles = (n_pages + 1) / 2;
     const int* table = page_table + (size_t)seq * table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -188,6 +193,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto p_ready = [&](int b) { return bars + 8u * (3 + 4 * NS + b); };   // P of a tile is in its buffer (and S has been read)
     auto pv_done = [&](int b) { return bars + 8u * (5 + 4 * NS + b); };   // the products that read P buffer b are done
     static_assert((7 + 4 * NS) * 8 <= 256, "barriers");
+    auto pages_of = [&](int i) { return min(2, n_pages - 2 * i); };        // pages (halves of 64 keys) in tile i
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -222,16 +228,25 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (uint32_t)(i / C::STAGES) & 1u;
-                const int page = table[kb_first + i];
-                const int krow = ((page * 2 + 0) * nkv + g) * BN, vrow = ((page * 2 + 1) * nkv + g) * BN;
+                const int np = pages_of(i);
+                const int page0 = table[pg_first + 2 * i], page1 = np > 1 ? table[pg_first + 2 * i + 1] : 0;
+                // a tile in shared memory: [column block of 64 elements][128 keys][128 bytes]; a page is 64 keys of it
                 if (!mbar_wait(k_empty(s), ph ^ 1u, &s_abort)) break;
-                mbar_expect_tx(k_full(s), (uint32_t)C::KV_BYTES);
+                mbar_expect_tx(k_full(s), (uint32_t)(np * C::PAGE_BYTES));
+                for (int pg = 0; pg < np; ++pg) {
+                    const int krow = (((pg ? page1 : page0) * 2 + 0) * nkv + g) * PAGE;
 #pragma unroll
-                for (int c = 0; c < C::HALVES; ++c) tma_load_2d(k_smem(s) + c * (BN * 128), &map_kv, c * 64, krow, k_full(s));
+                    for (int c = 0; c < C::HALVES; ++c)
+                        tma_load_2d(k_smem(s) + c * (BN * 128) + pg * (PAGE * 128), &map_kv, c * 64, krow, k_full(s));
+                }
                 if (!mbar_wait(v_empty(s), ph ^ 1u, &s_abort)) { issued = i + 1; break; }
-                mbar_expect_tx(v_full(s), (uint32_t)C::KV_BYTES);
+                mbar_expect_tx(v_full(s), (uint32_t)(np * C::PAGE_BYTES));
+                for (int pg = 0; pg < np; ++pg) {
+                    const int vrow = (((pg ? page1 : page0) * 2 + 1) * nkv + g) * PAGE;
 #pragma unroll
-                for (int c = 0; c < C::HALVES; ++c) tma_load_2d(v_smem(s) + c * (BN * 128), &map_kv, c * 64, vrow, v_full(s));
+                    for (int c = 0; c < C::HALVES; ++c)
+                        tma_load_2d(v_smem(s) + c * (BN * 128) + pg * (PAGE * 128), &map_kv, c * 64, vrow, v_full(s));
+                }
                 issued = i + 1;
             }
             if (s_abort) {      // let the copies this thread started land before the CTA goes away
@@ -246,14 +261,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
+        // A product of M = 128 costs some 130-145 cycles whatever its N up to 128: tiles of 128 keys make the
+        // most of each one (8 products for S, 8 for O per 128 keys).
         if (lane == 0) {
-            const uint32_t id_s = idesc(BN, 0), id_o = idesc(HD, 1);
+            const uint32_t id_o = idesc(HD, 1);
             bool ok = mbar_wait(q_full, 0u, &s_abort);
             // S = Q K^T of tile i into S buffer i & 1; issued one tile ahead of the P V product
             auto issue_qk = [&](int i) -> bool {
                 const int s = i % C::STAGES;
                 if (!mbar_wait(k_full(s), (uint32_t)(i / C::STAGES) & 1u, &s_abort)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t id_s = idesc(PAGE * pages_of(i), 0);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32, koff = (k / 4) * (BN * 128) + (k % 4) * 32;
@@ -273,17 +291,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 ok = mbar_wait(p_ready(b), (uint32_t)(i >> 1) & 1u, &s_abort) && mbar_wait(v_full(s), ph, &s_abort);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                for (int k = 0; k < BN / 16; ++k)            // O += P V (the first tile starts the sum)
-                    umma(tmem_o, desc_k_major(p_smem(b) + k * 32), desc_mn_major(v_smem(s) + k * 2048, BN * 128), id_o,
-                         (i > 0 || k > 0) ? 1u : 0u);
+                const int steps = (PAGE / 16) * pages_of(i);     // 16 keys per product; a missing second page is not read
+                for (int k = 0; k < steps; ++k)                  // O += P V (the first tile starts the sum)
+                    umma(tmem_o, desc_k_major(p_smem(b) + (k / 4) * (BM * 128) + (k % 4) * 32),
+                         desc_mn_major(v_smem(s) + k * 2048, BN * 128), id_o, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(pv_done(b));
                 umma_commit(v_empty(s));
             }
         }
     } else {
         // ------------------------------ softmax: two threads per query row ------------------------------
-        constexpr int HK = BN / 2, HDH = HD / 2;      // keys and head elements of one thread
+        constexpr int HK = PAGE / 2, HDH = HD / 2;    // keys of a page and head elements of one thread
         constexpr float RESCALE_LOG2 = 8.0f;          // O is rescaled when a row's maximum has grown by more than 2^8
         const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
@@ -296,29 +314,38 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int b = i & 1;
-            const int k0 = (kb_first + i) * BN;
+            const int np = pages_of(i);
+            const int k0 = (pg_first + 2 * i) * PAGE;
             ok = __all_sync(0xffffffffu, mbar_wait(s_ready(b), (uint32_t)(i >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t sv[32], other[32];
-            tmem_ld32(tmem_s(b) + lane_addr + part * HK, sv);
-            tmem_ld32(tmem_s(b) + lane_addr + (1 - part) * HK, other);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // this thread's 32 keys of each page of the tile, and (for the maximum only) the other thread's
+            uint32_t sv[2][32];
             float mx = m;
-            const bool visible = (k0 + BN - 1 <= p_first) && (window == 0 || k0 >= p_first + BM - window);
-            if (visible) {                             // every key of the tile is seen by every row: no masking
 #pragma unroll
-                for (int c = 0; c < HK; ++c)
-                    mx = fmaxf(mx, fmaxf(__uint_as_float(sv[c]), __uint_as_float(other[c])));
-            } else {
+            for (int hf = 0; hf < 2; ++hf) {
+                if (hf < np) {                                 // uniform across the CTA
+                    uint32_t other[32];
+                    tmem_ld32(tmem_s(b) + lane_addr + hf * PAGE + part * HK, sv[hf]);
+                    tmem_ld32(tmem_s(b) + lane_addr + hf * PAGE + (1 - part) * HK, other);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int kh = k0 + hf * PAGE;
+                    const bool visible = (kh + PAGE - 1 <= p_first) && (window == 0 || kh >= p_first + BM - window);
+                    if (visible) {                             // every key of the page is seen by every row: no masking
 #pragma unroll
-                for (int c = 0; c < HK; ++c) {         // the row's maximum needs all 64 scores
-                    const int kp = k0 + part * HK + c, kq = k0 + (1 - part) * HK + c;
-                    float a = __uint_as_float(sv[c]), bq = __uint_as_float(other[c]);
-                    if (kp > qpos || kp < start) a = -INFINITY;
-                    if (kq > qpos || kq < start) bq = -INFINITY;
-                    sv[c] = __float_as_uint(a);
-                    mx = fmaxf(mx, fmaxf(a, bq));
+                        for (int c = 0; c < HK; ++c)
+                            mx = fmaxf(mx, fmaxf(__uint_as_float(sv[hf][c]), __uint_as_float(other[c])));
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < HK; ++c) {
+                            const int kp = kh + part * HK + c, kq = kh + (1 - part) * HK + c;
+                            float a = __uint_as_float(sv[hf][c]), bq = __uint_as_float(other[c]);
+                            if (kp > qpos || kp < start) a = -INFINITY;
+                            if (kq > qpos || kq < start) bq = -INFINITY;
+                            sv[hf][c] = __float_as_uint(a);
+                            mx = fmaxf(mx, fmaxf(a, bq));
+                        }
+                    }
                 }
             }
             // keep m unless the maximum grew by more than 2^8 (or nothing had been seen yet)
@@ -351,23 +378,29 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const float mref = m == -INFINITY ? 0.f : m * scale_log2e;   // nothing visible yet: exponents of -inf
             float lsum = 0.f;
-            // P in bf16, 16-byte chunks of 8 keys, written with the 128-byte swizzle of a K-major operand
-            const uint32_t prow = p_smem(b) + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
+            // P in bf16: [page of the tile][128 rows][128 bytes = 64 keys], 16-byte chunks of 8 keys written with
+            // the 128-byte swizzle of a K-major operand
 #pragma unroll
-            for (int ch = 0; ch < HK / 8; ++ch) {
-                uint32_t packed[4];
+            for (int hf = 0; hf < 2; ++hf) {
+                if (hf < np) {
+                    const uint32_t prow = p_smem(b) + (uint32_t)hf * (BM * 128) + (uint32_t)(r / 8) * 1024u + (uint32_t)(r % 8) * 128u;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = ch * 8 + 2 * e;
-                    const float a = ex2(fmaf(__uint_as_float(sv[c]), scale_log2e, -mref));
-                    const float bq = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, -mref));
-                    lsum += a + bq;
-                    const __nv_bfloat162 pk = __floats2bfloat162_rn(a, bq);
-                    packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                    for (int ch = 0; ch < HK / 8; ++ch) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = ch * 8 + 2 * e;
+                            const float a = ex2(fmaf(__uint_as_float(sv[hf][c]), scale_log2e, -mref));
+                            const float bq = ex2(fmaf(__uint_as_float(sv[hf][c + 1]), scale_log2e, -mref));
+                            lsum += a + bq;
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(a, bq);
+                            packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        const uint32_t dst = prow + (uint32_t)(((part * (HK / 8) + ch) ^ (r % 8)) * 16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
+                                     "r"(packed[2]), "r"(packed[3]) : "memory");
+                    }
                 }
-                const uint32_t dst = prow + (uint32_t)(((part * (HK / 8) + ch) ^ (r % 8)) * 16);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]),
-                             "r"(packed[2]), "r"(packed[3]) : "memory");
             }
             l += lsum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
@@ -477,7 +510,7 @@ TQ_EXPORT int tq_attention_prefill(const void* q, const void* cache, const int* 
                                    int* status, cudaStream_t stream) {
     if (T_ == 0 || n_seqs == 0) return 0;
     TQ_REQUIRE(hd == 64 || hd == 128, "attention_prefill: head size %d is not 64 or 128", hd);
-    TQ_REQUIRE(page_size == BN, "attention_prefill: page size %d must be %d", page_size, BN);
+    TQ_REQUIRE(page_size == PAGE, "attention_prefill: page size %d must be %d", page_size, PAGE);
     TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "attention_prefill: %d heads are not a multiple of %d key/value heads", nh, nkv);
     TQ_REQUIRE(n_seqs <= 65535 && nh <= 65535, "attention_prefill: grid too large (%d sequences, %d heads)", n_seqs, nh);
     TQ_REQUIRE(window >= 0 && max_q_len >= 1, "attention_prefill: bad window %d or longest run %d", window, max_q_len);
@@ -487,7 +520,7 @@ TQ_EXPORT int tq_attention_prefill(const void* q, const void* cache, const int* 
     CUtensorMap mq, mkv;
     int rc = make_map(&mq, q, (uint64_t)T_, (uint64_t)nh * hd, BM);
     if (rc) return rc;
-    rc = make_map(&mkv, cache, (uint64_t)n_pages * 2 * nkv * BN, (uint64_t)hd, BN);
+    rc = make_map(&mkv, cache, (uint64_t)n_pages * 2 * nkv * PAGE, (uint64_t)hd, PAGE);
     if (rc) return rc;
     if (hd == 64)
         return launch<64>(mq, mkv, cu_seqlens, seq_start, page_table, table_stride, window, scale, out, n_seqs, max_q_len,
