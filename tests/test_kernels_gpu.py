@@ -190,6 +190,36 @@ def test_attention_prefill(nh, nkv, hd, window):
     close(out, want, 1e-2)      # P is rounded to bfloat16 before the second product, and so is the result
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 64, 0), (16, 4, 128, 0), (16, 16, 128, 300)])
+def test_attention_prefill_many_units_per_cta(nh, nkv, hd, window):
+    """More (query tile, sequence, head) units than SMs, some of them empty (short sequences): every persistent
+    CTA walks several units, reloading Q and alternating between its two accumulators."""
+    from turboquant_cpp_b200.kernels import attention as KA, gemm_tc as KT
+    rng = np.random.default_rng(nh + hd + window)
+    seq_lens, q_lens, page = [700, 130, 64, 1, 513, 333], [700, 70, 64, 1, 257, 333], 64
+    dtype = torch.bfloat16
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, dtype, n_pages=48)
+    T = sum(q_lens)
+    n_units = -(-max(q_lens) // 128) * len(seq_lens) * nh
+    assert n_units > 2 * torch.cuda.get_device_properties(0).multi_processor_count or nh == 8
+    q = bf16_values(rng.normal(size=(T, nh, hd)))
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)])
+    starts = np.array(seq_lens) - np.array(q_lens)
+    KA.attention_prefill(dev(q, dtype), dev(d["cache"], dtype), dev(cu, torch.int32), dev(starts, torch.int32),
+                         dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd), out, len(seq_lens), max(q_lens),
+                         nh, nkv, hd)
+    KT.check_status()
+    want = np.zeros((T, nh * hd))
+    t0 = 0
+    for i, (L, ql) in enumerate(zip(seq_lens, q_lens)):
+        qfull = np.zeros((L, nh, hd))
+        qfull[L - ql:] = q[t0:t0 + ql]
+        want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
+        t0 += ql
+    close(out, want, 1e-2)
+
+
 def test_attention_prefill_far_key_and_window_edge():
     """A key 600 positions back carries a huge score: every later query's output is that key's value;
     a window that ends one short of it hides it, a window that just reaches it shows it again."""
