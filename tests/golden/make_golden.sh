@@ -1,9 +1,10 @@
 #!/bin/bash
-# Builds the reference's CPU sources (read-only checkout at $1, default /root/reference) and runs
-# ref_driver.c against them; writes logits.bin next to this script.  No network, no GPU.
+# Usage: make_golden.sh PATH_TO_THE_REFERENCE_CHECKOUT
+# Builds the reference's CPU sources (a read-only checkout) and runs ref_driver.c against them; writes
+# logits.bin next to this script.  No network, no GPU.
 # The one flag the reference needs on x86-64 gcc is -D__fp16=_Float16 (src/engine/tq_transformer.c:3456).
 set -e
-R=${1:-/root/reference}
+R=${1:?path of the reference checkout}
 HERE=$(cd "$(dirname "$0")" && pwd)
 W=$(mktemp -d)
 for f in $R/src/core/*.c $R/src/cache/*.c $R/src/backend/cpu/*.c $R/src/engine/*.c; do
