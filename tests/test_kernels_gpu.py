@@ -515,7 +515,8 @@ def test_sample_rows_distribution():
 
 
 @pytest.mark.parametrize("T,E,k,H,renorm,shared", [(1, 8, 2, 64, False, True), (8, 60, 4, 2048, False, True),
-                                                    (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False)])
+                                                    (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False),
+                                                    (3, 1023, 40, 96, True, True), (128, 300, 4, 64, False, False)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype):
     """The one-launch decode path (a block per token for logits and selection; the block that finishes last

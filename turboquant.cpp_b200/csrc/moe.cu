@@ -360,7 +360,7 @@ TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int chun
 // must not overlap.
 // ---------------------------------------------------------------------------------------
 #define SMALL_MAX_PAIRS 512
-#define SMALL_MAX_EXPERTS 1024
+#define SMALL_MAX_EXPERTS 1023      // the scan over the experts gives thread E the totals: E < blockDim.x
 #define SMALL_THREADS 1024
 
 template <typename TA, typename TW>
@@ -378,7 +378,7 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     float* s_x = s_dyn;               // [H] the token's row
     float* s_logit = s_dyn + H;       // [E + 1] router logits, then the shared expert's gate logit
     __shared__ int s_ids[SMALL_MAX_PAIRS], s_row[SMALL_MAX_PAIRS];
-    __shared__ int s_count[SMALL_MAX_EXPERTS], s_off[SMALL_MAX_EXPERTS + 1], s_toff[SMALL_MAX_EXPERTS + 1];
+    __shared__ int s_count[SMALL_MAX_EXPERTS + 1], s_off[SMALL_MAX_EXPERTS + 1], s_toff[SMALL_MAX_EXPERTS + 1];
     __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -535,7 +535,7 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
 }
 
 // Router, expert-sorted layout and gathered rows for a step of few tokens, in one launch.
-// Needs T*k <= 512 pairs, E <= 1024 experts and (H + E + 1) floats of shared memory within 48 KiB;
+// Needs T*k <= 512 pairs, E <= 1023 experts and (H + E + 1) floats of shared memory within 48 KiB;
 // counter: one int in device memory, zero before the first launch (the kernel leaves it zero).
 TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
                               int* ids, float* wts, float* shared_scale, int tile_rows, int* counts, int* sorted_pair,

@@ -72,7 +72,7 @@ class ExpertLayout:
         self.chunk_hist = torch.empty(-(-max(1, n_pairs) // align_chunk(n_pairs)) * n_experts, **i32)     # scratch of moe_align
 
 
-SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS = 512, 1024      # what the kernel accepts
+SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS = 512, 1023      # what the kernel accepts
 SMALL_PAIRS_WORTH_IT = 128                           # beyond this one block is slower than the separate kernels
 
 
