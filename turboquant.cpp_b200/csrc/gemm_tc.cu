@@ -269,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
-               int* __restrict__ status) {
+               int stream_weights, int* __restrict__ status) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     using T = Tile<BN, PAIR>;
     constexpr int COLS = SWIGLU ? BM / 2 : BM;         // output columns of a weight-row tile
@@ -333,8 +333,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------- weight blocks: one stream of k-blocks across all of this CTA's tiles ----------------
         if (lane == 0) {
-            // one group's weights are read by every token tile (keep them); several groups' are streamed once
-            const uint64_t policy = tile_expert ? policy_evict_first() : policy_evict_last();
+            // weights that only one token tile reads (a decode step, a short prompt) are streamed: first to leave
+            // the L2; weights that several token tiles share stay
+            const uint64_t policy = stream_weights ? policy_evict_first() : policy_evict_last();
             int slot = 0, issued = 0;
             uint32_t phase = 0;      // parity of the slot's current use
             bool ok = true;
@@ -559,7 +560,7 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
 
 template <int BN, bool SWIGLU, typename TO, bool PAIR>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
-           const int* tc, const int* nt, int grid_y, int R, int N, int K, int* status, cudaStream_t stream) {
+           const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, cudaStream_t stream) {
     using T = Tile<BN, PAIR>;
     auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR>;
     static bool configured = false;
@@ -591,7 +592,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y;      // units of work
     const long long want = PAIR ? 2 * tiles : tiles;
     const int grid = (int)(want < resident ? want : resident);
-    tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K, status);
+    tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K,
+        /* stream_weights: on average at most one token tile per group */ (te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0, status);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -626,7 +628,7 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     if (rc) return rc;
     rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u);
     if (rc) return rc;
-#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, status, stream
+#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, stream
 #define TC_CASE(BN_, PAIR_)                                                                          \
     if (bn == BN_ && (pair != 0) == PAIR_) {                                                         \
         if (swiglu) {                                                                                \
