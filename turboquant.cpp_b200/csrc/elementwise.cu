@@ -277,8 +277,13 @@ __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restri
             const int n16 = (int)((size_t)H * sizeof(T) / 16);
             const uint4* s4 = reinterpret_cast<const uint4*>(src);
             uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll 4
-            for (int i = lane; i < n16; i += 32) d4[i] = s4[i];
+            for (int i0 = lane; i0 < n16; i0 += 256) {      // eight 16-byte loads in flight per lane, then the stores
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (i0 + 32 * j < n16) v[j] = s4[i0 + 32 * j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (i0 + 32 * j < n16) d4[i0 + 32 * j] = v[j];
+            }
         } else {
             for (int i = lane; i < H; i += 32) dst[i] = src[i];
         }
