@@ -6,7 +6,8 @@
 //   out[row, n] = silu(X.Wg[n]) * (X.Wu[n])                   (SwiGLU: W holds gate rows [0, N) and
 //                                                              up rows [N, 2N) of each group)
 // as the reference's expert loop computes them on the CPU (src/engine/tq_moe.c:975-999: g = Wg x,
-// u = Wu x, h = silu(g)*u, o = Wd h), with exact expf in the SiLU.
+// u = Wu x, h = silu(g)*u, o = Wd h); the SiLU's exponential and division are the exact ones for an fp32
+// result and the fast ones (a few units in the last place of fp32) for a bfloat16 result.
 //
 // The weights are packed once at load time into [128 rows x 64 elements] blocks of 16 KiB, so a
 // stage of the pipeline is one contiguous read and a CTA's stream walks memory sequentially instead

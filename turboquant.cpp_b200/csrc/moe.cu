@@ -3,8 +3,11 @@
 //   tq_router_topk    logits = Wr x (fp32), softmax over all experts, k largest (ties to the lowest
 //                     index), optional renormalisation; the shared expert's sigmoid gate in the
 //                     same pass
+//   tq_router_select  the selection alone, from logits that a tensor-core product left (prompts)
 //   tq_moe_align      stable counting sort of (token, choice) pairs by expert, and the list of row
 //                     tiles the grouped GEMMs walk
+//   tq_router_small   decode steps: logits, selection, layout, tile list and the expert-sorted copies
+//                     of the token rows in one launch
 //   tq_grouped_gemm   C[rows of expert e] = A[rows] W[e]^T, fp32 accumulation on CUDA cores (the
 //                     exact path; any sizes), optionally with SiLU(gate)*up fused in
 //   tq_moe_combine    y[t] = sum_j w[t,j] Y[row(t,j)] + s[t] Y_shared[t], in the order chosen
