@@ -46,6 +46,55 @@ class FakeEngine:
         return np.stack(rows)
 
 
+class FakeAheadEngine(FakeEngine):
+    """The stand-in with the optional run-ahead interface: a step launched from the samples, then kept or dropped."""
+    can_step_ahead = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.pending, self.kept, self.dropped = None, 0, 0
+
+    class Reader:
+        def __init__(self, n):
+            self.n = n
+
+        def start(self, tokens):
+            snap = [int(t) for t in tokens]
+            assert len(snap) <= self.n
+            return lambda: snap
+
+    def token_reader(self, n):
+        return self.Reader(n)
+
+    def step(self, entries):
+        assert self.pending is None, "a step while another, launched ahead, has neither been kept nor dropped"
+        return super().step(entries)
+
+    def step_ahead(self, seqs, tokens):
+        assert self.pending is None
+        self.book.reserve_all(list(seqs), [1] * len(seqs))
+        self.pending = (list(seqs), [int(t) for t in tokens])
+        rows = np.zeros((len(seqs), self.vocab))
+        for r, (s, t) in enumerate(zip(*self.pending)):
+            rows[r, (self.sums[s.id] + t) % self.vocab] = 1.0
+        return rows
+
+    def commit_ahead(self):
+        seqs, toks = self.pending
+        self.pending = None
+        for s, t in zip(seqs, toks):
+            assert s.id in self.book.live
+            self.sums[s.id] += t
+            self.book.commit(s, 1)
+        self.step_sizes.append(len(seqs))
+        self.kept += 1
+        self.book.check_invariants()
+
+    def drop_ahead(self):
+        assert self.pending is not None
+        self.pending = None
+        self.dropped += 1
+
 class ArgmaxSampler:
     def __init__(self):
         self.calls = []
@@ -84,6 +133,48 @@ def test_batches_of_unequal_prompts_and_early_ends():
             assert 0 <= s < 6 and 0 <= i < len(prompts)
     assert stats.generated_tokens == sum(len(r.tokens) for r in res)
     assert stats.prompt_tokens == sum(len(p) for p in prompts)
+
+
+@pytest.mark.parametrize("stop,max_new", [((), 6), ((24,), 6), ((24, 3, 7), 12), ((), 1), ((), 2)])
+def test_running_one_step_ahead_changes_no_result(stop, max_new):
+    prompts = [[1, 2, 3], [4] * 11, [5] * 17, [7], [9, 9], [3] * 290]
+    plain_eng, ahead_eng = FakeEngine(), FakeAheadEngine()
+    params = GenParams(max_new_tokens=max_new, stop_token_ids=stop)
+    want = generate(plain_eng, ArgmaxSampler(), prompts, params, max_batch=3)
+    seen = {}
+    got = generate(ahead_eng, ArgmaxSampler(), prompts, params, max_batch=3,
+                   on_tokens=lambda idx, toks: [seen.setdefault(i, []).append(t) for i, t in zip(idx, toks)])
+    assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+    assert [seen[i] for i in range(len(prompts))] == [r.tokens for r in got]
+    assert ahead_eng.step_sizes == plain_eng.step_sizes                 # the same steps were committed
+    assert ahead_eng.pending is None and not ahead_eng.book.live
+    assert ahead_eng.book.pools[0].n_free == ahead_eng.book.pools[0].n
+    if max_new > 2:
+        assert ahead_eng.kept > 0
+    if stop and any(r.finish_reason == "stop" and len(r.tokens) < max_new for r in want):
+        assert ahead_eng.dropped > 0                                    # an early end voided a step launched ahead
+    if not stop:
+        assert ahead_eng.dropped == 0                                   # ends by length are foreseen: nothing is wasted
+
+
+def test_a_full_cache_ends_run_ahead_like_a_plain_step():
+    for cls in (FakeEngine, FakeAheadEngine):
+        small = cls(capacity_tokens=128, max_slots=4)
+        res = generate(small, ArgmaxSampler(), [[1] * 60, [2] * 60], GenParams(max_new_tokens=200), max_batch=4)
+        assert [r.finish_reason for r in res] == ["context", "context"]
+        assert all(len(r.tokens) == 128 - 60 + 1 for r in res)
+        assert not small.book.live and getattr(small, "pending", None) is None
+
+
+def test_an_error_in_the_callback_leaves_no_step_pending():
+    eng = FakeAheadEngine()
+
+    def boom(idx, toks):
+        if len(toks) and eng.kept >= 1:
+            raise RuntimeError("stop here")
+    with pytest.raises(RuntimeError):
+        generate(eng, ArgmaxSampler(), [[1, 2], [3]], GenParams(max_new_tokens=8), on_tokens=boom)
+    assert eng.pending is None and not eng.book.live
 
 
 def test_streaming_callback_gets_every_token_once():

@@ -78,10 +78,15 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
     """Generates a continuation for every prompt.
 
     engine:   open(), close(seq), step(entries) -> logits rows, make_entry(seq, tokens, want),
-              capacity_tokens, max_slots, page_size, max_position
+              capacity_tokens, max_slots, page_size, max_position; optionally can_step_ahead, step_ahead(seqs,
+              sampled tokens) -> logits rows, commit_ahead(), drop_ahead(), token_reader(n)
     sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist())
     on_tokens(request indices, tokens) is called after every step with that step's new tokens.
-    A stop token ends its sequence and is part of the output."""
+    A stop token ends its sequence and is part of the output.
+
+    An engine that can (`can_step_ahead`) is kept one decode step ahead of the host: the next step is launched
+    from the samples while they are still on the device, and the host reads them meanwhile.  If a sequence
+    turns out to have ended, that step is dropped and run again without it, so the results are the same."""
     stats = stats if stats is not None else GenStats()
     sync = sync or (lambda: None)
     results = [GenResult() for _ in prompts]
@@ -95,17 +100,21 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
     for batch in batches:
         stats.batches += 1
         live = {i: engine.open() for i in batch}
+        ahead = None                                     # (request order, logits) of a step launched ahead
         try:
             # the prompts, whole, in one step; logits at each prompt's last token
             t0 = time.perf_counter()
             order = list(batch)
             logits = engine.step([engine.make_entry(live[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in order])
-            new = sampler.sample(logits, order, [0] * len(order)).tolist()
+            new_dev = sampler.sample(logits, order, [0] * len(order))
+            new = new_dev.tolist()
             sync()
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prompt_tokens += sum(len(prompts[i]) for i in order)
             stats.steps += 1
             t0 = time.perf_counter()
+            can_ahead = bool(getattr(engine, "can_step_ahead", False))
+            reader = engine.token_reader(len(order)) if can_ahead else None
             while True:
                 nxt: List[Tuple[int, int]] = []
                 for i, tok in zip(order, new):
@@ -126,19 +135,40 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
                     on_tokens(list(order), [int(t) for t in new])
                 if not nxt:
                     break
-                order = [i for i, _ in nxt]
-                try:
-                    logits = engine.step([engine.make_entry(live[i], [tok], [0]) for i, tok in nxt])
-                except CacheFull:
-                    for i in order:                      # no room for one more token each
-                        results[i].finish_reason = "context"
-                        engine.close(live.pop(i))
-                    break
-                new = sampler.sample(logits, order, [len(results[i].tokens) for i in order]).tolist()
+                if ahead is not None and ahead[0] == [i for i, _ in nxt]:
+                    engine.commit_ahead()                # nobody ended: the step launched ahead is this step
+                    logits = ahead[1]
+                    ahead = None
+                else:
+                    if ahead is not None:                # somebody ended: that step is void
+                        ahead = None
+                        engine.drop_ahead()
+                    order = [i for i, _ in nxt]
+                    try:
+                        logits = engine.step([engine.make_entry(live[i], [tok], [0]) for i, tok in nxt])
+                    except CacheFull:
+                        for i in order:                  # no room for one more token each
+                            results[i].finish_reason = "context"
+                            engine.close(live.pop(i))
+                        break
+                new_dev = sampler.sample(logits, order, [len(results[i].tokens) for i in order])
                 stats.steps += 1
+                # launch the step after this one now, unless a sequence is sure to end with this token
+                if can_ahead and all(len(results[i].tokens) + 1 < params.max_new_tokens
+                                     and live[i].length + 1 <= engine.max_position for i in order):
+                    arrived = reader.start(new_dev)
+                    try:
+                        ahead = (list(order), engine.step_ahead([live[i] for i in order], new_dev))
+                    except CacheFull:
+                        ahead = None
+                    new = arrived()
+                else:
+                    new = new_dev.tolist()
             sync()
             stats.decode_seconds += time.perf_counter() - t0
         finally:
+            if ahead is not None:                        # the batch ended, or an error, before the step's fate
+                engine.drop_ahead()
             for seq in live.values():
                 engine.close(seq)
     return results

@@ -8,6 +8,7 @@ kernel needs that changes from step to step lives in that buffer, never in a lau
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Sequence
 
 import numpy as np
@@ -72,9 +73,13 @@ class DecodeGraph:
         ev.record()
         self.copied[self.turn] = ev
 
-    def run(self, seqs, tokens: Sequence[int]) -> torch.Tensor:
+    def run(self, seqs, tokens: Sequence[int], tokens_dev: torch.Tensor = None) -> torch.Tensor:
+        """tokens_dev: the step's tokens as an int32 tensor on the device (the previous step's samples); they go
+        into the static buffer by a device copy, after the host's part of it."""
         eng = self.engine
         self.fill(seqs, tokens)
+        if tokens_dev is not None:
+            self.dev[self.offsets[0]:self.offsets[1]].copy_(tokens_dev, non_blocking=True)
         caches = eng.cache.layer_caches(self.tables)
         if self.graph is None:
             # the first step of this batch size runs eagerly (it also loads kernels and lets libraries
@@ -83,8 +88,18 @@ class DecodeGraph:
             torch.cuda.synchronize(eng.device)
             g = torch.cuda.CUDAGraph()
             before = _call.LAUNCHES
-            with torch.cuda.graph(g):
-                self.logits = eng.model.forward(self.ctx, caches)
+            # no garbage collection while the stream is capturing: a collected object that owns device memory or
+            # another CUDA graph (an engine that was dropped earlier) would free it in the middle of the capture,
+            # which invalidates it
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self.logits = eng.model.forward(self.ctx, caches)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.kernels = _call.LAUNCHES - before      # this library's kernels inside the graph
             _call.LAUNCHES = before
             self.graph = g
@@ -99,9 +114,22 @@ class DecodeGraphs:
         self.engine = engine
         self.graphs: Dict[int, DecodeGraph] = {}
 
+    def release(self) -> None:
+        """Drops the captured graphs (and their memory) now, not when a garbage collector finds them."""
+        for g in self.graphs.values():
+            g.graph = g.logits = g.engine = None
+        self.graphs.clear()
+
     def step(self, entries) -> torch.Tensor:
         B = len(entries)
         g = self.graphs.get(B)
         if g is None:
             g = self.graphs[B] = DecodeGraph(self.engine, B)
         return g.run([e.seq for e in entries], [int(e.tokens[0]) for e in entries])
+
+    def step_from_device(self, seqs, tokens_dev: torch.Tensor) -> torch.Tensor:
+        B = len(seqs)
+        g = self.graphs.get(B)
+        if g is None:
+            g = self.graphs[B] = DecodeGraph(self.engine, B)
+        return g.run(list(seqs), [0] * B, tokens_dev)

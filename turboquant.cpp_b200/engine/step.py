@@ -38,6 +38,28 @@ class StepEntry:
     want: Sequence[int] = ()      # places among `tokens` whose logits are asked for
 
 
+class TokenReader:
+    """Brings a step's sampled tokens to the host without waiting for work queued behind them: two pinned
+    buffers used in turn (allocated once: nothing is allocated or freed while steps are in flight), a copy and an
+    event per step."""
+
+    def __init__(self, n: int):
+        self.bufs = [torch.empty(max(1, n), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.turn = 0
+
+    def start(self, tokens_dev):
+        self.turn ^= 1
+        host = self.bufs[self.turn][:tokens_dev.numel()]
+        host.copy_(tokens_dev, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+
+        def wait():
+            done.synchronize()
+            return host.tolist()
+        return wait
+
+
 class Engine:
     """A model, its cache and the step function."""
 
@@ -60,6 +82,7 @@ class Engine:
             use_graphs = os.environ.get("TQ_NO_GRAPHS", "") in ("", "0")
         stateless = all(n is None for n in model.state_needs())      # a mixer with state of its own walks the
         self.graphs = DecodeGraphs(self) if use_graphs and stateless else None   # batch on the host: no graph
+        self._ahead = None                       # (sequences, tokens each) of a step launched ahead, if any
 
     # ---- what the generation loop asks -----------------------------------------------------------
     @property
@@ -87,6 +110,12 @@ class Engine:
         (it synchronises the device; call it where results are brought to the host anyway)."""
         from ..kernels.gemm_tc import check_status
         check_status(self.device)
+
+    def release(self) -> None:
+        """Gives back what the engine holds on the device besides the cache: its CUDA graphs."""
+        self._ahead = None
+        if self.graphs is not None:
+            self.graphs.release()
 
     # ---- sequences ------------------------------------------------------------------------------
     def open(self) -> Sequence_:
@@ -170,3 +199,46 @@ class Engine:
         self.cache.commit(seqs, n_new)
         self.steps_run += 1
         return logits
+
+    # ---- a decode step launched before its input tokens have reached the host --------------------------
+    @property
+    def can_step_ahead(self) -> bool:
+        """Decode steps can be launched from tokens that are still on the device (CUDA graphs, no per-sequence
+        state that a dropped step would have changed)."""
+        return self.graphs is not None and self.debug is None
+
+    def step_ahead(self, seqs: Sequence[Sequence_], tokens_dev: torch.Tensor) -> torch.Tensor:
+        """Launches the decode step whose tokens are `tokens_dev` (int32, one per sequence, on the device: the
+        samples of the step before) and returns its logits, without advancing the sequences: the caller reads the
+        samples on the host meanwhile and then either keeps the step (`commit_ahead`) or, if a sequence turned
+        out to have ended, drops it (`drop_ahead`) and steps again.  A dropped step leaves nothing behind: what it
+        wrote into the cache lies beyond the sequences' lengths and is written again by the step that replaces it."""
+        if not self.can_step_ahead:
+            raise StepError("this engine cannot launch a step ahead")
+        if self._ahead is not None:
+            raise StepError("a step launched ahead is still waiting to be kept or dropped")
+        seqs = list(seqs)
+        if len({s.id for s in seqs}) != len(seqs):
+            raise StepError("a sequence appears twice in one step")
+        for s in seqs:
+            if s.length + 1 > self.model.max_position:
+                raise StepError(f"sequence {s.id} would pass the model's max_position_embeddings")
+        n_new = [1] * len(seqs)
+        self.cache.reserve(seqs, n_new)          # raises CacheFull before anything is written
+        with torch.cuda.device(self.device):
+            logits = self.graphs.step_from_device(seqs, tokens_dev)
+        self._ahead = (seqs, n_new)
+        return logits
+
+    @staticmethod
+    def token_reader(n: int) -> TokenReader:
+        return TokenReader(n)
+
+    def commit_ahead(self) -> None:
+        seqs, n_new = self._ahead
+        self._ahead = None
+        self.cache.commit(seqs, n_new)
+        self.steps_run += 1
+
+    def drop_ahead(self) -> None:
+        self._ahead = None

@@ -132,6 +132,8 @@ class Model:
             raise RuntimeError("the model is closed")
 
     def close(self) -> None:
+        if self._engine is not None:
+            self._engine.release()
         self._engine = None
         self._model = None
         if torch.cuda.is_available():
