@@ -482,8 +482,11 @@ def test_argmax_first_maximum(V):
     assert out.cpu().tolist()[1] == 7
 
 
-@pytest.mark.parametrize("V,temp,top_p", [(257, 0.8, 1.0), (320, 0.7, 0.9), (5000, 1.5, 0.5), (151936, 0.8, 0.95)])
-def test_sample_rows_matches_plain(V, temp, top_p):
+@pytest.mark.parametrize("in_global", [False, True])
+@pytest.mark.parametrize("V,temp,top_p", [(257, 0.8, 1.0), (320, 0.7, 0.9), (5000, 1.5, 0.5), (20011, 1.0, 0.8),
+                                          (151936, 0.8, 0.95)])
+def test_sample_rows_matches_plain(V, temp, top_p, in_global):
+    """Rows shared by 1, 1, 2, 4 and 8 CTAs; the scratch in shared memory and in global memory."""
     from turboquant_cpp_b200.kernels import sampling as KS
     rng = np.random.default_rng(V)
     R = 24
@@ -492,12 +495,38 @@ def test_sample_rows_matches_plain(V, temp, top_p):
     u[0], u[1] = 0.0, 0.99999994
     out = torch.empty(R, dtype=torch.int32, device=DEV)
     work = torch.empty(R * V, dtype=torch.float32, device=DEV)
-    KS.sample_rows(dev(l), temp, top_p, dev(u), work, out)
+    KS.sample_rows(dev(l), temp, top_p, dev(u), work, out, scratch_in_global=in_global)
     want = [P.sample_top_p(l[r], temp, top_p, float(u[r])) for r in range(R)]
     got = out.cpu().tolist()
     # a draw within float rounding of a boundary of the cumulative sum may fall either side
     same = sum(g == w for g, w in zip(got, want))
     assert same >= R - 1, (got, want)
+    # u = 0 takes the first maximum; the largest u ends the walk at the last candidate even when the sums, added
+    # in different orders, disagree in their last bit about whether the target was reached
+    assert got[0] == want[0] == int(np.argmax(l[0])) and got[1] == want[1]
+
+
+@pytest.mark.parametrize("V", [700, 9001, 20000, 151936])
+def test_sample_rows_among_equal_values_goes_by_index(V):
+    """All logits equal: every p is 1, the sum is V exactly, and the draw u picks token ceil(u * V) - 1.  With a
+    row cut over several CTAs this is the hand-over of the count of equal values from one slice to the next."""
+    from turboquant_cpp_b200.kernels import sampling as KS
+    slices = min(8, 1 << ((-(-V // 4096)).bit_length() - 1))
+    edge = -(-V // slices)
+    u = [0.0, 0.5, 0.99999994, 1.0 / V, 0.25, 0.75]
+    for s in range(1, slices):                                # the last token of a slice and the first of the next
+        u += [(s * edge - 0.5) / V, (s * edge + 0.5) / V]
+    u = np.asarray(u, dtype=np.float32)
+    R = len(u)
+    l = np.full((R, V), -3.25, dtype=np.float32)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    work = torch.empty(R * V, dtype=torch.float32, device=DEV)
+    KS.sample_rows(dev(l), 1.0, 1.0, dev(u), work, out)
+    want = [max(1, int(np.ceil(np.float32(x) * np.float32(V)))) - 1 for x in u]
+    assert out.cpu().tolist() == want
+    clear = [r for r in range(R) if 0.25 < (float(u[r]) * V) % 1.0 < 0.75]      # not within rounding of a boundary
+    assert len(clear) >= 2 * (slices - 1)
+    assert [P.sample_top_p(l[r], 1.0, 1.0, float(u[r])) for r in clear] == [want[r] for r in clear]
 
 
 def test_sample_rows_distribution():

@@ -22,8 +22,9 @@ def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 def sample_rows(logits: torch.Tensor, temperature: float, top_p: float, uniforms: torch.Tensor,
-                work: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """Temperature / top-p draw per row from uniforms [R] in [0, 1); work holds R*V floats of scratch."""
+                work: torch.Tensor, out: torch.Tensor, scratch_in_global: bool = False) -> torch.Tensor:
+    """Temperature / top-p draw per row from uniforms [R] in [0, 1).  work holds R*V floats of scratch, used when
+    a row's share per CTA does not fit shared memory (beyond 360,448 columns) or when scratch_in_global asks."""
     want_f32(logits, "logits")
     want_f32(uniforms, "uniforms")
     want_f32(work, "work")
@@ -32,5 +33,5 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_p: float, uniforms
     assert work.numel() >= R * V
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_sample_rows(ptr(logits), c_int(R), c_int(V), c_float(temperature), c_float(top_p),
-                                   ptr(uniforms), ptr(work), ptr(out), stream()))
+                                   ptr(uniforms), ptr(work), c_int(int(scratch_in_global)), ptr(out), stream()))
     return out
