@@ -545,12 +545,20 @@ def test_sample_rows_distribution():
 
 @pytest.mark.parametrize("T,E,k,H,renorm,shared", [(1, 8, 2, 64, False, True), (8, 60, 4, 2048, False, True),
                                                     (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False),
-                                                    (3, 1023, 40, 96, True, True), (128, 300, 4, 64, False, False)])
+                                                    (3, 1023, 40, 96, True, True), (128, 300, 4, 64, False, False),
+                                                    (5, 17, 3, 100, True, True), (7, 60, 4, 2048, False, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype):
-    """The one-launch decode path (a block per token for logits and selection; the block that finishes last
-    does the layout and the gathered rows) gives exactly what the separate kernels give, call after call."""
+@pytest.mark.parametrize("cluster", [True, False])
+def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype, cluster, monkeypatch):
+    """The one-launch decode path gives exactly what the separate kernels give, call after call: a block per
+    token for logits and selection; then, with up to 8 tokens, the blocks are a cluster that passes the choices
+    round in shared memory and every block writes its own rows, else the block that finishes last (a counter)
+    does the layout and the gathered rows."""
     from turboquant_cpp_b200.kernels import elementwise as KE, moe as KM
+    if not cluster:
+        if T > 8:
+            pytest.skip("more than 8 tokens never form a cluster")
+        monkeypatch.setenv("TQ_ROUTER_NO_CLUSTER", "1")
     rng = np.random.default_rng(T + E)
     x = dev(bf16_values(rng.normal(size=(T, H))), dtype)
     wr = dev(bf16_values(rng.normal(size=(E, H)) * 0.3), dtype)

@@ -31,6 +31,15 @@ TQ_DEFINE_LAST_ERROR
 // 16-byte loads, eight elements per lane per step, in a fixed order; warp 0 then does the softmax
 // and the selection.
 // ---------------------------------------------------------------------------------------
+// 16 bytes from global memory with an L2 eviction policy (createpolicy): the router's matrix is a few hundred KB
+// that every step reads again; marked evict-last it stays in the L2 while the experts' weights stream through.
+__device__ __forceinline__ uint4 ld_global_policy(const void* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.b32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+    return v;
+}
+
 template <typename TW> struct RowVec { };
 template <> struct RowVec<__nv_bfloat16> {
     static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
@@ -39,11 +48,33 @@ template <> struct RowVec<__nv_bfloat16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
     }
+    static __device__ __forceinline__ void load_keep(const __nv_bfloat16* p, float (&f)[8], uint64_t policy) {
+        const uint4 v = ld_global_policy(p, policy);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+        uint4 v;
+        uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); u[i] = *reinterpret_cast<const uint32_t*>(&h); }
+        *reinterpret_cast<uint4*>(p) = v;
+    }
 };
 template <> struct RowVec<float> {
     static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
         const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    static __device__ __forceinline__ void load_keep(const float* p, float (&f)[8], uint64_t policy) {
+        const uint4 a = ld_global_policy(p, policy), b = ld_global_policy(p + 4, policy);
+        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
     }
 };
 
@@ -89,10 +120,65 @@ __device__ __forceinline__ float tq_order_value(unsigned key) {      // the inve
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
+// One warp chooses for one row of E <= 32 * SELECT_REGS logits (global or shared memory): a lane keeps its
+// logits in registers and a choice is two warp-wide integer reductions.  picks: where the choices go besides
+// ids_row (shared memory of the caller), or null.
+#define SELECT_REGS 8
+template <int NREG>
+__device__ __forceinline__ void select_with_registers(const float* row, int E, int k, int renorm, int lane,
+                                                      int* __restrict__ ids_row, float* __restrict__ wts_row, int* picks) {
+    float v[NREG];
+    unsigned key[NREG];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < NREG; ++c) {
+        const int e = lane + 32 * c;
+        v[c] = e < E ? row[e] : -INFINITY;
+        key[c] = e < E ? tq_order_key(v[c]) : 0u;
+        mx = fmaxf(mx, v[c]);
+    }
+    mx = tq_warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < NREG; ++c) if (lane + 32 * c < E) sum += expf(v[c] - mx);
+    sum = tq_warp_sum(sum);
+    float picked_sum = 0.f, mine = 0.f;             // lane j % 32 keeps the weight of choice j
+    for (int j = 0; j < k; ++j) {
+        unsigned best = 0;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int c = 0; c < NREG; ++c)
+            if (key[c] > best) { best = key[c]; best_e = lane + 32 * c; }      // lower e first within a lane
+        const unsigned top = __reduce_max_sync(0xffffffffu, best);
+        int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
+        const bool found = pick != 0x7fffffff;
+        if (!found) pick = j;                       // nothing left to pick: keep indices valid
+        const float p = expf((found ? tq_order_value(top) : -INFINITY) - mx) / sum;
+        picked_sum += p;                            // identical in every lane
+#pragma unroll
+        for (int c = 0; c < NREG; ++c) if (found && lane + 32 * c == pick) key[c] = 0u;
+        if (lane == 0) { ids_row[j] = pick; if (picks) picks[j] = pick; }
+        if (j < 32) { if (lane == j) mine = p; }
+        else if (lane == 0) wts_row[j] = p;         // more than 32 choices: the rest go through memory
+    }
+    if (lane < k) wts_row[lane] = renorm ? mine / picked_sum : mine;
+    if (k > 32 && renorm) {
+        __syncwarp();
+        for (int j = 32 + lane; j < k; j += 32) wts_row[j] = wts_row[j] / picked_sum;
+    }
+}
+
+// E <= 32 * SELECT_REGS; the fewer experts, the fewer registers a lane goes through for every choice.
+__device__ __forceinline__ void select_in_registers(const float* row, int E, int k, int renorm, int lane,
+                                                    int* __restrict__ ids_row, float* __restrict__ wts_row, int* picks) {
+    if (E <= 64) select_with_registers<2>(row, E, k, renorm, lane, ids_row, wts_row, picks);
+    else if (E <= 128) select_with_registers<4>(row, E, k, renorm, lane, ids_row, wts_row, picks);
+    else select_with_registers<SELECT_REGS>(row, E, k, renorm, lane, ids_row, wts_row, picks);
+}
+
 // Kernel 2: one warp per token: softmax over the E logits, k largest (ties to the lowest index; NaN never
 // wins), weights, shared gate.  Up to 256 experts a lane keeps its logits in registers and a choice is two
 // warp-wide integer reductions; beyond that the row is re-read from memory and chosen entries overwritten.
-#define SELECT_REGS 8
 __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ wts,
                                      float* __restrict__ shared_scale, int T_, int E, int k, int renorm) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
@@ -103,45 +189,7 @@ __global__ void router_select_kernel(float* __restrict__ logits, int* __restrict
     float* s_logit = logits + (size_t)t * (E + 1);      // this warp's row
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
     if (E <= 32 * SELECT_REGS) {
-        float v[SELECT_REGS];
-        unsigned key[SELECT_REGS];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < SELECT_REGS; ++c) {
-            const int e = lane + 32 * c;
-            v[c] = e < E ? s_logit[e] : -INFINITY;
-            key[c] = e < E ? tq_order_key(v[c]) : 0u;
-            mx = fmaxf(mx, v[c]);
-        }
-        mx = tq_warp_max(mx);
-        float sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < SELECT_REGS; ++c) if (lane + 32 * c < E) sum += expf(v[c] - mx);
-        sum = tq_warp_sum(sum);
-        float picked_sum = 0.f, mine = 0.f;             // lane j % 32 keeps the weight of choice j
-        for (int j = 0; j < k; ++j) {
-            unsigned best = 0;
-            int best_e = 0x7fffffff;
-#pragma unroll
-            for (int c = 0; c < SELECT_REGS; ++c)
-                if (key[c] > best) { best = key[c]; best_e = lane + 32 * c; }      // lower e first within a lane
-            const unsigned top = __reduce_max_sync(0xffffffffu, best);
-            int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
-            const bool found = pick != 0x7fffffff;
-            if (!found) pick = j;                       // nothing left to pick: keep indices valid
-            const float p = expf((found ? tq_order_value(top) : -INFINITY) - mx) / sum;
-            picked_sum += p;                            // identical in every lane
-#pragma unroll
-            for (int c = 0; c < SELECT_REGS; ++c) if (found && lane + 32 * c == pick) key[c] = 0u;
-            if (lane == 0) ids[(size_t)t * k + j] = pick;
-            if (j < 32) { if (lane == j) mine = p; }
-            else if (lane == 0) wts[(size_t)t * k + j] = p;          // more than 32 choices: the rest go through memory
-        }
-        if (lane < k) wts[(size_t)t * k + lane] = renorm ? mine / picked_sum : mine;
-        if (k > 32 && renorm) {
-            __syncwarp();
-            for (int j = 32 + lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / picked_sum;
-        }
+        select_in_registers(s_logit, E, k, renorm, lane, ids + (size_t)t * k, wts + (size_t)t * k, nullptr);
         return;
     }
     float mx = -INFINITY;
@@ -357,15 +405,224 @@ TQ_EXPORT int tq_moe_align(const int* ids, int P, int E, int tile_rows, int chun
 // ---------------------------------------------------------------------------------------
 // Steps with few tokens (decoding): router logits, selection, expert-sorted layout, tile list and the
 // expert-sorted copies of the token rows in ONE launch instead of six that each do microseconds of
-// work.  One block per token computes that token's logits (its row staged in shared memory) and its
-// choices; the block that finishes last (a counter in global memory) lays out all pairs and copies the
-// rows.  The counter is zero between launches: the last block resets it.  Launches that share a counter
-// must not overlap.
+// work.  Two forms:
+//  * up to 8 tokens and 256 experts: eight blocks that are one thread-block cluster.  Block b computes the
+//    logits of ITS SHARE OF THE EXPERTS for all tokens (an SM then reads an eighth of the router matrix, which
+//    it has asked the L2 for before the kernel ahead of it in the stream was done) and stores them into the
+//    shared memory of the block that owns the token; block t chooses for token t; the choices go round through
+//    distributed shared memory; every token's block works out the layout for itself and writes the copies of
+//    its own row from shared memory; block 0 writes the layout.  Between reading the rows and writing the
+//    outputs nothing waits for global memory.
+//  * otherwise: one block per token computes that token's logits and choices; the block that finishes last (a
+//    counter in global memory) lays out all pairs and copies the rows.  The counter is zero between launches:
+//    the last block resets it.  Launches that share a counter must not overlap.
 // ---------------------------------------------------------------------------------------
 #define SMALL_MAX_PAIRS 512
 #define SMALL_MAX_EXPERTS 1023      // the scan over the experts gives thread E the totals: E < blockDim.x
 #define SMALL_THREADS 1024
+#define SMALL_DYNAMIC_BYTES (27 * 1024)     // what the kernel's own arrays leave of the 48 KiB a block gets without asking
+#define SMALL_CLUSTER 8                     // blocks of the cluster form, and the most tokens it takes
+#define SMALL_CLUSTER_DYNAMIC_BYTES (160 * 1024)
 
+struct SmallShared {
+    int ids[SMALL_MAX_PAIRS], row[SMALL_MAX_PAIRS], mine[SMALL_MAX_PAIRS];
+    int count[SMALL_MAX_EXPERTS + 1], off[SMALL_MAX_EXPERTS + 1], toff[SMALL_MAX_EXPERTS + 1];
+    int wrows[32], wtiles[32];
+};
+
+// Layout of the P pairs whose experts are in S.ids, by all threads of a block of SMALL_THREADS: S.row[row] =
+// pair, and for the pairs of token `own` (if >= 0) S.mine[j] = row of its choice j.  writer: this block writes
+// the layout to global memory.
+__device__ __forceinline__ void small_layout(SmallShared& S, int P, int E, int k, int tile_rows, int own, bool writer,
+                                             int* __restrict__ counts, int* __restrict__ sorted_pair,
+                                             int* __restrict__ row_of_pair, int* __restrict__ expert_offset,
+                                             int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                             int* __restrict__ tile_count, int* __restrict__ n_tiles) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) S.count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&S.count[S.ids[p]], 1);
+    __syncthreads();
+    {   // offsets of rows and of tiles before expert e: a scan over the experts (E < blockDim.x = 1024)
+        const int e = threadIdx.x;
+        const int c = e < E ? S.count[e] : 0, tl = (c + tile_rows - 1) / tile_rows;
+        int r_incl = c, t_incl = tl;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, r_incl, o), u = __shfl_up_sync(0xffffffffu, t_incl, o);
+            if (lane >= o) { r_incl += r; t_incl += u; }
+        }
+        if (lane == 31) { S.wrows[warp] = r_incl; S.wtiles[warp] = t_incl; }
+        __syncthreads();
+        if (warp == 0) {
+            int r = lane < nwarps ? S.wrows[lane] : 0, u = lane < nwarps ? S.wtiles[lane] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int r2 = __shfl_up_sync(0xffffffffu, r, o), u2 = __shfl_up_sync(0xffffffffu, u, o);
+                if (lane >= o) { r += r2; u += u2; }
+            }
+            S.wrows[lane] = r;                                // inclusive over warps
+            S.wtiles[lane] = u;
+        }
+        __syncthreads();
+        const int r_before = (warp > 0 ? S.wrows[warp - 1] : 0) + r_incl - c;
+        const int t_before = (warp > 0 ? S.wtiles[warp - 1] : 0) + t_incl - tl;
+        if (e <= E) {
+            S.off[e] = r_before;
+            S.toff[e] = t_before;
+            if (writer) {
+                expert_offset[e] = r_before;
+                if (e < E) counts[e] = c;
+                if (e == E) n_tiles[0] = t_before;
+            }
+        }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {       // stable: pairs of an expert keep their order
+        const int e = S.ids[p];
+        int rank = 0;
+        for (int q = 0; q < p; ++q) rank += S.ids[q] == e;
+        const int row = S.off[e] + rank;
+        S.row[row] = p;
+        if (p / k == own) S.mine[p % k] = row;
+        if (writer) {
+            sorted_pair[row] = p;
+            row_of_pair[p] = row;
+        }
+    }
+    if (writer)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            const int c = S.count[e], nt = (c + tile_rows - 1) / tile_rows;     // c <= 512: the products fit an int
+            for (int i = 0; i < nt; ++i) {                    // an expert's rows split evenly over its tiles
+                const int r0 = c * i / nt, r1 = c * (i + 1) / nt;
+                tile_expert[S.toff[e] + i] = e;
+                tile_row0[S.toff[e] + i] = S.off[e] + r0;
+                tile_count[S.toff[e] + i] = r1 - r0;
+            }
+        }
+    __syncthreads();
+}
+
+// ---- the cluster form ----
+__device__ __forceinline__ unsigned small_cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void small_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned small_peer_addr(const void* mine, unsigned rank) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(mine);
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ int small_ld_peer(const int* mine, unsigned rank) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(small_peer_addr(mine, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void small_st_peer(float* mine, unsigned rank, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(small_peer_addr(mine, rank)), "f"(v) : "memory");
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(SMALL_THREADS)
+router_cluster_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
+                      int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_scale,
+                      int T_, int H, int E, int k, int renorm, int vec_dot, int tile_rows,
+                      int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                      int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                      int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x) {
+    const unsigned rank = small_cluster_rank();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    // a block's shared memory may be written by its peers only once it runs: every block says so here and
+    // waits for the others just before its first store
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    // this block's share of the rows of the router matrix (the shared expert's gate row counts as row E)
+    const int rows = E + (wsg ? 1 : 0);
+    const int per = (rows + SMALL_CLUSTER - 1) / SMALL_CLUSTER;
+    const int r0 = min(rows, (int)rank * per), r1 = min(rows, r0 + per);
+    {   // the weights do not depend on the kernel before this one: ask the L2 for them while that kernel still
+        // runs (between two uses a whole step's weights pass through the L2)
+        const long long bytes = (long long)(min(r1, E) - r0) * H * (long long)sizeof(TW);
+        const char* base = reinterpret_cast<const char*>(wr + (size_t)r0 * H);
+        for (long long off = (long long)threadIdx.x * 128; off < bytes; off += (long long)blockDim.x * 128)
+            asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(base + off));
+    }
+    uint64_t keep;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
+    tq_grid_wait();
+    tq_grid_launch_dependents();
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    float* s_logit = reinterpret_cast<float*>(s_raw);                         // [E + 1] the logits of this block's token
+    TA* s_x = reinterpret_cast<TA*>(s_raw + (((size_t)(E + 1) * 4 + 15) & ~(size_t)15));   // [T][H] the step's rows
+    __shared__ SmallShared S;
+    if (vec_x) {
+        const int n16 = (int)((size_t)T_ * H * sizeof(TA) / 16);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(x)[i];
+    } else {
+        for (int i = threadIdx.x; i < T_ * H; i += blockDim.x) s_x[i] = x[i];
+    }
+    __syncthreads();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // all blocks of the cluster run
+    // ---- logits of rows [r0, r1) for all tokens, two tokens per pass over a row (the same sums, in the same
+    //      order, as router_logits_kernel); each lands in the shared memory of its token's block ----
+    const int Hv = vec_dot ? (H / 8) * 8 : 0;
+    const int TG = (T_ + 1) / 2;
+    for (int item = warp; item < (r1 - r0) * TG; item += nwarps) {
+        const int e = r0 + item / TG, t0 = (item % TG) * 2, t1 = min(t0 + 1, T_ - 1);
+        const TW* w = e < E ? wr + (size_t)e * H : wsg;
+        const TA* xa = s_x + (size_t)t0 * H;
+        const TA* xb = s_x + (size_t)t1 * H;
+        float s = 0.f, s2 = 0.f;
+#pragma unroll 8
+        for (int i = lane * 8; i < Hv; i += 256) {
+            float f[8], a[8], b[8];
+            RowVec<TW>::load_keep(w + i, f, keep);
+            RowVec<TA>::load(xa + i, a);
+            RowVec<TA>::load(xb + i, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { s = fmaf(a[j], f[j], s); s2 = fmaf(b[j], f[j], s2); }
+        }
+        for (int i = Hv + lane; i < H; i += 32) {
+            const float f = tq_to_float(w[i]);
+            s = fmaf(tq_to_float(xa[i]), f, s);
+            s2 = fmaf(tq_to_float(xb[i]), f, s2);
+        }
+        s = tq_warp_sum(s);
+        s2 = tq_warp_sum(s2);
+        if (lane == 0) {
+            small_st_peer(&s_logit[e], (unsigned)t0, s);
+            if (t1 != t0) small_st_peer(&s_logit[e], (unsigned)t1, s2);
+        }
+    }
+    small_cluster_sync();                                     // every token's logits are in its block
+    const int t = (int)rank;
+    if (t < T_ && warp == 0) {
+        if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
+        select_in_registers(s_logit, E, k, renorm, lane, ids + (size_t)t * k, wts + (size_t)t * k, S.mine);
+    }
+    small_cluster_sync();                                     // every token's choices are in its block
+    const int P = T_ * k;
+    if (t < T_)
+        for (int p = threadIdx.x; p < P; p += blockDim.x) S.ids[p] = small_ld_peer(&S.mine[p % k], (unsigned)(p / k));
+    small_cluster_sync();                                     // nobody reads a peer's memory after this: blocks may leave
+    if (t >= T_) return;
+    small_layout(S, P, E, k, tile_rows, t, t == 0, counts, sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0,
+                 tile_count, n_tiles);
+    // this token's row, still in shared memory, to each of its k places
+    const TA* mine = s_x + (size_t)t * H;
+    if (vec_x) {
+        const int n16 = (int)((size_t)H * sizeof(TA) / 16);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+            const uint4 v = reinterpret_cast<const uint4*>(mine)[i];
+            for (int j = 0; j < k; ++j) reinterpret_cast<uint4*>(x_rows + (size_t)S.mine[j] * H)[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x)
+            for (int j = 0; j < k; ++j) x_rows[(size_t)S.mine[j] * H + i] = mine[i];
+    }
+}
+
+// ---- the counter form ----
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(SMALL_THREADS)
 router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const TW* __restrict__ wsg,
@@ -380,8 +637,7 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     extern __shared__ float s_dyn[];
     float* s_x = s_dyn;               // [H] the token's row
     float* s_logit = s_dyn + H;       // [E + 1] router logits, then the shared expert's gate logit
-    __shared__ int s_ids[SMALL_MAX_PAIRS], s_row[SMALL_MAX_PAIRS];
-    __shared__ int s_count[SMALL_MAX_EXPERTS + 1], s_off[SMALL_MAX_EXPERTS + 1], s_toff[SMALL_MAX_EXPERTS + 1];
+    __shared__ SmallShared S;
     __shared__ int s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -418,37 +674,41 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     // ---- selection: warp 0 (the same choices and weights as router_select_kernel) ----
     if (warp == 0) {
         if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
-        float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
-        mx = tq_warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
-        sum = tq_warp_sum(sum);
-        float* s_val = s_x;                                   // the row is no longer needed: its place holds the k picked logits
-        for (int j = 0; j < k; ++j) {
-            // largest remaining logit, ties to the lowest index; NaN and -inf (already picked) never win
-            unsigned best = 0;
-            int best_e = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const unsigned key = tq_order_key(s_logit[e]);
-                if (key > best) { best = key; best_e = e; }   // lower e first within a lane
+        if (E <= 32 * SELECT_REGS) {
+            select_in_registers(s_logit, E, k, renorm, lane, ids + (size_t)t * k, wts + (size_t)t * k, nullptr);
+        } else {
+            float mx = -INFINITY;
+            for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_logit[e]);
+            mx = tq_warp_max(mx);
+            float sum = 0.f;
+            for (int e = lane; e < E; e += 32) sum += expf(s_logit[e] - mx);
+            sum = tq_warp_sum(sum);
+            float* s_val = s_x;                               // the row is no longer needed: its place holds the k picked logits
+            for (int j = 0; j < k; ++j) {
+                // largest remaining logit, ties to the lowest index; NaN and -inf (already picked) never win
+                unsigned best = 0;
+                int best_e = 0x7fffffff;
+                for (int e = lane; e < E; e += 32) {
+                    const unsigned key = tq_order_key(s_logit[e]);
+                    if (key > best) { best = key; best_e = e; }   // lower e first within a lane
+                }
+                const unsigned top = __reduce_max_sync(0xffffffffu, best);
+                int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
+                if (pick == 0x7fffffff) pick = j;             // nothing left to pick: keep indices valid
+                if (lane == 0) {
+                    ids[(size_t)t * k + j] = pick;
+                    s_val[j] = top != 0u ? s_logit[pick] : -INFINITY;
+                    s_logit[pick] = -INFINITY;
+                }
+                __syncwarp();
             }
-            const unsigned top = __reduce_max_sync(0xffffffffu, best);
-            int pick = __reduce_min_sync(0xffffffffu, (best == top && top != 0u) ? best_e : 0x7fffffff);
-            if (pick == 0x7fffffff) pick = j;                 // nothing left to pick: keep indices valid
-            if (lane == 0) {
-                ids[(size_t)t * k + j] = pick;
-                s_val[j] = top != 0u ? s_logit[pick] : -INFINITY;
-                s_logit[pick] = -INFINITY;
-            }
+            // weights: lanes take the exponentials, every lane adds them up in the order of the choices
+            for (int j = lane; j < k; j += 32) s_val[j] = expf(s_val[j] - mx) / sum;
             __syncwarp();
+            float picked_sum = 0.f;
+            if (renorm) for (int j = 0; j < k; ++j) picked_sum += s_val[j];
+            for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = renorm ? s_val[j] / picked_sum : s_val[j];
         }
-        // weights: lanes take the exponentials, every lane adds them up in the order of the choices
-        for (int j = lane; j < k; j += 32) s_val[j] = expf(s_val[j] - mx) / sum;
-        __syncwarp();
-        float picked_sum = 0.f;
-        if (renorm) for (int j = 0; j < k; ++j) picked_sum += s_val[j];
-        for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = renorm ? s_val[j] / picked_sum : s_val[j];
         __threadfence();                                      // this token's choices are visible before the count
         __syncwarp();
         if (lane == 0) s_last = atomicAdd(counter, 1) == T_ - 1;
@@ -458,66 +718,12 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     // ---- the last block: layout of all pairs, tile list, expert-sorted copies of the rows ----
     __threadfence();
     const int P = T_ * k;
-    for (int p = threadIdx.x; p < P; p += blockDim.x) s_ids[p] = __ldcg(ids + p);
-    for (int e = threadIdx.x; e < E; e += blockDim.x) s_count[e] = 0;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) S.ids[p] = __ldcg(ids + p);
     __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&s_count[s_ids[p]], 1);
-    __syncthreads();
-    {   // offsets of rows and of tiles before expert e: a scan over the experts (E <= blockDim.x = 1024)
-        __shared__ int s_wrows[32], s_wtiles[32];
-        const int e = threadIdx.x;
-        const int c = e < E ? s_count[e] : 0, tl = (c + tile_rows - 1) / tile_rows;
-        int r_incl = c, t_incl = tl;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int r = __shfl_up_sync(0xffffffffu, r_incl, o), u = __shfl_up_sync(0xffffffffu, t_incl, o);
-            if (lane >= o) { r_incl += r; t_incl += u; }
-        }
-        if (lane == 31) { s_wrows[warp] = r_incl; s_wtiles[warp] = t_incl; }
-        __syncthreads();
-        if (warp == 0) {
-            int r = lane < nwarps ? s_wrows[lane] : 0, u = lane < nwarps ? s_wtiles[lane] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int r2 = __shfl_up_sync(0xffffffffu, r, o), u2 = __shfl_up_sync(0xffffffffu, u, o);
-                if (lane >= o) { r += r2; u += u2; }
-            }
-            s_wrows[lane] = r;                                // inclusive over warps
-            s_wtiles[lane] = u;
-        }
-        __syncthreads();
-        const int r_before = (warp > 0 ? s_wrows[warp - 1] : 0) + r_incl - c;
-        const int t_before = (warp > 0 ? s_wtiles[warp - 1] : 0) + t_incl - tl;
-        if (e <= E) {
-            s_off[e] = r_before;
-            s_toff[e] = t_before;
-            expert_offset[e] = r_before;
-            if (e < E) counts[e] = c;
-            if (e == E) n_tiles[0] = t_before;
-        }
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x) {       // stable: pairs of an expert keep their order
-        const int e = s_ids[p];
-        int rank = 0;
-        for (int q = 0; q < p; ++q) rank += s_ids[q] == e;
-        const int row = s_off[e] + rank;
-        s_row[row] = p;
-        sorted_pair[row] = p;
-        row_of_pair[p] = row;
-    }
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const int c = s_count[e], nt = (c + tile_rows - 1) / tile_rows;
-        for (int i = 0; i < nt; ++i) {                        // an expert's rows split evenly over its tiles
-            const int r0 = (int)((long long)c * i / nt), r1 = (int)((long long)c * (i + 1) / nt);
-            tile_expert[s_toff[e] + i] = e;
-            tile_row0[s_toff[e] + i] = s_off[e] + r0;
-            tile_count[s_toff[e] + i] = r1 - r0;
-        }
-    }
-    __syncthreads();
+    small_layout(S, P, E, k, tile_rows, -1, true, counts, sorted_pair, row_of_pair, expert_offset, tile_expert, tile_row0,
+                 tile_count, n_tiles);
     for (int row = warp; row < P; row += nwarps) {            // expert-sorted copies of the token rows
-        const TA* src = x + (size_t)(s_row[row] / k) * H;
+        const TA* src = x + (size_t)(S.row[row] / k) * H;
         TA* dst = x_rows + (size_t)row * H;
         if (vec_x) {
             const int n16 = (int)((size_t)H * sizeof(TA) / 16);
@@ -537,8 +743,21 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     if (threadIdx.x == 0) *counter = 0;                       // ready for the next launch
 }
 
+template <typename TA, typename TW, typename... Args>
+static cudaError_t launch_router_cluster(size_t smem, cudaStream_t stream, Args... args) {
+    auto kern = router_cluster_kernel<TA, TW>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMALL_CLUSTER_DYNAMIC_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    tq_launch(SMALL_CLUSTER, SMALL_THREADS, smem, stream, SMALL_CLUSTER)(kern, args...);
+    return cudaSuccess;
+}
+
 // Router, expert-sorted layout and gathered rows for a step of few tokens, in one launch.
-// Needs T*k <= 512 pairs, E <= 1023 experts and (H + E + 1) floats of shared memory within 48 KiB;
+// Needs T*k <= 512 pairs, E <= 1023 experts and (H + E + 1) floats of shared memory within 27 KiB;
 // counter: one int in device memory, zero before the first launch (the kernel leaves it zero).
 TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
                               int* ids, float* wts, float* shared_scale, int tile_rows, int* counts, int* sorted_pair,
@@ -552,15 +771,32 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
     TQ_REQUIRE((wsg == nullptr) == (shared_scale == nullptr), "router: shared gate weight and output must come together");
     TQ_REQUIRE(counter != nullptr, "router_small: a counter is required");
     const size_t smem = (size_t)(H + E + 1) * sizeof(float);
-    TQ_REQUIRE(smem <= 48 * 1024, "router_small: a row of %d values and %d logits do not fit 48 KiB of shared memory", H, E);
+    TQ_REQUIRE(smem <= SMALL_DYNAMIC_BYTES, "router_small: a row of %d values and %d logits do not fit %d bytes of shared memory",
+               H, E, SMALL_DYNAMIC_BYTES);
     const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
     const int vec_w = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
     const int abytes = act_dtype == TQ_F32 ? 4 : 2;
     const int vec_x = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
-    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
-        (tq_launch(T_, SMALL_THREADS, smem, stream)(router_small_kernel<TA, TW>, (const TA*)x, (const TW*)wr, (const TW*)wsg,
-            ids, wts, shared_scale, T_, H, E, k, renorm, vec_w, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
-            tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter))));
+    // the cluster form (TQ_ROUTER_NO_CLUSTER=1: the counter form after all)
+    const size_t smem_cluster = (((size_t)(E + 1) * 4 + 15) & ~(size_t)15) + (size_t)T_ * H * abytes;
+    const char* no_cluster = getenv("TQ_ROUTER_NO_CLUSTER");
+    const bool cluster = T_ <= SMALL_CLUSTER && E <= 32 * SELECT_REGS && smem_cluster <= SMALL_CLUSTER_DYNAMIC_BYTES &&
+                         (vec_x || !vec_w) &&       // the order of a sum follows the weights' loads; the rows must allow the same
+                         !(no_cluster && no_cluster[0] && no_cluster[0] != '0');
+    if (cluster) {
+        const int vec_dot = vec_w;                            // 16-byte loads of the weights and of the rows in shared memory
+        cudaError_t cfg = cudaSuccess;
+        TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
+            (cfg = launch_router_cluster<TA, TW>(smem_cluster, stream, (const TA*)x, (const TW*)wr, (const TW*)wsg,
+                ids, wts, shared_scale, T_, H, E, k, renorm, vec_dot, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
+                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x))));
+        TQ_REQUIRE(cfg == cudaSuccess, "router_small: %zu bytes of shared memory refused: %s", smem_cluster, cudaGetErrorString(cfg));
+    } else {
+        TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
+            (tq_launch(T_, SMALL_THREADS, smem, stream)(router_small_kernel<TA, TW>, (const TA*)x, (const TW*)wr, (const TW*)wsg,
+                ids, wts, shared_scale, T_, H, E, k, renorm, vec_w, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
+                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter))));
+    }
     TQ_CHECK_LAUNCH("router_small");
     return 0;
 }

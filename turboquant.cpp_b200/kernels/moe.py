@@ -78,7 +78,7 @@ SMALL_PAIRS_WORTH_IT = 128                           # beyond this one block is 
 
 def router_small_usable(n_tokens: int, top_k: int, n_experts: int, hidden: int) -> bool:
     return (n_tokens * top_k <= SMALL_MAX_PAIRS and n_experts <= SMALL_MAX_EXPERTS
-            and (hidden + n_experts + 1) * 4 <= 48 * 1024)
+            and (hidden + n_experts + 1) * 4 <= 27 * 1024)
 
 
 def router_small_pays(n_tokens: int, top_k: int, n_experts: int, hidden: int) -> bool:
