@@ -135,7 +135,8 @@ def test_attention(nh, nkv, hd, window, dtype, tol):
     close(out, want, tol)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (8, 1, 64), (16, 16, 128), (14, 2, 128), (3, 1, 256)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (8, 1, 64), (16, 16, 128), (14, 2, 128), (3, 1, 256),
+                                       (5, 5, 64)])
 @pytest.mark.parametrize("window", [0, 7, 70])
 @pytest.mark.parametrize("n_splits", [1, 3, 16])
 @pytest.mark.parametrize("dtype,tol", DTYPES)
@@ -160,6 +161,31 @@ def test_attention_split(nh, nkv, hd, window, n_splits, dtype, tol):
         want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
         t0 += ql
     close(out, want, tol)
+
+
+@pytest.mark.parametrize("nh,hd", [(3, 128), (2, 64)])
+@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 4), (900, 7)])
+def test_attention_split_ring_equals_registers(nh, hd, window, n_splits, monkeypatch):
+    """With one query head per KV head in bfloat16 the keys and values go through a ring of cp.async copies in
+    shared memory; the arithmetic is that of the register path, so both give the same bits, also where a
+    range of keys is shorter than the ring is deep, ends inside a group of eight, or starts at a window's edge."""
+    from turboquant_cpp_b200.kernels import attention as KA
+    rng = np.random.default_rng(nh + hd + window)
+    seq_lens, q_lens, page = [2000, 1, 9, 37, 1333], [1, 1, 2, 1, 3], 64
+    d = paged_inputs(rng, seq_lens, q_lens, nh, hd, page, torch.bfloat16)
+    T = sum(q_lens)
+    q = dev(bf16_values(rng.normal(size=(T, nh, hd))), torch.bfloat16)
+    outs = []
+    for no_ring in ("0", "1"):
+        monkeypatch.setenv("TQ_SPLIT_NO_RING", no_ring)
+        out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+        partial = torch.full((T * nh * n_splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
+        KA.attention_split(q, dev(d["cache"], torch.bfloat16), dev(d["positions"], torch.int32),
+                           dev(d["seq_of"], torch.int32), dev(d["table"], torch.int32), page, window, 1 / math.sqrt(hd),
+                           out, nh, nh, hd, n_splits, partial)
+        outs.append((out, partial))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1].nan_to_num(nan=-7.0), outs[1][1].nan_to_num(nan=-7.0))
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(2, 2, 128), (6, 2, 128), (4, 1, 64), (3, 3, 64)])

@@ -281,10 +281,30 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
 // each (two for fp32), so a warp covers 32/LPK keys per instruction and eight keys per iteration
 // with all loads in flight together; the G query heads that share the KV head are computed from
 // the same registers.  Partial state per (token, head, split): max, sum, hd weighted values (fp32).
+// STAGES > 0 (bfloat16, one query head per KV head, head size 64 or 128): the loads are 16-byte
+// cp.async copies into a ring in shared memory, STAGES - 1 groups ahead of the one being computed,
+// every lane copying and reading back only its own 16 bytes (no barrier between the warps).  The speed
+// of this kernel is the bytes it keeps in flight over the DRAM's latency under load; with one group ahead
+// in registers that is 64 KiB per SM, with the ring 128 KiB.  The arithmetic and its order are the same.
 // ---------------------------------------------------------------------------------------
 #define SPLIT_WARPS 4
 
-template <typename TA, int LPK, int GC>
+__device__ __forceinline__ void split_copy16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void split_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void split_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// bytes of the ring: warps x stages x (K and V loads of a group) x 32 lanes x 16 bytes
+template <typename TA, int LPK, int STAGES> constexpr int split_ring_bytes() {
+    constexpr int KPI = 32 / LPK, GS = KPI > 8 ? KPI : 8, LOADS = GS / KPI;
+    return SPLIT_WARPS * STAGES * 2 * LOADS * 32 * 16;
+}
+
+// stages of the ring for an element type and head size (0: loads through registers)
+template <typename TA, int LPK> constexpr int split_stages() { return sizeof(TA) == 2 ? (LPK == 16 ? 3 : (LPK == 8 ? 5 : 0)) : 0; }
+
+template <typename TA, int LPK, int GC, int STAGES>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
@@ -322,6 +342,7 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
         for (int i = 0; i < 8; ++i) { qv[h][i] = f[i] * scale; acc[h][i] = 0.f; }
     }
     using Raw = typename Vec8<TA>::Raw;
+    static_assert(STAGES == 0 || sizeof(Raw) == 16, "the ring holds 16-byte loads");
     // the keys and values of a group of GS positions, as this lane reads them
     auto fetch_group = [&](int grp, Raw (&kr)[LOADS], Raw (&vr)[LOADS]) {
         const int p0 = grp * GS;
@@ -334,13 +355,48 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
         for (int j = 0; j < LOADS; ++j) vr[j] = Vec8<TA>::fetch(vbase + (size_t)(j * KPI + part) * HD + sub * 8);
     };
     Raw kr[LOADS], vr[LOADS];
-    if (gb + warp < ge) fetch_group(gb + warp, kr, vr);
+    // the ring: [warp][stage][K loads, then V loads][lane] of 16 bytes, a lane's own slots only
+    extern __shared__ __align__(16) unsigned char s_split_ring[];
+    Raw* ring = reinterpret_cast<Raw*>(s_split_ring) + (size_t)warp * (STAGES > 0 ? STAGES : 1) * 2 * LOADS * 32 + lane;
+    auto copy_group = [&](int grp, int stage) {
+        const int p0 = grp * GS;
+        const int page = table[p0 / page_size];
+        const TA* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
+        const TA* vbase = kbase + (size_t)nkv * page_size * HD;
+        Raw* dst = ring + (size_t)stage * 2 * LOADS * 32;
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) split_copy16(dst + j * 32, kbase + (size_t)(j * KPI + part) * HD + sub * 8);
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) split_copy16(dst + (LOADS + j) * 32, vbase + (size_t)(j * KPI + part) * HD + sub * 8);
+    };
+    int next_grp = gb + warp, next_stage = 0, stage = 0;     // ring: the next group to copy and where; the stage to read
+    if (STAGES > 0) {
+#pragma unroll
+        for (int i = 0; i < STAGES - 1; ++i) {                // one commit per group, also past the end: the count is uniform
+            if (next_grp < ge) copy_group(next_grp, next_stage);
+            split_commit();
+            next_grp += SPLIT_WARPS;
+            next_stage = next_stage + 1 == STAGES ? 0 : next_stage + 1;
+        }
+    } else if (gb + warp < ge) fetch_group(gb + warp, kr, vr);
     for (int grp = gb + warp; grp < ge; grp += SPLIT_WARPS) {
         const int p0 = grp * GS;
         float kf[LOADS][8], vf[LOADS][8];
+        if (STAGES > 0) {
+            // the slot filled now was read one iteration ago, and what was read there has been used since
+            if (next_grp < ge) copy_group(next_grp, next_stage);
+            split_commit();
+            next_grp += SPLIT_WARPS;
+            next_stage = next_stage + 1 == STAGES ? 0 : next_stage + 1;
+            split_wait<(STAGES > 0 ? STAGES - 1 : 0)>();      // all but the newest STAGES - 1 groups have landed: this one has
+            const Raw* src = ring + (size_t)stage * 2 * LOADS * 32;
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) { kr[j] = src[j * 32]; vr[j] = src[(LOADS + j) * 32]; }
+            stage = stage + 1 == STAGES ? 0 : stage + 1;
+        }
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) { Vec8<TA>::widen(kr[j], kf[j]); Vec8<TA>::widen(vr[j], vf[j]); }
-        if (grp + SPLIT_WARPS < ge) fetch_group(grp + SPLIT_WARPS, kr, vr);      // next group's loads fly during this one's math
+        if (STAGES == 0 && grp + SPLIT_WARPS < ge) fetch_group(grp + SPLIT_WARPS, kr, vr);      // next group's loads fly during this one's math
         float s[LOADS][GC];
 #pragma unroll
         for (int j = 0; j < LOADS; ++j)
@@ -446,13 +502,28 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_split: bad grid (%d splits, %d KV heads)", n_splits, nkv);
     TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
     dim3 grid(T_, nkv, n_splits);
-#define SPLIT_LAUNCH(TA, LPK, GC)                                                                               \
-    tq_launch(grid, SPLIT_WARPS * 32, 0, stream)(attention_split_kernel<TA, LPK, GC>,                                  \
-        (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window,   \
-        scale, partial, n_splits, nh, nkv)
+    const char* no_ring_env = getenv("TQ_SPLIT_NO_RING");     // 1: loads through registers for every shape
+    const bool no_ring = no_ring_env && no_ring_env[0] && no_ring_env[0] != '0';
+#define SPLIT_LAUNCH(TA, LPK, GC, STAGES)                                                                       \
+    do {                                                                                                        \
+        auto kern = attention_split_kernel<TA, LPK, GC, STAGES>;                                                \
+        constexpr int ring = split_ring_bytes<TA, LPK, STAGES>();                                               \
+        static bool configured = false;                                                                         \
+        if (ring > 0 && !configured) {                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ring);      \
+            if (e != cudaSuccess) TQ_FAIL(-1, "attention_split: %d bytes of shared memory refused: %s", ring, cudaGetErrorString(e)); \
+            configured = true;                                                                                  \
+        }                                                                                                       \
+        tq_launch(grid, SPLIT_WARPS * 32, ring, stream)(kern,                                                   \
+            (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window, \
+            scale, partial, n_splits, nh, nkv);                                                                 \
+    } while (0)
+    // the shared-memory ring: bfloat16, one query head per KV head, head size 128 (three stages) or 64 (five)
 #define SPLIT_GC(TA, LPK)                                                                                       \
-    do { if (G == 1) SPLIT_LAUNCH(TA, LPK, 1); else if (G == 2) SPLIT_LAUNCH(TA, LPK, 2);                       \
-         else if (G <= 4) SPLIT_LAUNCH(TA, LPK, 4); else SPLIT_LAUNCH(TA, LPK, 8); } while (0)
+    do { if (G == 1) { if (!no_ring && split_stages<TA, LPK>() > 0) SPLIT_LAUNCH(TA, LPK, 1, (split_stages<TA, LPK>()));   \
+                       else SPLIT_LAUNCH(TA, LPK, 1, 0); }                                                      \
+         else if (G == 2) SPLIT_LAUNCH(TA, LPK, 2, 0);                                                          \
+         else if (G <= 4) SPLIT_LAUNCH(TA, LPK, 4, 0); else SPLIT_LAUNCH(TA, LPK, 8, 0); } while (0)
 #define SPLIT_HD(TA)                                                                                            \
     do { if (hd == 16) SPLIT_GC(TA, 2); else if (hd == 32) SPLIT_GC(TA, 4); else if (hd == 64) SPLIT_GC(TA, 8);         \
          else if (hd == 128) SPLIT_GC(TA, 16); else SPLIT_GC(TA, 32); } while (0)
