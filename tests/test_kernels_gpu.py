@@ -163,12 +163,13 @@ def test_attention_split(nh, nkv, hd, window, n_splits, dtype, tol):
     close(out, want, tol)
 
 
-@pytest.mark.parametrize("nh,hd", [(3, 128), (2, 64)])
+@pytest.mark.parametrize("nh,hd", [(3, 128), (1, 128)])
 @pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 4), (900, 7)])
 def test_attention_split_ring_equals_registers(nh, hd, window, n_splits, monkeypatch):
-    """With one query head per KV head in bfloat16 the keys and values go through a ring of cp.async copies in
-    shared memory; the arithmetic is that of the register path, so both give the same bits, also where a
-    range of keys is shorter than the ring is deep, ends inside a group of eight, or starts at a window's edge."""
+    """With one query head per KV head of size 128 in bfloat16, large launches bring keys and values in through a
+    ring of cp.async copies in shared memory; the arithmetic is that of the register form, so both give the same
+    bits, also where a range of keys is shorter than the ring is deep, ends inside a group of eight, or starts at a
+    window's edge."""
     from turboquant_cpp_b200.kernels import attention as KA
     rng = np.random.default_rng(nh + hd + window)
     seq_lens, q_lens, page = [2000, 1, 9, 37, 1333], [1, 1, 2, 1, 3], 64
@@ -176,8 +177,8 @@ def test_attention_split_ring_equals_registers(nh, hd, window, n_splits, monkeyp
     T = sum(q_lens)
     q = dev(bf16_values(rng.normal(size=(T, nh, hd))), torch.bfloat16)
     outs = []
-    for no_ring in ("0", "1"):
-        monkeypatch.setenv("TQ_SPLIT_NO_RING", no_ring)
+    for ring in ("1", "0"):
+        monkeypatch.setenv("TQ_SPLIT_RING", ring)
         out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
         partial = torch.full((T * nh * n_splits * (hd + 2),), float("nan"), dtype=torch.float32, device=DEV)
         KA.attention_split(q, dev(d["cache"], torch.bfloat16), dev(d["positions"], torch.int32),

@@ -281,13 +281,17 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
 // each (two for fp32), so a warp covers 32/LPK keys per instruction and eight keys per iteration
 // with all loads in flight together; the G query heads that share the KV head are computed from
 // the same registers.  Partial state per (token, head, split): max, sum, hd weighted values (fp32).
-// STAGES > 0 (bfloat16, one query head per KV head, head size 64 or 128): the loads are 16-byte
-// cp.async copies into a ring in shared memory, STAGES - 1 groups ahead of the one being computed,
-// every lane copying and reading back only its own 16 bytes (no barrier between the warps).  The speed
-// of this kernel is the bytes it keeps in flight over the DRAM's latency under load; with one group ahead
-// in registers that is 64 KiB per SM, with the ring 128 KiB.  The arithmetic and its order are the same.
+// STAGES > 0 (bfloat16, one query head per KV head, head size 128): the loads are 16-byte cp.async
+// copies into a ring in shared memory, STAGES - 1 groups ahead of the one being computed, every lane
+// copying and reading back only its own 16 bytes (no barrier between the warps).  The arithmetic and its
+// order are the same, so both forms give the same bits.  With two stages the kernel needs 48 registers
+// instead of 113 and 36 KiB of shared memory: six CTAs per SM instead of four.  Measured on B200 at 16
+// heads x 128 and 2,048 keys: 64 tokens (4,096 CTAs) 170 us against 180 us; 8 tokens (512 CTAs, less than
+// one wave either way) 28 us against 29 us alone but 2 us per layer slower inside a decode step.  So the
+// ring serves launches of more than two waves of the register form, and the registers the others.
 // ---------------------------------------------------------------------------------------
 #define SPLIT_WARPS 4
+#define SPLIT_REGISTER_RESIDENT 592     // CTAs of the register form a B200 runs at once (148 SMs x 4)
 
 __device__ __forceinline__ void split_copy16(void* smem_dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
@@ -301,8 +305,8 @@ template <typename TA, int LPK, int STAGES> constexpr int split_ring_bytes() {
     return SPLIT_WARPS * STAGES * 2 * LOADS * 32 * 16;
 }
 
-// stages of the ring for an element type and head size (0: loads through registers)
-template <typename TA, int LPK> constexpr int split_stages() { return sizeof(TA) == 2 ? (LPK == 16 ? 3 : (LPK == 8 ? 5 : 0)) : 0; }
+// stages of the ring for an element type and head size (0: this shape has no ring form)
+template <typename TA, int LPK> constexpr int split_stages() { return sizeof(TA) == 2 && LPK == 16 ? 2 : 0; }
 
 template <typename TA, int LPK, int GC, int STAGES>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
@@ -502,8 +506,10 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_split: bad grid (%d splits, %d KV heads)", n_splits, nkv);
     TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
     dim3 grid(T_, nkv, n_splits);
-    const char* no_ring_env = getenv("TQ_SPLIT_NO_RING");     // 1: loads through registers for every shape
-    const bool no_ring = no_ring_env && no_ring_env[0] && no_ring_env[0] != '0';
+    // the ring form for launches of more than two waves of the register form (TQ_SPLIT_RING=1: wherever the
+    // shape has one, =0: never)
+    const char* ring_env = getenv("TQ_SPLIT_RING");
+    const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0' : (long long)T_ * nkv * n_splits > 2 * SPLIT_REGISTER_RESIDENT;
 #define SPLIT_LAUNCH(TA, LPK, GC, STAGES)                                                                       \
     do {                                                                                                        \
         auto kern = attention_split_kernel<TA, LPK, GC, STAGES>;                                                \
@@ -518,9 +524,8 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
             (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window, \
             scale, partial, n_splits, nh, nkv);                                                                 \
     } while (0)
-    // the shared-memory ring: bfloat16, one query head per KV head, head size 128 (three stages) or 64 (five)
 #define SPLIT_GC(TA, LPK)                                                                                       \
-    do { if (G == 1) { if (!no_ring && split_stages<TA, LPK>() > 0) SPLIT_LAUNCH(TA, LPK, 1, (split_stages<TA, LPK>()));   \
+    do { if (G == 1) { if (ring && split_stages<TA, LPK>() > 0) SPLIT_LAUNCH(TA, LPK, 1, (split_stages<TA, LPK>()));   \
                        else SPLIT_LAUNCH(TA, LPK, 1, 0); }                                                      \
          else if (G == 2) SPLIT_LAUNCH(TA, LPK, 2, 0);                                                          \
          else if (G <= 4) SPLIT_LAUNCH(TA, LPK, 4, 0); else SPLIT_LAUNCH(TA, LPK, 8, 0); } while (0)
