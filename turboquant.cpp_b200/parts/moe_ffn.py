@@ -144,7 +144,7 @@ class MoEFeedForward(FeedForward):
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
         if KM.router_small_pays(T, k, self.n_experts, H):
-            # few tokens (decoding): router, layout and the sorted copies of the rows in two launches
+            # few tokens (decoding): router, layout and the sorted copies of the rows in one launch
             KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows)
         else:
             if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
