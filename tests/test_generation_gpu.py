@@ -108,3 +108,20 @@ def test_command_line(tiny_folders, plain_models):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "quant"), tiny_folders["A"], "--info"],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "num_experts: 8" in r.stdout
+
+
+def test_command_line_measurements(tiny_folders):
+    """--bench-prefill and --bench-memory print the reference's machine-readable lines (tools/quant.c:788, 848):
+    prompt length, milliseconds and tokens a second; context and decoded tokens a second, for every context that
+    leaves room for the 20 decoded tokens."""
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "quant"), tiny_folders["A"], "--dtype", "float32",
+           "--bench-prefill", "--bench-memory"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    pre = [l for l in r.stderr.splitlines() if l.startswith("PREFILL_CSV:")]
+    mem = [l for l in r.stderr.splitlines() if l.startswith("BENCH_CSV:")]
+    assert len(pre) == 1
+    n, ms, rate = pre[0].split(":")[1].split(",")
+    assert int(n) == 128 and float(ms) > 0 and float(rate) > 0            # Tiny A holds 128 positions
+    assert [int(l.split(":")[1].split(",")[0]) for l in mem] == [16, 64]   # 256 + 20 is beyond them
+    assert all(float(l.split(",")[1]) > 0 for l in mem)
