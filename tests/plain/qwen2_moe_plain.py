@@ -359,16 +359,37 @@ def sample_top_p(logits: np.ndarray, temperature: float, top_p: float, u: float)
     return int(ids[min(j, n_top - 1)])
 
 
+def repetition_penalty(logits: np.ndarray, recent: Sequence[int], penalty: float) -> np.ndarray:
+    """The reference lowers the logits of the tokens it saw last before it samples
+    (src/engine/tq_generate.c:586-600; before the first sample :386-399): for each of them, once per
+    occurrence, a positive logit is divided by the penalty and any other multiplied by it (float32)."""
+    out = np.array(logits, dtype=np.float32, copy=True)
+    p = np.float32(penalty)
+    for tok in recent:
+        if 0 <= tok < out.shape[0]:
+            out[tok] = out[tok] / p if out[tok] > 0 else out[tok] * p
+    return out
+
+
+def recent_tokens(prompt: Sequence[int], generated: Sequence[int], window: int) -> List[int]:
+    """What the penalty looks at: the last `window` (at most 128) tokens of the prompt followed by the
+    generated ones (src/engine/tq_generate.c:365-367, 381-384, 607-609)."""
+    window = min(int(window), 128)
+    return (list(prompt) + list(generated))[-window:] if window > 0 else []
+
+
 def generate(m: PlainModel, prompt: Sequence[int], max_new_tokens: int, temperature: float = 0.0,
              top_p: float = 1.0, seed: int = 0, sequence: int = 0, stop: Sequence[int] = (),
-             rnd: Round = no_round) -> List[int]:
+             rnd: Round = no_round, rep_penalty: float = 1.0, rep_window: int = 32) -> List[int]:
     """Greedy or sampled continuation by recomputing the whole sequence for every token
-    (loop of src/engine/tq_generate.c:441-605 without penalty, loop detector or text stops).
-    A stop token ends the sequence and is part of the output."""
+    (loop of src/engine/tq_generate.c:441-605 without loop detector or text stops; the repetition
+    penalty :586-600 when rep_penalty > 1).  A stop token ends the sequence and is part of the output."""
     toks = list(prompt)
     out: List[int] = []
     for step in range(max_new_tokens):
         logits = forward(m, toks, rnd)[-1]
+        if rep_penalty > 1.0:
+            logits = repetition_penalty(logits, recent_tokens(prompt, out, rep_window), rep_penalty)
         if temperature <= 0.0:
             t = sample_argmax(logits)
         else:

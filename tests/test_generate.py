@@ -224,3 +224,43 @@ def test_uniforms_do_not_depend_on_the_batch_and_match_the_plain_stream():
         assert float(uniforms_for(seed, [r], [s])[0]) == pytest.approx(uniform_for(seed, r, s), abs=0)
     many = uniforms_for(1, np.arange(20000) % 64, np.arange(20000) // 64)
     assert abs(many.mean() - 0.5) < 0.01 and abs(np.mean(many < 0.1) - 0.1) < 0.01
+
+
+class PenalizingSampler(ArgmaxSampler):
+    """A sampler that asks for each request's tokens so far, as the library's does with a repetition penalty."""
+    penalizes = True
+
+    def __init__(self):
+        super().__init__()
+        self.seen = []
+
+    def sample(self, logits, requests, steps, recent=None):
+        assert recent is not None and len(recent) == len(requests)
+        self.seen.append({i: list(r) for i, r in zip(requests, recent)})
+        return super().sample(logits, requests, steps)
+
+
+@pytest.mark.parametrize("engine", [FakeEngine, FakeAheadEngine])
+def test_a_penalizing_sampler_is_handed_each_requests_tokens_so_far(engine):
+    """Prompt first, then everything generated before this draw, per request, whether or not the engine runs a
+    step ahead and whichever requests are left in the batch; a sampler that does not ask gets no such argument."""
+    prompts = [[1, 2, 3], [4] * 11, [7]]
+    smp = PenalizingSampler()
+    res = generate(engine(), smp, prompts, GenParams(max_new_tokens=5, stop_token_ids=(24,)), max_batch=3)
+    plain = generate(engine(), ArgmaxSampler(), prompts, GenParams(max_new_tokens=5, stop_token_ids=(24,)), max_batch=3)
+    assert [r.tokens for r in res] == [r.tokens for r in plain]
+    draws = {i: 0 for i in range(len(prompts))}
+    for call in smp.seen:
+        for i, recent in call.items():
+            assert recent == prompts[i] + res[i].tokens[:draws[i]]
+            draws[i] += 1
+    assert all(draws[i] == len(res[i].tokens) for i in draws)
+
+
+def test_sampler_settings_for_the_penalty():
+    from turboquant_cpp_b200.sampling import Sampler
+    assert not Sampler(0.0).penalizes and not Sampler(0.7, 0.9, 1, rep_penalty=1.0).penalizes
+    s = Sampler(0.0, rep_penalty=1.1, rep_window=1000)
+    assert s.penalizes and s.rep_window == 128            # the reference keeps at most 128 recent tokens
+    assert not Sampler(0.0, rep_penalty=1.1, rep_window=0).penalizes
+    assert GenParams().rep_penalty == 1.0 and GenParams().rep_window == 32

@@ -18,12 +18,14 @@ def prompts_for(name, lens, seed):
     return [rng.integers(0, V, size=n).tolist() for n in lens]
 
 
-def greedy_with_margin(plain, prompt, n, rnd=P.no_round):
+def greedy_with_margin(plain, prompt, n, rnd=P.no_round, rep_penalty=1.0, rep_window=32):
     """Plain greedy continuation, and for every generated token the gap between the two largest
     logits (a tiny gap may legitimately resolve the other way under another summation order)."""
     toks, out, gaps = list(prompt), [], []
     for _ in range(n):
         l = P.forward(plain, toks, rnd)[-1]
+        if rep_penalty > 1.0:
+            l = P.repetition_penalty(l, P.recent_tokens(prompt, out, rep_window), rep_penalty)
         top = np.sort(l)[-2:]
         gaps.append(top[1] - top[0])
         t = int(np.argmax(l))
@@ -125,3 +127,30 @@ def test_command_line_measurements(tiny_folders):
     assert int(n) == 128 and float(ms) > 0 and float(rate) > 0            # Tiny A holds 128 positions
     assert [int(l.split(":")[1].split(",")[0]) for l in mem] == [16, 64]   # 256 + 20 is beyond them
     assert all(float(l.split(",")[1]) > 0 for l in mem)
+
+
+
+def test_repetition_penalty_through_the_entry_point(tiny_folders, plain_models):
+    """With a repetition penalty the greedy continuation is the plain loop's with the same penalty (the last
+    `window` tokens of prompt and output lower their logits before every draw); it differs from the
+    continuation without one, does not depend on the batch, and a window of 3 differs from one of 32."""
+    import turboquant_cpp_b200 as tq
+    prompts = prompts_for("A", [5, 11, 17], 44)
+    n_new = 10
+    with tq.Model(tiny_folders["A"], temperature=0.0, max_tokens=n_new, dtype="float32", max_batch=4,
+                  context_length=128, rep_penalty=3.0) as m:
+        outs = m.generate_batch(prompts)
+        assert [m.ask(p) for p in prompts] == outs
+        plain_outs = m.generate_batch(prompts, rep_penalty=1.0)
+        short = m.generate_batch(prompts, rep_window=3)
+    assert outs != plain_outs and short != outs
+    for window, got in ((32, outs), (3, short), (32, plain_outs)):
+        pen = 1.0 if got is plain_outs else 3.0
+        for p, o in zip(prompts, got):
+            want, gaps = greedy_with_margin(plain_models["A"], p, n_new, rep_penalty=pen, rep_window=window)
+            for i, (a, b) in enumerate(zip(o, want)):
+                if a != b:
+                    assert gaps[i] < 1e-5, f"token {i}: engine {a}, plain {b}, gap {gaps[i]:.3e}"
+                    break
+            else:
+                assert o == want

@@ -614,3 +614,18 @@ def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dt
                  (lay1.tile_expert[:n], lay2.tile_expert[:n]), (lay1.tile_row0[:n], lay2.tile_row0[:n]),
                  (lay1.tile_count[:n], lay2.tile_count[:n])):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("R,V,W", [(1, 7, 1), (5, 1000, 32), (70, 151, 128)])
+def test_rep_penalty(R, V, W):
+    """In place, once per occurrence, positive logits divided and the others multiplied; -1 and ids beyond the
+    vocabulary are skipped; rows do not touch one another."""
+    from turboquant_cpp_b200.kernels import sampling as KS
+    rng = np.random.default_rng(R + V)
+    logits = rng.normal(size=(R, V)).astype(np.float32)
+    logits[:, 0] = 0.0
+    recent = rng.integers(-1, min(V, 12) + 2, size=(R, W)).astype(np.int32)      # few ids: many repeats; some -1, some >= V
+    recent[recent >= min(V, 12)] = V + 3
+    got = KS.rep_penalty(dev(logits, torch.float32), dev(recent, torch.int32), 1.3)
+    want = np.stack([P.repetition_penalty(logits[r], recent[r].tolist(), 1.3) for r in range(R)])
+    assert np.allclose(got.cpu().numpy(), want, rtol=1e-6, atol=0)

@@ -71,3 +71,15 @@ def test_bf16_rounding():
     r = P.round_bf16(a)
     assert r.tolist()[:4] == [1.0, 1.0, 1.0, 1.0078125]                      # ties to even
     assert abs(r[4] + 3.140625) < 1e-9
+
+
+def test_repetition_penalty_of_the_plain_loop():
+    """Once per occurrence among the last `window` tokens; positive logits are divided, the others multiplied
+    (src/engine/tq_generate.c:586-600); ids outside the vocabulary are skipped (:592)."""
+    l = np.array([2.0, -1.0, 0.0, 4.0, 0.5], dtype=np.float32)
+    out = P.repetition_penalty(l, [0, 1, 3, 3, 7, -1], 2.0)
+    assert np.allclose(out, [1.0, -2.0, 0.0, 1.0, 0.5]) and out.dtype == np.float32
+    assert np.array_equal(l, np.array([2.0, -1.0, 0.0, 4.0, 0.5], dtype=np.float32))       # the input is left alone
+    assert P.recent_tokens([1, 2, 3, 4], [5, 6], 3) == [4, 5, 6]
+    assert P.recent_tokens([1, 2], [], 32) == [1, 2] and P.recent_tokens([1], [2], 0) == []
+    assert len(P.recent_tokens(list(range(300)), [], 1000)) == 128

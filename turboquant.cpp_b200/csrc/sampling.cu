@@ -11,6 +11,10 @@
 // memory and are added in rank order, so every CTA sees the same totals and takes the same branches.
 // All sums have a fixed order: a draw is reproducible, and the sum over a superset is never smaller.
 // The uniform u of each row is an input, so a draw depends on the caller's (seed, sequence, step) only.
+//
+// Before it samples, the reference lowers the logits of the tokens it saw last (:586-600, the first token
+// :386-399): for each of the last `window` tokens of the request, once per occurrence, a positive logit is
+// divided by the penalty and any other multiplied by it.  tq_rep_penalty does the same in place.
 #include "common.cuh"
 
 TQ_DEFINE_LAST_ERROR
@@ -344,5 +348,34 @@ TQ_EXPORT int tq_sample_rows(const float* logits, int R, int V, float temperatur
     tq_launch(R * cluster, SAMPLE_THREADS, smem, stream, cluster)(sample_rows_kernel, logits, V, slice, temperature,
                                                                   top_p, uniforms, work, p_in_global, out);
     TQ_CHECK_LAUNCH("sample_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Repetition penalty.  recent [R, W]: the last tokens of each row's request, -1 where it has fewer.
+// One thread per row walks its W entries in order, so a token that occurs twice is lowered twice,
+// as in the reference's loop, and no two threads touch the same logit.
+// ---------------------------------------------------------------------------------------
+__global__ void rep_penalty_kernel(float* __restrict__ logits, int R, int V, const int* __restrict__ recent, int W,
+                                   float penalty) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    float* row = logits + (size_t)r * V;
+    for (int j = 0; j < W; ++j) {
+        const int tok = recent[(size_t)r * W + j];
+        if (tok < 0 || tok >= V) continue;
+        const float x = row[tok];
+        row[tok] = x > 0.f ? x / penalty : x * penalty;
+    }
+}
+
+TQ_EXPORT int tq_rep_penalty(float* logits, int R, int V, const int* recent, int W, float penalty, cudaStream_t stream) {
+    if (R == 0 || W == 0) return 0;
+    TQ_REQUIRE(R > 0 && V > 0 && W > 0, "rep_penalty: bad sizes R=%d V=%d W=%d", R, V, W);
+    TQ_REQUIRE(penalty > 0.f, "rep_penalty: the penalty %g must be positive", (double)penalty);
+    tq_launch((R + 63) / 64, 64, 0, stream)(rep_penalty_kernel, logits, R, V, recent, W, penalty);
+    TQ_CHECK_LAUNCH("rep_penalty");
     return 0;
 }

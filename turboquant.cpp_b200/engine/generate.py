@@ -3,8 +3,9 @@ as many batches one after another as there are requests.
 
 The reference generates one sequence per call: prompt, first sample, then a loop of
 {stop check, forward, sample} until max_tokens (src/engine/tq_generate.c:167-643; end-of-sequence
-ids at :426-438, the loop at :441-605).  Its repetition penalty, loop detector and text stops are
-not carried over: stop tokens are a set the caller gives (the configuration's eos ids by default).
+ids at :426-438, the loop at :441-605).  Its loop detector and text stops are not carried over:
+stop tokens are a set the caller gives (the configuration's eos ids by default).  Its repetition
+penalty (:586-600) is the sampler's: a sampler that penalizes is handed each request's tokens so far.
 
 The decisions — which requests share a batch, when a sequence ends, when a batch ends — are host
 code over an engine-like object, so they are tested on a CPU with a stand-in engine.
@@ -25,6 +26,8 @@ class GenParams:
     top_p: float = 1.0
     seed: int = 42
     stop_token_ids: Tuple[int, ...] = ()
+    rep_penalty: float = 1.0         # > 1: the sampler lowers the logits of the last rep_window tokens
+    rep_window: int = 32
 
 
 @dataclass
@@ -80,7 +83,8 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
     engine:   open(), close(seq), step(entries) -> logits rows, make_entry(seq, tokens, want),
               capacity_tokens, max_slots, page_size, max_position; optionally can_step_ahead, step_ahead(seqs,
               sampled tokens) -> logits rows, commit_ahead(), drop_ahead(), token_reader(n)
-    sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist())
+    sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist());
+              if it has `penalizes` set, also recent=[tokens of each request so far, prompt first]
     on_tokens(request indices, tokens) is called after every step with that step's new tokens.
     A stop token ends its sequence and is part of the output.
 
@@ -106,7 +110,11 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
             t0 = time.perf_counter()
             order = list(batch)
             logits = engine.step([engine.make_entry(live[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in order])
-            new_dev = sampler.sample(logits, order, [0] * len(order))
+            penalizes = bool(getattr(sampler, "penalizes", False))
+
+            def so_far(rows):                            # what a penalizing sampler looks back at
+                return {"recent": [list(prompts[i]) + results[i].tokens for i in rows]} if penalizes else {}
+            new_dev = sampler.sample(logits, order, [0] * len(order), **so_far(order))
             new = new_dev.tolist()
             sync()
             stats.prefill_seconds += time.perf_counter() - t0
@@ -151,7 +159,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
                             results[i].finish_reason = "context"
                             engine.close(live.pop(i))
                         break
-                new_dev = sampler.sample(logits, order, [len(results[i].tokens) for i in order])
+                new_dev = sampler.sample(logits, order, [len(results[i].tokens) for i in order], **so_far(order))
                 stats.steps += 1
                 # launch the step after this one now, unless a sequence is sure to end with this token
                 if can_ahead and all(len(results[i].tokens) + 1 < params.max_new_tokens

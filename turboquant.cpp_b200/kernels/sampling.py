@@ -1,4 +1,4 @@
-"""Sampling kernels (csrc/sampling.cu): argmax, temperature with a nucleus."""
+"""Sampling kernels (csrc/sampling.cu): argmax, temperature with a nucleus, repetition penalty."""
 from __future__ import annotations
 
 from ctypes import c_float, c_int
@@ -35,3 +35,17 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_p: float, uniforms
     check(_LIB, lib.tq_sample_rows(ptr(logits), c_int(R), c_int(V), c_float(temperature), c_float(top_p),
                                    ptr(uniforms), ptr(work), c_int(int(scratch_in_global)), ptr(out), stream()))
     return out
+
+
+def rep_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: float) -> torch.Tensor:
+    """In place: for each entry of recent [R, W] (a token id, or -1) the logit of that token in its row is divided
+    by the penalty if positive and multiplied by it otherwise, once per occurrence."""
+    want_f32(logits, "logits")
+    want_int32(recent, "recent tokens")
+    R, V = logits.shape
+    if recent.dim() != 2 or recent.shape[0] != R or not recent.is_contiguous() or not logits.is_contiguous():
+        raise ValueError("rep_penalty: recent must be a contiguous [rows, window] table and logits contiguous")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_rep_penalty(ptr(logits), c_int(R), c_int(V), ptr(recent), c_int(recent.shape[1]),
+                                   c_float(penalty), stream()))
+    return logits

@@ -5,6 +5,10 @@ nucleus otherwise (src/engine/tq_generate.c:30-40, 81-156); it keeps one xorshif
 generation call (:53-58), so a draw depends on everything sampled before it.  Here each draw's
 uniform number is a pure function of (seed, index of the request, index of the generated token):
 a request's tokens do not depend on what else is in its batch.
+
+Before it samples, the reference lowers the logits of the last tokens of the request (rep_penalty 1.1
+over rep_window 32 by default, include/turboquant/tq_engine.h:408-409, src/engine/tq_generate.c:586-600).
+Here the penalty is off unless asked for (rep_penalty > 1), so that greedy output is the model's argmax.
 """
 from __future__ import annotations
 
@@ -36,20 +40,41 @@ def uniforms_for(seed: int, requests: Sequence[int], steps: Sequence[int]) -> np
     return ((z >> np.uint64(40)).astype(np.float64) / float(1 << 24)).astype(np.float32)
 
 
+REP_WINDOW_MAX = 128      # the reference keeps at most this many recent tokens (src/engine/tq_generate.c:367)
+
+
 class Sampler:
-    def __init__(self, temperature: float = 0.0, top_p: float = 1.0, seed: int = 42):
+    def __init__(self, temperature: float = 0.0, top_p: float = 1.0, seed: int = 42, rep_penalty: float = 1.0,
+                 rep_window: int = 32):
         self.temperature, self.top_p = float(temperature), float(top_p)
         self.seed = int(seed) if int(seed) != 0 else 42      # 0 means "the default", as in the reference's CLI
+        self.rep_penalty = float(rep_penalty)
+        self.rep_window = max(0, min(int(rep_window), REP_WINDOW_MAX))
         self._work: Optional[torch.Tensor] = None
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0 or self.top_p <= 0.0
 
-    def sample(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
-        """One token per row of float32 logits [R, V] (int32, on the device)."""
+    @property
+    def penalizes(self) -> bool:
+        """Whether sample() wants each request's recent tokens."""
+        return self.rep_penalty > 1.0 and self.rep_window > 0
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],
+               recent: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """One token per row of float32 logits [R, V] (int32, on the device).  recent: for each row the tokens
+        of its request so far (prompt, then generated); with a repetition penalty the last rep_window of them
+        lower their logits first, in place."""
         R, V = logits.shape
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        if self.penalizes and recent is not None:
+            W = self.rep_window
+            table = np.full((R, W), -1, dtype=np.int32)
+            for r, toks in enumerate(recent):
+                tail = list(toks)[-W:]
+                table[r, :len(tail)] = tail
+            KS.rep_penalty(logits, torch.from_numpy(table).to(logits.device, non_blocking=True), self.rep_penalty)
         if self.greedy:
             return KS.argmax_rows(logits, out)
         u = torch.from_numpy(uniforms_for(self.seed, requests, steps)).to(logits.device, non_blocking=True)
