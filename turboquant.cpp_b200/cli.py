@@ -64,6 +64,9 @@ def main(argv=None) -> int:
         return 0
 
     import torch
+    if not torch.cuda.is_available():
+        print("quant: no CUDA device; the engine has no CPU path", file=sys.stderr)
+        return 2
     from .model import Model
     seed = args.seed if args.seed != 0 else 42
     m = Model(args.model, temperature=args.temperature, top_p=args.top_p, max_tokens=args.max_tokens,
