@@ -264,3 +264,38 @@ def test_sampler_settings_for_the_penalty():
     assert s.penalizes and s.rep_window == 128            # the reference keeps at most 128 recent tokens
     assert not Sampler(0.0, rep_penalty=1.1, rep_window=0).penalizes
     assert GenParams().rep_penalty == 1.0 and GenParams().rep_window == 32
+
+
+def test_random_requests_give_the_same_results_with_and_without_running_ahead():
+    """Many random mixes of prompt lengths, stop tokens, limits, batch sizes and cache sizes: the loop over the
+    plain stand-in and over the one that runs a step ahead give every request the tokens of its own closed-form
+    continuation (cut by a stop token, the limit, the model's positions or a full cache), commit the same steps,
+    and leave nothing held."""
+    import random
+    rng = random.Random(5)
+    for case in range(150):
+        n = rng.randint(1, 9)
+        prompts = [[rng.randrange(50) for _ in range(rng.choice([1, 2, 3, 17, 63, 64, 65, 120]))] for _ in range(n)]
+        stop = tuple(rng.sample(range(50), rng.choice([0, 0, 1, 3, 10])))
+        params = GenParams(max_new_tokens=rng.choice([1, 2, 3, 8, 40]), stop_token_ids=stop)
+        max_batch = rng.choice([1, 2, 3, 8])
+        pages = rng.choice([4, 6, 16, 64])
+        slots = rng.choice([1, 2, 8])
+        engines = [FakeEngine(capacity_tokens=64 * pages, max_slots=slots), FakeAheadEngine(capacity_tokens=64 * pages, max_slots=slots)]
+        runs = [generate(e, ArgmaxSampler(), prompts, params, max_batch=max_batch) for e in engines]
+        a, b = ([(r.tokens, r.finish_reason) for r in run] for run in runs)
+        assert a == b, f"case {case}"
+        assert engines[0].step_sizes == engines[1].step_sizes, f"case {case}"
+        for e in engines:
+            assert not e.book.live and e.book.pools[0].n_free == e.book.pools[0].n and e.book.slots.n_held == 0
+            assert e.max_live <= min(max_batch, slots)
+        assert engines[1].pending is None
+        for p, (toks, why) in zip(prompts, a):
+            full = expected(p, params.max_new_tokens, stop=stop)
+            assert toks == full[:len(toks)] and len(toks) >= 1, f"case {case}"
+            if why == "stop":
+                assert toks[-1] in stop and toks == full
+            elif why == "length":
+                assert len(toks) == params.max_new_tokens
+            else:
+                assert why == "context" and len(toks) < params.max_new_tokens       # positions or pages ran out
