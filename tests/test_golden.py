@@ -8,6 +8,10 @@ weights, and uses a fast exp in the experts' SiLU and the shared gate's sigmoid
 (src/engine/tq_ops.c:1418-1448, src/engine/tq_moe.c:659-678, :42-48); with those three switches set
 the same way the plain model reproduces its logits to float32 rounding.  With the exact exp, which
 is the library's formula, the difference is the approximation's error (about 1e-2 of the logits).
+
+tests/golden/samples.bin, from tests/golden/ref_sampler.c, holds what the reference's samplers picked on
+drawn logits; the plain samplers pick the same tokens from the same uniform numbers (1 of 1,944 draws
+falls on the other side of a float32 rounding).
 """
 import os
 import types
@@ -96,3 +100,42 @@ def test_plain_model_reproduces_the_reference_build():
     assert 1e-4 < err < 3e-2                                  # the fast exp's own error, nothing else
     other = P.forward(m, toks, pairing="half")
     assert np.abs(other - ref).max() / scale > 3e-2           # the pairing matters and is not the reference's
+
+
+def reference_uniforms(state, n):
+    """n numbers of the reference's generator from one state (xorshift64*, src/engine/tq_generate.c:53-58):
+    the top 31 bits of state * 0x2545F4914F6CDD1D as a float32 over 2^31."""
+    M, out = (1 << 64) - 1, []
+    for _ in range(n):
+        state ^= state >> 12
+        state ^= (state << 25) & M
+        state ^= state >> 27
+        out.append(np.float32(((state * 0x2545F4914F6CDD1D) & M) >> 33) / np.float32(1 << 31))
+    return out
+
+
+def test_plain_samplers_pick_the_reference_builds_tokens():
+    """tests/golden/samples.bin holds what the reference's tq_sample_argmax and tq_sample_topp picked on 81 cases
+    (3 vocabularies x 3 spreads of logits x 3 temperatures x 3 values of top-p), 24 draws each
+    (tests/golden/ref_sampler.c).  The plain samplers, given the same logits and the same uniform numbers, pick the
+    same tokens, except where a draw lands within float32 rounding of a boundary of the cumulative sum."""
+    ref = np.fromfile(os.path.join(HERE, "golden", "samples.bin"), dtype="<i4")
+    DRAWS = 24
+    g = XorShift()
+    case, at, differ, total = 0, 0, 0, 0
+    for V in (256, 1000, 5003):
+        for spread in (4.0, 10.0, 25.0):
+            raw = g.draw(V) / np.float32(0.2)                   # the generator's number in [-0.5, 0.5)
+            logits = (raw * np.float32(spread)).astype(np.float32)
+            for T in (0.7, 1.0, 0.3):
+                for top_p in (0.9, 1.0, 0.5):
+                    assert P.sample_argmax(logits) == ref[at]
+                    us = reference_uniforms(1000 + case, DRAWS)
+                    for d in range(DRAWS):
+                        got = P.sample_top_p(logits, float(np.float32(T)), float(np.float32(top_p)), float(us[d]))
+                        differ += int(got != ref[at + 1 + d])
+                        total += 1
+                    at += 1 + DRAWS
+                    case += 1
+    assert at == ref.size and case == 81
+    assert differ <= total // 200, f"{differ} of {total} draws differ"
