@@ -378,6 +378,26 @@ def recent_tokens(prompt: Sequence[int], generated: Sequence[int], window: int) 
     return (list(prompt) + list(generated))[-window:] if window > 0 else []
 
 
+def closes_a_loop(prompt: Sequence[int], generated: Sequence[int], window: int = 32) -> bool:
+    """Whether the last of `generated` closes a repetition loop as the reference sees it
+    (src/engine/tq_generate.c:370-384, 610-630): from the second sampled token on, the last four tokens
+    (the last `window` tokens of the prompt count) are hashed, h = h * 31 + token in 32 bits, and compared
+    with the hashes of up to 64 draws before; three matches are a loop.  Recomputed from scratch here."""
+    tail = list(prompt)[-min(int(window), 128):] if window > 0 else []
+    hashes = []
+    for n in range(2, len(generated) + 1):
+        seen = (tail + list(generated[:n]))[-128:]
+        if len(seen) < 4:
+            continue
+        h = 0
+        for t in seen[-4:]:
+            h = (h * 31 + t) % (1 << 32)
+        hashes.append(h)
+    if not hashes or len(generated) < 2 or len((tail + list(generated))[-128:]) < 4:
+        return False
+    return hashes[:-1][-64:].count(hashes[-1]) >= 3
+
+
 def generate(m: PlainModel, prompt: Sequence[int], max_new_tokens: int, temperature: float = 0.0,
              top_p: float = 1.0, seed: int = 0, sequence: int = 0, stop: Sequence[int] = (),
              rnd: Round = no_round, rep_penalty: float = 1.0, rep_window: int = 32) -> List[int]:

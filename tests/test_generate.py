@@ -299,3 +299,35 @@ def test_random_requests_give_the_same_results_with_and_without_running_ahead():
                 assert len(toks) == params.max_new_tokens
             else:
                 assert why == "context" and len(toks) < params.max_new_tokens       # positions or pages ran out
+
+
+def test_loop_detector_ends_a_request_as_the_reference_does():
+    """Off by default.  On, a request ends with 'loop' at the first token whose 4-gram has come up three times among
+    the 64 draws before, and that token is not part of the output; the plain restatement, which recomputes
+    everything from the tokens, names the same place; other requests of the batch go on."""
+    from plain.qwen2_moe_plain import closes_a_loop
+    from turboquant_cpp_b200.engine.generate import LoopDetector
+    prompts = [[0], [1, 2, 3], [25, 25]]           # 0 -> 0 0 0 ... ; 25+25 = 50 -> 0 0 0 ...
+    for cls in (FakeEngine, FakeAheadEngine):
+        off = generate(cls(), ArgmaxSampler(), prompts, GenParams(max_new_tokens=30), max_batch=4)
+        assert all(r.finish_reason == "length" and len(r.tokens) == 30 for r in off)
+        seen = {}
+        on = generate(cls(), ArgmaxSampler(), prompts, GenParams(max_new_tokens=30, detect_loops=True), max_batch=4,
+                      on_tokens=lambda idx, toks: [seen.setdefault(i, []).append(t) for i, t in zip(idx, toks)])
+        for p, r, full in zip(prompts, on, off):
+            assert r.tokens == full.tokens[:len(r.tokens)] and seen[prompts.index(p)] == r.tokens
+            if r.finish_reason == "loop":
+                n = len(r.tokens)
+                assert closes_a_loop(p, full.tokens[:n + 1]) and not any(closes_a_loop(p, full.tokens[:k]) for k in range(1, n + 1))
+            else:
+                assert r.finish_reason == "length" and not any(closes_a_loop(p, full.tokens[:k]) for k in range(1, 31))
+        assert on[0].finish_reason == "loop" and on[2].finish_reason == "loop"
+    # the detector against the restatement on random tokens from a small alphabet (loops are frequent)
+    import random
+    rng = random.Random(3)
+    for _ in range(200):
+        prompt = [rng.randrange(3) for _ in range(rng.choice([0, 1, 2, 5, 40, 200]))]
+        det, out = LoopDetector(prompt, 32), []
+        for _ in range(120):
+            out.append(rng.randrange(3))
+            assert det.push(out[-1]) == closes_a_loop(prompt, out)

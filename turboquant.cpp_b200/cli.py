@@ -2,7 +2,7 @@
 
     quant <model folder> [-p "ids"]… [-n max_tokens] [-T temperature] [-P top_p] [-s seed]
           [--ctx N] [--dtype bfloat16|float32] [--batch N] [--stop id]… [--rep-penalty F] [--rep-window N]
-          [--info] [--profile]
+          [--detect-loops] [--info] [--profile]
           [--bench-prefill] [--bench-memory]
 
 Names and meanings follow the reference where it has them: -p prompt (default "Hello" there; here
@@ -11,7 +11,8 @@ temperature (0.7), -P top-p (0.9), -s seed (42; 0 means the default), --ctx cont
 print the model and exit, --profile time the kernels' groups, --bench-prefill and --bench-memory
 (decode speed at growing context).  --rep-penalty and --rep-window set what the reference keeps as
 engine defaults without an option (1.1 over 32 tokens, include/turboquant/tq_engine.h:408-409); here
-the penalty is off unless asked for.  -j (threads) is accepted and ignored.  -p may be given several
+the penalty is off unless asked for, and so is the reference's detector of repetition loops
+(--detect-loops; src/engine/tq_generate.c:610-630).  -j (threads) is accepted and ignored.  -p may be given several
 times: the prompts run as batches.  Token ids go to stdout, one line per prompt; the summary
 "N tokens in X s (Y tok/s)" goes to stderr as the reference prints it (tools/quant.c:1371-1376).
 """
@@ -47,6 +48,8 @@ def main(argv=None) -> int:
     ap.add_argument("--rep-penalty", type=float, default=1.0,
                     help="repetition penalty over the last --rep-window tokens (the reference's engine applies 1.1; 1 = off)")
     ap.add_argument("--rep-window", type=int, default=32)
+    ap.add_argument("--detect-loops", action="store_true",
+                    help="end a request whose last four tokens have come up three times before (the reference always does)")
     ap.add_argument("--info", action="store_true")
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--bench-prefill", action="store_true")
@@ -71,7 +74,8 @@ def main(argv=None) -> int:
     seed = args.seed if args.seed != 0 else 42
     m = Model(args.model, temperature=args.temperature, top_p=args.top_p, max_tokens=args.max_tokens,
               context_length=args.ctx, seed=seed, dtype=args.dtype, device=args.device, max_batch=args.batch,
-              stop_token_ids=args.stop, rep_penalty=args.rep_penalty, rep_window=args.rep_window)
+              stop_token_ids=args.stop, rep_penalty=args.rep_penalty, rep_window=args.rep_window,
+              detect_loops=args.detect_loops)
     if args.bench_prefill or args.bench_memory:
         from .engine.bench_tools import bench_memory, bench_prefill
         if args.bench_prefill:

@@ -3,9 +3,10 @@ as many batches one after another as there are requests.
 
 The reference generates one sequence per call: prompt, first sample, then a loop of
 {stop check, forward, sample} until max_tokens (src/engine/tq_generate.c:167-643; end-of-sequence
-ids at :426-438, the loop at :441-605).  Its loop detector and text stops are not carried over:
-stop tokens are a set the caller gives (the configuration's eos ids by default).  Its repetition
-penalty (:586-600) is the sampler's: a sampler that penalizes is handed each request's tokens so far.
+ids at :426-438, the loop at :441-605).  Its text stops are not carried over: stop tokens are a
+set the caller gives (the configuration's eos ids by default).  Its repetition penalty (:586-600)
+is the sampler's: a sampler that penalizes is handed each request's tokens so far.  Its detector of
+repetition loops (:610-630) is LoopDetector below, off unless GenParams.detect_loops asks for it.
 
 The decisions — which requests share a batch, when a sequence ends, when a batch ends — are host
 code over an engine-like object, so they are tested on a CPU with a stand-in engine.
@@ -28,12 +29,13 @@ class GenParams:
     stop_token_ids: Tuple[int, ...] = ()
     rep_penalty: float = 1.0         # > 1: the sampler lowers the logits of the last rep_window tokens
     rep_window: int = 32
+    detect_loops: bool = False       # end a request whose last four tokens have come up three times before
 
 
 @dataclass
 class GenResult:
     tokens: List[int] = field(default_factory=list)
-    finish_reason: str = ""          # 'stop' | 'length' | 'context'
+    finish_reason: str = ""          # 'stop' | 'length' | 'context' | 'loop'
 
 
 @dataclass
@@ -44,6 +46,35 @@ class GenStats:
     decode_seconds: float = 0.0
     batches: int = 0
     steps: int = 0
+
+
+class LoopDetector:
+    """The reference's detector of repetition loops (src/engine/tq_generate.c:370-384, 610-630): after every
+    sampled token but a request's first, the last four tokens (the tail of the prompt counts) are hashed
+    (h = h * 31 + token, 32 bits) and compared with the hashes of the 64 draws before; three matches mean a
+    loop.  The reference then stops without emitting the token that closed the loop."""
+
+    def __init__(self, prompt: Sequence[int], window: int = 32):
+        self.recent = list(prompt)[-max(0, min(int(window), 128)):] if window > 0 else []
+        self.hashes: List[int] = []
+        self.first = True
+
+    def push(self, token: int) -> bool:
+        """Takes the newly sampled token; True if it closes a loop."""
+        self.recent.append(int(token))
+        del self.recent[:-128]
+        if self.first:
+            self.first = False
+            return False
+        if len(self.recent) < 4:
+            return False
+        h = 0
+        for t in self.recent[-4:]:
+            h = (h * 31 + (t & 0xFFFFFFFF)) & 0xFFFFFFFF
+        matches = self.hashes[-64:].count(h)
+        self.hashes.append(h)
+        del self.hashes[:-64]
+        return matches >= 3
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int, capacity_tokens: int,
@@ -86,7 +117,8 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
     sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist());
               if it has `penalizes` set, also recent=[tokens of each request so far, prompt first]
     on_tokens(request indices, tokens) is called after every step with that step's new tokens.
-    A stop token ends its sequence and is part of the output.
+    A stop token ends its sequence and is part of the output; with params.detect_loops a token that closes a
+    repetition loop ends its sequence and is not (finish_reason 'loop').
 
     An engine that can (`can_step_ahead`) is kept one decode step ahead of the host: the next step is launched
     from the samples while they are still on the device, and the host reads them meanwhile.  If a sequence
@@ -104,6 +136,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
     for batch in batches:
         stats.batches += 1
         live = {i: engine.open() for i in batch}
+        loops = {i: LoopDetector(prompts[i], params.rep_window) for i in batch} if params.detect_loops else None
         ahead = None                                     # (request order, logits) of a step launched ahead
         try:
             # the prompts, whole, in one step; logits at each prompt's last token
@@ -125,9 +158,17 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
             reader = engine.token_reader(len(order)) if can_ahead else None
             while True:
                 nxt: List[Tuple[int, int]] = []
+                told_idx: List[int] = []
+                told_tok: List[int] = []
                 for i, tok in zip(order, new):
                     res = results[i]
+                    if loops is not None and loops[i].push(int(tok)):
+                        res.finish_reason = "loop"       # the token that closed the loop is not part of the output
+                        engine.close(live.pop(i))
+                        continue
                     res.tokens.append(int(tok))
+                    told_idx.append(i)
+                    told_tok.append(int(tok))
                     stats.generated_tokens += 1
                     if int(tok) in stop:
                         res.finish_reason = "stop"
@@ -139,8 +180,8 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
                         nxt.append((i, int(tok)))
                         continue
                     engine.close(live.pop(i))            # the sequence ends: its slot and pages go back
-                if on_tokens is not None:
-                    on_tokens(list(order), [int(t) for t in new])
+                if on_tokens is not None and told_idx:
+                    on_tokens(told_idx, told_tok)
                 if not nxt:
                     break
                 if ahead is not None and ahead[0] == [i for i, _ in nxt]:

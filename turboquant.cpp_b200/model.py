@@ -25,33 +25,34 @@ class Model:
     def __init__(self, path: str, *, temperature: float = 0.7, top_p: float = 0.9, max_tokens: int = 256,
                  context_length: int = 0, seed: int = 42, dtype: str = "bfloat16", device: str = "cuda:0",
                  max_batch: int = 8, stop_token_ids: Optional[Sequence[int]] = None, rep_penalty: float = 1.0,
-                 rep_window: int = 32):
+                 rep_window: int = 32, detect_loops: bool = False):
         """path: folder with config.json and safetensors.  context_length: most tokens one request
         may hold (0: the model's max_position_embeddings, capped at 4096 as the reference caps its
         default context, src/engine/tq_model.c:2951).  The cache is sized for max_batch such requests.
         rep_penalty > 1 lowers the logits of a request's last rep_window tokens before each draw, as the
         reference does with 1.1 over 32 tokens (include/turboquant/tq_engine.h:408-409); 1 (the default
-        here) leaves the logits alone."""
+        here) leaves the logits alone.  detect_loops ends a request when its last four tokens have come up three
+        times among the 64 draws before, as the reference always does (src/engine/tq_generate.c:610-630)."""
         if not os.path.isdir(path):
             raise FileNotFoundError(f"model folder '{path}' does not exist")
         self._setup(load_model(path, dtype, device), path, temperature, top_p, max_tokens, context_length, seed,
-                    device, max_batch, stop_token_ids, rep_penalty, rep_window)
+                    device, max_batch, stop_token_ids, rep_penalty, rep_window, detect_loops)
 
     @classmethod
     def from_model(cls, model, *, temperature: float = 0.7, top_p: float = 0.9, max_tokens: int = 256,
                    context_length: int = 0, seed: int = 42, device: str = "cuda:0", max_batch: int = 8,
                    stop_token_ids: Optional[Sequence[int]] = None, rep_penalty: float = 1.0,
-                   rep_window: int = 32) -> "Model":
+                   rep_window: int = 32, detect_loops: bool = False) -> "Model":
         """Wraps a model that is already on the device (for instance one with random weights)."""
         self = cls.__new__(cls)
         self._setup(model, "", temperature, top_p, max_tokens, context_length, seed, device, max_batch, stop_token_ids,
-                    rep_penalty, rep_window)
+                    rep_penalty, rep_window, detect_loops)
         return self
 
     def _setup(self, model, path, temperature, top_p, max_tokens, context_length, seed, device, max_batch,
-               stop_token_ids, rep_penalty=1.0, rep_window=32) -> None:
+               stop_token_ids, rep_penalty=1.0, rep_window=32, detect_loops=False) -> None:
         self._path = path
-        self.rep_penalty, self.rep_window = float(rep_penalty), int(rep_window)
+        self.rep_penalty, self.rep_window, self.detect_loops = float(rep_penalty), int(rep_window), bool(detect_loops)
         self.temperature, self.top_p, self.max_tokens, self.seed = temperature, top_p, max_tokens, seed
         self.max_batch = int(max_batch)
         self._model = model
@@ -80,7 +81,8 @@ class Model:
         return self._engine
 
     # ---- generation ---------------------------------------------------------------------------
-    def _params(self, max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty=None, rep_window=None) -> GenParams:
+    def _params(self, max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty=None, rep_window=None,
+                detect_loops=None) -> GenParams:
         return GenParams(
             max_new_tokens=self.max_tokens if max_tokens is None else int(max_tokens),
             temperature=self.temperature if temperature is None else float(temperature),
@@ -88,16 +90,17 @@ class Model:
             seed=self.seed if seed is None else int(seed),
             stop_token_ids=self.stop_token_ids if stop_token_ids is None else tuple(stop_token_ids),
             rep_penalty=self.rep_penalty if rep_penalty is None else float(rep_penalty),
-            rep_window=self.rep_window if rep_window is None else int(rep_window))
+            rep_window=self.rep_window if rep_window is None else int(rep_window),
+            detect_loops=self.detect_loops if detect_loops is None else bool(detect_loops))
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], *, max_tokens: Optional[int] = None,
                        temperature: Optional[float] = None, top_p: Optional[float] = None,
                        seed: Optional[int] = None, stop_token_ids: Optional[Sequence[int]] = None,
                        on_tokens=None, rep_penalty: Optional[float] = None,
-                       rep_window: Optional[int] = None) -> List[List[int]]:
+                       rep_window: Optional[int] = None, detect_loops: Optional[bool] = None) -> List[List[int]]:
         """Continuations of several prompts (token ids in, token ids out, on the host)."""
         self._check_open()
-        p = self._params(max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty, rep_window)
+        p = self._params(max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty, rep_window, detect_loops)
         stats = GenStats()
         sampler = Sampler(p.temperature, p.top_p, p.seed, p.rep_penalty, p.rep_window)
         results = _generate(self._engine, sampler, prompts, p, self.max_batch,
