@@ -50,6 +50,20 @@ def round_bf16(a: np.ndarray) -> np.ndarray:
 # ------------------------------------------------------------------------------------
 # reading a model folder (own reader; layout as in src/engine/tq_model.c:185-305)
 # ------------------------------------------------------------------------------------
+def _widen(raw, dt: str, name: str, shape) -> np.ndarray:
+    if dt == "BF16":       # widen by a 16-bit shift, src/engine/tq_model.c:367-412
+        a = (np.frombuffer(raw, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+    elif dt == "F32":
+        a = np.frombuffer(raw, dtype=np.float32)
+    elif dt == "F16":
+        a = np.frombuffer(raw, dtype=np.float16)
+    elif dt == "I32":
+        a = np.frombuffer(raw, dtype=np.int32)
+    else:
+        raise ValueError(f"plain reader: dtype {dt} of '{name}' not handled")
+    return a.astype(np.float64 if dt != "I32" else np.int64).reshape(shape)
+
+
 def read_safetensors(path: str) -> Dict[str, np.ndarray]:
     with open(path, "rb") as f:
         blob = f.read()
@@ -61,32 +75,57 @@ def read_safetensors(path: str) -> Dict[str, np.ndarray]:
         if name == "__metadata__":
             continue
         b, e = info["data_offsets"]
-        raw = data[b:e]
-        dt = info["dtype"]
-        if dt == "BF16":       # widen by a 16-bit shift, src/engine/tq_model.c:367-412
-            a = (np.frombuffer(raw, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
-        elif dt == "F32":
-            a = np.frombuffer(raw, dtype=np.float32)
-        elif dt == "F16":
-            a = np.frombuffer(raw, dtype=np.float16)
-        elif dt == "I32":
-            a = np.frombuffer(raw, dtype=np.int32)
-        else:
-            raise ValueError(f"plain reader: dtype {dt} of '{name}' not handled")
-        out[name] = a.astype(np.float64 if dt != "I32" else np.int64).reshape(info["shape"])
+        out[name] = _widen(data[b:e], info["dtype"], name, info["shape"])
     return out
 
 
-class PlainModel:
-    """config.json (as a dict) and the tensors of a folder, by name."""
+class TensorsOnDemand:
+    """The tensors of a folder's files, each widened to float64 when it is asked for and not kept (small ones
+    are): for models whose tensors do not fit the host's memory as float64 all at once."""
+    KEEP_BELOW = 1 << 20          # elements
 
-    def __init__(self, folder: str):
+    def __init__(self, paths: Sequence[str]):
+        self.where, self.kept, self.maps = {}, {}, []
+        for path in paths:
+            mm = np.memmap(path, dtype=np.uint8, mode="r")
+            (hlen,) = struct.unpack("<Q", bytes(mm[:8]))
+            header = json.loads(bytes(mm[8:8 + hlen]).decode("utf-8"))
+            self.maps.append(mm)
+            for name, info in header.items():
+                if name != "__metadata__":
+                    b, e = info["data_offsets"]
+                    self.where[name] = (mm, 8 + hlen + b, 8 + hlen + e, info["dtype"], info["shape"])
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.where
+
+    def __getitem__(self, name: str) -> np.ndarray:
+        if name in self.kept:
+            return self.kept[name]
+        mm, b, e, dt, shape = self.where[name]
+        a = _widen(mm[b:e], dt, name, shape)
+        if a.size < self.KEEP_BELOW:
+            self.kept[name] = a
+        return a
+
+    def get(self, name: str, default=None):
+        return self[name] if name in self.where else default
+
+
+class PlainModel:
+    """config.json (as a dict) and the tensors of a folder, by name.  on_demand: tensors are widened when they
+    are used instead of all at once (for layers of real models' widths)."""
+
+    def __init__(self, folder: str, on_demand: bool = False):
         with open(os.path.join(folder, "config.json")) as f:
             self.cfg = json.load(f)
-        self.w: Dict[str, np.ndarray] = {}
-        for n in sorted(os.listdir(folder)):
-            if n.endswith(".safetensors"):
-                self.w.update(read_safetensors(os.path.join(folder, n)))
+        files = [os.path.join(folder, n) for n in sorted(os.listdir(folder)) if n.endswith(".safetensors")]
+        if on_demand:
+            self.w = TensorsOnDemand(files)
+        else:
+            self.w: Dict[str, np.ndarray] = {}
+            for path in files:
+                self.w.update(read_safetensors(path))
         c = self.cfg
         self.L = c["num_hidden_layers"]
         self.H = c["hidden_size"]
@@ -175,13 +214,13 @@ def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int) -> np.nd
     nkv = k.shape[1]
     out = np.zeros((T, nh, hd))
     scale = 1.0 / np.sqrt(hd)
+    t = np.arange(T)
+    start = np.maximum(0, t + 1 - window) if window > 0 else np.zeros(T, dtype=np.int64)
+    seen = (t[None, :] <= t[:, None]) & (t[None, :] >= start[:, None])        # [query, key]
     for h in range(nh):
         g = h // (nh // nkv)
-        for t in range(T):
-            start = max(0, t + 1 - window) if window > 0 else 0
-            s = (k[start:t + 1, g] @ q[t, h]) * scale
-            p = softmax(s)
-            out[t, h] = p @ v[start:t + 1, g]
+        s = np.where(seen, (q[:, h] @ k[:, g].T) * scale, -np.inf)          # one head, all queries at once
+        out[:, h] = softmax(s) @ v[:, g]
     return out.reshape(T, nh * hd)
 
 
@@ -246,13 +285,12 @@ def moe_feed_forward(m: PlainModel, l: int, x: np.ndarray, rnd: Round = no_round
         record.setdefault("weights", {})[l] = wts
         record.setdefault("margin", {})[l] = margin
     y = np.zeros_like(x)
-    for t in range(x.shape[0]):
-        for j in range(m.k):
-            e = int(ids[t, j])
-            pe = f"{p}experts.{e}."
-            o = swiglu(x[t:t + 1], w[pe + "gate_proj.weight"], w[pe + "up_proj.weight"],
-                       w[pe + "down_proj.weight"], rnd, MOE_EXP)
-            y[t] += wts[t, j] * o[0]
+    for e in np.unique(ids):                 # expert by expert: each one's weights are fetched once
+        rows, cols = np.nonzero(ids == e)    # a token chooses an expert at most once
+        pe = f"{p}experts.{int(e)}."
+        o = swiglu(x[rows], w[pe + "gate_proj.weight"], w[pe + "up_proj.weight"],
+                   w[pe + "down_proj.weight"], rnd, MOE_EXP)
+        y[rows] += wts[rows, cols][:, None] * o
     if m.cfg.get("shared_expert_intermediate_size", 0) > 0:
         s = 1.0 / (1.0 + MOE_EXP(-linear(x, w[p + "shared_expert_gate.weight"])))      # [T,1]
         o = swiglu(x, w[p + "shared_expert.gate_proj.weight"], w[p + "shared_expert.up_proj.weight"],
@@ -300,14 +338,17 @@ def block(m: PlainModel, l: int, x: np.ndarray, positions: np.ndarray, rnd: Roun
 
 
 def forward(m: PlainModel, tokens: Sequence[int], rnd: Round = no_round, pairing: str = "half",
-            forced_ids=None, record=None) -> np.ndarray:
+            forced_ids=None, record=None, rows: Optional[Sequence[int]] = None) -> np.ndarray:
     """Logits [T, V] of one whole sequence (src/engine/tq_transformer.c:2281-3029:
     embedding, layers, final norm :2922, logits :2931-2942; a model without lm_head.weight
-    reuses the embedding, src/engine/tq_model.c:1499-1516)."""
+    reuses the embedding, src/engine/tq_model.c:1499-1516).  rows: the positions whose logits are wanted
+    ([len(rows), V] comes back; the layers still run on every position)."""
     positions = np.arange(len(tokens))
     x = embedding(m.w["model.embed_tokens.weight"], tokens)
     for l in range(m.L):
         x = block(m, l, x, positions, rnd, pairing, forced_ids, record)
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     xn = rnd(rmsnorm(x, m.w["model.norm.weight"], m.eps))
     head = m.w["model.embed_tokens.weight"] if m.tied else m.w["lm_head.weight"]
     return linear(xn, head)

@@ -26,26 +26,30 @@ from plain.qwen2_moe_plain import PlainModel, forward as plain_forward, no_round
 TOL = {"float32": (2e-5, 1e-5), "bfloat16": (1.5e-2, 2.5e-2)}
 
 
-def whole(rid: str, tokens: Sequence[int]):
-    """The request alone, whole, logits everywhere."""
-    return [[(rid, list(tokens), list(range(len(tokens))))]], {0: [rid]}
+def whole(rid: str, tokens: Sequence[int], keep=None):
+    """The request alone, whole, logits everywhere (or at the positions `keep` holds)."""
+    want = [p for p in range(len(tokens)) if keep is None or p in keep]
+    return [[(rid, list(tokens), want)]], {0: [rid]}
 
 
-def with_tail(rid: str, tokens: Sequence[int], tail: int = 32):
-    """All but the last `tail` tokens in one step, then the rest one by one."""
+def with_tail(rid: str, tokens: Sequence[int], tail: int = 32, keep=None):
+    """All but the last `tail` tokens in one step, then the rest one by one (logits of the first step
+    everywhere, or at the positions `keep` holds)."""
     n = len(tokens)
     head = max(1, n - tail)
-    steps = [[(rid, list(tokens[:head]), list(range(head)))]]
+    steps = [[(rid, list(tokens[:head]), [p for p in range(head) if keep is None or p in keep])]]
     for i in range(head, n):
         steps.append([(rid, [tokens[i]], [0])])
     return steps, {len(steps) - 1: [rid]}
 
 
-def batched(requests: Dict[str, Sequence[int]], prompt_lens: Dict[str, int]):
+def batched(requests: Dict[str, Sequence[int]], prompt_lens: Dict[str, int], keep=None):
     """Requests start together with prompts of unequal lengths, then go on one token each; a
-    request leaves when its tokens are used up.  Logits are wanted everywhere."""
+    request leaves when its tokens are used up.  Logits are wanted everywhere (of the prompts: at the
+    positions `keep` holds, if given)."""
     steps, ends = [], {}
-    steps.append([(r, list(t[:prompt_lens[r]]), list(range(prompt_lens[r]))) for r, t in requests.items()])
+    steps.append([(r, list(t[:prompt_lens[r]]), [p for p in range(prompt_lens[r]) if keep is None or p in keep])
+                  for r, t in requests.items()])
     done = {r: prompt_lens[r] for r in requests}
     for r in requests:
         if done[r] == len(requests[r]):
@@ -97,8 +101,12 @@ def run_schedule(engine, steps, ends):
     return logits, routing
 
 
+_plain_runs: Dict[tuple, tuple] = {}      # (plain model, tokens, dtype, rows) -> (record, logits of the plain model's own choices)
+
+
 def check_against_plain(plain: PlainModel, tokens: Sequence[int], logits: Dict[int, np.ndarray],
-                        routing: Dict[int, Dict[int, np.ndarray]], dtype: str, what: str = ""):
+                        routing: Dict[int, Dict[int, np.ndarray]], dtype: str, what: str = "", report: dict = None):
+    """report: a dict that receives the worst logit error and the smallest router margin seen."""
     tol, flip_margin = TOL[dtype]
     rnd = round_bf16 if dtype == "bfloat16" else no_round
     sparse = [l for l in range(plain.L) if plain.layer_is_sparse(l)]
@@ -107,8 +115,13 @@ def check_against_plain(plain: PlainModel, tokens: Sequence[int], logits: Dict[i
     for li, l in enumerate(sparse):
         assert sorted(routing[li]) == list(range(n)), f"{what}: layer {l} did not see every position exactly once"
         forced[l] = np.stack([routing[li][p] for p in range(n)])
-    rec = {}
-    plain_forward(plain, tokens, rnd, record=rec)
+    rows = sorted(logits)
+    key = (id(plain), tuple(tokens), dtype, tuple(rows))
+    if key not in _plain_runs:                # the same request comes back under several schedules
+        rec = {}
+        own = plain_forward(plain, tokens, rnd, record=rec, rows=rows)
+        _plain_runs[key] = (rec, own)
+    rec, own = _plain_runs[key]
     n_diff = 0
     for l in sparse:
         differ = np.nonzero(np.any(np.sort(rec["ids"][l], axis=1) != np.sort(forced[l], axis=1), axis=1))[0]
@@ -120,12 +133,17 @@ def check_against_plain(plain: PlainModel, tokens: Sequence[int], logits: Dict[i
     # near-ties are a few per cent of all choices (the gap to the next expert is a fraction of the spread
     # divided by the number of experts); more than that would be a fault, not rounding
     assert n_diff <= max(2, (n * len(sparse)) // 20), f"{what}: {n_diff} expert choices differ"
-    ref = plain_forward(plain, tokens, rnd, forced_ids=forced)
+    ref = own if n_diff == 0 else plain_forward(plain, tokens, rnd, forced_ids=forced, rows=rows)
     scale = np.abs(ref).max()
     worst, worst_p = 0.0, -1
-    for p, row in logits.items():
-        e = np.abs(row - ref[p]).max() / scale
+    for i, p in enumerate(rows):
+        e = np.abs(logits[p] - ref[i]).max() / scale
         if e > worst:
             worst, worst_p = e, p
     assert worst < tol, f"{what}: logits at position {worst_p} differ by {worst:.3e} of scale (tolerance {tol:.1e})"
+    if report is not None:
+        report["worst"] = max(report.get("worst", 0.0), worst)
+        if sparse:
+            report["margin"] = min(report.get("margin", np.inf), min(float(rec["margin"][l].min()) for l in sparse))
+        report["flips"] = report.get("flips", 0) + n_diff
     return worst

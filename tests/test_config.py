@@ -114,3 +114,15 @@ def test_registry_accepts_a_new_architecture():
     finally:
         from turboquant_cpp_b200.config import unregister_architecture
         unregister_architecture("ToyTestArch")
+
+
+def test_sizes_no_kernel_takes_are_refused_when_the_configuration_is_read():
+    from turboquant_cpp_b200.config import ConfigError
+    from turboquant_cpp_b200.config.qwen2_moe import Qwen2MoeConfig
+    from conftest import TINY_A
+    for key, value, needle in (("head_dim", 24, "multiple of 16"), ("head_dim", 272, "multiple of 16"),
+                               ("num_experts", 5000, "num_experts")):
+        raw = dict(TINY_A)
+        raw[key] = value
+        with pytest.raises(ConfigError, match=needle):
+            Qwen2MoeConfig.from_dict(raw, "config.json")

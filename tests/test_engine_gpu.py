@@ -21,7 +21,7 @@ def engines(tiny_folders):
     def get(name, dtype):
         if (name, dtype) not in cache:
             model = tq.load_model(tiny_folders[name], dtype, "cuda:0")
-            cache[(name, dtype)] = tq.Engine(model, max_tokens=1024)
+            cache[(name, dtype)] = tq.Engine(model, max_tokens=1024, record_routing=True)
         return cache[(name, dtype)]
     return get
 
@@ -97,6 +97,28 @@ def test_first_tokens(engines, plain_models, name, dtype):
     toks = tokens_for(name, 4, 13)
     logits, routing = run_schedule(eng, *with_tail("r", toks, 3))
     check_against_plain(plain_models[name], toks, logits["r"], routing.get("r", {}), dtype, f"{name} first")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_decode_steps_run_as_graphs_and_give_the_bits_of_eager_steps(engines, tiny_folders, name, dtype):
+    """The strict comparisons above go through the path generation uses: decode steps of the shared engines are
+    replays of captured CUDA graphs (with the experts' choices read from memory of the graph).  The same steps
+    launched one kernel at a time give the same logits bit for bit."""
+    import turboquant_cpp_b200 as tq
+    eng = engines(name, dtype)
+    toks = tokens_for(name, min(90, max_len(name)), 14)
+    before = eng.graphs.replays
+    graph_logits, graph_routing = run_schedule(eng, *with_tail("r", toks, 40))
+    assert eng.graphs.replays - before >= 39                   # all but the first step of a new batch size
+    eager = tq.Engine(eng.model, max_tokens=1024, use_graphs=False)
+    assert eager.graphs is None
+    eager_logits, eager_routing = run_schedule(eager, *with_tail("r", toks, 40))
+    for p in range(len(toks)):
+        assert np.array_equal(graph_logits["r"][p], eager_logits["r"][p]), f"position {p}"
+    for li in graph_routing.get("r", {}):
+        for p in range(len(toks)):
+            assert np.array_equal(graph_routing["r"][li][p], eager_routing["r"][li][p])
 
 
 def test_step_refuses_bad_input(engines):

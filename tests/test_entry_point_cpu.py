@@ -99,3 +99,25 @@ def test_command_line_options_reach_the_model(stand_ins, monkeypatch, capsys):
     assert cli.parse_ids("1, 2 3") == [1, 2, 3]
     with pytest.raises(SystemExit):
         cli.parse_ids("1,x")
+
+
+def test_a_dropped_iterator_stops_its_decoding_and_gives_everything_back(stand_ins):
+    m = model_module.Model(stand_ins, temperature=0.0, max_tokens=200, max_batch=2, context_length=250,
+                           stop_token_ids=[])
+    eng = StandInEngine.made[-1]
+    import time
+    slow = eng.step_ahead
+    eng.step_ahead = lambda *a: (time.sleep(0.002), slow(*a))[1]        # 200 tokens take 0.4 s and more
+    it = m.generate([5, 6, 7], detect_loops=False)
+    first = [next(it), next(it), next(it)]
+    assert first == expected([5, 6, 7], 3)
+    with pytest.raises(RuntimeError, match="still running"):
+        m.ask([1])                                    # one generation at a time on one engine
+    it.close()                                        # the consumer walks away
+    assert m._worker is None and not eng.book.live    # the thread has ended and its sequence is closed
+    assert len(eng.step_sizes) < 100                  # long before the 200 tokens it was asked for
+    assert m.ask([4, 4], max_tokens=3) == expected([4, 4], 3)      # the model is usable again
+    it = m.generate([5, 6, 7], detect_loops=False)
+    next(it)
+    m.close()                                         # close() with an iterator half way: stops and joins it
+    assert eng.released and not eng.book.live

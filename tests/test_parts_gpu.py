@@ -138,7 +138,7 @@ def test_dense_feed_forward_alone():
     w = plain_weights(store, specs)
     ff.bind(store)
     x = torch.randn(11, 50, device=DEV)
-    ctx = types.SimpleNamespace(act_dtype=torch.float32, debug=None)
+    ctx = types.SimpleNamespace(act_dtype=torch.float32, debug=None, status=None)
     m = types.SimpleNamespace(w=w)
     close(ff.forward(x, ctx), P.dense_feed_forward(m, 0, x.double().cpu().numpy()), 5e-6)
 
@@ -153,7 +153,7 @@ def test_moe_feed_forward_alone(E, k, I, S, norm):
     w = plain_weights(store, specs)
     ff.bind(store)
     x = torch.randn(40, H, device=DEV)
-    ctx = types.SimpleNamespace(act_dtype=torch.float32, debug={})
+    ctx = types.SimpleNamespace(act_dtype=torch.float32, debug={}, status=None)
     y = ff.forward(x, ctx)
     m = types.SimpleNamespace(w=w, k=k, norm_topk=norm, cfg={"shared_expert_intermediate_size": S})
     rec = {}
@@ -190,17 +190,23 @@ def define_toy():
             return StateNeed((self.hidden + 1,), torch.float32)
 
         def forward(self, xn, ctx, cache):
-            out = torch.empty((xn.shape[0], self.hidden), dtype=torch.float32, device=xn.device)
-            t0 = 0
-            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):       # every token updates the state exactly once
-                st = cache.state[slot]
-                sums = st[:self.hidden] + torch.cumsum(xn[t0:t0 + n].float(), dim=0)
-                counts = st[self.hidden] + torch.arange(1, n + 1, device=xn.device, dtype=torch.float32)
-                out[t0:t0 + n] = (sums / counts[:, None]) @ self.w.t()
-                st[:self.hidden] = sums[-1]
-                st[self.hidden] = counts[-1]
-                t0 += n
-            return out
+            # everything that changes from step to step comes from device tensors of the context (slots,
+            # seq_of_token, cu_seqlens), so a decode step of this mixer can be recorded into a CUDA graph; every
+            # token updates its sequence's state exactly once
+            H = self.hidden
+            seq = ctx.seq_of_token.long()
+            slots = ctx.slots.long()
+            x = xn.float()
+            run = torch.cumsum(x, dim=0)                                   # over the whole step …
+            first = ctx.cu_seqlens[:-1].long()                             # … minus what came before each sequence
+            before = torch.cat([torch.zeros((1, H), device=x.device), run])[first]
+            st = cache.state[slots]                                        # [B, H + 1]: running sum, count
+            sums = run - before[seq] + st[seq, :H]
+            place = torch.arange(x.shape[0], device=x.device) - first[seq] + 1
+            counts = st[seq, H] + place.float()
+            last = ctx.cu_seqlens[1:].long() - 1
+            cache.state[slots] = torch.cat([sums[last], counts[last, None]], dim=1)
+            return (sums / counts[:, None]) @ self.w.t()
 
     class ToyConfig:
         def __init__(self, raw, where):
@@ -293,7 +299,9 @@ def test_toy_architecture_registers_builds_loads_and_steps(tmp_path):
     model = tq.load_model(folder, "float32", DEV)                       # the class is chosen by config.json
     assert type(model).__name__ == "ToyModel" and len(model.schedule) == 4
     assert model.schedule[3].cache_of == 1 and model.schedule[2].block == 0
-    eng = tq.Engine(model, max_tokens=1024)
+    eng = tq.Engine(model, max_tokens=1024, record_routing=True)
+    assert eng.graphs is not None and not eng.can_step_ahead     # decode steps run as CUDA graphs; with state of its own
+    #                                                              no step is launched before the one before is kept
     assert len(eng.cache.groups) == 1 and eng.cache.kv[3] is eng.cache.kv[1] and eng.cache.kv[0] is None
     assert eng.cache.state[0] is not None and eng.cache.state[2] is not None and eng.cache.state[0] is not eng.cache.state[2]
     w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
@@ -318,6 +326,13 @@ def test_toy_architecture_registers_builds_loads_and_steps(tmp_path):
         check(logits, "batched")
         assert all(sorted(logits[r]) == list(range(len(reqs[r]))) for r in reqs)
     eng.cache.book.check_invariants()
+    assert eng.graphs.graphs, "no decode step was captured"
+    # a part that says it cannot be captured keeps the model's decode steps out of graphs, nothing else changes
+    model.blocks[0].mixer.capturable = lambda: False
+    eager = tq.Engine(model, max_tokens=1024)
+    assert eager.graphs is None
+    logits, _ = run_schedule(eager, *with_tail("b", reqs["b"], 8))
+    check(logits, "uncaptured tail")
     tq.config.unregister_architecture("ToyStatefulLM")
 
 

@@ -1,6 +1,7 @@
-"""Two more kinds of parts defined in a test and plugged into the framework without a change to its files:
+"""More kinds of parts defined in a test and plugged into the framework without a change to its files:
 a position encoding of its own (rotation angles that grow linearly with the pair index, handed to the
-attention mixer as tables) and a feed-forward with routing of its own (every token goes to ONE of a few linear
+attention mixer as tables), one that is no rotation at all (queries and keys scaled by their position, through
+the encoding's own apply()), and a feed-forward with routing of its own (every token goes to ONE of a few linear
 maps, picked by the largest of its first features; built from the framework's layout, gather, grouped-product and
 combine kernels).  A toy architecture made of them is registered, written as a random model folder, loaded by
 its config.json and stepped whole, with a decoded tail, and in batches of unequal lengths, against a numpy
@@ -45,6 +46,20 @@ def define_toy():
         def tables(self):
             return self.cos, self.sin, "half"
 
+    class ScaledByPosition(PositionEncoding):
+        """Not a rotation: queries and keys are multiplied element by element by 1 + rate * pos * (i + 1) / head_dim.
+        It has no tables, so the attention mixer calls apply() between the bias and the cache write."""
+
+        def __init__(self, head_dim, rate):
+            self.head_dim, self.rate = head_dim, rate
+
+        def apply(self, q, k, positions):
+            ramp = torch.arange(1, self.head_dim + 1, device=q.device, dtype=torch.float32) / self.head_dim
+            f = (1.0 + self.rate * positions.float()[:, None, None] * ramp[None, None, :])
+            q.mul_(f.to(q.dtype))
+            if k is not None:
+                k.mul_(f.to(k.dtype))
+
     class SwitchFeedForward(FeedForward):
         """y_t = W[e_t] x_t with e_t = argmax of the token's first n_maps features (ties to the lowest index)."""
 
@@ -84,6 +99,8 @@ def define_toy():
             self.eps = r.real("rms_norm_eps", positive=True)
             self.step = r.real("angle_step", positive=True)
             self.window = r.integer("window", minimum=0)
+            self.scaled_layers = r.int_list("scaled_layers", default=[])
+            self.rate = r.real("scale_rate", default=0.01, positive=True)
 
         @classmethod
         def from_dict(cls, raw, where="config.json"):
@@ -93,13 +110,15 @@ def define_toy():
         def __init__(self, cfg, dtype):
             H = cfg.hidden_size
             pe = make_position_encoding("toy_linear_angles", head_dim=HEAD, step=cfg.step, max_position=cfg.max_position_embeddings)
+            scaled = make_position_encoding("toy_scaled_by_position", head_dim=HEAD, rate=cfg.rate)
             blocks = []
             for l in range(cfg.n_layers):
                 p = f"layers.{l}."
                 blocks.append(PreNormBlock(
                     make_norm("rmsnorm", name=p + "n1.weight", size=H, eps=cfg.eps),
                     make_mixer("attention", prefix=p + "attn.", hidden=H, n_heads=cfg.heads, n_kv_heads=cfg.kv_heads,
-                               head_dim=HEAD, qkv_bias=True, position=pe, window=cfg.window if l % 2 else 0),
+                               head_dim=HEAD, qkv_bias=True, position=scaled if l in cfg.scaled_layers else pe,
+                               window=cfg.window if l % 2 else 0),
                     make_norm("rmsnorm", name=p + "n2.weight", size=H, eps=cfg.eps),
                     make_feed_forward("toy_switch", prefix=p + "ff.", hidden=H, n_maps=cfg.n_maps)))
             super().__init__(cfg, dtype, Embedding("embed.weight", cfg.vocab_size, H), blocks,
@@ -108,13 +127,14 @@ def define_toy():
                              LMHead("head.weight", cfg.vocab_size, H))
 
     register_position_encoding("toy_linear_angles", LinearAngles, replace=True)
+    register_position_encoding("toy_scaled_by_position", ScaledByPosition, replace=True)
     register_feed_forward("toy_switch", SwitchFeedForward, replace=True)
     tq.register_architecture("ToySwitchLM", ToyConfig, ToyModel, replace=True)
 
 
 TOY_CONFIG = {"architectures": ["ToySwitchLM"], "hidden_size": 40, "vocab_size": 83, "max_position_embeddings": 200,
               "num_attention_heads": 4, "num_key_value_heads": 2, "n_maps": 5, "num_hidden_layers": 3,
-              "rms_norm_eps": 1e-5, "angle_step": 0.013, "window": 24}
+              "rms_norm_eps": 1e-5, "angle_step": 0.013, "window": 24, "scaled_layers": [1], "scale_rate": 0.01}
 
 
 def rotate(x, positions, step):
@@ -136,8 +156,13 @@ def toy_plain_forward(w, cfg, tokens, margins=None):
         p = f"layers.{l}."
         xn = P.rmsnorm(x, w[p + "n1.weight"], cfg["rms_norm_eps"])
         a = p + "attn."
-        q = rotate((P.linear(xn, w[a + "q_proj.weight"]) + w[a + "q_proj.bias"]).reshape(T, nh, HEAD), pos, cfg["angle_step"])
-        k = rotate((P.linear(xn, w[a + "k_proj.weight"]) + w[a + "k_proj.bias"]).reshape(T, nkv, HEAD), pos, cfg["angle_step"])
+        if l in cfg.get("scaled_layers", []):
+            f = 1.0 + cfg["scale_rate"] * pos[:, None, None] * (np.arange(1, HEAD + 1) / HEAD)[None, None, :]
+            encode = lambda x: x * f
+        else:
+            encode = lambda x: rotate(x, pos, cfg["angle_step"])
+        q = encode((P.linear(xn, w[a + "q_proj.weight"]) + w[a + "q_proj.bias"]).reshape(T, nh, HEAD))
+        k = encode((P.linear(xn, w[a + "k_proj.weight"]) + w[a + "k_proj.bias"]).reshape(T, nkv, HEAD))
         v = (P.linear(xn, w[a + "v_proj.weight"]) + w[a + "v_proj.bias"]).reshape(T, nkv, HEAD)
         x = x + P.linear(P.attention(q, k, v, cfg["window"] if l % 2 else 0), w[a + "o_proj.weight"])
         xn = P.rmsnorm(x, w[p + "n2.weight"], cfg["rms_norm_eps"])
@@ -158,7 +183,7 @@ def test_toy_position_encoding_and_routed_feed_forward_plug_in(tmp_path):
     assert json.load(open(os.path.join(folder, "config.json")))["architectures"] == ["ToySwitchLM"]
     model = tq.load_model(folder, "float32", DEV)                       # the class is chosen by config.json
     assert type(model).__name__ == "ToyModel" and len(model.schedule) == 3
-    eng = tq.Engine(model, max_tokens=1024)
+    eng = tq.Engine(model, max_tokens=1024, record_routing=True)
     assert len(eng.cache.groups) == 2                                   # full and windowed layers keep their own pages
     w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
     rng = np.random.default_rng(12)

@@ -117,3 +117,35 @@ def test_fp32_stored_tensors_stay_fp32_in_a_bfloat16_run():
     src = RandomSource(specs, 3, fp32_names=["r"])
     store = WeightStore(src, specs, "cpu", torch.bfloat16)
     assert store.get("r").dtype == torch.float32 and store.get("m").dtype == torch.bfloat16
+
+
+def test_random_values_are_a_pure_function_of_seed_name_and_index():
+    """An element's value does not depend on how the tensor is cut or where it is drawn: recomputed here with
+    plain Python integers and numpy float32 from the documented recipe."""
+    from turboquant_cpp_b200.weights.random_init import _tensor_key, normal_knots, standard_normal
+    left, width = (t.numpy() for t in normal_knots("cpu"))
+    assert np.all(width > 0) and left[32768] == 0.0 and np.allclose(left[1:32768], -(left + width)[65534:32767:-1], atol=1e-6)
+    M = (1 << 64) - 1
+    key = _tensor_key(7, "some.tensor")
+
+    def element(i):
+        z = (key + (i + 1) * 0x9E3779B97F4A7C15) & M
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        z ^= z >> 31
+        j, frac = (z >> 48) & 0xFFFF, np.float32(((z >> 24) & 0xFFFFFF) / float(1 << 24))
+        return np.float32(left[j] + np.float32(frac * width[j]))
+    whole = standard_normal(key, 0, 5000, "cpu").numpy()
+    for i in (0, 1, 2, 77, 4999):
+        assert whole[i] == element(i)
+    piece = standard_normal(key, 4000, 1000, "cpu").numpy()
+    assert np.array_equal(piece, whole[4000:])
+    far = standard_normal(key, (1 << 35) + 3, 2, "cpu").numpy()           # indices beyond 32 bits
+    assert far[0] == element((1 << 35) + 3) and far[1] == element((1 << 35) + 4)
+    # through the source: the tensor is the stream of its name, scaled, rounded to the stored dtype
+    spec = WeightSpec("some.tensor", (50, 100))
+    t = RandomSource([spec], 7, std=0.5, dtype=torch.float32).read("some.tensor", "cpu").numpy()
+    assert np.array_equal(t.reshape(-1), whole * np.float32(0.5))
+    big = standard_normal(key, 0, 1 << 20, "cpu")
+    assert abs(big.mean().item()) < 5e-3 and abs(big.std().item() - 1.0) < 5e-3
+    assert abs(((big - big.mean()) ** 4).mean().item() / big.var().item() ** 2 - 3.0) < 0.05     # normal, not uniform sums

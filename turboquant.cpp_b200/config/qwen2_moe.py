@@ -19,6 +19,11 @@ from typing import Any, Dict, List, Tuple
 from .reader import ConfigError, KeyReader
 
 ARCHITECTURE = "Qwen2MoeForCausalLM"
+# limits of the kernels this architecture's parts launch, checked when the configuration is read so that a model
+# that cannot run is refused before its weights are loaded (csrc/attention.cu TQ_MAX_HEAD_DIM, csrc/moe.cu
+# ROUTER_MAX_EXPERTS)
+MAX_HEAD_DIM = 256
+MAX_EXPERTS = 4096
 
 
 @dataclass(frozen=True)
@@ -80,8 +85,9 @@ class Qwen2MoeConfig:
         if heads % kv_heads:
             raise ConfigError(f"{where}: 'num_attention_heads' ({heads}) is not a multiple of "
                               f"'num_key_value_heads' ({kv_heads})")
-        if head_dim % 2:
-            raise ConfigError(f"{where}: 'head_dim' ({head_dim}) must be even for rotary pairs")
+        if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+            raise ConfigError(f"{where}: 'head_dim' ({head_dim}) must be a multiple of 16 between 16 and "
+                              f"{MAX_HEAD_DIM}: the attention kernels take no other head size")
         layers = r.integer("num_hidden_layers", minimum=1)
         act = r.string("hidden_act")
         if act != "silu":
@@ -91,6 +97,9 @@ class Qwen2MoeConfig:
             top_k = r.integer("num_experts_per_tok", minimum=1)
         else:
             top_k = r.integer("num_experts_per_tok", default=0, minimum=0)
+        if n_experts > MAX_EXPERTS:
+            raise ConfigError(f"{where}: 'num_experts' ({n_experts}) exceeds the {MAX_EXPERTS} experts the router "
+                              f"kernels take")
         if n_experts > 0 and not (1 <= top_k <= n_experts):
             raise ConfigError(f"{where}: 'num_experts_per_tok' ({top_k}) must be in 1..num_experts ({n_experts})")
         moe_inter = r.integer("moe_intermediate_size", minimum=1) if n_experts > 0 else \

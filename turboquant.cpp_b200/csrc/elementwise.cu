@@ -236,6 +236,27 @@ TQ_EXPORT int tq_residual_add(float* x, const void* y, int y_dtype, long long n,
 }
 
 // ---------------------------------------------------------------------------------------
+// x[t, i] += bias[i], in place, summed in fp32 (for a projection whose bias no fused kernel adds)
+// ---------------------------------------------------------------------------------------
+template <typename TX, typename TB>
+__global__ void add_bias_kernel(TX* __restrict__ x, const TB* __restrict__ bias, int N) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    TX* row = x + (size_t)blockIdx.x * N;
+    for (int i = threadIdx.x; i < N; i += blockDim.x)
+        row[i] = tq_from_float<TX>(tq_to_float(row[i]) + tq_to_float(bias[i]));
+}
+
+TQ_EXPORT int tq_add_bias(void* x, int x_dtype, const void* bias, int bias_dtype, int T_, int N, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && N > 0, "add_bias: bad sizes T=%d N=%d", T_, N);
+    TQ_DISPATCH(x_dtype, TX, TQ_DISPATCH(bias_dtype, TB,
+        (tq_launch(T_, 256, 0, stream)(add_bias_kernel<TX, TB>, (TX*)x, (const TB*)bias, N))));
+    TQ_CHECK_LAUNCH("add_bias");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // h[t, i] = silu(gu[t, i]) * gu[t, I + i]   (gate rows first, then up rows)
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>

@@ -113,7 +113,9 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
 
     engine:   open(), close(seq), step(entries) -> logits rows, make_entry(seq, tokens, want),
               capacity_tokens, max_slots, page_size, max_position; optionally can_step_ahead, step_ahead(seqs,
-              sampled tokens) -> logits rows, commit_ahead(), drop_ahead(), token_reader(n)
+              sampled tokens) -> logits rows, commit_ahead(), drop_ahead(), token_reader(n); optionally
+              tokens_to_host(sampled tokens) -> list, which may raise if the step's kernels reported a fault (the
+              tokens are then neither appended nor told)
     sampler:  sample(logits, request indices, token indices) -> one token per row (anything with .tolist());
               if it has `penalizes` set, also recent=[tokens of each request so far, prompt first]
     on_tokens(request indices, tokens) is called after every step with that step's new tokens.
@@ -147,8 +149,9 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
 
             def so_far(rows):                            # what a penalizing sampler looks back at
                 return {"recent": [list(prompts[i]) + results[i].tokens for i in rows]} if penalizes else {}
+            to_host = getattr(engine, "tokens_to_host", None) or (lambda t: t.tolist())
             new_dev = sampler.sample(logits, order, [0] * len(order), **so_far(order))
-            new = new_dev.tolist()
+            new = to_host(new_dev)
             sync()
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prompt_tokens += sum(len(prompts[i]) for i in order)
@@ -212,7 +215,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
                         ahead = None
                     new = arrived()
                 else:
-                    new = new_dev.tolist()
+                    new = to_host(new_dev)
             sync()
             stats.decode_seconds += time.perf_counter() - t0
         finally:

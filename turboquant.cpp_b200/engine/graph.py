@@ -40,7 +40,7 @@ class DecodeGraph:
             n_tokens=B, n_seqs=B, tokens=parts[0], positions=parts[1], seq_of_token=parts[2], cu_seqlens=parts[3],
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=B, max_q_len=1,
             max_kv_len=engine.table_width * cache.page_size, act_dtype=engine.act_dtype, device=engine.device,
-            host_q_lens=[1] * B, host_slots=[], debug=None)
+            host_q_lens=[1] * B, host_slots=[], debug={} if engine.record_routing else None, status=engine.status)
         for host in self.hosts:              # constant parts of the buffer
             h = host.numpy()
             h[:] = 0
@@ -49,6 +49,7 @@ class DecodeGraph:
             h[self.offsets[6]:self.offsets[7]] = np.arange(B)
         self.graph = None
         self.logits = None
+        self.first_debug = None
 
     def fill(self, seqs, tokens: Sequence[int]) -> None:
         self.turn ^= 1
@@ -87,6 +88,11 @@ class DecodeGraph:
             logits = eng.model.forward(self.ctx, caches)
             torch.cuda.synchronize(eng.device)
             g = torch.cuda.CUDAGraph()
+            if self.ctx.debug is not None:
+                # this step's records are the eager run's; from the next step on, the captured launches'
+                self.first_debug = {k: [t.clone() if isinstance(t, torch.Tensor) else t for t in v]
+                                    for k, v in self.ctx.debug.items()}
+                self.ctx.debug.clear()
             before = _call.LAUNCHES
             # no garbage collection while the stream is capturing: a collected object that owns device memory or
             # another CUDA graph (an engine that was dropped earlier) would free it in the middle of the capture,
@@ -95,7 +101,7 @@ class DecodeGraph:
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g, pool=self.engine.graphs.pool):
                     self.logits = eng.model.forward(self.ctx, caches)
             finally:
                 if gc_was_on:
@@ -105,6 +111,7 @@ class DecodeGraph:
             self.graph = g
             return logits
         self.graph.replay()
+        eng.graphs.replays += 1
         _call.LAUNCHES += self.kernels
         return self.logits.clone()
 
@@ -113,6 +120,20 @@ class DecodeGraphs:
     def __init__(self, engine):
         self.engine = engine
         self.graphs: Dict[int, DecodeGraph] = {}
+        self.replays = 0                      # decode steps that ran as a replay of a captured graph
+        # one memory pool for all batch sizes: replays are serial on one stream and every result is copied out
+        # of the pool before the next replay, so the graphs can share their activations' memory
+        self.pool = torch.cuda.graph_pool_handle()
+
+    def copy_debug(self, batch: int, into: Dict) -> None:
+        """Copies of what the parts recorded during the last step of this batch size."""
+        g = self.graphs[batch]
+        if g.first_debug is not None:
+            into.update(g.first_debug)
+            g.first_debug = None
+            return
+        for k, v in (g.ctx.debug or {}).items():
+            into[k] = [t.clone() if isinstance(t, torch.Tensor) else t for t in v]
 
     def release(self) -> None:
         """Drops the captured graphs (and their memory) now, not when a garbage collector finds them."""

@@ -42,7 +42,8 @@ def load_model(folder: str, dtype: Union[str, torch.dtype] = "bfloat16", device=
 
 def random_model(config_dict: Dict[str, Any], seed: int, dtype: Union[str, torch.dtype] = "bfloat16",
                  device="cuda:0", std: float = 0.02):
-    """A model with seeded random weights made on the device, without a folder in between."""
+    """A model with seeded random weights drawn on the device, without a folder in between; the same weights
+    that write_random_folder writes for this configuration, seed and std."""
     model = build_model(config_dict, dtype)
     ensure_built(model.kernels())
     specs = model.weight_specs()
@@ -52,8 +53,9 @@ def random_model(config_dict: Dict[str, Any], seed: int, dtype: Union[str, torch
 
 
 def write_random_folder(folder: str, config_dict: Dict[str, Any], seed: int, std: float = 0.02,
-                        dtype: torch.dtype = torch.bfloat16, fp32_names=()) -> None:
-    """Writes config.json and model.safetensors with seeded random weights for a configuration."""
+                        dtype: torch.dtype = torch.bfloat16, fp32_names=(), device="cpu") -> None:
+    """Writes config.json and model.safetensors with seeded random weights for a configuration: the tensors that
+    random_model(config_dict, seed) holds.  `device`: where the values are drawn (the same values everywhere)."""
     model = build_model(config_dict, torch.float32)
     write_random_model(folder, model.config.to_dict() if hasattr(model.config, "to_dict") else config_dict,
-                       model.weight_specs(), seed, std, dtype, fp32_names)
+                       model.weight_specs(), seed, std, dtype, fp32_names, device)

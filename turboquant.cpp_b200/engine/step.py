@@ -23,6 +23,8 @@ import torch
 
 from ..cache import CacheFull, PagedCache, Sequence_
 from ..csrc.build import ensure_built
+from ..kernels._call import KernelError
+from ..kernels.gemm_tc import GAVE_UP, check_status
 from ..parts.base import StepContext
 from .graph import DecodeGraphs
 
@@ -41,22 +43,30 @@ class StepEntry:
 class TokenReader:
     """Brings a step's sampled tokens to the host without waiting for work queued behind them: two pinned
     buffers used in turn (allocated once: nothing is allocated or freed while steps are in flight), a copy and an
-    event per step."""
+    event per step.  The engine's status word travels with the tokens: if a kernel gave up on a bounded wait,
+    the tokens sampled from its output are never handed out."""
 
-    def __init__(self, n: int):
-        self.bufs = [torch.empty(max(1, n), dtype=torch.int32).pin_memory() for _ in range(2)]
+    def __init__(self, n: int, status: Optional[torch.Tensor] = None):
+        self.bufs = [torch.empty(max(1, n) + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.turn = 0
+        self.status = status
 
     def start(self, tokens_dev):
         self.turn ^= 1
-        host = self.bufs[self.turn][:tokens_dev.numel()]
-        host.copy_(tokens_dev, non_blocking=True)
+        n = tokens_dev.numel()
+        host = self.bufs[self.turn]
+        host[:n].copy_(tokens_dev, non_blocking=True)
+        if self.status is not None:
+            host[n:n + 1].copy_(self.status, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
 
         def wait():
             done.synchronize()
-            return host.tolist()
+            if self.status is not None and int(host[n]) != 0:
+                self.status.zero_()
+                raise KernelError("step: " + GAVE_UP + "; the tokens sampled from it are withheld")
+            return host[:n].tolist()
         return wait
 
 
@@ -64,7 +74,11 @@ class Engine:
     """A model, its cache and the step function."""
 
     def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None, device="cuda:0",
-                 use_graphs: Optional[bool] = None):
+                 use_graphs: Optional[bool] = None, record_routing: bool = False):
+        """record_routing: decode steps captured into CUDA graphs keep what the parts record into the step's
+        `debug` (the experts chosen) in memory of the graph, so that setting `engine.debug = {}` before a step
+        fills it from the very launches that generation replays; without it, a step with `debug` set runs
+        outside the graphs."""
         self.model = model
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -74,14 +88,18 @@ class Engine:
         self.cache = PagedCache(model.cache_needs(), model.state_needs(), [e.cache_of for e in model.schedule],
                                 max_tokens, self.act_dtype, self.device, max_slots=max_slots)
         self.debug: Optional[Dict[str, Any]] = None
+        self.record_routing = bool(record_routing)
+        # set by a kernel whose bounded wait ran out (one word per engine: a fault is seen by the engine it spoiled)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         # widest page table a sequence can need; decode graphs keep tables of this width
         longest = min(self.model.max_position, max(self.capacity_tokens, self.cache.page_size))
         self.table_width = -(-longest // self.cache.page_size)
         if use_graphs is None:
             use_graphs = os.environ.get("TQ_NO_GRAPHS", "") in ("", "0")
-        stateless = all(n is None for n in model.state_needs())      # a mixer with state of its own walks the
-        self.graphs = DecodeGraphs(self) if use_graphs and stateless else None   # batch on the host: no graph
+        # a part that cannot run inside a captured step (it says so itself) keeps the whole model out of graphs
+        self.graphs = DecodeGraphs(self) if use_graphs and model.capturable() else None
+        self._stateless = all(n is None for n in model.state_needs())
         self._ahead = None                       # (sequences, tokens each) of a step launched ahead, if any
 
     # ---- what the generation loop asks -----------------------------------------------------------
@@ -108,8 +126,7 @@ class Engine:
     def check_kernels(self) -> None:
         """Raises if a tensor-core kernel gave up on one of its bounded waits since the last check
         (it synchronises the device; call it where results are brought to the host anyway)."""
-        from ..kernels.gemm_tc import check_status
-        check_status(self.device)
+        check_status(word=self.status)
 
     def release(self) -> None:
         """Gives back what the engine holds on the device besides the cache: its CUDA graphs."""
@@ -176,7 +193,7 @@ class Engine:
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=int(want.size),
             max_q_len=int(q_lens.max()), max_kv_len=int((starts + q_lens).max()), act_dtype=self.act_dtype,
             device=self.device, host_q_lens=[int(n) for n in q_lens], host_slots=[int(s) for s in slots],
-            debug=self.debug)
+            debug=self.debug, status=self.status)
         return ctx, dev_tables
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -190,9 +207,11 @@ class Engine:
         self.cache.reserve(seqs, n_new)          # raises CacheFull before anything is written
         decode = all(n == 1 and len(e.want) == 1 for n, e in zip(n_new, entries))
         with torch.cuda.device(self.device):
-            if decode and self.graphs is not None and self.debug is None:
+            if decode and self.graphs is not None and (self.debug is None or self.record_routing):
                 self._check_tokens(np.asarray([e.tokens[0] for e in entries], dtype=np.int64))
                 logits = self.graphs.step(entries)
+                if self.debug is not None:
+                    self.graphs.copy_debug(len(entries), self.debug)
             else:
                 ctx, dev_tables = self.build_context(entries)
                 logits = self.model.forward(ctx, self.cache.layer_caches(dev_tables))
@@ -205,7 +224,7 @@ class Engine:
     def can_step_ahead(self) -> bool:
         """Decode steps can be launched from tokens that are still on the device (CUDA graphs, no per-sequence
         state that a dropped step would have changed)."""
-        return self.graphs is not None and self.debug is None
+        return self.graphs is not None and self.debug is None and self._stateless
 
     def step_ahead(self, seqs: Sequence[Sequence_], tokens_dev: torch.Tensor) -> torch.Tensor:
         """Launches the decode step whose tokens are `tokens_dev` (int32, one per sequence, on the device: the
@@ -230,9 +249,16 @@ class Engine:
         self._ahead = (seqs, n_new)
         return logits
 
-    @staticmethod
-    def token_reader(n: int) -> TokenReader:
-        return TokenReader(n)
+    def token_reader(self, n: int) -> TokenReader:
+        return TokenReader(n, self.status)
+
+    def tokens_to_host(self, tokens_dev: torch.Tensor) -> List[int]:
+        """A step's sampled tokens as a list, after a look at the status word (one synchronisation for both)."""
+        both = torch.cat([tokens_dev.to(torch.int32).reshape(-1), self.status]).tolist()
+        if both[-1] != 0:
+            self.status.zero_()
+            raise KernelError("step: " + GAVE_UP + "; the tokens sampled from it are withheld")
+        return both[:-1]
 
     def commit_ahead(self) -> None:
         seqs, n_new = self._ahead

@@ -110,7 +110,8 @@ def prefill_usable(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
 
 def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, cu_seqlens: torch.Tensor, seq_start: torch.Tensor,
                       page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
-                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of whole runs of new tokens (prompts, or pieces of them) on tcgen05 tensor
     cores (csrc/attention_prefill.cu).  Row t of q belongs to the sequence whose [cu_seqlens[i],
     cu_seqlens[i+1]) holds t and sits at position seq_start[i] + (t - cu_seqlens[i]); the step's keys
@@ -126,5 +127,6 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, cu_seqlens: to
     check("attention_prefill", lib.tq_attention_prefill(
         ptr(q), ptr(cache_layer), ptr(cu_seqlens), ptr(seq_start), ptr(page_table), c_int(page_table.shape[1]),
         c_int(page_size), c_int(cache_layer.shape[0]), c_int(window), c_float(scale), ptr(out), c_int(T), c_int(n_seqs),
-        c_int(max_q_len), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), ptr(status_word(q.device)), stream()))
+        c_int(max_q_len), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+        ptr(status if status is not None else status_word(q.device)), stream()))
     return out

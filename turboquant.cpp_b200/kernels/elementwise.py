@@ -49,6 +49,15 @@ def residual_add(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[t, :] += bias, in place, summed in float32.  x [T, N]; bias [N] (any of the two dtypes)."""
+    T, N = x.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_add_bias(ptr(x), c_int(code(x.dtype)), ptr(bias), c_int(code(bias.dtype)), c_int(T), c_int(N),
+                                stream()))
+    return x
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     T, I = out.shape

@@ -16,22 +16,28 @@ TOKEN_TILES = (16, 32, 64, 128, 256)
 _status: Dict[int, torch.Tensor] = {}
 
 
+GAVE_UP = "a wait inside a tensor-core kernel ran out; its output is not valid"
+
+
 def status_word(device: torch.device) -> torch.Tensor:
-    """One int32 per device that a kernel sets when one of its bounded waits ran out."""
+    """The int32 that a tensor-core kernel sets when one of its bounded waits ran out, for launches that name
+    no word of their own (one per device).  An engine passes its own word, so that a fault is seen by the
+    engine whose step it spoiled."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _status:
         _status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[idx]
 
 
-def check_status(device=None) -> None:
-    """Raises if a tensor-core kernel gave up on a wait since the last check (synchronises)."""
-    for idx, t in _status.items():
-        if device is not None and torch.device(device).index not in (None, idx):
-            continue
+def check_status(device=None, word: Optional[torch.Tensor] = None) -> None:
+    """Raises if a tensor-core kernel gave up on a wait since the last check (synchronises).  `word`: a status
+    word of the caller's; without it, the per-device words."""
+    words = [word] if word is not None else [t for idx, t in _status.items()
+                                             if device is None or torch.device(device).index in (None, idx)]
+    for t in words:
         if int(t.item()) != 0:
             t.zero_()
-            raise KernelError("gemm_tc: a wait inside a tensor-core kernel ran out; its output is not valid")
+            raise KernelError("gemm_tc: " + GAVE_UP)
 
 
 BLOCK_ROWS, BLOCK_K = 128, 64
@@ -104,10 +110,11 @@ _NO_PAIRS = os.environ.get("TQ_NO_PAIRS", "") not in ("", "0")
 
 
 def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
-            token_tile: int, pair: Optional[bool] = None) -> torch.Tensor:
+            token_tile: int, pair: Optional[bool] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
     silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group).
-    pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1)."""
+    pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1).  status: the int32 the
+    kernel sets if a bounded wait runs out (default: the device's word)."""
     if pair is None:
         pair = token_tile >= PAIR_MIN_TILE and not _NO_PAIRS
     if not usable(x, w):
@@ -127,5 +134,5 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None, ptr(lo.tile_count) if lo else None,
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
         c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
-        ptr(status_word(x.device)), stream()))
+        ptr(status if status is not None else status_word(x.device)), stream()))
     return out

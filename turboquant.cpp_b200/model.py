@@ -17,6 +17,7 @@ import torch
 
 from .engine.generate import GenParams, GenResult, GenStats, generate as _generate
 from .engine.loading import load_model
+from .cache import PAGE_SIZE
 from .engine.step import Engine
 from .sampling import Sampler
 
@@ -58,7 +59,7 @@ class Model:
         self._model = model
         ctx = int(context_length) if context_length and context_length > 0 else min(self._model.max_position, 4096)
         self.context_length = min(ctx, self._model.max_position)
-        page = 64
+        page = PAGE_SIZE
         per_request = -(-self.context_length // page) * page
         self._engine = Engine(self._model, max_tokens=per_request * self.max_batch, max_slots=max(self.max_batch, 1),
                               device=device)
@@ -66,6 +67,7 @@ class Model:
         self.stop_token_ids = tuple(stop_token_ids) if stop_token_ids is not None else tuple(eos)
         self.last_stats: Optional[GenStats] = None
         self.last_results: List[GenResult] = []
+        self._worker = self._worker_stop = None
 
     # ---- properties ---------------------------------------------------------------------------
     @property
@@ -100,6 +102,9 @@ class Model:
                        rep_window: Optional[int] = None, detect_loops: Optional[bool] = None) -> List[List[int]]:
         """Continuations of several prompts (token ids in, token ids out, on the host)."""
         self._check_open()
+        import threading
+        if self._worker is not None and self._worker.is_alive() and threading.current_thread() is not self._worker:
+            raise RuntimeError("a generate() of this model is still running; finish or close its iterator first")
         p = self._params(max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty, rep_window, detect_loops)
         stats = GenStats()
         sampler = Sampler(p.temperature, p.top_p, p.seed, p.rep_penalty, p.rep_window)
@@ -115,30 +120,51 @@ class Model:
         return self.generate_batch([prompt], **kw)[0]
 
     def generate(self, prompt: Sequence[int], **kw) -> Iterator[int]:
-        """Yields the continuation's tokens one by one as they are sampled."""
+        """Yields the continuation's tokens one by one as they are sampled.  The decoding runs in a thread of its
+        own; a consumer that stops early (break, an exception, close()) stops it too: the thread is told at its
+        next token, gives its sequences back and is joined before this generator, or close(), returns."""
         self._check_open()
+        if self._worker is not None and self._worker.is_alive():
+            raise RuntimeError("a generate() of this model is still running; finish or close its iterator first")
         import queue
         import threading
         q: "queue.Queue" = queue.Queue()
         done = object()
+        stop = threading.Event()
+
+        class _Stopped(Exception):
+            pass
+
+        def told(idx, toks):
+            if stop.is_set():
+                raise _Stopped()                 # unwinds through the generation loop, which closes its sequences
+            for t in toks:
+                q.put(t)
 
         def run():
             try:
-                self.generate_batch([prompt], on_tokens=lambda idx, toks: [q.put(t) for t in toks], **kw)
+                self.generate_batch([prompt], on_tokens=told, **kw)
+                q.put(done)
+            except _Stopped:
                 q.put(done)
             except BaseException as e:  # noqa: BLE001 - handed to the consumer
                 q.put(e)
 
         t = threading.Thread(target=run, daemon=True)
+        self._worker, self._worker_stop = t, stop
         t.start()
-        while True:
-            item = q.get()
-            if item is done:
-                break
-            if isinstance(item, BaseException):
-                raise item
-            yield item
-        t.join()
+        try:
+            while True:
+                item = q.get()
+                if item is done:
+                    break
+                if isinstance(item, BaseException):
+                    raise item
+                yield item
+        finally:
+            stop.set()
+            t.join()
+            self._worker = None
 
     # ---- lifetime -----------------------------------------------------------------------------
     def _check_open(self) -> None:
@@ -146,6 +172,11 @@ class Model:
             raise RuntimeError("the model is closed")
 
     def close(self) -> None:
+        worker = getattr(self, "_worker", None)
+        if worker is not None and worker.is_alive():          # an iterator that was dropped half way
+            self._worker_stop.set()
+            worker.join()
+        self._worker = None
         if self._engine is not None:
             self._engine.release()
         self._engine = None

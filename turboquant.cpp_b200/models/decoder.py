@@ -18,7 +18,7 @@ import torch
 
 from ..kernels import elementwise as K
 from ..kernels.linear import linear
-from ..parts.base import KVNeed, LayerCache, Norm, Part, StateNeed, StepContext
+from ..parts.base import Block, KVNeed, LayerCache, Norm, Part, StateNeed, StepContext
 from ..weights.loader import WeightSpec, WeightStore
 
 
@@ -68,7 +68,7 @@ class LMHead(Part):
 
 
 class DecoderModel:
-    def __init__(self, config, dtype: torch.dtype, embedding: Embedding, blocks: Sequence[Part],
+    def __init__(self, config, dtype: torch.dtype, embedding: Embedding, blocks: Sequence[Block],
                  schedule: Sequence[ScheduleEntry], final_norm: Norm, head: LMHead):
         self.config, self.dtype = config, dtype
         self.embedding, self.blocks, self.schedule = embedding, list(blocks), list(schedule)
@@ -84,7 +84,7 @@ class DecoderModel:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")
                 if self.schedule[e.cache_of].cache_of is not None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps none of its own")
-                a, b = self.blocks[e.block].mixer.cache_need(), self.blocks[self.schedule[e.cache_of].block].mixer.cache_need()
+                a, b = self.blocks[e.block].cache_need(), self.blocks[self.schedule[e.cache_of].block].cache_need()
                 if a is None or b is None or (a.n_kv_heads, a.head_dim) != (b.n_kv_heads, b.head_dim):
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {e.cache_of}: different shapes")
 
@@ -119,10 +119,14 @@ class DecoderModel:
 
     def cache_needs(self) -> List[Optional[KVNeed]]:
         """Per schedule entry: the key/value need of an entry that keeps a cache, else None."""
-        return [self.blocks[e.block].mixer.cache_need() if e.cache_of is None else None for e in self.schedule]
+        return [self.blocks[e.block].cache_need() if e.cache_of is None else None for e in self.schedule]
 
     def state_needs(self) -> List[Optional[StateNeed]]:
-        return [self.blocks[e.block].mixer.state_need() for e in self.schedule]
+        return [self.blocks[e.block].state_need() for e in self.schedule]
+
+    def capturable(self) -> bool:
+        """Whether decode steps can be recorded into CUDA graphs: every block says so of its own parts."""
+        return all(b.capturable() for b in self.blocks)
 
     # ---- one step ------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, layer_caches: Sequence[LayerCache]) -> Optional[torch.Tensor]:

@@ -14,6 +14,7 @@ from typing import List, Optional
 import torch
 
 from ..kernels import attention as KA
+from ..kernels import elementwise as KE
 from ..kernels.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 from .base import KVNeed, LayerCache, Mixer, PositionEncoding, StepContext, register_mixer
@@ -60,7 +61,7 @@ class AttentionMixer(Mixer):
             self.position.prepare(store.device)
 
     def kernels(self) -> List[str]:
-        names = ["attention"]
+        names = ["attention", "elementwise"]
         if getattr(self, "run_dtype", None) == torch.bfloat16 and self.head_dim in (64, 128):
             names.append("attention_prefill")
         return names
@@ -74,10 +75,17 @@ class AttentionMixer(Mixer):
         qkv = linear(xn, self.w_qkv, out_dtype=act)
         q = torch.empty((T, self.n_heads, self.head_dim), dtype=act, device=xn.device)
         tables = self.position.tables() if self.position is not None else None
+        bias = self.b_qkv
         if self.position is not None and tables is None:
-            raise NotImplementedError("attention: a position encoding without tables needs an unfused pass")
+            # an encoding that is not a table-driven rotation: the bias first, then the encoding's own pass over
+            # the projection's queries and keys in place, then the fused kernel only splits and writes the cache
+            if bias is not None:
+                KE.add_bias(qkv, bias)
+                bias = None
+            rows = qkv.view(T, self.n_heads + 2 * self.n_kv_heads, self.head_dim)
+            self.position.apply(rows[:, :self.n_heads], rows[:, self.n_heads:self.n_heads + self.n_kv_heads], ctx.positions)
         cos, sin, pairing = tables if tables is not None else (None, None, "half")
-        KA.qkv_rope_cache(qkv, self.b_qkv, cos, sin, pairing, ctx.positions, ctx.seq_of_token, cache.page_table,
+        KA.qkv_rope_cache(qkv, bias, cos, sin, pairing, ctx.positions, ctx.seq_of_token, cache.page_table,
                           cache.page_size, q, cache.kv if cache.writes else None,
                           self.n_heads, self.n_kv_heads, self.head_dim)
         o = torch.empty((T, self.q_size), dtype=act, device=xn.device)
@@ -85,7 +93,7 @@ class AttentionMixer(Mixer):
             # long runs of new tokens (prompts): tensor cores
             KA.attention_prefill(q, cache.kv, ctx.cu_seqlens, ctx.seq_start, cache.page_table, cache.page_size,
                                  self.window, self.scale, o, ctx.n_seqs, ctx.max_q_len, self.n_heads, self.n_kv_heads,
-                                 self.head_dim)
+                                 self.head_dim, status=ctx.status)
         elif KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
             n_splits = KA.splits_for(T, self.n_kv_heads)
             partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32, device=xn.device)

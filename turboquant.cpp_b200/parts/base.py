@@ -18,11 +18,17 @@ Interfaces
 Part            weight_specs() -> [WeightSpec]; bind(store); kernels() -> names of kernel files
 Norm            forward(x, out_dtype, rows, add) -> xn; add_forward(x, y) -> xn (x += y in fp32, then the norm)
 PositionEncoding  tables() -> (cos, sin, pairing) or None; apply(q, k, positions)
-Mixer           cache_need() -> KVNeed | None; state_need() -> StateNeed | None;
+Mixer           cache_need() -> KVNeed | None; state_need() -> StateNeed | None; capturable() -> bool;
                 forward(xn, ctx, cache) -> y [T, hidden]
-FeedForward     forward(xn, ctx) -> y [T, hidden]
-Block           forward(x, pending, ctx, cache) -> (x, pending): pending is a sub-layer output
-                not yet added to the residual stream x (the sum is fused into the next norm)
+FeedForward     capturable() -> bool; forward(xn, ctx) -> y [T, hidden]
+Block           cache_need(); state_need(); capturable(); forward(x, pending, ctx, cache) -> (x, pending):
+                pending is a sub-layer output not yet added to the residual stream x (the sum is fused
+                into the next norm).  A model talks to its blocks only through this interface.
+
+capturable(): whether the part's forward can be recorded into a CUDA graph for decode steps: it reads
+everything that changes from step to step from device tensors of the StepContext (positions, slots, page
+tables, …), never from its host fields, and never synchronises.  One part that says no keeps the model's
+decode steps out of graphs; nothing else changes.
 """
 from __future__ import annotations
 
@@ -83,6 +89,7 @@ class StepContext:
     host_q_lens: Sequence[int] = ()
     host_slots: Sequence[int] = ()
     debug: Optional[Dict[str, Any]] = None      # tests: parts may record what they decided
+    status: Optional[torch.Tensor] = None       # int32 [1]: kernels with bounded waits report here when one ran out
 
 
 class Part:
@@ -127,14 +134,42 @@ class Mixer(Part):
         return None
 
     def state_need(self) -> Optional[StateNeed]:
+        """Per-sequence state of fixed size: the step hands the mixer `cache.state` [max_slots, *shape], zero at
+        a sequence's start; row ctx.slots[i] belongs to the step's i-th sequence.  Every token must update it
+        exactly once."""
         return None
+
+    def capturable(self) -> bool:
+        return True
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
 
 
 class FeedForward(Part):
+    def capturable(self) -> bool:
+        return True
+
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """One entry of a model's list of layers: the arrangement of a mixer, a feed-forward and norms around the
+    residual stream.  The model asks a block what its layer needs from the cache and runs it; it never looks
+    inside."""
+
+    def cache_need(self) -> Optional[KVNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def capturable(self) -> bool:
+        return True
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         raise NotImplementedError
 
 

@@ -11,15 +11,24 @@ from typing import List, Optional, Tuple
 import torch
 
 from ..weights.loader import WeightSpec, WeightStore
-from .base import FeedForward, LayerCache, Mixer, Norm, Part, StepContext
+from .base import Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, StateNeed, StepContext
 
 
-class PreNormBlock(Part):
+class PreNormBlock(Block):
     def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def cache_need(self) -> Optional[KVNeed]:
+        return self.mixer.cache_need()
+
+    def state_need(self) -> Optional[StateNeed]:
+        return self.mixer.state_need()
+
+    def capturable(self) -> bool:
+        return self.mixer.capturable() and self.ffn.capturable()
 
     def weight_specs(self) -> List[WeightSpec]:
         return [s for p in self.parts() for s in p.weight_specs()]

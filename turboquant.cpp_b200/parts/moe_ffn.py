@@ -58,8 +58,10 @@ class MoEFeedForward(FeedForward):
     def bind(self, store: WeightStore) -> None:
         p, H, I, S, E = self.prefix, self.hidden, self.intermediate, self.shared_intermediate, self.n_experts
         self.w_router = store.get(p + "gate.weight")
-        first = store.get(f"{p}experts.0.gate_proj.weight")
-        dt = first.dtype
+        # a tensor stored in 32 bits stays 32-bit: if any of the experts' tensors is kept in float32, the stacked
+        # buffers are float32 (the others widen exactly), never the other way round
+        names = [f"{p}experts.{e}.{n}_proj.weight" for e in range(E) for n in ("gate", "up", "down")]
+        dt = torch.float32 if any(store.kept_dtype_of(n) == torch.float32 for n in names) else store.kept_dtype_of(names[0])
         self.w13 = torch.empty((E, 2 * I, H), dtype=dt, device=store.device)
         self.w2 = torch.empty((E, H, I), dtype=dt, device=store.device)
         for e in range(E):
@@ -70,9 +72,9 @@ class MoEFeedForward(FeedForward):
         if S > 0:
             q = p + "shared_expert."
             g, u, d = (store.take(q + n + "_proj.weight") for n in ("gate", "up", "down"))
-            sdt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+            sdt = torch.float32 if torch.float32 in (g.dtype, u.dtype, d.dtype) else g.dtype
             self.ws13 = torch.cat([g.to(sdt), u.to(sdt)], dim=0).unsqueeze(0).contiguous()
-            self.ws2 = d.unsqueeze(0).contiguous()
+            self.ws2 = d.to(sdt).unsqueeze(0).contiguous()
             if self.shared_gate:
                 self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
         if store.run_dtype == torch.bfloat16 and H % 8 == 0 and self.w_router.dtype == torch.bfloat16:
@@ -108,11 +110,11 @@ class MoEFeedForward(FeedForward):
             cls._side_streams[key] = torch.cuda.Stream(device=device)
         return cls._side_streams[key]
 
-    def _product(self, x, w, out, layout, swiglu, token_tile):
+    def _product(self, x, w, out, layout, swiglu, token_tile, status=None):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
         kernel otherwise."""
         if isinstance(w, KT.PackedWeights):
-            return KT.gemm_tc(x, w, out, layout, token_tile)
+            return KT.gemm_tc(x, w, out, layout, token_tile, status=status)
         return KM.grouped_gemm(x, w, out, layout, swiglu)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
@@ -131,9 +133,9 @@ class MoEFeedForward(FeedForward):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 hs = torch.empty((T, S), dtype=act, device=dev)
-                self._product(xn, self.ws13, hs, None, True, stile)
+                self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
                 y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
-                self._product(hs, self.ws2, y_shared, None, False, stile)
+                self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status)
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
@@ -151,19 +153,21 @@ class MoEFeedForward(FeedForward):
                 # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products
                 # are exact in fp32 and the sum is fp32), then the selection kernel
                 logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
-                KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1))
+                KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1), status=ctx.status)
                 KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
             else:
                 KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
             KM.moe_align(ids, layout)
             KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
         if ctx.debug is not None:
-            ctx.debug.setdefault("router_ids", []).append(ids.clone())
-            ctx.debug.setdefault("router_weights", []).append(wts.clone())
+            # the tensors themselves: nothing below writes them, and inside a captured step a reference keeps their
+            # memory from being reused, so that they hold every replay's choices
+            ctx.debug.setdefault("router_ids", []).append(ids)
+            ctx.debug.setdefault("router_weights", []).append(wts)
         h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
-        self._product(x_rows, self.w13, h_rows, layout, True, tile)
+        self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
-        self._product(h_rows, self.w2, y_rows, layout, False, tile)
+        self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)

@@ -168,6 +168,10 @@ class WeightStore:
         self._cache[name] = t
         return t
 
+    def kept_dtype_of(self, name: str) -> torch.dtype:
+        """The dtype get(name) will return, without reading the tensor."""
+        return kept_dtype(self._index[name][0], self.run_dtype)
+
     def take(self, name: str) -> torch.Tensor:
         """Like get, but forgets the tensor: for parts that copy it into a stacked buffer."""
         t = self.get(name)
