@@ -1,11 +1,12 @@
 #!/usr/bin/env python3
 """Decode and prefill speed of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model a2.7b|57b] [--layers L] [--batch B]
+                    [--impl reference]
 
-The model has the layer sizes of Qwen1.5-MoE-A2.7B with seeded random weights in bfloat16; token ids
-are synthetic (uniform).  A "step" is one decode step of a batch of 8 sequences that start from
-2,048-token prompts (context 4,096).  One JSON line is printed:
+The model has the layer sizes of Qwen1.5-MoE-A2.7B (default) or of Qwen2-57B-A14B (--model 57b) with seeded
+random weights in bfloat16; token ids are synthetic (uniform).  A "step" is one decode step of a batch of 8
+sequences that start from 2,048-token prompts (cache for 4,096 each).  One JSON line is printed:
   value     decoded tokens per second, timed on the device with CUDA events over exactly K steps
             (every step reads far more weight and cache bytes than the L2 holds, so no flush)
   e2e       the same through the Python entry point (Model.generate_batch): host token ids in,
@@ -13,7 +14,10 @@ are synthetic (uniform).  A "step" is one decode step of a batch of 8 sequences 
   prefill   one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak
   roofline  bytes the decode step has to read (each weight it uses once, and the cache of the live
             requests) / its time, against the measured copy bandwidth
-  points    decode tokens per second at batch 1 and batch 64
+  points    decode tokens per second at batch 1 and batch 64 from 2,048-token prompts, and at batch 1, 8 and 64
+            with the context at 4,096 by the last timed step; points_frac: each point's fraction of the roofline
+  vs_baseline  against the reference's own CPU forward, timed once on this architecture's sizes (`baseline` says how):
+            the reference has no GPU path, no batch and no prompt step for it, so this is context, not a race
 Only one GPU is supported: for --gpus N > 1 a line says so and the exit code is 2.
 """
 from __future__ import annotations
@@ -39,8 +43,28 @@ A27B = {
     "sliding_window": 0, "max_window_layers": 24, "tie_word_embeddings": False, "decoder_sparse_step": 1,
     "mlp_only_layers": [], "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
-FULL_LAYERS = 24
+# Layer sizes of Qwen2-57B-A14B.
+B57 = dict(A27B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, num_experts=64,
+           num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
+           intermediate_size=20480, max_position_embeddings=32768, max_window_layers=28)
+MODELS = {"a2.7b": ("Qwen1.5-MoE-A2.7B sizes", A27B), "57b": ("Qwen2-57B-A14B sizes", B57)}
 PROMPT, CONTEXT = 2048, 4096
+
+
+def reference_cpu_rate(layers):
+    """Tokens per second of the reference's own CPU forward at Qwen1.5-MoE-A2.7B sizes with `layers` layers, from
+    the committed record of one timed run on 1 and 2 layers (tests/golden/reference_cpu_timing.txt, made by
+    tests/golden/time_reference.sh): head and embedding once, the layer's cost times the number of layers."""
+    try:
+        ms = {}
+        for line in open(os.path.join(ROOT, "tests", "golden", "reference_cpu_timing.txt")):
+            f = line.split()
+            if f and f[0] == "layers":
+                ms[int(f[1])] = float(f[5])
+        layer = ms[2] - ms[1]
+        return 1e3 / (ms[1] - layer + layers * layer), ms
+    except (OSError, KeyError, ValueError, IndexError):
+        return None, {}
 
 
 def peaks():
@@ -116,7 +140,8 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--model", choices=sorted(MODELS), default="a2.7b")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
@@ -141,7 +166,10 @@ def main() -> int:
     from turboquant_cpp_b200.kernels import _call
 
     pk = peaks()
-    cfg = dict(A27B)
+    model_name, cfg = MODELS[args.model]
+    cfg = dict(cfg)
+    FULL_LAYERS = cfg["num_hidden_layers"]
+    args.layers = args.layers or FULL_LAYERS
     cfg["num_hidden_layers"] = args.layers
     cfg["max_window_layers"] = args.layers
     n = model_numbers(cfg, args.layers)
@@ -153,13 +181,13 @@ def main() -> int:
     rng = np.random.default_rng(0)
     V = cfg["vocab_size"]
 
-    def run_decode(batch, steps, warmup, want_experts=False):
-        """Prefill `batch` prompts of PROMPT tokens, then time `steps` decode steps on the device."""
+    def run_decode(batch, steps, warmup, want_experts=False, prompt=PROMPT):
+        """Prefill `batch` prompts of `prompt` tokens, then time `steps` decode steps on the device."""
         eng = tq.Engine(model, max_tokens=batch * CONTEXT, max_slots=batch)
         seqs = [eng.open() for _ in range(batch)]
         group = 8
         for g0 in range(0, batch, group):
-            eng.step([tq.StepEntry(s, rng.integers(0, V, size=PROMPT).tolist(), []) for s in seqs[g0:g0 + group]])
+            eng.step([tq.StepEntry(s, rng.integers(0, V, size=prompt).tolist(), []) for s in seqs[g0:g0 + group]])
         smp = tq.Sampler(0.0)
         toks = rng.integers(0, V, size=(warmup + steps + 1, batch))
 
@@ -215,12 +243,19 @@ def main() -> int:
     d2h = 4 * args.batch
     m.close()
 
+    ref_rate, ref_ms = reference_cpu_rate(args.layers) if args.model == "a2.7b" else (None, {})
     out = {
-        "metric": "decode tok/s @ batch 8 (Qwen1.5-MoE-A2.7B sizes, random weights)", "value": round(main_run["tok_s"], 1),
+        "metric": f"decode tok/s @ batch {args.batch} ({model_name}, random weights)", "value": round(main_run["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, seeded random weights", "impl": "ours",
-        "config": {"model": "Qwen1.5-MoE-A2.7B sizes", "layers": args.layers, "layers_of_model": FULL_LAYERS,
+        "vs_baseline": round(main_run["tok_s"] / ref_rate, 1) if ref_rate else None,
+        "baseline": ({"value": round(ref_rate, 4), "unit": "tokens/s", "what": "the reference's own forward (tq_forward) on a CPU, "
+                      "float32, one token of one sequence at a time: it has no GPU path, no batch and no prompt step for "
+                      "this architecture; timed on 1 and 2 layers of these sizes and scaled to this run's layers "
+                      "(tests/golden/reference_cpu_timing.txt); other hardware, so context, not a race",
+                      "ms_per_token_1_layer": ref_ms.get(1), "ms_per_token_2_layers": ref_ms.get(2)} if ref_rate else None),
+        "dtype": "bf16", "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "config": {"model": model_name, "layers": args.layers, "layers_of_model": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "experts": cfg["num_experts"],
                    "top_k": cfg["num_experts_per_tok"], "moe_inter": cfg["moe_intermediate_size"],
@@ -256,8 +291,15 @@ def main() -> int:
         out["prefill"] = {"value": round(PROMPT / best * 1e3, 1), "tokens": PROMPT, "ms": round(best, 3),
                           "frac": round(fl / (best * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         k_pts = max(8, min(args.steps, 32))
-        out["points"] = {"decode_b1": round(run_decode(1, k_pts, 3)["tok_s"], 1),
-                         "decode_b64": round(run_decode(64, k_pts, 3)["tok_s"], 1)}
+        out["points"], out["points_frac"] = {}, {}
+        # from 2,048-token prompts, and with the context at 4,096 by the last timed step
+        for name, batch, prompt in (("decode_b1", 1, PROMPT), ("decode_b64", 64, PROMPT),
+                                    ("decode_b1_ctx4096", 1, CONTEXT - k_pts - 3), ("decode_b8_ctx4096", 8, CONTEXT - k_pts - 3),
+                                    ("decode_b64_ctx4096", 64, CONTEXT - k_pts - 3)):
+            r = run_decode(batch, k_pts, 3, want_experts=True, prompt=prompt)
+            by = decode_bytes(n, r["distinct"], batch, r["ctx_tokens"])
+            out["points"][name] = round(r["tok_s"], 1)
+            out["points_frac"][name] = round(by / (r["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     if args.kernel_table:
         kernel_table(tq, model, rng, V, args.batch, args.kernel_table)
     print(json.dumps(out))
