@@ -112,6 +112,35 @@ def test_command_line(tiny_folders, plain_models):
     assert r.returncode == 0 and "Qwen2MoeForCausalLM" in r.stdout and "num_experts: 8" in r.stdout
 
 
+def test_command_line_random_weights_tokens_file_profile_and_layer_sums(tiny_folders, tmp_path):
+    """--random CONFIG --seed-weights N runs the model that write_random_folder writes for the same configuration
+    and seed (the folder of Tiny A was written with seed 0); --tokens-file gives the prompts; --profile prints the
+    reference's bucket line and the buckets' rates; TQ_DEBUG_LAYERS prints per-layer sums of the residual stream."""
+    import json
+    from conftest import TINY_A
+    p = prompts_for("A", [7, 4], 45)
+    quant = [sys.executable, os.path.join(ROOT, "bin", "quant")]
+    common = ["-n", "5", "-T", "0", "--dtype", "float32"]
+    cfg_file, tok_file = str(tmp_path / "cfg.json"), str(tmp_path / "prompts.txt")
+    json.dump(TINY_A, open(cfg_file, "w"))
+    open(tok_file, "w").write("# two prompts\n" + "\n".join(" ".join(map(str, q)) for q in p) + "\n\n")
+    a = subprocess.run(quant + [tiny_folders["A"]] + common + ["--tokens-file", tok_file], capture_output=True, text=True, timeout=600)
+    b = subprocess.run(quant + ["--random", cfg_file, "--seed-weights", "0"] + common + ["--tokens-file", tok_file, "--profile"],
+                       capture_output=True, text=True, timeout=600, env=dict(os.environ, TQ_DEBUG_LAYERS="1"))
+    assert a.returncode == 0 and b.returncode == 0, a.stderr + b.stderr
+    assert a.stdout == b.stdout and len(a.stdout.strip().splitlines()) == 2
+    line = [l for l in b.stderr.splitlines() if l.startswith("[Profile 10 tok]")]
+    assert len(line) == 1 and all(k in line[0] for k in ("matmul=", "moe=", "attn=", "other=", "per-tok:"))
+    rates = [l for l in b.stderr.splitlines() if l.startswith("[Profile] ")]
+    assert {l.split()[1].rstrip(":") for l in rates} >= {"matmul", "moe", "attn"} and all("GB/s" in l and "TFLOP/s" in l for l in rates)
+    sums = [l for l in b.stderr.splitlines() if l.startswith("[fwd]   L")]
+    assert any("L0 pos=0 final x sum=" in l for l in sums) and any("L1 pos=1 " in l for l in sums)
+    c = subprocess.run(quant + ["--random", cfg_file, "--seed-weights", "1"] + common + ["--tokens-file", tok_file],
+                       capture_output=True, text=True, timeout=600)
+    assert c.returncode == 0 and c.stdout != a.stdout                       # another seed, another model
+    assert subprocess.run(quant + common, capture_output=True, text=True).returncode != 0       # neither folder nor --random
+
+
 def test_command_line_measurements(tiny_folders):
     """--bench-prefill and --bench-memory print the reference's machine-readable lines (tools/quant.c:788, 848):
     prompt length, milliseconds and tokens a second; context and decoded tokens a second, for every context that

@@ -161,6 +161,28 @@ def test_attention_split(nh, nkv, hd, window, n_splits, dtype, tol):
         want[t0:t0 + ql] = P.attention(qfull, d["k"][i], d["v"][i], window)[L - ql:]
         t0 += ql
     close(out, want, tol)
+    assert int(KA.tickets(torch.device(DEV)).abs().sum()) == 0       # every row's last range put its ticket back
+
+
+def test_attention_split_merges_in_range_order_whoever_comes_last():
+    """The range that finishes last merges; which one that is differs from launch to launch, the result does not."""
+    from turboquant_cpp_b200.kernels import attention as KA
+    rng = np.random.default_rng(5)
+    nh, nkv, hd, page, n_splits = 8, 2, 128, 64, 9
+    seq_lens, q_lens = [700, 40, 1300, 64], [2, 1, 1, 1]
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, torch.bfloat16)
+    T = sum(q_lens)
+    q = dev(bf16_values(rng.normal(size=(T, nh, hd))), torch.bfloat16)
+    args = (dev(d["cache"], torch.bfloat16), dev(d["positions"], torch.int32), dev(d["seq_of"], torch.int32),
+            dev(d["table"], torch.int32), page, 0, 1 / math.sqrt(hd))
+    outs = []
+    for _ in range(20):
+        out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+        partial = torch.empty(T * nh * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+        KA.attention_split(q, *args, out, nh, nkv, hd, n_splits, partial)
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    assert int(KA.tickets(torch.device(DEV)).abs().sum()) == 0
 
 
 @pytest.mark.parametrize("nh,hd", [(3, 128), (1, 128)])

@@ -1,6 +1,7 @@
 """Command line in the manner of the reference's `quant` tool (tools/quant.c:126-163, 241-346).
 
-    quant <model folder> [-p "ids"]… [-n max_tokens] [-T temperature] [-P top_p] [-s seed]
+    quant <model folder> | --random CONFIG.json [--seed-weights N]
+          [-p "ids"]… [--tokens-file FILE] [-n max_tokens] [-T temperature] [-P top_p] [-s seed]
           [--ctx N] [--dtype bfloat16|float32] [--batch N] [--stop id]… [--rep-penalty F] [--rep-window N]
           [--detect-loops] [--info] [--profile]
           [--bench-prefill] [--bench-memory]
@@ -8,8 +9,14 @@
 Names and meanings follow the reference where it has them: -p prompt (default "Hello" there; here
 a prompt is a list of token ids, "1,2,3" or "1 2 3", default "0"), -n max tokens (256), -T
 temperature (0.7), -P top-p (0.9), -s seed (42; 0 means the default), --ctx context length, --info
-print the model and exit, --profile time the kernels' groups, --bench-prefill and --bench-memory
-(decode speed at growing context).  --rep-penalty and --rep-window set what the reference keeps as
+print the model and exit, --profile the share and time per token of matmul / moe / attn / other as the reference
+prints them (src/engine/tq_transformer.c:2994-3021) plus each bucket's bytes and operations against the device's
+peaks, --bench-prefill and --bench-memory (decode speed at growing context).  Instead of a model folder,
+--random CONFIG.json runs the configuration with random weights drawn from --seed-weights (the reference has
+no such mode; its tests fill weights by hand).  --tokens-file FILE reads prompts from a file, one per line
+(the reference reads its text prompts from a file the same way for --ppl, tools/quant.c:430-470).
+TQ_DEBUG_LAYERS=1 in the environment prints per-layer checksums of the residual stream as the reference's
+TQ_DEBUG_PREFILL does.  --rep-penalty and --rep-window set what the reference keeps as
 engine defaults without an option (1.1 over 32 tokens, include/turboquant/tq_engine.h:408-409); here
 the penalty is off unless asked for, and so is the reference's detector of repetition loops
 (--detect-loops; src/engine/tq_generate.c:610-630).  -j (threads) is accepted and ignored.  -p may be given several
@@ -34,8 +41,11 @@ def parse_ids(text: str) -> List[int]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="quant", description="Generate tokens with a model folder on one B200.")
-    ap.add_argument("model", help="folder with config.json and model.safetensors")
+    ap.add_argument("model", nargs="?", help="folder with config.json and model.safetensors")
+    ap.add_argument("--random", metavar="CONFIG.json", help="a configuration to run with random weights instead of a folder")
+    ap.add_argument("--seed-weights", type=int, default=0, help="seed of the random weights (with --random)")
     ap.add_argument("-p", dest="prompts", action="append", help="prompt as token ids; may repeat")
+    ap.add_argument("--tokens-file", help="file with one prompt (token ids) per line; empty lines and # lines are skipped")
     ap.add_argument("-n", dest="max_tokens", type=int, default=256)
     ap.add_argument("-T", dest="temperature", type=float, default=0.7)
     ap.add_argument("-P", dest="top_p", type=float, default=0.9)
@@ -57,10 +67,25 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
-    from .config.registry import load_config
+    import json
+    import os
+    from .config.registry import load_config, parse_config
     from . import models  # noqa: F401
+    if (args.model is None) == (args.random is None):
+        ap.error("give a model folder or --random CONFIG.json (one of the two)")
+    raw = None
+    if args.random is not None:
+        try:
+            with open(args.random, encoding="utf-8") as f:
+                raw = json.load(f)
+        except (OSError, ValueError) as e:
+            print(f"quant: cannot read the configuration '{args.random}': {e}", file=sys.stderr)
+            return 2
+    if args.profile:
+        os.environ.setdefault("TQ_NO_PDL", "1")       # a kernel's time without its wait for the one before
+        os.environ.setdefault("TQ_NO_GRAPHS", "1")    # kernels launched one by one show up under their names
     if args.info:
-        arch, cfg = load_config(args.model)
+        arch, cfg = parse_config(raw, args.random) if raw is not None else load_config(args.model)
         print(f"architecture: {arch.name}")
         for k, v in sorted(cfg.to_dict().items()):
             print(f"  {k}: {v}")
@@ -72,10 +97,15 @@ def main(argv=None) -> int:
         return 2
     from .model import Model
     seed = args.seed if args.seed != 0 else 42
-    m = Model(args.model, temperature=args.temperature, top_p=args.top_p, max_tokens=args.max_tokens,
-              context_length=args.ctx, seed=seed, dtype=args.dtype, device=args.device, max_batch=args.batch,
-              stop_token_ids=args.stop, rep_penalty=args.rep_penalty, rep_window=args.rep_window,
-              detect_loops=args.detect_loops)
+    options = dict(temperature=args.temperature, top_p=args.top_p, max_tokens=args.max_tokens,
+                   context_length=args.ctx, seed=seed, device=args.device, max_batch=args.batch,
+                   stop_token_ids=args.stop, rep_penalty=args.rep_penalty, rep_window=args.rep_window,
+                   detect_loops=args.detect_loops)
+    if raw is not None:
+        from .engine.loading import random_model
+        m = Model.from_model(random_model(raw, args.seed_weights, args.dtype, args.device), **options)
+    else:
+        m = Model(args.model, dtype=args.dtype, **options)
     if args.bench_prefill or args.bench_memory:
         from .engine.bench_tools import bench_memory, bench_prefill
         if args.bench_prefill:
@@ -83,19 +113,25 @@ def main(argv=None) -> int:
         if args.bench_memory:
             bench_memory(m, file=sys.stderr)
         return 0
-    prompts = [parse_ids(p) for p in (args.prompts or ["0"])]
-    prof = None
-    if args.profile:
-        from torch.profiler import ProfilerActivity, profile
-        prof = profile(activities=[ProfilerActivity.CUDA])
-        prof.__enter__()
+    prompts = [parse_ids(p) for p in (args.prompts or [])]
+    if args.tokens_file:
+        try:
+            with open(args.tokens_file, encoding="utf-8") as f:
+                prompts += [parse_ids(line) for line in f if line.strip() and not line.lstrip().startswith("#")]
+        except OSError as e:
+            print(f"quant: cannot read the prompts' file '{args.tokens_file}': {e}", file=sys.stderr)
+            return 2
+    if not prompts:
+        prompts = [parse_ids("0")]
     t0 = time.perf_counter()
-    outs = m.generate_batch(prompts)
+    if args.profile:
+        from .engine.bench_tools import device_peaks, profile_generation
+        hbm, tf = device_peaks()
+        outs = profile_generation(m, prompts, hbm, tf, file=sys.stderr)["outs"]
+    else:
+        outs = m.generate_batch(prompts)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    if prof is not None:
-        prof.__exit__(None, None, None)
-        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12), file=sys.stderr)
     for o in outs:
         print(" ".join(str(t) for t in o))
     n = sum(len(o) for o in outs)

@@ -65,7 +65,8 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
                                       int pairing, const int* __restrict__ positions,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
                                       int table_stride, int page_size, TA* __restrict__ q_out,
-                                      TA* __restrict__ cache, int heads, int nh, int nkv, int hd, int vec8) {
+                                      TA* __restrict__ cache, int heads, int nh, int nkv, int hd, int vec8,
+                                      int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
@@ -77,7 +78,9 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
     const float* sn_row = sin_t ? sin_t + (size_t)pos * half : nullptr;
     size_t page_base = 0;
     if (heads > nh) {
-        const int page = page_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+        const int page = TQ_CHECKED(page_table[(size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride
+                                               + TQ_CHECKED(pos / page_size, table_stride, TQ_IDX_TABLE_COLUMN)],
+                                    n_pages, TQ_IDX_PAGE);
         page_base = (size_t)page * 2 * nkv * page_size * hd + (size_t)(pos % page_size) * hd;
     }
     if (vec8) {
@@ -149,7 +152,7 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
                                 const float* cos_t, const float* sin_t, int pairing,
                                 const int* positions, const int* seq_of_token, const int* page_table,
                                 int table_stride, int page_size, void* q_out, void* cache, int write_kv,
-                                int T_, int nh, int nkv, int hd, cudaStream_t stream) {
+                                int T_, int nh, int nkv, int hd, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(hd % 2 == 0 && hd >= 2 && hd <= 2048, "qkv_rope_cache: head size %d must be even and <= 2048", hd);
     TQ_REQUIRE(pairing == 0 || pairing == 1, "qkv_rope_cache: pairing %d is neither half (0) nor interleaved (1)", pairing);
@@ -170,7 +173,7 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
         (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB>, 
             (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
-            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8))));
+            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8, n_seqs, n_pages))));
     TQ_CHECK_LAUNCH("qkv_rope_cache");
     return 0;
 }
@@ -187,7 +190,8 @@ template <typename TA>
 __global__ void attention_kernel(const TA* __restrict__ q, const TA* __restrict__ cache,
                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                  const int* __restrict__ page_table, int table_stride, int page_size,
-                                 int window, float scale, TA* __restrict__ out, int nh, int nkv, int hd) {
+                                 int window, float scale, TA* __restrict__ out, int nh, int nkv, int hd,
+                                 int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS];
@@ -197,7 +201,7 @@ __global__ void attention_kernel(const TA* __restrict__ q, const TA* __restrict_
     const int g = h / (nh / nkv);
     const int pos = positions[t];
     const int start = window > 0 ? max(0, pos + 1 - window) : 0;
-    const int* table = page_table + (size_t)seq_of_token[t] * table_stride;
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
 
     float qv[ATT_EPL], acc[ATT_EPL];
     const TA* qp = q + ((size_t)t * nh + h) * hd;
@@ -209,7 +213,7 @@ __global__ void attention_kernel(const TA* __restrict__ q, const TA* __restrict_
     }
     float m = -INFINITY, l = 0.f;
     for (int p = start + warp; p <= pos; p += ATT_WARPS) {
-        const int page = table[p / page_size];
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
         const TA* kp = cache + ((((size_t)page * 2 + 0) * nkv + g) * page_size + p % page_size) * hd;
         const TA* vp = kp + (size_t)nkv * page_size * hd;
         float s = 0.f;
@@ -258,7 +262,7 @@ __global__ void attention_kernel(const TA* __restrict__ q, const TA* __restrict_
 
 TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, const int* positions,
                            const int* seq_of_token, const int* page_table, int table_stride, int page_size,
-                           int window, float scale, void* out, int T_, int nh, int nkv, int hd,
+                           int window, float scale, void* out, int T_, int nh, int nkv, int hd, int n_seqs, int n_pages,
                            cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(hd >= 1 && hd <= TQ_MAX_HEAD_DIM, "attention: head size %d exceeds %d", hd, TQ_MAX_HEAD_DIM);
@@ -269,15 +273,15 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
     TQ_DISPATCH(act_dtype, TA,
         (tq_launch(grid, ATT_WARPS * 32, 0, stream)(attention_kernel<TA>, 
             (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size,
-            window, scale, (TA*)out, nh, nkv, hd)));
+            window, scale, (TA*)out, nh, nkv, hd, n_seqs, n_pages)));
     TQ_CHECK_LAUNCH("attention");
     return 0;
 }
 
 // ---------------------------------------------------------------------------------------
 // Split attention for decoding (and any step with few tokens per sequence): the keys of one
-// (token, KV head) are cut into `n_splits` ranges, one CTA per range; a second kernel merges the
-// ranges' partial softmax states.  A key row is read by LPK = hd/8 lanes with one 16-byte load
+// (token, KV head) are cut into `n_splits` ranges, one CTA per range; the CTA that finishes last
+// (found by a ticket counter, without waiting) merges the ranges' partial softmax states in range order.  A key row is read by LPK = hd/8 lanes with one 16-byte load
 // each (two for fp32), so a warp covers 32/LPK keys per instruction and eight keys per iteration
 // with all loads in flight together; the G query heads that share the KV head are computed from
 // the same registers.  Partial state per (token, head, split): max, sum, hd weighted values (fp32).
@@ -291,7 +295,7 @@ TQ_EXPORT int tq_attention(const void* q, const void* cache, int act_dtype, cons
 // ring serves launches of more than two waves of the register form, and the registers the others.
 // ---------------------------------------------------------------------------------------
 #define SPLIT_WARPS 4
-#define SPLIT_REGISTER_RESIDENT 592     // CTAs of the register form a B200 runs at once (148 SMs x 4)
+#define SPLIT_REGISTER_CTAS_PER_SM 4     // CTAs of the register form an SM runs at once
 
 __device__ __forceinline__ void split_copy16(void* smem_dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
@@ -313,7 +317,7 @@ __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
                        int page_size, int window, float scale, float* __restrict__ partial, int n_splits,
-                       int nh, int nkv) {
+                       int* __restrict__ arrived, TA* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     constexpr int HD = LPK * 8;
@@ -329,7 +333,7 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
     const int sub = lane % LPK, part = lane / LPK;       // part: which of the KPI keys of a load
     const int pos = positions[t];
     const int start = window > 0 ? max(0, pos + 1 - window) : 0;
-    const int* table = page_table + (size_t)seq_of_token[t] * table_stride;
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
     // this split's keys: whole groups of GS absolute positions
     const int first8 = start / GS, last8 = pos / GS;                   // inclusive groups
     const int groups = last8 - first8 + 1;
@@ -350,7 +354,7 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
     // the keys and values of a group of GS positions, as this lane reads them
     auto fetch_group = [&](int grp, Raw (&kr)[LOADS], Raw (&vr)[LOADS]) {
         const int p0 = grp * GS;
-        const int page = table[p0 / page_size];
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p0 / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
         const TA* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
         const TA* vbase = kbase + (size_t)nkv * page_size * HD;
 #pragma unroll
@@ -364,7 +368,7 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
     Raw* ring = reinterpret_cast<Raw*>(s_split_ring) + (size_t)warp * (STAGES > 0 ? STAGES : 1) * 2 * LOADS * 32 + lane;
     auto copy_group = [&](int grp, int stage) {
         const int p0 = grp * GS;
-        const int page = table[p0 / page_size];
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p0 / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
         const TA* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
         const TA* vbase = kbase + (size_t)nkv * page_size * HD;
         Raw* dst = ring + (size_t)stage * 2 * LOADS * 32;
@@ -462,40 +466,54 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
             L += s_l[w][h] * f;
             a += s_acc[w][h][d] * f;
         }
+        if (n_splits == 1) {                      // the only range of its row: the result itself
+            out[((size_t)t * nh + (size_t)g * G + h) * HD + d] = tq_from_float<TA>(a / L);
+            continue;
+        }
         float* dst = partial + (((size_t)t * nh + (size_t)g * G + h) * n_splits + split) * (HD + 2);
         dst[2 + d] = a;
         if (d == 0) { dst[0] = M; dst[1] = L; }
     }
-}
-
-template <typename TA>
-__global__ void attention_merge_kernel(const float* __restrict__ partial, int n_splits, int hd, TA* __restrict__ out) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    const size_t th = blockIdx.x;                        // token * nh + head
-    const float* p = partial + th * n_splits * (hd + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[(size_t)s * (hd + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = p[(size_t)s * (hd + 2)];
-        if (ms != -INFINITY) L += p[(size_t)s * (hd + 2) + 1] * expf(ms - M);
+    if (n_splits == 1) return;
+    // The CTA that finishes last among the n_splits of this (token, KV head) merges their partial states, in the
+    // order of the ranges whichever CTA it is.  Nobody waits: each CTA publishes its state, takes a ticket and
+    // leaves unless the ticket is the last one.
+    __shared__ int s_last;
+    __threadfence();                              // this thread's part of the state is visible before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* ticket = arrived + (size_t)t * nkv + g;
+        const int n = atomicAdd(ticket, 1);
+        s_last = n == n_splits - 1;
+        if (s_last) *ticket = 0;                  // every ticket of this launch has been taken: ready for the next launch
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float a = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = p[(size_t)s * (hd + 2)];
-            if (ms != -INFINITY) a += p[(size_t)s * (hd + 2) + 2 + d] * expf(ms - M);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();                              // the others' states, published before their tickets, are visible now
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx % HD;
+        const float* p = partial + ((size_t)t * nh + (size_t)g * G + h) * n_splits * (HD + 2);
+        float M = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(p + (size_t)sp * (HD + 2)));
+        float L = 0.f, a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float ms = __ldcg(p + (size_t)sp * (HD + 2));
+            if (ms != -INFINITY) {
+                const float f = expf(ms - M);
+                L += __ldcg(p + (size_t)sp * (HD + 2) + 1) * f;
+                a += __ldcg(p + (size_t)sp * (HD + 2) + 2 + d) * f;
+            }
         }
-        out[th * hd + d] = tq_from_float<TA>(a / L);
+        out[((size_t)t * nh + (size_t)g * G + h) * HD + d] = tq_from_float<TA>(a / L);
     }
 }
 
-// partial: T * nh * n_splits * (hd + 2) floats of scratch.
+// partial: T * nh * n_splits * (hd + 2) floats of scratch; arrived: T * nkv ints that are zero before the launch and
+// zero again after it (both unused, and may be null, with one range).
 TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype, const int* positions,
                                  const int* seq_of_token, const int* page_table, int table_stride, int page_size,
-                                 int window, float scale, float* partial, int n_splits, void* out, int T_, int nh,
-                                 int nkv, int hd, cudaStream_t stream) {
+                                 int window, float scale, float* partial, int n_splits, int* arrived, void* out, int T_,
+                                 int nh, int nkv, int hd, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256,
                "attention_split: head size %d is not 16, 32, 64, 128 or 256", hd);
@@ -505,11 +523,21 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_REQUIRE(page_size % 16 == 0, "attention_split: page size %d must be a multiple of 16", page_size);
     TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "attention_split: bad grid (%d splits, %d KV heads)", n_splits, nkv);
     TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
+    TQ_REQUIRE(n_splits == 1 || (partial != nullptr && arrived != nullptr),
+               "attention_split: %d ranges need scratch for their partial states and their tickets", n_splits);
     dim3 grid(T_, nkv, n_splits);
     // the ring form for launches of more than two waves of the register form (TQ_SPLIT_RING=1: wherever the
     // shape has one, =0: never)
     const char* ring_env = getenv("TQ_SPLIT_RING");
-    const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0' : (long long)T_ * nkv * n_splits > 2 * SPLIT_REGISTER_RESIDENT;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess
+            || sm_count <= 0)
+            TQ_FAIL(-1, "attention_split: cannot read the device's SM count");
+    }
+    const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0'
+                                               : (long long)T_ * nkv * n_splits > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count;
 #define SPLIT_LAUNCH(TA, LPK, GC, STAGES)                                                                       \
     do {                                                                                                        \
         auto kern = attention_split_kernel<TA, LPK, GC, STAGES>;                                                \
@@ -522,7 +550,7 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
         }                                                                                                       \
         tq_launch(grid, SPLIT_WARPS * 32, ring, stream)(kern,                                                   \
             (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window, \
-            scale, partial, n_splits, nh, nkv);                                                                 \
+            scale, partial, n_splits, arrived, (TA*)out, nh, nkv, n_seqs, n_pages);                             \
     } while (0)
 #define SPLIT_GC(TA, LPK)                                                                                       \
     do { if (G == 1) { if (ring && split_stages<TA, LPK>() > 0) SPLIT_LAUNCH(TA, LPK, 1, (split_stages<TA, LPK>()));   \
@@ -536,9 +564,6 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     else if (act_dtype == TQ_F32) SPLIT_HD(float);
     else TQ_FAIL(-2, "attention_split: unknown element type %d", act_dtype);
     TQ_CHECK_LAUNCH("attention_split");
-    TQ_DISPATCH(act_dtype, TA,
-        (tq_launch(T_ * nh, hd >= 128 ? 128 : 64, 0, stream)(attention_merge_kernel<TA>, partial, n_splits, hd, (TA*)out)));
-    TQ_CHECK_LAUNCH("attention_merge");
     return 0;
 }
 
@@ -550,14 +575,20 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
 #include "attention_no_alloc.h"
 
 static __device__ __align__(256) float tq_static_partial[TQ_ATTENTION_STATIC_SCRATCH_FLOATS];
+// tickets of the (token, KV head) rows: zero when the library is loaded, and every launch leaves them zero
+static __device__ __align__(256) int tq_static_arrived[TQ_ATTENTION_STATIC_ROWS];
 
 #define TQ_MAX_DEVICES 64
-static float* tq_static_partial_addr[TQ_MAX_DEVICES];      // device address of the array, per device
+// device addresses of the two arrays, per device.  Two host threads making a device's first call at the same time
+// both look the addresses up and store the same values: harmless.
+static float* tq_static_partial_addr[TQ_MAX_DEVICES];
+static int* tq_static_arrived_addr[TQ_MAX_DEVICES];
 
 TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int act_dtype, const int* positions,
                                         const int* seq_of_token, const int* page_table, int table_stride,
                                         int page_size, int window, float scale, int n_splits, void* out, int T_,
                                         int nh, int nkv, int hd, cudaStream_t stream) {
+    // the caller's tables are taken as they are: a debug build's index checks get limits that nothing exceeds
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ > 0 && nh > 0 && n_splits > 0 && hd > 0, "attention_split_static: bad sizes T=%d nh=%d splits=%d hd=%d",
                T_, nh, n_splits, hd);
@@ -566,6 +597,9 @@ TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int ac
                "attention_split_static: %llu floats of scratch needed (T=%d, heads=%d, splits=%d, head size=%d) but the "
                "built-in array holds %d; use tq_attention_split with a buffer of your own",
                need, T_, nh, n_splits, hd, TQ_ATTENTION_STATIC_SCRATCH_FLOATS);
+    TQ_REQUIRE(nkv > 0 && (long long)T_ * nkv <= TQ_ATTENTION_STATIC_ROWS,
+               "attention_split_static: %lld (token, KV head) rows exceed the %d the built-in ticket array holds; use "
+               "tq_attention_split with buffers of your own", (long long)T_ * nkv, TQ_ATTENTION_STATIC_ROWS);
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) TQ_FAIL(-1, "attention_split_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
@@ -575,8 +609,14 @@ TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int ac
         e = cudaGetSymbolAddress((void**)&p, tq_static_partial);
         if (e != cudaSuccess || p == nullptr)
             TQ_FAIL(-1, "attention_split_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+        int* a = nullptr;
+        e = cudaGetSymbolAddress((void**)&a, tq_static_arrived);
+        if (e != cudaSuccess || a == nullptr)
+            TQ_FAIL(-1, "attention_split_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+        tq_static_arrived_addr[device] = a;
         tq_static_partial_addr[device] = p;
     }
     return tq_attention_split(q, cache, act_dtype, positions, seq_of_token, page_table, table_stride, page_size, window,
-                              scale, tq_static_partial_addr[device], n_splits, out, T_, nh, nkv, hd, stream);
+                              scale, tq_static_partial_addr[device], n_splits, tq_static_arrived_addr[device], out, T_, nh,
+                              nkv, hd, 0x7fffffff, 0x7fffffff, stream);
 }

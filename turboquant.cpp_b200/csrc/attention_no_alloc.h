@@ -10,25 +10,31 @@
 // running inside such a program, or code on a path where an allocation (and the implicit
 // synchronisation cudaMalloc/cudaFree can cause) is not acceptable.  For them this variant keeps the
 // scratch inside the library: a file-scope `static __device__ __align__(256)` array of
-// TQ_ATTENTION_STATIC_SCRATCH_FLOATS floats (8 MiB).  Every GPU on which the library is loaded holds
-// that array until the process exits, whether or not this entry point is ever called.
+// TQ_ATTENTION_STATIC_SCRATCH_FLOATS floats (8 MiB) for the ranges' partial states, and one of
+// TQ_ATTENTION_STATIC_ROWS ints (64 KiB) for the tickets by which the last range of a row finds that it is
+// the last.  Every GPU on which the library is loaded holds both arrays until the process exits, whether
+// or not this entry point is ever called.
 //
 // Contract.
 //  * Same arguments and same result as tq_attention_split, without `partial`.  Inputs and the output
 //    are still the caller's.
 //  * It calls no cudaMalloc, cudaFree or any allocating library routine.
-//  * It needs T * nh * n_splits * (hd + 2) floats of scratch; if that exceeds
-//    TQ_ATTENTION_STATIC_SCRATCH_FLOATS it returns an error (see tq_last_error) and launches nothing.
-//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
-//    device current) and remembers it per device.  Make that first call before any stream capture.
-//  * All calls on a device share the one array, which keeps whatever the last call left in it.
-//    Nothing in it has to start at zero: every partial state that is read is written first by the
-//    same call.  Two calls that overlap on the GPU (different streams, no ordering between them) race
-//    on the array; order them.
+//  * It needs T * nh * n_splits * (hd + 2) floats of scratch and T * nkv tickets; if that exceeds
+//    TQ_ATTENTION_STATIC_SCRATCH_FLOATS or TQ_ATTENTION_STATIC_ROWS it returns an error (see
+//    tq_last_error) and launches nothing.
+//  * The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with that
+//    device current) and remembers them per device.  Make that first call before any stream capture.
+//  * All calls on a device share the arrays, which keep whatever the last call left in them.  The
+//    partial states need not start at zero: every one that is read is written first by the same call.
+//    The tickets must be zero when a call starts: they are when the library is loaded, and the kernel
+//    itself sets a row's ticket back to zero once the row's last range has taken it, so a call that
+//    ran to its end leaves them zero for the next.  Two calls that overlap on the GPU (different
+//    streams, no ordering between them) race on both arrays; order them.
 #pragma once
 #include <cuda_runtime.h>
 
 #define TQ_ATTENTION_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
+#define TQ_ATTENTION_STATIC_ROWS (16 * 1024)
 
 #ifdef __cplusplus
 extern "C" {

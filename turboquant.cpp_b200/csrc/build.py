@@ -32,6 +32,15 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # extra flags per kernel file (libraries to link, include paths)
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 
+# TQ_DEBUG_INDEX=1 in the environment builds and loads the kernels with their index checks compiled in
+# (common.cuh: TQ_CHECKED); the libraries of the two builds carry different hashes and live side by side.
+DEBUG_INDEX = os.environ.get("TQ_DEBUG_INDEX", "") not in ("", "0")
+
+
+def _flags(name: str, debug_index: Optional[bool] = None) -> List[str]:
+    debug = DEBUG_INDEX if debug_index is None else debug_index
+    return NVCC_FLAGS + (["-DTQ_DEBUG_INDEX"] if debug else []) + EXTRA_FLAGS.get(name, [])
+
 _HEADERS = ["common.cuh"]
 
 
@@ -82,38 +91,40 @@ def build_dir() -> str:
     raise KernelBuildError(f"neither '{local}' nor '{fallback}' can be written; set $TQ_BUILD_DIR")
 
 
-def _source_hash(name: str) -> str:
+def _source_hash(name: str, debug_index: Optional[bool] = None) -> str:
     h = hashlib.sha256()
     for fn in [name + ".cu"] + _HEADERS + [f for f in sorted(os.listdir(_HERE)) if f.endswith(".cuh")
                                            and f not in _HEADERS]:
         with open(os.path.join(_HERE, fn), "rb") as f:
             h.update(fn.encode())
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS.get(name, [])).encode())
+    h.update(" ".join(_flags(name, debug_index)).encode())
     return h.hexdigest()[:16]
 
 
-def library_path(name: str) -> str:
-    return os.path.join(build_dir(), f"tq_{name}_{_source_hash(name)}.so")
+def library_path(name: str, debug_index: Optional[bool] = None) -> str:
+    debug = DEBUG_INDEX if debug_index is None else debug_index
+    return os.path.join(build_dir(), f"tq_{name}{'_checked' if debug else ''}_{_source_hash(name, debug)}.so")
 
 
 def kernel_files() -> List[str]:
     return sorted(f[:-3] for f in os.listdir(_HERE) if f.endswith(".cu"))
 
 
-def compile_kernel(name: str, verbose: bool = True) -> str:
+def compile_kernel(name: str, verbose: bool = True, debug_index: Optional[bool] = None) -> str:
     """Builds one kernel file if its library is not there yet; returns the library's path."""
     src = os.path.join(_HERE, name + ".cu")
     if not os.path.isfile(src):
         raise KernelBuildError(f"no kernel file '{src}'")
-    out = library_path(name)
+    debug = DEBUG_INDEX if debug_index is None else debug_index
+    out = library_path(name, debug)
     if os.path.isfile(out):
         return out
     nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + EXTRA_FLAGS.get(name, []) + ["-I", _HERE, "-o", tmp, src]
+    cmd = [nvcc] + _flags(name, debug) + ["-I", _HERE, "-o", tmp, src]
     if verbose:
-        _say(f"compiling {name}.cu for sm_100a …")
+        _say(f"compiling {name}.cu for sm_100a{' with index checks' if debug else ''} …")
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -131,8 +142,9 @@ def compile_kernel(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         raise KernelBuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
-    for old in os.listdir(os.path.dirname(out)):          # libraries of earlier versions of this file
-        stem = old[len(f"tq_{name}_"):-3] if old.startswith(f"tq_{name}_") and old.endswith(".so") else ""
+    prefix = f"tq_{name}{'_checked' if debug else ''}_"
+    for old in os.listdir(os.path.dirname(out)):          # libraries of earlier versions of this file, same build
+        stem = old[len(prefix):-3] if old.startswith(prefix) and old.endswith(".so") else ""
         if len(stem) == 16 and all(ch in "0123456789abcdef" for ch in stem) and os.path.join(os.path.dirname(out), old) != out:
             try:
                 os.remove(os.path.join(os.path.dirname(out), old))
@@ -143,16 +155,18 @@ def compile_kernel(name: str, verbose: bool = True) -> str:
     return out
 
 
-def ensure_built(names: Iterable[str], verbose: bool = True) -> None:
+def ensure_built(names: Iterable[str], verbose: bool = True, debug_index: Optional[bool] = None) -> None:
     """Builds several kernel files at once (one nvcc process each)."""
-    names = [n for n in dict.fromkeys(names) if n not in _loaded and not os.path.isfile(library_path(n))]
+    own = debug_index is None or debug_index == DEBUG_INDEX
+    names = [n for n in dict.fromkeys(names)
+             if not (own and n in _loaded) and not os.path.isfile(library_path(n, debug_index))]
     if not names:
         return
     errors: List[BaseException] = []
 
     def work(n: str) -> None:
         try:
-            compile_kernel(n, verbose)
+            compile_kernel(n, verbose, debug_index)
         except BaseException as e:  # noqa: BLE001 - reported below
             errors.append(e)
 
@@ -179,6 +193,26 @@ def load_kernel(name: str) -> ctypes.CDLL:
         lib.tq_last_error.restype = ctypes.c_char_p
         _loaded[name] = lib
         return lib
+
+
+INDEX_KINDS = {1: "a token id outside the vocabulary", 2: "a page id outside the cache", 3: "a position beyond the page table",
+               4: "a sequence index outside the batch", 5: "an expert id outside the layer's experts",
+               6: "a row outside the expert-sorted layout"}
+
+
+def index_faults() -> List[str]:
+    """What the index checks of the loaded libraries recorded since the last call (debug builds only; a release
+    build records nothing).  Reading synchronises the device."""
+    found = []
+    for name, lib in list(_loaded.items()):
+        rec = (ctypes.c_int * 4)()
+        rc = lib.tq_index_fault_read(rec)
+        if rc < 0:
+            raise KernelBuildError(f"{name}: {lib.tq_last_error().decode('utf-8', 'replace')}")
+        if rc == 1 and rec[0] != 0:
+            found.append(f"{name}: {INDEX_KINDS.get(rec[0], f'index of kind {rec[0]}')}: {rec[1]} is not in "
+                         f"0..{rec[2] - 1} (seen {rec[3]} time{'' if rec[3] == 1 else 's'} by the kernels' threads in all)")
+    return found
 
 
 def loaded_libraries() -> Dict[str, str]:

@@ -37,8 +37,53 @@ static thread_local char tq_error_message[512] = "";
             TQ_FAIL(-1, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
     } while (0)
 
+// ---------------------------------------------------------------------------------------
+// Index checks of debug builds (-DTQ_DEBUG_INDEX; TQ_DEBUG_INDEX=1 in the environment builds and loads them).
+// Kernels index memory with values they are handed: token ids, page ids from the page tables, expert ids, rows of
+// the expert-sorted layout.  The host validates what it can before a launch; these checks are the net below that.
+// TQ_CHECKED(value, limit, kind) is `value` in a release build.  In a debug build a value outside [0, limit) is
+// recorded (the first one wins: kind, value, limit; every one is counted) and replaced by 0, so the access that
+// follows goes to valid memory: nothing traps, the kernel runs to its end with a wrong result, and the host, which
+// reads the record with tq_index_fault_read() where it reads results anyway, raises.
+// ---------------------------------------------------------------------------------------
+#define TQ_IDX_TOKEN 1          // a token id outside the vocabulary
+#define TQ_IDX_PAGE 2           // a page id outside the cache (a page that was given back reads -1)
+#define TQ_IDX_TABLE_COLUMN 3   // a position beyond the page table's width
+#define TQ_IDX_SEQUENCE 4       // a token's sequence index outside the step's batch
+#define TQ_IDX_EXPERT 5         // an expert id outside the layer's experts
+#define TQ_IDX_ROW 6            // a row of the expert-sorted layout, or a gathered row, outside its tensor
+
+#ifdef TQ_DEBUG_INDEX
+static __device__ int tq_index_fault[4];      // kind (0: none), value, limit, how many
+template <typename I, typename J>
+__device__ __forceinline__ I tq_checked_index(I value, J limit, int kind) {
+    if ((long long)value >= 0 && (long long)value < (long long)limit) return value;
+    if (atomicCAS(&tq_index_fault[0], 0, kind) == 0) {
+        tq_index_fault[1] = (int)value;
+        tq_index_fault[2] = (int)limit;
+    }
+    atomicAdd(&tq_index_fault[3], 1);
+    return (I)0;
+}
+#define TQ_CHECKED(value, limit, kind) tq_checked_index((value), (limit), (kind))
+#define TQ_DEFINE_INDEX_FAULT_READ                                                                        \
+    TQ_EXPORT int tq_index_fault_read(int* out4) {                                                         \
+        int zero[4] = {0, 0, 0, 0};                                                                        \
+        cudaError_t e = cudaMemcpyFromSymbol(out4, tq_index_fault, sizeof(zero));                          \
+        if (e == cudaSuccess && out4[0] != 0) e = cudaMemcpyToSymbol(tq_index_fault, zero, sizeof(zero));  \
+        if (e != cudaSuccess) TQ_FAIL(-1, "index fault record: %s", cudaGetErrorString(e));                \
+        return 1;                                                                                          \
+    }
+#else
+#define TQ_CHECKED(value, limit, kind) (value)
+// a release build keeps no record: 0 tells the caller so
+#define TQ_DEFINE_INDEX_FAULT_READ                                                                        \
+    TQ_EXPORT int tq_index_fault_read(int* out4) { out4[0] = out4[1] = out4[2] = out4[3] = 0; return 0; }
+#endif
+
 #define TQ_DEFINE_LAST_ERROR                                                 \
-    TQ_EXPORT const char* tq_last_error() { return tq_error_message; }
+    TQ_EXPORT const char* tq_last_error() { return tq_error_message; }      \
+    TQ_DEFINE_INDEX_FAULT_READ
 
 __device__ __forceinline__ float tq_to_float(float v) { return v; }
 __device__ __forceinline__ float tq_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

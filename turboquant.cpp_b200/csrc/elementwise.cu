@@ -14,22 +14,22 @@ TQ_DEFINE_LAST_ERROR
 // ---------------------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                                  float* __restrict__ x, int H) {
+                                  float* __restrict__ x, int H, int V) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
-    const TW* row = table + (size_t)tokens[t] * H;
+    const TW* row = table + (size_t)TQ_CHECKED(tokens[t], V, TQ_IDX_TOKEN) * H;
     float* out = x + (size_t)t * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = tq_to_float(row[i]);
 }
 
 TQ_EXPORT int tq_embed_rows(const int* tokens, const void* table, int table_dtype, float* x,
-                            int T, int H, cudaStream_t stream) {
+                            int T, int H, int V, cudaStream_t stream) {
     if (T == 0) return 0;
     TQ_REQUIRE(T > 0 && H > 0, "embed_rows: bad sizes T=%d H=%d", T, H);
     const int threads = H >= 1024 ? 256 : 128;
     TQ_DISPATCH(table_dtype, TW,
-        tq_launch(T, threads, 0, stream)(embed_rows_kernel<TW>, tokens, (const TW*)table, x, H));
+        tq_launch(T, threads, 0, stream)(embed_rows_kernel<TW>, tokens, (const TW*)table, x, H, V));
     TQ_CHECK_LAUNCH("embed_rows");
     return 0;
 }
@@ -287,12 +287,12 @@ TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, 
 // A warp copies a row (16-byte accesses when rows allow it); a block takes several rows.
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ idx, int divisor,
-                                   T* __restrict__ out, int R, int H, int vec) {
+                                   T* __restrict__ out, int R, int H, int vec, int S) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
-        const T* src = in + (size_t)(idx[r] / divisor) * H;
+        const T* src = in + (size_t)TQ_CHECKED(idx[r] / divisor, S, TQ_IDX_ROW) * H;
         T* dst = out + (size_t)r * H;
         if (vec) {          // rows are a multiple of 16 bytes and 16-byte aligned
             const int n16 = (int)((size_t)H * sizeof(T) / 16);
@@ -311,7 +311,8 @@ __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restri
     }
 }
 
-TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* out, int dtype, int R, int H,
+// S: rows of `in` (what the indices are checked against in a debug build).
+TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* out, int dtype, int R, int H, int S,
                              cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0 && divisor > 0, "gather_rows: bad sizes R=%d H=%d divisor=%d", R, H, divisor);
@@ -320,7 +321,7 @@ TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* 
     int blocks = (R + 7) / 8;                     // eight warps, a row each, per block
     if (blocks > 148 * 8) blocks = 148 * 8;
     TQ_DISPATCH(dtype, T,
-        tq_launch(blocks, 256, 0, stream)(gather_rows_kernel<T>, (const T*)in, idx, divisor, (T*)out, R, H, vec));
+        tq_launch(blocks, 256, 0, stream)(gather_rows_kernel<T>, (const T*)in, idx, divisor, (T*)out, R, H, vec, S));
     TQ_CHECK_LAUNCH("gather_rows");
     return 0;
 }

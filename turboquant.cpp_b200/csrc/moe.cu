@@ -289,7 +289,7 @@ __global__ void moe_chunk_hist_kernel(const int* __restrict__ ids, int P, int E,
     for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
     __syncthreads();
     const int p0 = blockIdx.x * chunk, p1 = min(P, p0 + chunk);
-    for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) atomicAdd(&s_hist[ids[p]], 1);
+    for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) atomicAdd(&s_hist[TQ_CHECKED(ids[p], E, TQ_IDX_EXPERT)], 1);
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_hist[(size_t)blockIdx.x * E + e] = s_hist[e];
 }
@@ -358,7 +358,7 @@ __global__ void moe_chunk_place_kernel(const int* __restrict__ ids, int P, int E
     const int p0 = blockIdx.x * chunk, p1 = min(P, p0 + chunk);
     for (int r0 = p0; r0 < p1; r0 += blockDim.x) {
         const int p = r0 + threadIdx.x;
-        const int e = p < p1 ? ids[p] : -1;
+        const int e = p < p1 ? TQ_CHECKED(ids[p], E, TQ_IDX_EXPERT) : -1;
         const unsigned peers = __match_any_sync(0xffffffffu, e);        // lanes of this warp with the same expert
         const int rank = __popc(peers & ((1u << lane) - 1u));
         const bool leader = rank == 0 && e >= 0;
@@ -925,7 +925,7 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
 // ---------------------------------------------------------------------------------------
 __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ wts, const float* __restrict__ Ys,
-                                   const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k) {
+                                   const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k, int R) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
@@ -936,7 +936,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
 #pragma unroll 4
             for (int j = 0; j < k; ++j) {                   // unrolled: the chosen experts' rows load side by side
                 const float wj = wts[(size_t)t * k + j];
-                const float4 a = *reinterpret_cast<const float4*>(Y + (size_t)row_of_pair[(size_t)t * k + j] * H + i);
+                const float4 a = *reinterpret_cast<const float4*>(Y + (size_t)TQ_CHECKED(row_of_pair[(size_t)t * k + j], R, TQ_IDX_ROW) * H + i);
                 v.x += wj * a.x; v.y += wj * a.y; v.z += wj * a.z; v.w += wj * a.w;
             }
             if (Ys) {
@@ -950,21 +950,22 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
         float v = 0.f;
         for (int j = 0; j < k; ++j)
-            v += wts[(size_t)t * k + j] * Y[(size_t)row_of_pair[(size_t)t * k + j] * H + i];
+            v += wts[(size_t)t * k + j] * Y[(size_t)TQ_CHECKED(row_of_pair[(size_t)t * k + j], R, TQ_IDX_ROW) * H + i];
         if (Ys) v += (shared_scale ? shared_scale[t] : 1.0f) * Ys[(size_t)t * H + i];
         y[(size_t)t * H + i] = v;
     }
 }
 
+// R: rows of Y (what row_of_pair is checked against in a debug build).
 TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float* wts, const float* Ys,
-                             const float* shared_scale, float* y, int T_, int H, int k, cudaStream_t stream) {
+                             const float* shared_scale, float* y, int T_, int H, int k, int R, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(H > 0 && k >= 0, "moe_combine: bad sizes H=%d k=%d", H, k);
     // few tokens: narrow blocks, several per row, so that the step still fills the GPU
     const int threads = T_ >= 512 ? 256 : 64;
     int cols = T_ >= 512 ? 1 : (H + threads * 4 - 1) / (threads * 4);
     if (cols > 64) cols = 64;
-    tq_launch(dim3(T_, cols), threads, 0, stream)(moe_combine_kernel, Y, row_of_pair, wts, Ys, shared_scale, y, H, k);
+    tq_launch(dim3(T_, cols), threads, 0, stream)(moe_combine_kernel, Y, row_of_pair, wts, Ys, shared_scale, y, H, k, R);
     TQ_CHECK_LAUNCH("moe_combine");
     return 0;
 }

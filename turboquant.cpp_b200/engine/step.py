@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheFull, PagedCache, Sequence_
-from ..csrc.build import ensure_built
+from ..csrc.build import ensure_built, index_faults
 from ..kernels._call import KernelError
 from ..kernels.gemm_tc import GAVE_UP, check_status
 from ..parts.base import StepContext
@@ -100,6 +100,12 @@ class Engine:
         # a part that cannot run inside a captured step (it says so itself) keeps the whole model out of graphs
         self.graphs = DecodeGraphs(self) if use_graphs and model.capturable() else None
         self._stateless = all(n is None for n in model.state_needs())
+        # TQ_DEBUG_LAYERS=1 (or =all): every step prints the residual stream's sum and sum of magnitudes after each
+        # layer, for positions 0 and 1 (or all), in the manner of the reference's TQ_DEBUG_PREFILL
+        # (src/engine/tq_transformer.c:2827-2831); such steps run outside the CUDA graphs
+        self.layer_dump = os.environ.get("TQ_DEBUG_LAYERS", "")
+        if self.layer_dump in ("0", ""):
+            self.layer_dump = ""
         self._ahead = None                       # (sequences, tokens each) of a step launched ahead, if any
 
     # ---- what the generation loop asks -----------------------------------------------------------
@@ -127,6 +133,9 @@ class Engine:
         """Raises if a tensor-core kernel gave up on one of its bounded waits since the last check
         (it synchronises the device; call it where results are brought to the host anyway)."""
         check_status(word=self.status)
+        faults = index_faults()                 # kernels built with their index checks (TQ_DEBUG_INDEX=1) report here
+        if faults:
+            raise KernelError("a kernel was handed an index outside its tensor: " + "; ".join(faults))
 
     def release(self) -> None:
         """Gives back what the engine holds on the device besides the cache: its CUDA graphs."""
@@ -206,6 +215,8 @@ class Engine:
         n_new = [len(e.tokens) for e in entries]
         self.cache.reserve(seqs, n_new)          # raises CacheFull before anything is written
         decode = all(n == 1 and len(e.want) == 1 for n, e in zip(n_new, entries))
+        if self.layer_dump:
+            return self._step_with_layer_dump(entries, seqs, n_new)
         with torch.cuda.device(self.device):
             if decode and self.graphs is not None and (self.debug is None or self.record_routing):
                 self._check_tokens(np.asarray([e.tokens[0] for e in entries], dtype=np.int64))
@@ -219,12 +230,31 @@ class Engine:
         self.steps_run += 1
         return logits
 
+    def _step_with_layer_dump(self, entries, seqs, n_new):
+        import sys
+        saved, self.debug = self.debug, dict(self.debug or {}, layer_sums=[])
+        try:
+            with torch.cuda.device(self.device):
+                ctx, dev_tables = self.build_context(entries)
+                logits = self.model.forward(ctx, self.cache.layer_caches(dev_tables))
+            positions = ctx.positions.tolist()
+            for layer, sums, mags in self.debug["layer_sums"]:
+                sums, mags = sums.tolist(), mags.tolist()
+                for t, pos in enumerate(positions):
+                    if self.layer_dump == "all" or pos <= 1:
+                        print(f"[fwd]   L{layer} pos={pos} final x sum={sums[t]:.9f} sumabs={mags[t]:.9f}", file=sys.stderr)
+        finally:
+            self.debug = saved
+        self.cache.commit(seqs, n_new)
+        self.steps_run += 1
+        return logits
+
     # ---- a decode step launched before its input tokens have reached the host --------------------------
     @property
     def can_step_ahead(self) -> bool:
         """Decode steps can be launched from tokens that are still on the device (CUDA graphs, no per-sequence
         state that a dropped step would have changed)."""
-        return self.graphs is not None and self.debug is None and self._stateless
+        return self.graphs is not None and self.debug is None and self._stateless and not self.layer_dump
 
     def step_ahead(self, seqs: Sequence[Sequence_], tokens_dev: torch.Tensor) -> torch.Tensor:
         """Launches the decode step whose tokens are `tokens_dev` (int32, one per sequence, on the device: the

@@ -37,7 +37,7 @@ def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optiona
         ptr(cos), ptr(sin), c_int(PAIRING[pairing]), ptr(positions), ptr(seq_of_token), ptr(page_table),
         c_int(page_table.shape[1]), c_int(page_size), ptr(q_out), ptr(cache_layer),
         c_int(0 if cache_layer is None else 1), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-        stream()))
+        c_int(page_table.shape[0]), c_int(0 if cache_layer is None else cache_layer.shape[0]), stream()))
 
 
 def attention(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
@@ -52,7 +52,8 @@ def attention(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tenso
     check(_LIB, lib.tq_attention(ptr(q), ptr(cache_layer), c_int(code(q.dtype)), ptr(positions),
                                  ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]), c_int(page_size),
                                  c_int(window), c_float(scale), ptr(out), c_int(T), c_int(n_heads),
-                                 c_int(n_kv_heads), c_int(head_dim), stream()))
+                                 c_int(n_kv_heads), c_int(head_dim), c_int(page_table.shape[0]),
+                                 c_int(cache_layer.shape[0]), stream()))
     return out
 
 
@@ -64,42 +65,76 @@ def split_usable(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -
 
 
 RESIDENT_CTAS = 592      # CTAs of the split kernel a B200 runs at once (148 SMs x 4, register-limited)
+_resident = {}
 
 
-def splits_for(n_tokens: int, n_kv_heads: int) -> int:
+def resident_ctas(device=None) -> int:
+    """CTAs of the split kernel the device runs at once: four per SM (the register form's limit), from the
+    device's own SM count."""
+    if not torch.cuda.is_available():
+        return RESIDENT_CTAS
+    idx = torch.device(device).index if device is not None and torch.device(device).index is not None \
+        else torch.cuda.current_device()
+    if idx not in _resident:
+        _resident[idx] = 4 * torch.cuda.get_device_properties(idx).multi_processor_count
+    return _resident[idx]
+
+
+def splits_for(n_tokens: int, n_kv_heads: int, resident: int = RESIDENT_CTAS) -> int:
     """Ranges the keys of one (token, KV head) are cut into.  All CTAs do equal work, so what matters is
     how full the last wave is: with few rows the CTAs should fit one wave; with many, the count that
     leaves the smallest tail.  (Measured on B200 at context 2,048: 8 tokens x 16 heads, 4 ranges 40 us,
     5 ranges 50 us; 64 x 16, 4 ranges 191 us against 197 us for 1 or 2.)"""
     rows = max(1, n_tokens * n_kv_heads)
-    if rows <= RESIDENT_CTAS:
-        return max(1, min(16, RESIDENT_CTAS // rows))
-    if rows >= 4 * RESIDENT_CTAS:          # many waves anyway: the tail is small, more ranges only add merging
+    if rows <= resident:
+        return max(1, min(16, resident // rows))
+    if rows >= 4 * resident:               # many waves anyway: the tail is small, more ranges only add merging
         return 1
 
     def fill(s: int) -> float:
         ctas = rows * s
-        return ctas / (-(-ctas // RESIDENT_CTAS) * RESIDENT_CTAS)
+        return ctas / (-(-ctas // resident) * resident)
     return max(range(1, 9), key=lambda s: (round(fill(s), 3), -s))
+
+
+TICKET_ROWS = 1 << 16
+_tickets = {}
+
+
+def tickets(device: torch.device) -> torch.Tensor:
+    """TICKET_ROWS int32 per device, zero between launches: with them the split kernel's CTAs find out which of a
+    row's ranges finishes last (that one merges).  Launches that use them must not overlap on the device."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _tickets:
+        _tickets[idx] = torch.zeros(TICKET_ROWS, dtype=torch.int32, device=device)
+    return _tickets[idx]
 
 
 def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                     page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
-                    n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, partial: torch.Tensor) -> torch.Tensor:
-    """Attention with the keys of each (token, KV head) cut into n_splits ranges and merged; `partial`
-    holds T * n_heads * n_splits * (head_dim + 2) floats of scratch."""
+                    n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int,
+                    partial: Optional[torch.Tensor]) -> torch.Tensor:
+    """Attention with the keys of each (token, KV head) cut into n_splits ranges and merged, in one launch;
+    `partial` holds T * n_heads * n_splits * (head_dim + 2) floats of scratch (not needed with one range)."""
     T = q.shape[0]
     want_int32(positions, "positions")
     want_int32(page_table, "page table")
-    want_f32(partial, "partial states")
-    if partial.numel() < T * n_heads * n_splits * (head_dim + 2):
-        raise KernelError("attention_split: the scratch for partial states is too small")
+    arrived = None
+    if n_splits > 1:
+        want_f32(partial, "partial states")
+        if partial.numel() < T * n_heads * n_splits * (head_dim + 2):
+            raise KernelError("attention_split: the scratch for partial states is too small")
+        if T * n_kv_heads > TICKET_ROWS:
+            raise KernelError(f"attention_split: {T * n_kv_heads} (token, KV head) rows with several ranges exceed "
+                              f"the {TICKET_ROWS} tickets; use one range")
+        arrived = tickets(q.device)
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_attention_split(ptr(q), ptr(cache_layer), c_int(code(q.dtype)), ptr(positions),
                                        ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]),
-                                       c_int(page_size), c_int(window), c_float(scale), ptr(partial), c_int(n_splits),
+                                       c_int(page_size), c_int(window), c_float(scale),
+                                       ptr(partial) if n_splits > 1 else None, c_int(n_splits), ptr(arrived),
                                        ptr(out), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-                                       stream()), kernels=2)
+                                       c_int(page_table.shape[0]), c_int(cache_layer.shape[0]), stream()))
     return out
 
 

@@ -19,7 +19,7 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> 
     T, H = out.shape
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_embed_rows(ptr(tokens), ptr(table), c_int(code(table.dtype)), ptr(out),
-                                  c_int(T), c_int(H), stream()))
+                                  c_int(T), c_int(H), c_int(table.shape[0]), stream()))
     return out
 
 
@@ -73,5 +73,5 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, out: torch
     R, H = out.shape
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_gather_rows(ptr(src), ptr(index), c_int(divisor), ptr(out), c_int(code(out.dtype)),
-                                   c_int(R), c_int(H), stream()))
+                                   c_int(R), c_int(H), c_int(src.shape[0]), stream()))
     return out

@@ -160,5 +160,5 @@ def moe_combine(y_rows: torch.Tensor, row_of_pair: torch.Tensor, weights: torch.
     T, H = out.shape
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_moe_combine(ptr(y_rows), ptr(row_of_pair), ptr(weights), ptr(y_shared), ptr(shared_scale),
-                                   ptr(out), c_int(T), c_int(H), c_int(top_k), stream()))
+                                   ptr(out), c_int(T), c_int(H), c_int(top_k), c_int(y_rows.shape[0]), stream()))
     return out

@@ -66,6 +66,10 @@ class LMHead(Part):
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         return linear(xn, self.weight, out_dtype=torch.float32)
 
+    def step_work(self, n_tokens, kv_tokens):
+        w = self.weight
+        return {"matmul": (0 if w is None else w.numel() * w.element_size(), 2.0 * n_tokens * self.vocab * self.hidden)}
+
 
 class DecoderModel:
     def __init__(self, config, dtype: torch.dtype, embedding: Embedding, blocks: Sequence[Block],
@@ -128,14 +132,32 @@ class DecoderModel:
         """Whether decode steps can be recorded into CUDA graphs: every block says so of its own parts."""
         return all(b.capturable() for b in self.blocks)
 
+    def step_work(self, n_tokens: int, kv_tokens: int, n_want: int = None):
+        """{bucket: (bytes, flops)} of one step, summed over the schedule's entries and the head."""
+        total = {}
+        runs = [self.blocks[e.block] for e in self.schedule]
+        for part in runs:
+            for sub in (part.parts() if hasattr(part, "parts") else [part]):
+                for bucket, (b, f) in sub.step_work(n_tokens, kv_tokens).items():
+                    tb, tf = total.get(bucket, (0.0, 0.0))
+                    total[bucket] = (tb + b, tf + f)
+        for bucket, (b, f) in self.head.step_work(n_tokens if n_want is None else n_want, kv_tokens).items():
+            tb, tf = total.get(bucket, (0.0, 0.0))
+            total[bucket] = (tb + b, tf + f)
+        return total
+
     # ---- one step ------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, layer_caches: Sequence[LayerCache]) -> Optional[torch.Tensor]:
         """Runs the step's tokens through the schedule; float32 logits [n_want, vocab] (None if
         nothing is wanted)."""
         x = self.embedding.forward(ctx.tokens)
         pending = None
-        for e, cache in zip(self.schedule, layer_caches):
+        dump = ctx.debug.get("layer_sums") if ctx.debug is not None else None
+        for i, (e, cache) in enumerate(zip(self.schedule, layer_caches)):
             x, pending = self.blocks[e.block].forward(x, pending, ctx, cache)
+            if dump is not None:             # sum and sum of magnitudes of the residual stream after this layer
+                full = x if pending is None else x + pending.float()
+                dump.append((i, full.sum(dim=1, dtype=torch.float64), full.abs().sum(dim=1, dtype=torch.float64)))
         if ctx.n_want == 0:
             return None
         xn = self.final_norm.forward(x, ctx.act_dtype, rows=ctx.want_rows, add=pending)

@@ -69,6 +69,14 @@ class AttentionMixer(Mixer):
     def cache_need(self) -> KVNeed:
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
+    def step_work(self, n_tokens, kv_tokens):
+        wb = lambda w: 0 if w is None else w.numel() * w.element_size()
+        proj = self.hidden * (self.q_size + 2 * self.kv_size) + self.q_size * self.hidden
+        kv_el = 2 if getattr(self, "run_dtype", None) == torch.bfloat16 else 4
+        seen = min(kv_tokens, n_tokens * self.window) if self.window else kv_tokens
+        return {"matmul": (wb(self.w_qkv) + wb(self.w_o), 2.0 * n_tokens * proj),
+                "attn": (2.0 * self.kv_size * kv_el * seen, 4.0 * self.q_size * seen)}
+
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         T = xn.shape[0]
         act = ctx.act_dtype
@@ -95,8 +103,9 @@ class AttentionMixer(Mixer):
                                  self.window, self.scale, o, ctx.n_seqs, ctx.max_q_len, self.n_heads, self.n_kv_heads,
                                  self.head_dim, status=ctx.status)
         elif KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
-            n_splits = KA.splits_for(T, self.n_kv_heads)
-            partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32, device=xn.device)
+            n_splits = KA.splits_for(T, self.n_kv_heads, KA.resident_ctas(xn.device))
+            partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32,
+                                  device=xn.device) if n_splits > 1 else None
             KA.attention_split(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
                                self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim, n_splits, partial)
         else:

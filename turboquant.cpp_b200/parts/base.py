@@ -103,6 +103,13 @@ class Part:
         """Kernel files (csrc/<name>.cu) this part launches; they are built before the first step."""
         return []
 
+    def step_work(self, n_tokens: int, kv_tokens: int) -> Dict[str, Tuple[float, float]]:
+        """What a step of n_tokens tokens over sequences that hold kv_tokens tokens together has to do in this
+        part, for the command line's profile: {bucket: (bytes it must read, floating-point operations)} with the
+        reference's bucket names 'matmul', 'moe', 'attn' (src/engine/tq_transformer.c:65-72); anything else is
+        'other'.  Parts that say nothing are counted as nothing."""
+        return {}
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,

@@ -34,6 +34,10 @@ class SwiGLUFeedForward(FeedForward):
     def kernels(self) -> List[str]:
         return ["elementwise"]
 
+    def step_work(self, n_tokens, kv_tokens):
+        wb = lambda w: 0 if w is None else w.numel() * w.element_size()
+        return {"matmul": (wb(self.w_gate_up) + wb(self.w_down), 6.0 * n_tokens * self.hidden * self.intermediate)}
+
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         gu = linear(xn, self.w_gate_up, out_dtype=torch.float32)     # gate and up stay fp32 until the product
         h = torch.empty((xn.shape[0], self.intermediate), dtype=ctx.act_dtype, device=xn.device)

@@ -101,6 +101,13 @@ class MoEFeedForward(FeedForward):
             names.append("gemm_tc")       # float32 runs never launch the tensor-core kernel
         return names
 
+    def step_work(self, n_tokens, kv_tokens):
+        E, k, H, I, S = self.n_experts, self.top_k, self.hidden, self.intermediate, self.shared_intermediate
+        el = 4 if getattr(self, "run_dtype", None) == torch.float32 else 2
+        touched = E * (1.0 - ((E - k) / E) ** n_tokens)          # distinct experts under uniform routing
+        byt = el * (touched * 3 * H * I + 3 * H * S + (E + 1) * H)
+        return {"moe": (byt, 2.0 * n_tokens * (k * 3 * H * I + 3 * H * S + (E + 1) * H))}
+
     _side_streams = {}
 
     @classmethod
