@@ -1,7 +1,7 @@
 #!/bin/bash
 # Usage: make_golden.sh PATH_TO_THE_REFERENCE_CHECKOUT
-# Builds the reference's CPU sources (a read-only checkout) and runs ref_driver.c and ref_sampler.c against
-# them; writes logits.bin and samples.bin next to this script.  No network, no GPU.
+# Builds the reference's CPU sources (a read-only checkout) and runs ref_driver.c, ref_driver2.c and ref_sampler.c
+# against them; writes logits.bin, logits2.bin, route.bin and samples.bin next to this script.  No network, no GPU.
 # The one flag the reference needs on x86-64 gcc is -D__fp16=_Float16 (src/engine/tq_transformer.c:3456).
 set -e
 R=${1:?path of the reference checkout}
@@ -12,9 +12,9 @@ for f in $R/src/core/*.c $R/src/cache/*.c $R/src/backend/cpu/*.c $R/src/engine/*
 done
 ar rcs "$W/libtq.a" "$W"/*.o
 gcc -O2 -std=c11 -I$R/include "$HERE/ref_driver.c" "$W/libtq.a" -lm -lpthread -o "$W/ref_driver"
+gcc -O2 -std=c11 -I$R/include "$HERE/ref_driver2.c" "$W/libtq.a" -lm -lpthread -o "$W/ref_driver2"
 gcc -O2 -std=c11 -I$R/include "$HERE/ref_sampler.c" "$W/libtq.a" -lm -lpthread -o "$W/ref_sampler"
-(cd "$W" && ./ref_driver && ./ref_sampler)
-cp "$W/logits.bin" "$HERE/logits.bin"
-cp "$W/samples.bin" "$HERE/samples.bin"
+(cd "$W" && ./ref_driver && ./ref_driver2 && ./ref_sampler)
+for f in logits.bin logits2.bin route.bin samples.bin; do cp "$W/$f" "$HERE/$f"; done
 rm -rf "$W"
-echo "wrote $HERE/logits.bin and $HERE/samples.bin"
+echo "wrote logits.bin, logits2.bin, route.bin and samples.bin in $HERE"

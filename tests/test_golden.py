@@ -100,6 +100,91 @@ def test_plain_model_reproduces_the_reference_build():
     assert 1e-4 < err < 3e-2                                  # the fast exp's own error, nothing else
     other = P.forward(m, toks, pairing="half")
     assert np.abs(other - ref).max() / scale > 3e-2           # the pairing matters and is not the reference's
+    # the half-split pairing (x[i], x[i+hd/2]) is the reference's rotation on the same pairs stored in another
+    # order: with the rows of every head of the query and key projections (and biases) reordered from
+    # (0, 1, 2, 3, …) to (0, 2, 4, …, 1, 3, 5, …), pair i sits at (i, i + hd/2), each head's dot products are
+    # unchanged, and the half-split model must give the reference's logits
+    hd = m.hd
+    order = np.concatenate([np.arange(0, hd, 2), np.arange(1, hd, 2)])
+    halved = types.SimpleNamespace(**m.__dict__)
+    halved.w = dict(m.w)
+    for name, a in m.w.items():
+        if ".self_attn.q_proj." in name or ".self_attn.k_proj." in name:
+            heads = a.shape[0] // hd
+            halved.w[name] = a.reshape((heads, hd) + a.shape[1:])[:, order].reshape(a.shape)
+    P.MOE_EXP = reference_fast_exp
+    try:
+        half = P.forward(halved, toks, pairing="half")
+    finally:
+        P.MOE_EXP = np.exp
+    assert np.abs(half - ref).max() / scale < 5e-6
+
+
+def build_model_with_a_dense_layer_and_a_tied_head():
+    """The model of tests/golden/ref_driver2.c: layer 0 with experts, layer 1 dense, the head is the embedding."""
+    L, D, NH, NKV, HD, E, K, I, S, ID, V = 2, 64, 4, 2, 16, 8, 2, 32, 64, 80, 256
+    g = XorShift()
+    w = {"model.embed_tokens.weight": g.fill(V, D), "model.norm.weight": g.ones(D)}
+    for l in range(L):
+        p = f"model.layers.{l}."
+        w[p + "input_layernorm.weight"] = g.ones(D)
+        w[p + "post_attention_layernorm.weight"] = g.ones(D)
+        w[p + "self_attn.q_proj.weight"] = g.fill(NH * HD, D)
+        w[p + "self_attn.k_proj.weight"] = g.fill(NKV * HD, D)
+        w[p + "self_attn.v_proj.weight"] = g.fill(NKV * HD, D)
+        w[p + "self_attn.o_proj.weight"] = g.fill(D, NH * HD)
+        w[p + "self_attn.q_proj.bias"] = g.fill(NH * HD)
+        w[p + "self_attn.k_proj.bias"] = g.fill(NKV * HD)
+        w[p + "self_attn.v_proj.bias"] = g.fill(NKV * HD)
+        if l == 1:
+            w[p + "mlp.gate_proj.weight"] = g.fill(ID, D)
+            w[p + "mlp.up_proj.weight"] = g.fill(ID, D)
+            w[p + "mlp.down_proj.weight"] = g.fill(D, ID)
+            continue
+        w[p + "mlp.gate.weight"] = g.fill(E, D)
+        for e in range(E):
+            q = f"{p}mlp.experts.{e}."
+            w[q + "gate_proj.weight"] = g.fill(I, D)
+            w[q + "up_proj.weight"] = g.fill(I, D)
+            w[q + "down_proj.weight"] = g.fill(D, I)
+        w[p + "mlp.shared_expert.gate_proj.weight"] = g.fill(S, D)
+        w[p + "mlp.shared_expert.up_proj.weight"] = g.fill(S, D)
+        w[p + "mlp.shared_expert.down_proj.weight"] = g.fill(D, S)
+        w[p + "mlp.shared_expert_gate.weight"] = g.fill(1, D)
+    m = types.SimpleNamespace(
+        w=w, L=L, H=D, nh=NH, nkv=NKV, hd=HD, eps=1e-6, theta=10000.0, E=E, k=K, norm_topk=True, tied=True,
+        cfg={"shared_expert_intermediate_size": S}, layer_is_sparse=lambda l: l == 0, layer_window=lambda l: 0)
+    return m, g
+
+
+def test_dense_layer_tied_head_and_router_against_the_reference_build():
+    """tests/golden/ref_driver2.c: a dense SwiGLU layer (exact exp there, src/engine/tq_ops.c:1454-1478) behind a
+    layer with experts, logits through the embedding table, and tq_moe_route alone."""
+    ref = np.fromfile(os.path.join(HERE, "golden", "logits2.bin"), dtype="<f4").reshape(7, 256).astype(np.float64)
+    m, g = build_model_with_a_dense_layer_and_a_tied_head()
+    toks = [3, 17, 200, 42, 9, 77, 255]
+    scale = np.abs(ref).max()
+    P.MOE_EXP = reference_fast_exp
+    try:
+        same = P.forward(m, toks, pairing="interleaved")
+    finally:
+        P.MOE_EXP = np.exp
+    assert np.abs(same - ref).max() / scale < 5e-6
+    untied = types.SimpleNamespace(**{**m.__dict__, "tied": False})
+    untied.w = dict(m.w, **{"lm_head.weight": m.w["model.embed_tokens.weight"][::-1].copy()})
+    assert np.abs(P.forward(untied, toks, pairing="interleaved") - ref).max() / scale > 1e-2     # the head matters
+    # the router alone: the reference's ids and weights of the 3 largest of 8 logits are this library's formula with
+    # renormalisation (softmax over all, the 3 most probable, divided by their sum)
+    raw = np.fromfile(os.path.join(HERE, "golden", "route.bin"), dtype="<i4")
+    ids_ref = raw[:18].reshape(6, 3)
+    wts_ref = raw[18:].view("<f4").reshape(6, 3).astype(np.float64)
+    wr, hid = g.fill(8, 64), g.fill(6, 64)
+    ids, wts, margin = P.router(hid, wr, 3, True)
+    assert margin.min() > 1e-4                                   # no near-tie decides this comparison
+    assert np.array_equal(ids, ids_ref)
+    assert np.abs(wts - wts_ref).max() < 2e-6
+    loose, _, _ = P.router(hid, wr, 3, False)[1], None, None     # without renormalisation the weights are smaller
+    assert np.all(loose.sum(axis=1) < 1.0) and np.allclose(loose / loose.sum(axis=1, keepdims=True), wts_ref, atol=2e-6)
 
 
 def reference_uniforms(state, n):
