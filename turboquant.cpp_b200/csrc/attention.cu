@@ -620,3 +620,204 @@ TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int ac
                               scale, tq_static_partial_addr[device], n_splits, tq_static_arrived_addr[device], out, T_, nh,
                               nkv, hd, 0x7fffffff, 0x7fffffff, stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// Tiled attention for runs of new tokens where the tensor-core prompt kernel does not apply (float32, or head
+// sizes other than 64 and 128): a CTA takes 32 consecutive new tokens of one sequence and one query head, walks
+// the keys they see in tiles of 64 through shared memory, and keeps an online softmax per row.  Keys and values
+// are read once per 32 queries instead of once per query.  All arithmetic is IEEE fp32 on CUDA cores (fmaf,
+// expf); nothing is rounded below fp32 on the way except what the cache's own element type stores.
+//   warp w owns rows 8w..8w+7 of the query tile; for the scores a lane owns keys `lane` and `lane + 32` of the key tile, for the
+//   weighted sum of values it owns head elements lane, lane+32, ...
+// Row t of q belongs to the sequence i with cu_seqlens[i] <= t < cu_seqlens[i+1] and sits at position
+// seq_start[i] + (t - cu_seqlens[i]); the step's keys and values are already in the cache.
+// ---------------------------------------------------------------------------------------
+#define TILED_BQ 32
+#define TILED_BK 64                               // two keys per lane
+#define TILED_WARPS 4
+#define TILED_ROWS (TILED_BQ / TILED_WARPS)       // query rows per warp
+#define TILED_MAX_EPL (TQ_MAX_HEAD_DIM / 32)      // head elements per lane, at most
+
+__device__ __forceinline__ float4 tiled_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 tiled_load4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// EPL: head elements per lane that the instantiation provides for (head size <= 32 * EPL)
+template <typename TA, int EPL>
+__global__ void __launch_bounds__(TILED_WARPS * 32)
+attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ seq_start, const int* __restrict__ page_table, int table_stride,
+                       int page_size, int window, float scale, TA* __restrict__ out, int n_seqs, int nh, int nkv,
+                       int hd, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ __align__(16) float s_tiled[];
+    const int ks = hd + 4;                                   // row stride of the key and query tiles (16-byte rows, no bank conflicts)
+    float* s_q = s_tiled;                                    // [BQ][ks], scaled
+    float* s_k = s_q + TILED_BQ * ks;                        // [BK][ks]
+    float* s_v = s_k + TILED_BK * ks;                        // [BK][hd]
+    float* s_p = s_v + TILED_BK * hd;                        // [WARPS][BK][ROWS]
+    __shared__ int s_seq, s_row0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {                                  // which sequence's which 32 rows this CTA takes
+        // later rows of a sequence see more keys: they are handed out first, so that the launch does not end
+        // with its longest tiles
+        int tile = blockIdx.x, seq = -1, row0 = 0;
+        for (int i = 0; i < n_seqs; ++i) {
+            const int n = cu_seqlens[i + 1] - cu_seqlens[i], tiles = (n + TILED_BQ - 1) / TILED_BQ;
+            if (tile < tiles) { seq = i; row0 = (tiles - 1 - tile) * TILED_BQ; break; }
+            tile -= tiles;
+        }
+        s_seq = seq; s_row0 = row0;
+    }
+    __syncthreads();
+    const int seq = s_seq;
+    if (seq < 0) return;                                     // the grid is an upper bound of the number of tiles
+    const int h = blockIdx.y, g = h / (nh / nkv);
+    const int t_first = cu_seqlens[seq] + s_row0;
+    const int rows = min(TILED_BQ, cu_seqlens[seq + 1] - t_first);
+    const int pos0 = seq_start[seq] + s_row0;                // position of the tile's first row
+    const int* table = page_table + (size_t)seq * table_stride;
+    for (int idx = threadIdx.x; idx < TILED_BQ * hd; idx += blockDim.x) {
+        const int r = idx / hd, d = idx - r * hd;
+        s_q[r * ks + d] = r < rows ? tq_to_float(q[((size_t)(t_first + r) * nh + h) * hd + d]) * scale : 0.f;
+    }
+    float m[TILED_ROWS], l[TILED_ROWS], acc[TILED_ROWS][EPL];
+#pragma unroll
+    for (int r = 0; r < TILED_ROWS; ++r) {
+        m[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+        for (int c = 0; c < EPL; ++c) acc[r][c] = 0.f;
+    }
+    // keys any row of the tile sees: from the first row's window start to the last row's own position
+    const int k_lo = window > 0 ? max(0, pos0 + 1 - window) : 0, k_hi = pos0 + rows - 1;
+    float* my_p = s_p + warp * TILED_BK * TILED_ROWS;
+    const float* my_q = s_q + warp * TILED_ROWS * ks;
+    for (int k0 = (k_lo / TILED_BK) * TILED_BK; k0 <= k_hi; k0 += TILED_BK) {
+        __syncthreads();                                     // the previous tile has been used (and s_q is complete)
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < TILED_BK * (hd / 4); idx += blockDim.x) {
+            const int j = idx / (hd / 4), d = (idx - j * (hd / 4)) * 4;
+            const int p = k0 + j;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (p <= k_hi && p >= k_lo) {
+                const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+                const TA* kp = cache + ((((size_t)page * 2 + 0) * nkv + g) * page_size + p % page_size) * hd + d;
+                kv = tiled_load4(kp);                        // hd is a multiple of 4: rows of 4 elements are aligned
+                vv = tiled_load4(kp + (size_t)nkv * page_size * hd);
+            }
+            *reinterpret_cast<float4*>(s_k + j * ks + d) = kv;
+            *reinterpret_cast<float4*>(s_v + j * hd + d) = vv;
+        }
+        __syncthreads();
+        // scores of this warp's rows against keys `lane` and `lane + 32` of the tile
+        float s0[TILED_ROWS], s1[TILED_ROWS];
+#pragma unroll
+        for (int r = 0; r < TILED_ROWS; ++r) { s0[r] = 0.f; s1[r] = 0.f; }
+        const float* krow0 = s_k + lane * ks;
+        const float* krow1 = krow0 + 32 * ks;
+#pragma unroll 2
+        for (int d = 0; d < hd; d += 4) {
+            const float4 ka = *reinterpret_cast<const float4*>(krow0 + d);
+            const float4 kb = *reinterpret_cast<const float4*>(krow1 + d);
+#pragma unroll
+            for (int r = 0; r < TILED_ROWS; ++r) {
+                const float4 qq = *reinterpret_cast<const float4*>(my_q + r * ks + d);
+                s0[r] = fmaf(qq.x, ka.x, s0[r]); s1[r] = fmaf(qq.x, kb.x, s1[r]);
+                s0[r] = fmaf(qq.y, ka.y, s0[r]); s1[r] = fmaf(qq.y, kb.y, s1[r]);
+                s0[r] = fmaf(qq.z, ka.z, s0[r]); s1[r] = fmaf(qq.z, kb.z, s1[r]);
+                s0[r] = fmaf(qq.w, ka.w, s0[r]); s1[r] = fmaf(qq.w, kb.w, s1[r]);
+            }
+        }
+        const int pa = k0 + lane, pb = pa + 32;
+#pragma unroll
+        for (int r = 0; r < TILED_ROWS; ++r) {
+            const int row = warp * TILED_ROWS + r, pos = pos0 + row;
+            const int start = window > 0 ? max(0, pos + 1 - window) : 0;
+            const float sa = row < rows && pa >= start && pa <= pos ? s0[r] : -INFINITY;
+            const float sb = row < rows && pb >= start && pb <= pos ? s1[r] : -INFINITY;
+            const float mx = fmaxf(m[r], tq_warp_max(fmaxf(sa, sb)));
+            float ea = 0.f, eb = 0.f, corr = 1.f;
+            if (mx != -INFINITY) {                           // something of this row is visible by now
+                corr = expf(m[r] - mx);                      // exp(-inf) = 0 the first time
+                ea = expf(sa - mx);                          // exp(-inf) = 0 for what the row does not see
+                eb = expf(sb - mx);
+                l[r] = l[r] * corr + tq_warp_sum(ea + eb);
+                m[r] = mx;
+            }
+#pragma unroll
+            for (int c = 0; c < EPL; ++c) acc[r][c] *= corr;
+            my_p[lane * TILED_ROWS + r] = ea;
+            my_p[(lane + 32) * TILED_ROWS + r] = eb;
+        }
+        __syncwarp();
+        // weighted sum of the tile's values: this lane's head elements, this warp's rows
+#pragma unroll 2
+        for (int j = 0; j < TILED_BK; ++j) {
+            float pj[TILED_ROWS];
+#pragma unroll
+            for (int r = 0; r < TILED_ROWS; r += 4) {
+                const float4 t4 = *reinterpret_cast<const float4*>(my_p + j * TILED_ROWS + r);
+                pj[r] = t4.x; pj[r + 1] = t4.y; pj[r + 2] = t4.z; pj[r + 3] = t4.w;
+            }
+#pragma unroll
+            for (int c = 0; c < EPL; ++c) {
+                const int d = lane + 32 * c;
+                if (d < hd) {
+                    const float vv = s_v[j * hd + d];
+#pragma unroll
+                    for (int r = 0; r < TILED_ROWS; ++r) acc[r][c] = fmaf(pj[r], vv, acc[r][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int r = 0; r < TILED_ROWS; ++r) {
+        const int row = warp * TILED_ROWS + r;
+        if (row >= rows) continue;
+        TA* op = out + ((size_t)(t_first + row) * nh + h) * hd;
+        const float inv = 1.0f / l[r];
+#pragma unroll
+        for (int c = 0; c < EPL; ++c) {
+            const int d = lane + 32 * c;
+            if (d < hd) op[d] = tq_from_float<TA>(acc[r][c] * inv);
+        }
+    }
+}
+
+// T_: rows of q; n_tiles_bound: an upper bound of the number of 32-row tiles (T_ / 32 + n_seqs serves).
+TQ_EXPORT int tq_attention_tiled(const void* q, const void* cache, int act_dtype, const int* cu_seqlens,
+                                 const int* seq_start, const int* page_table, int table_stride, int page_size,
+                                 int window, float scale, void* out, int T_, int n_seqs, int nh, int nkv, int hd,
+                                 int n_pages, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(hd % 4 == 0 && hd >= 4 && hd <= TQ_MAX_HEAD_DIM, "attention_tiled: head size %d must be a multiple of 4, at most %d", hd, TQ_MAX_HEAD_DIM);
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "attention_tiled: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    TQ_REQUIRE(nh <= 65535 && n_seqs >= 1, "attention_tiled: bad grid (%d heads, %d sequences)", nh, n_seqs);
+    TQ_REQUIRE(window >= 0, "attention_tiled: negative window %d", window);
+    const size_t smem = ((size_t)(TILED_BQ + TILED_BK) * (hd + 4) + (size_t)TILED_BK * hd + TILED_WARPS * TILED_BK * TILED_ROWS) * sizeof(float);
+    dim3 grid(T_ / TILED_BQ + n_seqs, nh);
+#define TILED_LAUNCH(TA, EPL)                                                                                   \
+    do {                                                                                                        \
+        auto kern = attention_tiled_kernel<TA, EPL>;                                                            \
+        static size_t configured = 0;                                                                           \
+        if (smem > 48 * 1024 && smem > configured) {                                                            \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) TQ_FAIL(-1, "attention_tiled: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e)); \
+            configured = smem;                                                                                  \
+        }                                                                                                       \
+        tq_launch(grid, TILED_WARPS * 32, smem, stream)(kern, (const TA*)q, (const TA*)cache, cu_seqlens, seq_start, \
+            page_table, table_stride, page_size, window, scale, (TA*)out, n_seqs, nh, nkv, hd, n_pages);        \
+    } while (0)
+#define TILED_EPL(TA) do { if (hd <= 64) TILED_LAUNCH(TA, 2); else if (hd <= 128) TILED_LAUNCH(TA, 4); else TILED_LAUNCH(TA, TILED_MAX_EPL); } while (0)
+    if (act_dtype == TQ_BF16) TILED_EPL(__nv_bfloat16);
+    else if (act_dtype == TQ_F32) TILED_EPL(float);
+    else TQ_FAIL(-2, "attention_tiled: unknown element type %d", act_dtype);
+    TQ_CHECK_LAUNCH("attention_tiled");
+    return 0;
+}

@@ -138,6 +138,26 @@ def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch
     return out
 
 
+def attention_tiled(q: torch.Tensor, cache_layer: torch.Tensor, cu_seqlens: torch.Tensor, seq_start: torch.Tensor,
+                    page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
+                    n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Causal attention of whole runs of new tokens in exact fp32 arithmetic on CUDA cores: 32 queries share every
+    tile of keys and values through shared memory.  For float32 runs and for head sizes the tensor-core prompt
+    kernel does not take.  Rows as in attention_prefill."""
+    T = q.shape[0]
+    want_int32(cu_seqlens, "cu_seqlens")
+    want_int32(seq_start, "seq_start")
+    want_int32(page_table, "page table")
+    if head_dim % 4:
+        raise KernelError(f"attention_tiled: head size {head_dim} must be a multiple of 4")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_attention_tiled(ptr(q), ptr(cache_layer), c_int(code(q.dtype)), ptr(cu_seqlens), ptr(seq_start),
+                                       ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(window),
+                                       c_float(scale), ptr(out), c_int(T), c_int(n_seqs), c_int(n_heads),
+                                       c_int(n_kv_heads), c_int(head_dim), c_int(cache_layer.shape[0]), stream()))
+    return out
+
+
 def prefill_usable(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
     """The tensor-core prompt kernel takes bfloat16, head sizes 64 and 128 and pages of 64 tokens."""
     return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64

@@ -102,6 +102,11 @@ class AttentionMixer(Mixer):
             KA.attention_prefill(q, cache.kv, ctx.cu_seqlens, ctx.seq_start, cache.page_table, cache.page_size,
                                  self.window, self.scale, o, ctx.n_seqs, ctx.max_q_len, self.n_heads, self.n_kv_heads,
                                  self.head_dim, status=ctx.status)
+        elif ctx.max_q_len >= self.PREFILL_MIN_RUN and self.head_dim % 4 == 0:
+            # long runs where the tensor-core kernel does not apply (float32, other head sizes): exact fp32 on CUDA
+            # cores, 32 queries sharing each tile of keys
+            KA.attention_tiled(q, cache.kv, ctx.cu_seqlens, ctx.seq_start, cache.page_table, cache.page_size,
+                               self.window, self.scale, o, ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim)
         elif KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
             n_splits = KA.splits_for(T, self.n_kv_heads, KA.resident_ctas(xn.device))
             partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32,
