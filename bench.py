@@ -312,7 +312,8 @@ def kernel_table(tq, model, rng, V, batch, path):
     from torch.profiler import ProfilerActivity, profile
     eng = tq.Engine(model, max_tokens=batch * CONTEXT, max_slots=batch)
     seqs = [eng.open() for _ in range(batch)]
-    eng.step([tq.StepEntry(s, rng.integers(0, V, size=PROMPT).tolist(), []) for s in seqs])
+    for g0 in range(0, batch, 8):
+        eng.step([tq.StepEntry(s, rng.integers(0, V, size=PROMPT).tolist(), []) for s in seqs[g0:g0 + 8]])
     step = lambda: eng.step([tq.StepEntry(s, [1], [0]) for s in seqs])
     step()
     torch.cuda.synchronize()

@@ -68,6 +68,11 @@ def test_one_group(R, N, K, swiglu, pair):
     out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
     KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), out, None, bn, pair)
     KT.check_status()
+    # with a share of the GPU only (fewer persistent CTAs walk the same tiles): the same bits
+    part = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
+    KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w, torch.bfloat16), swiglu), part, None, bn, pair, sm_share=3)
+    KT.check_status()
+    assert torch.equal(part, out)
     want = P.silu(a @ w[0, :N].T) * (a @ w[0, N:].T) if swiglu else a @ w[0].T
     assert rel(out, want) < 2e-5
 
@@ -111,3 +116,37 @@ def test_packing_layout():
     pp = KT.pack_weights(w, False)                                      # plain: 260 rows -> 3 tiles of 128
     assert pp.data.shape == (2 * 3, 2, 128, 64)
     assert torch.equal(pp.data.view(2, 3, 2, 128, 64)[1, 2, 1, 3, :8], w[1, 259, 64:72])
+
+
+@pytest.mark.parametrize("R,N,K,bn,pair", [(1, 2048, 5632, 16, False), (8, 300, 1408, 16, False), (64, 3584, 2048, 128, True),
+                                           (40, 256, 4096, 64, False)])
+def test_k_shared_out_over_the_gpu(R, N, K, bn, pair):
+    """A product with few tiles and a long K, its K cut into shares that write partial sums to slices of their own:
+    the slices add up to the product, every share holds at least one k-block, and the result does not depend on
+    the launch (fixed shares, no atomics)."""
+    from turboquant_cpp_b200.kernels import gemm_tc as KT
+    rng = np.random.default_rng(R + N + K)
+    a = P.round_bf16(rng.normal(size=(R, K)))
+    w = P.round_bf16(rng.normal(size=(1, N, K)) / math.sqrt(K))
+    pw = KT.pack_weights(dev(w, torch.bfloat16), False)
+    want = a @ w[0].T
+    for ks in sorted({2, 3, KT.k_splits_for(R, N, K, bn), (K + 63) // 64}):
+        if ks < 2:
+            continue
+        per = -(-((K + 63) // 64) // ks)
+        if (ks - 1) * per >= (K + 63) // 64:
+            with pytest.raises(KT.KernelError, match="empty"):
+                KT.gemm_tc(dev(a, torch.bfloat16), pw, torch.empty((ks, R, N), dtype=torch.float32, device=DEV), None, bn, pair, k_splits=ks)
+            continue
+        out = torch.full((ks, R, N), float("nan"), dtype=torch.float32, device=DEV)
+        KT.gemm_tc(dev(a, torch.bfloat16), pw, out, None, bn, pair, k_splits=ks)
+        KT.check_status()
+        assert rel(out.sum(dim=0), want) < 2e-5
+        again = torch.empty_like(out)
+        KT.gemm_tc(dev(a, torch.bfloat16), pw, again, None, bn, pair, k_splits=ks)
+        assert torch.equal(out, again)
+    assert KT.k_splits_for(8, 2048, 5632, 16) > 4 and KT.k_splits_for(2048, 2048, 5632, 256) == 1
+    assert KT.k_splits_for(8, 2048, 512, 16) == 1                       # a short K is not cut
+    with pytest.raises(KT.KernelError):                                  # the SwiGLU epilogue needs the whole sum
+        KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w[:, :N // 2 * 2], torch.bfloat16), True),
+                   torch.empty((2, R, N // 2), dtype=torch.float32, device=DEV), None, bn, pair, k_splits=2)

@@ -142,7 +142,7 @@ def test_attention(nh, nkv, hd, window, dtype, tol):
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 16), (6, 2, 32), (8, 1, 64), (16, 16, 128), (14, 2, 128), (3, 1, 256),
-                                       (5, 5, 64)])
+                                       (5, 5, 64), (12, 1, 64), (28, 4, 128), (17, 1, 32)])
 @pytest.mark.parametrize("window", [0, 7, 70])
 @pytest.mark.parametrize("n_splits", [1, 3, 16])
 @pytest.mark.parametrize("dtype,tol", DTYPES)
@@ -584,6 +584,12 @@ def test_moe_combine():
     close(out, want, 2e-6)
     KM.moe_combine(dev(Y), dev(inv, torch.int32), dev(w), None, None, out, k)
     close(out, np.einsum("tk,tkh->th", w, Y[inv].reshape(T, k, H)), 2e-6)
+    # the shared expert's output as partial sums (slices [T, H]) that are added up first; both row widths
+    for H2 in (70, 72):
+        Y2, parts = rng.normal(size=(T * k, H2)), rng.normal(size=(5, T, H2))
+        out2 = torch.empty((T, H2), dtype=torch.float32, device=DEV)
+        KM.moe_combine(dev(Y2), dev(inv, torch.int32), dev(w), dev(parts), dev(s), out2, k)
+        close(out2, np.einsum("tk,tkh->th", w, Y2[inv].reshape(T, k, H2)) + s[:, None] * parts.sum(axis=0), 2e-6)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -62,6 +62,6 @@ def test_attention_head_sizes():
         with pytest.raises(KA.KernelError):
             KA.check_head_dim(hd)
     assert KA.split_usable(16, 16, 128, 64) and KA.split_usable(28, 4, 128, 64)
-    assert not KA.split_usable(16, 1, 128, 64)         # 16 query heads per KV head: the exact kernel takes it
+    assert KA.split_usable(16, 1, 128, 64)             # 16 query heads per KV head: shared out over two CTAs
     assert not KA.split_usable(4, 4, 48, 64)           # head size 48: the exact kernel takes it
     assert KA.prefill_usable(__import__("torch").bfloat16, 128, 64) and not KA.prefill_usable(__import__("torch").float32, 128, 64)

@@ -19,7 +19,7 @@
 //  * Same arguments and same result as tq_attention_split, without `partial`.  Inputs and the output
 //    are still the caller's.
 //  * It calls no cudaMalloc, cudaFree or any allocating library routine.
-//  * It needs T * nh * n_splits * (hd + 2) floats of scratch and T * nkv tickets; if that exceeds
+//  * It needs T * nh * n_splits * (hd + 2) floats of scratch and at most T * nh tickets; if that exceeds
 //    TQ_ATTENTION_STATIC_SCRATCH_FLOATS or TQ_ATTENTION_STATIC_ROWS it returns an error (see
 //    tq_last_error) and launches nothing.
 //  * The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with that

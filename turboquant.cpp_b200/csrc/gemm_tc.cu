@@ -270,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
-               int stream_weights, int* __restrict__ status) {
+               int stream_weights, int* __restrict__ status, int k_splits) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     using T = Tile<BN, PAIR>;
     constexpr int COLS = SWIGLU ? BM / 2 : BM;         // output columns of a weight-row tile
@@ -285,9 +285,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int n_m1 = (N + COLS - 1) / COLS;                              // weight-row tiles
     const int n_mx = PAIR ? (n_m1 + 1) / 2 : n_m1;                       // ... as units of work
     const int total = n_ty * n_mx;
-    if (worker >= total) return;                                         // both CTAs of a pair leave together
+    // k_splits > 1: a tile's k-blocks are shared out over that many units of work, each writing its partial sums to
+    // a slice of its own of `out` ([k_splits][R][N]; the caller adds the slices up in order).  For products with few
+    // tiles and a long K (a down projection of a few tokens), which would otherwise keep a few SMs busy for long.
+    const int units = total * k_splits;
+    if (worker >= units) return;                                         // both CTAs of a pair leave together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
+    const int kb_per = (num_kb + k_splits - 1) / k_splits;              // the host made sure every share holds a block
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
     constexpr int SA = T::A_SLOTS, SB = T::B_SLOTS;
@@ -340,10 +345,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int slot = 0, issued = 0;
             uint32_t phase = 0;      // parity of the slot's current use
             bool ok = true;
-            for (int id = worker; id < total && ok; id += workers) {
+            for (int u = worker; u < units && ok; u += workers) {
+                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     // the slot is free once the products of the block SA before this one are done
                     if (!mbar_wait(done_bar(slot), phase ^ 1u, &s_abort)) { ok = false; break; }
                     if (PAIR) {
@@ -373,7 +379,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int freed = 0;           // done[] index of the block SB before this one ...
             uint32_t freed_phase = 0;   // ... and the parity of that block's use of it
             bool ok = true;
-            for (int id = worker; id < total && ok; id += workers) {
+            for (int u = worker; u < units && ok; u += workers) {
+                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 const int n_mma = (t.count + 15) & ~15;                                   // N of the products
                 const int rows = PAIR ? n_mma / 2 : t.count;                              // token rows this CTA loads ...
@@ -381,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int boxes = rows / T::BOX_ROWS;
                 const int tails = (rows - boxes * T::BOX_ROWS + T::TAIL_ROWS - 1) / T::TAIL_ROWS;
                 const uint32_t bytes = (uint32_t)(boxes * T::BOX_BYTES + tails * T::TAIL_BYTES);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (issued >= SB) {
                         if (!mbar_wait(done_bar(freed), freed_phase, &s_abort)) { ok = false; break; }
                         if (++freed == SA) { freed = 0; freed_phase ^= 1u; }
@@ -415,7 +422,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int sa = 0, sb = 0, it = 0;      // weight slot (and barrier) and token slot of the next block
             uint32_t phase = 0;
             bool ok = true;
-            for (int id = worker; id < total && ok; id += workers, ++it) {
+            for (int u = worker; u < units && ok; u += workers, ++it) {
+                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 // N of the products: this tile's rows; pairs: M = 256, 128 weight rows from each CTA
                 const uint32_t idesc = umma_idesc((t.count + 15) & ~15) + (PAIR ? ((uint32_t)(BM >> 4) << 24) : 0u);
@@ -425,13 +433,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (it >= 2) ok = mbar_wait(acc_empty(b), (uint32_t)((it >> 1) - 1) & 1u, &s_abort);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     ok = mbar_wait(full_bar(sa), phase, &s_abort);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
                         const uint64_t ad = umma_desc(a_tile(sa) + k * UMMA_K * 2), bd = umma_desc(b_tile(sb) + k * UMMA_K * 2);
                         if (PAIR) umma_pair(acc, ad, bd, idesc, accum); else umma(acc, ad, bd, idesc, accum);
                     }
@@ -456,10 +464,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int r = SWIGLU ? quarter * 16 + (lane & 15) : quarter * 32 + lane;     // output column within the tile
         int it = 0;
         bool ok = true;
-        for (int id = worker; id < total && ok; id += workers, ++it) {
+        for (int u = worker; u < units && ok; u += workers, ++it) {
+                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
             const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
             const int b = it & 1;
             const int n = (PAIR ? 2 * t.mx + (int)rank : t.mx) * COLS + r;           // output column
+            TO* out_u = out + (size_t)(u / total) * R * N;                           // this share's slice (kb0, kb1 unused here)
+            (void)kb0; (void)kb1;
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -482,12 +493,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const float gate = __uint_as_float(high ? got : g[j]);
                         const float up = __uint_as_float(high ? g[8 + j] : got);
                         const int c = c0 + j + (high ? 8 : 0);
-                        if (n < N && c < t.count) out[(size_t)(t.row0 + c) * N + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
+                        if (n < N && c < t.count) out_u[(size_t)(t.row0 + c) * N + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
                     }
                 } else if (n < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c0 + j < t.count) out[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(__uint_as_float(g[j]));
+                        if (c0 + j < t.count) out_u[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(__uint_as_float(g[j]));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -561,7 +572,8 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
 
 template <int BN, bool SWIGLU, typename TO, bool PAIR>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
-           const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, cudaStream_t stream) {
+           const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, int sm_share_pct,
+           int k_splits, cudaStream_t stream) {
     using T = Tile<BN, PAIR>;
     auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR>;
     static bool configured = false;
@@ -590,11 +602,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     }
     constexpr int COLS = SWIGLU ? BM / 2 : BM;
     const long long n_m1 = (N + COLS - 1) / COLS;
-    const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y;      // units of work
+    const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y * k_splits;      // units of work
     const long long want = PAIR ? 2 * tiles : tiles;
-    const int grid = (int)(want < resident ? want : resident);
+    // sm_share_pct in 1..99: this launch takes only that share of the CTAs the GPU runs at once, so that another
+    // launch on another stream runs beside it instead of behind it (a compute-bound product beside a memory-bound one)
+    long long room = resident;
+    if (sm_share_pct > 0 && sm_share_pct < 100) {
+        room = (long long)resident * sm_share_pct / 100;
+        if (PAIR) room &= ~1LL;
+        if (room < (PAIR ? 2 : 1)) room = PAIR ? 2 : 1;
+    }
+    const int grid = (int)(want < room ? want : room);
     tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K,
-        /* stream_weights: on average at most one token tile per group */ (te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0, status);
+        /* stream_weights: on average at most one token tile per group */ (te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0, status,
+        k_splits);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -608,11 +629,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
 // tile_* describe token tiles of at most `bn` rows that never span two groups (null: one group, tiles
 // of bn consecutive rows).  pair: token tiles of 128 or 256 rows run on pairs of CTAs (cta_group::2: each
 // CTA holds 128 weight rows and half of the token rows).  status: one int in device memory, set to 1 if
-// a bounded wait ran out.
+// a bounded wait ran out.  sm_share_pct: 0 or 100 = the launch may fill the GPU; 1..99 = it takes that share of the
+// CTAs the GPU runs at once.  k_splits > 1 (plain products, fp32 out): out is [k_splits][R][N], slice s holding the
+// partial sums over the s-th share of K; the caller adds them up.
 TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
                          const int* tile_row0, const int* tile_count, const int* n_tiles, int max_tiles, int bn,
-                         int R, int N, int K, int G, int swiglu, int pair, int* status, cudaStream_t stream) {
+                         int R, int N, int K, int G, int swiglu, int pair, int* status, int sm_share_pct,
+                         int k_splits, cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
+    TQ_REQUIRE(k_splits >= 1, "gemm_tc: %d shares of K", k_splits);
+    if (k_splits > 1) {
+        TQ_REQUIRE(!swiglu && out_dtype == TQ_F32, "gemm_tc: K is shared out only for plain products with float32 partial sums");
+        const int num_kb = (K + BK - 1) / BK, per = (num_kb + k_splits - 1) / k_splits;
+        TQ_REQUIRE((k_splits - 1) * per < num_kb, "gemm_tc: %d shares of %d k-blocks would leave a share empty", k_splits, num_kb);
+    }
     TQ_REQUIRE(R > 0 && N > 0 && K > 0 && G > 0, "gemm_tc: bad sizes R=%d N=%d K=%d G=%d", R, N, K, G);
     TQ_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     TQ_REQUIRE(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
@@ -629,7 +659,7 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     if (rc) return rc;
     rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u);
     if (rc) return rc;
-#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, stream
+#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, sm_share_pct, k_splits, stream
 #define TC_CASE(BN_, PAIR_)                                                                          \
     if (bn == BN_ && (pair != 0) == PAIR_) {                                                         \
         if (swiglu) {                                                                                \

@@ -921,11 +921,13 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
 }
 
 // ---------------------------------------------------------------------------------------
-// y[t] = sum_j wts[t,j] * Y[row_of_pair[t*k+j]] + shared_scale[t] * Ys[t]   (fp32)
+// y[t] = sum_j wts[t,j] * Y[row_of_pair[t*k+j]] + shared_scale[t] * sum_s Ys[s][t]   (fp32; Ys holds `parts`
+// slices [T][H]: the shared expert's output, or its partial sums over shares of K, added in slice order)
 // ---------------------------------------------------------------------------------------
 __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ wts, const float* __restrict__ Ys,
-                                   const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k, int R) {
+                                   const float* __restrict__ shared_scale, float* __restrict__ y, int H, int k, int R,
+                                   int parts) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
@@ -940,7 +942,11 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
                 v.x += wj * a.x; v.y += wj * a.y; v.z += wj * a.z; v.w += wj * a.w;
             }
             if (Ys) {
-                const float4 a = *reinterpret_cast<const float4*>(Ys + (size_t)t * H + i);
+                float4 a = *reinterpret_cast<const float4*>(Ys + (size_t)t * H + i);
+                for (int sp = 1; sp < parts; ++sp) {
+                    const float4 b = *reinterpret_cast<const float4*>(Ys + ((size_t)sp * gridDim.x + t) * H + i);
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
                 v.x += sc * a.x; v.y += sc * a.y; v.z += sc * a.z; v.w += sc * a.w;
             }
             *reinterpret_cast<float4*>(y + (size_t)t * H + i) = v;
@@ -951,21 +957,26 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
         float v = 0.f;
         for (int j = 0; j < k; ++j)
             v += wts[(size_t)t * k + j] * Y[(size_t)TQ_CHECKED(row_of_pair[(size_t)t * k + j], R, TQ_IDX_ROW) * H + i];
-        if (Ys) v += (shared_scale ? shared_scale[t] : 1.0f) * Ys[(size_t)t * H + i];
+        if (Ys) {
+            float a = Ys[(size_t)t * H + i];
+            for (int sp = 1; sp < parts; ++sp) a += Ys[((size_t)sp * gridDim.x + t) * H + i];
+            v += (shared_scale ? shared_scale[t] : 1.0f) * a;
+        }
         y[(size_t)t * H + i] = v;
     }
 }
 
-// R: rows of Y (what row_of_pair is checked against in a debug build).
+// R: rows of Y (what row_of_pair is checked against in a debug build).  parts: slices of Ys, [parts][T][H].
 TQ_EXPORT int tq_moe_combine(const float* Y, const int* row_of_pair, const float* wts, const float* Ys,
-                             const float* shared_scale, float* y, int T_, int H, int k, int R, cudaStream_t stream) {
+                             const float* shared_scale, float* y, int T_, int H, int k, int R, int parts,
+                             cudaStream_t stream) {
     if (T_ == 0) return 0;
-    TQ_REQUIRE(H > 0 && k >= 0, "moe_combine: bad sizes H=%d k=%d", H, k);
+    TQ_REQUIRE(H > 0 && k >= 0 && parts >= 1, "moe_combine: bad sizes H=%d k=%d parts=%d", H, k, parts);
     // few tokens: narrow blocks, several per row, so that the step still fills the GPU
     const int threads = T_ >= 512 ? 256 : 64;
     int cols = T_ >= 512 ? 1 : (H + threads * 4 - 1) / (threads * 4);
     if (cols > 64) cols = 64;
-    tq_launch(dim3(T_, cols), threads, 0, stream)(moe_combine_kernel, Y, row_of_pair, wts, Ys, shared_scale, y, H, k, R);
+    tq_launch(dim3(T_, cols), threads, 0, stream)(moe_combine_kernel, Y, row_of_pair, wts, Ys, shared_scale, y, H, k, R, parts);
     TQ_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -61,7 +61,13 @@ SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
 
 
 def split_usable(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
-    return head_dim in SPLIT_HEAD_DIMS and n_heads // n_kv_heads <= 8 and page_size % 16 == 0
+    """Any number of query heads per KV head: a CTA keeps up to eight in registers, more are shared out."""
+    return head_dim in SPLIT_HEAD_DIMS and page_size % 16 == 0
+
+
+def head_chunks(n_heads: int, n_kv_heads: int) -> int:
+    """CTAs that share the query heads of one KV head (a CTA keeps up to 8 of them in registers)."""
+    return -(-(n_heads // n_kv_heads) // 8)
 
 
 RESIDENT_CTAS = 592      # CTAs of the split kernel a B200 runs at once (148 SMs x 4, register-limited)
@@ -124,8 +130,8 @@ def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch
         want_f32(partial, "partial states")
         if partial.numel() < T * n_heads * n_splits * (head_dim + 2):
             raise KernelError("attention_split: the scratch for partial states is too small")
-        if T * n_kv_heads > TICKET_ROWS:
-            raise KernelError(f"attention_split: {T * n_kv_heads} (token, KV head) rows with several ranges exceed "
+        if T * n_heads > TICKET_ROWS:
+            raise KernelError(f"attention_split: {T * n_heads} (token, head) rows with several ranges exceed "
                               f"the {TICKET_ROWS} tickets; use one range")
         arrived = tickets(q.device)
     lib = load_kernel(_LIB)

@@ -105,22 +105,46 @@ def token_tile_for(rows: int, groups: int) -> int:
     return TOKEN_TILES[-1]
 
 
+def k_splits_for(rows: int, n: int, k: int, token_tile: int, resident: int = 296) -> int:
+    """Into how many shares the K of a plain one-group product is cut: a product of few tokens whose output is
+    narrow has few tiles (rows of 128 output columns), so without this a handful of SMs would stream all its
+    weights; with it about `resident` units of work do.  1 where the tiles fill the GPU anyway, where K is short,
+    or where the partial sums (rows x n floats per share) would weigh against the weights they save time on."""
+    tiles = -(-n // BLOCK_ROWS) * -(-rows // max(1, token_tile))
+    num_kb = -(-k // BLOCK_K)
+    if tiles * 2 > resident or num_kb < 16:
+        return 1
+    want = min(resident // tiles, num_kb // 8, 32)
+    while want > 1 and want * rows * n * 4 * 2 > n * k * 2 // 2:        # partial sums written and read vs. weight bytes
+        want -= 1
+    if want <= 1:
+        return 1
+    per = -(-num_kb // want)
+    return -(-num_kb // per)
+
+
 PAIR_MIN_TILE = 128      # token tiles from this width on run on pairs of CTAs (cta_group::2)
 _NO_PAIRS = os.environ.get("TQ_NO_PAIRS", "") not in ("", "0")
 
 
 def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
-            token_tile: int, pair: Optional[bool] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+            token_tile: int, pair: Optional[bool] = None, status: Optional[torch.Tensor] = None,
+            sm_share: int = 0, k_splits: int = 1) -> torch.Tensor:
     """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
     silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group).
     pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1).  status: the int32 the
-    kernel sets if a bounded wait runs out (default: the device's word)."""
+    kernel sets if a bounded wait runs out (default: the device's word).  sm_share: 1..99 = the launch takes only
+    that percentage of the CTAs the GPU runs at once and leaves the rest to a launch on another stream.
+    k_splits > 1: out is [k_splits, R, N] float32; slice s holds the partial sums over the s-th share of K (see
+    k_splits_for) and the caller adds the slices up in order."""
     if pair is None:
         pair = token_tile >= PAIR_MIN_TILE and not _NO_PAIRS
     if not usable(x, w):
         raise KernelError("gemm_tc: needs bfloat16 activations with K a multiple of 8 and weights packed for this K")
     R, K = x.shape
-    N = out.shape[1]
+    N = out.shape[-1]
+    if k_splits > 1 and (out.dim() != 3 or out.shape[0] != k_splits or out.shape[1] != R or out.dtype != torch.float32 or w.swiglu):
+        raise KernelError("gemm_tc: with K shared out, out must be [k_splits, R, N] float32 and the product plain")
     if N != w.n:
         raise KernelError(f"gemm_tc: weights give {w.n} columns, out has {N}")
     if layout is not None and layout.tile_rows != token_tile:
@@ -134,5 +158,5 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None, ptr(lo.tile_count) if lo else None,
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
         c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
-        ptr(status if status is not None else status_word(x.device)), stream()))
+        ptr(status if status is not None else status_word(x.device)), c_int(int(sm_share)), c_int(int(k_splits)), stream()))
     return out

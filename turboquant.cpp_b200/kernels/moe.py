@@ -152,13 +152,18 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Op
 def moe_combine(y_rows: torch.Tensor, row_of_pair: torch.Tensor, weights: torch.Tensor,
                 y_shared: Optional[torch.Tensor], shared_scale: Optional[torch.Tensor],
                 out: torch.Tensor, top_k: int) -> torch.Tensor:
-    """out[t] = sum_j weights[t, j] * y_rows[row_of_pair[t*k + j]] + shared_scale[t] * y_shared[t]."""
+    """out[t] = sum_j weights[t, j] * y_rows[row_of_pair[t*k + j]] + shared_scale[t] * y_shared[t]; y_shared may be
+    [parts, T, H]: partial sums that are added up in order first."""
     want_f32(y_rows, "expert outputs")
     want_f32(out, "combined output")
+    T, H = out.shape
+    parts = 1
     if y_shared is not None:
         want_f32(y_shared, "shared expert output")
-    T, H = out.shape
+        parts = y_shared.shape[0] if y_shared.dim() == 3 else 1
+        if y_shared.numel() != parts * T * H:
+            raise ValueError(f"moe_combine: shared expert output of shape {tuple(y_shared.shape)} for {T} x {H}")
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_moe_combine(ptr(y_rows), ptr(row_of_pair), ptr(weights), ptr(y_shared), ptr(shared_scale),
-                                   ptr(out), c_int(T), c_int(H), c_int(top_k), c_int(y_rows.shape[0]), stream()))
+                                   ptr(out), c_int(T), c_int(H), c_int(top_k), c_int(y_rows.shape[0]), c_int(parts), stream()))
     return out

@@ -12,6 +12,7 @@ order above.  Router logits, softmax and the weighted sum are fp32 on both paths
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -23,8 +24,15 @@ from ..weights.loader import WeightSpec, WeightStore
 from .base import FeedForward, StepContext, register_feed_forward
 
 
+def KA_resident(device) -> int:
+    """SMs of the device (the tensor-core product runs up to two CTAs on each)."""
+    from ..kernels.attention import resident_ctas
+    return resident_ctas(device) // 4
+
+
 class MoEFeedForward(FeedForward):
     ROUTER_TC_MIN_TOKENS = 256     # steps with at least this many tokens compute router logits on tensor cores
+    SHARED_SM_SHARE = int(os.environ.get("TQ_SHARED_SM_SHARE", "0"))      # per cent of the SMs for the shared expert in long steps
 
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
                  norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True):
@@ -117,11 +125,11 @@ class MoEFeedForward(FeedForward):
             cls._side_streams[key] = torch.cuda.Stream(device=device)
         return cls._side_streams[key]
 
-    def _product(self, x, w, out, layout, swiglu, token_tile, status=None):
+    def _product(self, x, w, out, layout, swiglu, token_tile, status=None, sm_share=0):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
         kernel otherwise."""
         if isinstance(w, KT.PackedWeights):
-            return KT.gemm_tc(x, w, out, layout, token_tile, status=status)
+            return KT.gemm_tc(x, w, out, layout, token_tile, status=status, sm_share=sm_share)
         return KM.grouped_gemm(x, w, out, layout, swiglu)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
@@ -132,6 +140,14 @@ class MoEFeedForward(FeedForward):
         # most of the GPU idle on their own, and the router's small kernels hide behind its weight stream)
         y_shared = None
         side = None
+        tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
+        # long steps: both products fill the GPU with one persistent CTA per SM, so whichever starts first would
+        # keep the other waiting.  The shared expert's products are bound by the tensor cores, the routed experts'
+        # by the stream of their weights: each gets a share of the SMs and they run beside each other.
+        share_shared = share_routed = 0
+        if self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and isinstance(self.ws13, KT.PackedWeights):
+            share_shared = self.SHARED_SM_SHARE
+            share_routed = 100 - share_shared
         if self.ws13 is not None:
             S = self.shared_intermediate
             stile = KT.token_tile_for(T, 1) if isinstance(self.ws13, KT.PackedWeights) else 0
@@ -140,16 +156,27 @@ class MoEFeedForward(FeedForward):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 hs = torch.empty((T, S), dtype=act, device=dev)
-                self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
-                y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
-                self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status)
+                self._product(xn, self.ws13, hs, None, True, stile, ctx.status, share_shared)
+                # The down projection has few tiles (rows of 128 output columns) and a long K: a handful of SMs stream
+                # all its weights (measured on B200: 0.8 TB/s at 2,048 x 5,632, 1.5 TB/s at 3,584 x 20,480).  While the
+                # routed experts read several times the shared expert's bytes on the main stream that does not
+                # matter, the shared expert ends first either way; with one or two tokens it is the longer chain.
+                # Then its K is shared out over the GPU and the partial sums are added up where the experts'
+                # outputs are summed anyway (measured at the 57B-A14B sizes, batch 1: 144 -> 165 tokens/s; sharing
+                # it out at larger batches takes SMs from the routed experts and costs 3-10 %).
+                few = T * k * self.intermediate <= 2 * S
+                splits = KT.k_splits_for(T, H, S, stile, 2 * KA_resident(dev)) if few and isinstance(self.ws2, KT.PackedWeights) else 1
+                y_shared = torch.empty((splits, T, H) if splits > 1 else (T, H), dtype=torch.float32, device=dev)
+                if splits > 1:
+                    KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits)
+                else:
+                    self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status, share_shared)
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
         ids = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
-        tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
         if KM.router_small_pays(T, k, self.n_experts, H):
@@ -172,9 +199,9 @@ class MoEFeedForward(FeedForward):
             ctx.debug.setdefault("router_ids", []).append(ids)
             ctx.debug.setdefault("router_weights", []).append(wts)
         h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
-        self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status)
+        self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status, share_routed)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
-        self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status)
+        self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, share_routed)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
