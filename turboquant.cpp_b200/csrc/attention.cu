@@ -312,6 +312,42 @@ template <typename TA, int LPK, int STAGES> constexpr int split_ring_bytes() {
 // stages of the ring for an element type and head size (0: this shape has no ring form)
 template <typename TA, int LPK> constexpr int split_stages() { return sizeof(TA) == 2 && LPK == 16 ? 2 : 0; }
 
+// The CTA that finishes last among the n_splits of a (token, KV head) merges their partial states, in the order of
+// the ranges whichever CTA it is.  Nobody waits: each CTA publishes its state, takes a ticket and leaves unless the
+// ticket is the last one.  Kept out of line: the split kernel's loop should not pay registers for it.
+// rows: the first of this CTA's G heads in `partial` ([head][split][HD + 2]); out_rows: the same heads in `out`.
+template <typename TA, int HD>
+__device__ __noinline__ void split_merge_by_last(const float* __restrict__ partial, int n_splits, int* __restrict__ ticket,
+                                                 TA* __restrict__ out_rows, const float* __restrict__ rows, int G) {
+    __shared__ int s_last;
+    __threadfence();                              // this thread's part of the state is visible before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int n = atomicAdd(ticket, 1);
+        s_last = n == n_splits - 1;
+        if (s_last) *ticket = 0;                  // every ticket of this launch has been taken: ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();                              // the others' states, published before their tickets, are visible now
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx % HD;
+        const float* p = rows + (size_t)h * n_splits * (HD + 2);
+        float M = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(p + (size_t)sp * (HD + 2)));
+        float L = 0.f, a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float ms = __ldcg(p + (size_t)sp * (HD + 2));
+            if (ms != -INFINITY) {
+                const float f = expf(ms - M);
+                L += __ldcg(p + (size_t)sp * (HD + 2) + 1) * f;
+                a += __ldcg(p + (size_t)sp * (HD + 2) + 2 + d) * f;
+            }
+        }
+        out_rows[(size_t)h * HD + d] = tq_from_float<TA>(a / L);
+    }
+}
+
 template <typename TA, int LPK, int GC, int STAGES>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ positions,
@@ -479,37 +515,36 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
         dst[2 + d] = a;
         if (d == 0) { dst[0] = M; dst[1] = L; }
     }
-    if (n_splits == 1) return;
-    // The CTA that finishes last among the n_splits of this (token, KV head) merges their partial states, in the
-    // order of the ranges whichever CTA it is.  Nobody waits: each CTA publishes its state, takes a ticket and
-    // leaves unless the ticket is the last one.
-    __shared__ int s_last;
-    __threadfence();                              // this thread's part of the state is visible before the ticket is taken
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* ticket = arrived + ((size_t)t * nkv + g) * chunks + chunk;
-        const int n = atomicAdd(ticket, 1);
-        s_last = n == n_splits - 1;
-        if (s_last) *ticket = 0;                  // every ticket of this launch has been taken: ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();                              // the others' states, published before their tickets, are visible now
-    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
-        const int h = idx / HD, d = idx % HD;
-        const float* p = partial + ((size_t)t * nh + (size_t)g * G_all + h0 + h) * n_splits * (HD + 2);
-        float M = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(p + (size_t)sp * (HD + 2)));
+    // The ring form never merges here: it serves launches of many short CTAs, which get a merge launch of their own,
+    // and the mere presence of this call cost it 13 % (B200, 64 tokens x 16 heads x 4 ranges: 188 us against 167 us).
+    if (STAGES > 0 || n_splits == 1 || arrived == nullptr) return;          // no tickets: attention_merge_kernel follows
+    if constexpr (STAGES == 0) split_merge_by_last<TA, HD>(partial, n_splits, arrived + ((size_t)t * nkv + g) * chunks + chunk,
+                                out + ((size_t)t * nh + (size_t)g * G_all + h0) * HD,
+                                partial + ((size_t)t * nh + (size_t)g * G_all + h0) * n_splits * (HD + 2), G);
+}
+
+// The merge as a launch of its own, for launches of many short CTAs: there a fence and a ticket per CTA cost more than
+// the second launch (measured on B200, 64 tokens x 16 heads x 4 ranges of 512 keys: 4.65 ms of split kernels per
+// step with tickets against 3.95 + 0.10 ms with this kernel).  The same sums in the same order as the last CTA's.
+template <typename TA>
+__global__ void attention_merge_kernel(const float* __restrict__ partial, int n_splits, int hd, TA* __restrict__ out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const size_t th = blockIdx.x;                        // token * nh + head
+    const float* p = partial + th * n_splits * (hd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[(size_t)s * (hd + 2)]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float L = 0.f, a = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float ms = __ldcg(p + (size_t)sp * (HD + 2));
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = p[(size_t)s * (hd + 2)];
             if (ms != -INFINITY) {
                 const float f = expf(ms - M);
-                L += __ldcg(p + (size_t)sp * (HD + 2) + 1) * f;
-                a += __ldcg(p + (size_t)sp * (HD + 2) + 2 + d) * f;
+                L += p[(size_t)s * (hd + 2) + 1] * f;
+                a += p[(size_t)s * (hd + 2) + 2 + d] * f;
             }
         }
-        out[((size_t)t * nh + (size_t)g * G_all + h0 + h) * HD + d] = tq_from_float<TA>(a / L);
+        out[th * hd + d] = tq_from_float<TA>(a / L);
     }
 }
 
@@ -535,10 +570,8 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     TQ_REQUIRE(window >= 0, "attention_split: negative window %d", window);
     TQ_REQUIRE(n_splits == 1 || (partial != nullptr && arrived != nullptr),
                "attention_split: %d ranges need scratch for their partial states and their tickets", n_splits);
-    dim3 grid(T_ * chunks, nkv, n_splits);
-    // the ring form for launches of more than two waves of the register form (TQ_SPLIT_RING=1: wherever the
-    // shape has one, =0: never)
-    const char* ring_env = getenv("TQ_SPLIT_RING");
+    // one launch with tickets while the CTAs fit about two waves (there the second launch is what costs), a merge
+    // launch of its own for more and shorter CTAs
     static int sm_count = 0;
     if (sm_count == 0) {
         int dev = 0;
@@ -546,8 +579,14 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
             || sm_count <= 0)
             TQ_FAIL(-1, "attention_split: cannot read the device's SM count");
     }
-    const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0'
-                                               : (long long)T_ * nkv * n_splits > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count;
+    const long long n_ctas = (long long)T_ * chunks * nkv * n_splits;
+    dim3 grid(T_ * chunks, nkv, n_splits);
+    // the ring form for launches of more than two waves of the register form (TQ_SPLIT_RING=1: wherever the
+    // shape has one, =0: never)
+    const char* ring_env = getenv("TQ_SPLIT_RING");
+    const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0' : n_ctas > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count;
+    const bool own_merge = n_splits > 1 && (n_ctas > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count || ring);
+    if (own_merge) arrived = nullptr;
 #define SPLIT_LAUNCH(TA, LPK, GC, STAGES)                                                                       \
     do {                                                                                                        \
         auto kern = attention_split_kernel<TA, LPK, GC, STAGES>;                                                \
@@ -574,6 +613,11 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     else if (act_dtype == TQ_F32) SPLIT_HD(float);
     else TQ_FAIL(-2, "attention_split: unknown element type %d", act_dtype);
     TQ_CHECK_LAUNCH("attention_split");
+    if (own_merge) {
+        TQ_DISPATCH(act_dtype, TA,
+            (tq_launch(T_ * nh, hd >= 128 ? 128 : 64, 0, stream)(attention_merge_kernel<TA>, partial, n_splits, hd, (TA*)out)));
+        TQ_CHECK_LAUNCH("attention_merge");
+    }
     return 0;
 }
 

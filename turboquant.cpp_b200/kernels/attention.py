@@ -1,6 +1,7 @@
 """Attention kernels over the paged cache (csrc/attention.cu)."""
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int
 from typing import Optional
 
@@ -140,7 +141,10 @@ def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch
                                        c_int(page_size), c_int(window), c_float(scale),
                                        ptr(partial) if n_splits > 1 else None, c_int(n_splits), ptr(arrived),
                                        ptr(out), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-                                       c_int(page_table.shape[0]), c_int(cache_layer.shape[0]), stream()))
+                                       c_int(page_table.shape[0]), c_int(cache_layer.shape[0]), stream()),
+          kernels=2 if n_splits > 1 and (T * head_chunks(n_heads, n_kv_heads) * n_kv_heads * n_splits
+                                         > 2 * resident_ctas(q.device) or os.environ.get("TQ_SPLIT_RING", "0") not in ("", "0"))
+          else 1)      # many short CTAs: the launcher adds a merge launch of its own
     return out
 
 
