@@ -548,6 +548,228 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int n_
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Split attention for grouped queries on tensor cores (bfloat16, head size 64 or 128, 3 to 16 query heads per KV
+// head).  With several query heads per KV head the register form above is bound by its arithmetic, not by the
+// stream of keys: every key costs 2 * head size multiply-adds PER QUERY HEAD on CUDA cores (measured on B200 at 7
+// heads per KV head, 64 tokens x 4 KV heads x 2,048 keys: 165 us for 268 MB, 1.6 TB/s).  Here the query heads of a
+// KV head are the 16 rows of one mma.sync tile (m16n8k16, bf16 in, fp32 out), so keys and values are read once per
+// group and the arithmetic rides on the tensor pipe.  The op stays memory-bound and its M is 3..16 rows, which is why
+// this is the warp-level mma and not tcgen05 (whose tiles start at 64 rows and want a CTA-wide TMEM pipeline).
+//   grid (token, KV head, range) as above; a warp takes groups of 16 consecutive positions (never across a page),
+//   brings each group's 16 key rows and 16 value rows into its own two-stage ring with 16-byte cp.async copies
+//   (16-byte chunks XOR-swizzled by the row so that ldmatrix is conflict-free), computes S = Q K^T (scores in fp32,
+//   scaled and masked there), keeps an online softmax per row in fp32, rounds P to bfloat16 as the A operand of
+//   O += P V (as the prompt kernel does), and the warps' states are merged through shared memory into the same
+//   partial-state format as the register form, so the merge (tickets or merge launch) is shared.
+// ---------------------------------------------------------------------------------------
+#define GQA_WARPS 4
+#define GQA_STAGES 2
+#define GQA_KEYS 16                              // positions per group
+
+__device__ __forceinline__ void gqa_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void gqa_ldmatrix(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(smem_row)));
+}
+__device__ __forceinline__ void gqa_ldmatrix_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(smem_row)));
+}
+__device__ __forceinline__ uint32_t gqa_pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int HD> constexpr int gqa_smem_bytes() {
+    // the ring: [warp][stage][K tile, V tile][16 rows][HD] bf16; reused by the merge: [warp][16 rows][HD + 2] floats
+    constexpr int ring = GQA_WARPS * GQA_STAGES * 2 * GQA_KEYS * HD * 2;
+    constexpr int merge = GQA_WARPS * 16 * (HD + 2) * 4;
+    return ring > merge ? ring : merge;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(GQA_WARPS * 32)
+attention_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                     const int* __restrict__ page_table, int table_stride, int page_size, int window, float scale,
+                     float* __restrict__ partial, int n_splits, int* __restrict__ arrived,
+                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int CPR = HD / 8;                          // 16-byte chunks per row
+    constexpr int TILE = GQA_KEYS * HD;                  // elements of a K (or V) tile
+    extern __shared__ __align__(128) unsigned char s_gqa[];
+    const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+    const int G = nh / nkv;                              // 3..16 rows of the tile are query heads, the rest zero
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tig = lane & 3;           // row of the fragments / column pair
+    const int pos = positions[t];
+    const int start = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+    const int first = start / GQA_KEYS, last = pos / GQA_KEYS;          // inclusive groups of 16 positions
+    const int groups = last - first + 1;
+    const int per = (groups + n_splits - 1) / n_splits;
+    const int gb = first + split * per, ge = min(last + 1, gb + per);
+
+    // the queries as A fragments: rows gid and gid + 8 (heads), 16 head elements per k-step
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* q0 = q + ((size_t)t * nh + (size_t)g * G + gid) * HD + tig * 2;
+        const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qa[ks][0] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16) : 0u;
+            qa[ks][1] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16) : 0u;
+            qa[ks][2] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8) : 0u;
+            qa[ks][3] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8) : 0u;
+        }
+    }
+    float o[HD / 8][4];                                  // rows gid (0,1) and gid + 8 (2,3), head elements nd*8 + tig*2 + {0,1}
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) { o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;          // running maximum and this lane's share of the sum
+
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(s_gqa) + (size_t)warp * GQA_STAGES * 2 * TILE;
+    auto copy_group = [&](int grp, int stage) {
+        const int p0 = grp * GQA_KEYS;
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p0 / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+        const __nv_bfloat16* kbase = cache + (((size_t)page * 2 + 0) * nkv + g) * page_size * HD + (size_t)(p0 % page_size) * HD;
+        const __nv_bfloat16* vbase = kbase + (size_t)nkv * page_size * HD;
+        __nv_bfloat16* kt = ring + (size_t)stage * 2 * TILE;
+        __nv_bfloat16* vt = kt + TILE;
+#pragma unroll
+        for (int i = 0; i < GQA_KEYS * CPR / 32; ++i) {
+            const int idx = lane + 32 * i, r = idx / CPR, c = idx % CPR;
+            const int dst = (r * CPR + (c ^ (r & 7))) * 8;
+            split_copy16(kt + dst, kbase + (size_t)r * HD + c * 8);
+            split_copy16(vt + dst, vbase + (size_t)r * HD + c * 8);
+        }
+    };
+    int next_grp = gb + warp, next_stage = 0, stage = 0;
+    if (next_grp < ge) copy_group(next_grp, next_stage);
+    split_commit();
+    next_grp += GQA_WARPS;
+    next_stage ^= 1;
+    for (int grp = gb + warp; grp < ge; grp += GQA_WARPS) {
+        if (next_grp < ge) copy_group(next_grp, next_stage);          // the stage read one iteration ago
+        split_commit();
+        next_grp += GQA_WARPS;
+        next_stage ^= 1;
+        split_wait<1>();                                              // all but the newest group have landed: this one has
+        __syncwarp();
+        const __nv_bfloat16* kt = ring + (size_t)stage * 2 * TILE;
+        const __nv_bfloat16* vt = kt + TILE;
+        stage ^= 1;
+        // ---- S = Q K^T: two tiles of 8 keys ----
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mi = lane >> 3, key = (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                uint32_t b[4];
+                const int chunk = ks * 2 + (mi & 1);
+                gqa_ldmatrix(b, kt + (key * CPR + (chunk ^ (key & 7))) * 8);
+                gqa_mma(s[0], qa[ks], b[0], b[1]);
+                gqa_mma(s[1], qa[ks], b[2], b[3]);
+            }
+        }
+        // ---- scale, mask, online softmax (rows gid and gid + 8; a row's 16 scores sit in the 4 lanes of a quad) ----
+        const int p0 = grp * GQA_KEYS;
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int p = p0 + nt * 8 + tig * 2 + e;
+                const bool seen = p >= start && p <= pos;
+                s[nt][e] = seen ? s[nt][e] * scale : -INFINITY;
+                s[nt][2 + e] = seen ? s[nt][2 + e] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // a group always holds a position its rows see (it lies between start and pos), so mx is finite here
+        const float c0 = expf(m0 - mx0), c1 = expf(m1 - mx1);         // exp(-inf) = 0 the first time
+        m0 = mx0; m1 = mx1;
+        l0 *= c0; l1 *= c1;
+        uint32_t pa[4];
+        {
+            const float e00 = expf(s[0][0] - mx0), e01 = expf(s[0][1] - mx0), e10 = expf(s[1][0] - mx0), e11 = expf(s[1][1] - mx0);
+            const float f00 = expf(s[0][2] - mx1), f01 = expf(s[0][3] - mx1), f10 = expf(s[1][2] - mx1), f11 = expf(s[1][3] - mx1);
+            l0 += (e00 + e01) + (e10 + e11);
+            l1 += (f00 + f01) + (f10 + f11);
+            pa[0] = gqa_pack(e00, e01);      // row gid,     keys tig*2 + {0,1}
+            pa[1] = gqa_pack(f00, f01);      // row gid + 8, keys tig*2 + {0,1}
+            pa[2] = gqa_pack(e10, e11);      // row gid,     keys 8 + tig*2 + {0,1}
+            pa[3] = gqa_pack(f10, f11);      // row gid + 8, keys 8 + tig*2 + {0,1}
+        }
+        // ---- O = O * corr + P V ----
+        {
+            const int mi = lane >> 3, key = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int nd = 0; nd < HD / 8; nd += 2) {
+                uint32_t b[4];
+                const int chunk = nd + (mi >> 1);
+                gqa_ldmatrix_trans(b, vt + (key * CPR + (chunk ^ (key & 7))) * 8);
+                o[nd][0] *= c0; o[nd][1] *= c0; o[nd][2] *= c1; o[nd][3] *= c1;
+                o[nd + 1][0] *= c0; o[nd + 1][1] *= c0; o[nd + 1][2] *= c1; o[nd + 1][3] *= c1;
+                gqa_mma(o[nd], pa, b[0], b[1]);
+                gqa_mma(o[nd + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();                                                 // the stage may be overwritten two iterations on
+    }
+    split_wait<0>();
+    // ---- the warps' states through shared memory (the ring is no longer needed) ----
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();
+    float* st = reinterpret_cast<float*>(s_gqa) + (size_t)warp * 16 * (HD + 2);      // [row][m, l, HD values]
+    if (tig == 0) {
+        st[(size_t)gid * (HD + 2)] = m0; st[(size_t)gid * (HD + 2) + 1] = l0;
+        st[(size_t)(gid + 8) * (HD + 2)] = m1; st[(size_t)(gid + 8) * (HD + 2) + 1] = l1;
+    }
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) {
+        float* r0 = st + (size_t)gid * (HD + 2) + 2 + nd * 8 + tig * 2;
+        float* r1 = st + (size_t)(gid + 8) * (HD + 2) + 2 + nd * 8 + tig * 2;
+        r0[0] = o[nd][0]; r0[1] = o[nd][1]; r1[0] = o[nd][2]; r1[1] = o[nd][3];
+    }
+    __syncthreads();
+    const float* all = reinterpret_cast<const float*>(s_gqa);
+    for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < GQA_WARPS; ++w) M = fmaxf(M, all[((size_t)w * 16 + h) * (HD + 2)]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < GQA_WARPS; ++w) {
+            const float* sw = all + ((size_t)w * 16 + h) * (HD + 2);
+            const float f = sw[0] == -INFINITY ? 0.f : expf(sw[0] - M);
+            L += sw[1] * f;
+            a += sw[2 + d] * f;
+        }
+        if (n_splits == 1) {
+            out[((size_t)t * nh + (size_t)g * G + h) * HD + d] = __float2bfloat16_rn(a / L);
+            continue;
+        }
+        float* dst = partial + (((size_t)t * nh + (size_t)g * G + h) * n_splits + split) * (HD + 2);
+        dst[2 + d] = a;
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+    }
+    if (n_splits == 1 || arrived == nullptr) return;          // no tickets: attention_merge_kernel follows
+    split_merge_by_last<__nv_bfloat16, HD>(partial, n_splits, arrived + (size_t)t * nkv + g,
+                                           out + ((size_t)t * nh + (size_t)g * G) * HD,
+                                           partial + ((size_t)t * nh + (size_t)g * G) * n_splits * (HD + 2), G);
+}
+
 // partial: T * nh * n_splits * (hd + 2) floats of scratch; arrived: T * nkv * ceil(G / 8) ints (G = nh / nkv) that are
 // zero before the launch and zero again after it (both unused, and may be null, with one range).
 TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype, const int* positions,
@@ -587,6 +809,32 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
     const bool ring = ring_env && ring_env[0] ? ring_env[0] != '0' : n_ctas > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count;
     const bool own_merge = n_splits > 1 && (n_ctas > 2LL * SPLIT_REGISTER_CTAS_PER_SM * sm_count || ring);
     if (own_merge) arrived = nullptr;
+    // grouped queries in bfloat16: the tensor-core form (TQ_NO_GQA_MMA=1: the register form everywhere)
+    static const bool gqa_mma = [] { const char* e = getenv("TQ_NO_GQA_MMA"); return !(e && e[0] && e[0] != '0'); }();
+    if (gqa_mma && act_dtype == TQ_BF16 && (hd == 64 || hd == 128) && G >= 3 && G <= 16) {
+#define GQA_LAUNCH(HD_)                                                                                         \
+        do {                                                                                                    \
+            auto kern = attention_gqa_kernel<HD_>;                                                              \
+            constexpr int smem = gqa_smem_bytes<HD_>();                                                         \
+            static bool configured = false;                                                                     \
+            if (!configured) {                                                                                  \
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);  \
+                if (e != cudaSuccess) TQ_FAIL(-1, "attention_split: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e)); \
+                configured = true;                                                                              \
+            }                                                                                                   \
+            tq_launch(dim3(T_, nkv, n_splits), GQA_WARPS * 32, smem, stream)(kern,                              \
+                (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, positions, seq_of_token, page_table, table_stride, \
+                page_size, window, scale, partial, n_splits, arrived, (__nv_bfloat16*)out, nh, nkv, n_seqs, n_pages); \
+        } while (0)
+        if (hd == 64) GQA_LAUNCH(64); else GQA_LAUNCH(128);
+#undef GQA_LAUNCH
+        TQ_CHECK_LAUNCH("attention_gqa");
+        if (own_merge) {
+            tq_launch(T_ * nh, hd >= 128 ? 128 : 64, 0, stream)(attention_merge_kernel<__nv_bfloat16>, partial, n_splits, hd, (__nv_bfloat16*)out);
+            TQ_CHECK_LAUNCH("attention_merge");
+        }
+        return 0;
+    }
 #define SPLIT_LAUNCH(TA, LPK, GC, STAGES)                                                                       \
     do {                                                                                                        \
         auto kern = attention_split_kernel<TA, LPK, GC, STAGES>;                                                \

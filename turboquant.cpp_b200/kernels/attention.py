@@ -87,6 +87,20 @@ def resident_ctas(device=None) -> int:
     return _resident[idx]
 
 
+def gqa_mma_usable(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether the split attention runs its tensor-core form: bfloat16, head size 64 or 128 and 3 to 16 query
+    heads per KV head (the launcher decides the same way; TQ_NO_GQA_MMA=1 switches it off)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 3 <= n_heads // n_kv_heads <= 16
+            and os.environ.get("TQ_NO_GQA_MMA", "0") in ("", "0"))
+
+
+def split_resident(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, device=None) -> int:
+    """CTAs of the split attention the device runs at once for this shape: four per SM in the register form, three
+    in the tensor-core form (64 KiB of shared memory each)."""
+    r = resident_ctas(device)
+    return r * 3 // 4 if gqa_mma_usable(dtype, n_heads, n_kv_heads, head_dim) else r
+
+
 def splits_for(n_tokens: int, n_kv_heads: int, resident: int = RESIDENT_CTAS) -> int:
     """Ranges the keys of one (token, KV head) are cut into.  All CTAs do equal work, so what matters is
     how full the last wave is: with few rows the CTAs should fit one wave; with many, the count that
