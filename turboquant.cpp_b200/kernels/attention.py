@@ -101,6 +101,10 @@ def split_resident(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: 
     return r * 3 // 4 if gqa_mma_usable(dtype, n_heads, n_kv_heads, head_dim) else r
 
 
+GQA_MAX_SPLITS = 8       # measured on B200 (7 heads per KV head, 2,048 keys): 1, 2 and 8 tokens all run fastest with 8 ranges
+#                          (18-20 us; 16 ranges 20, 32 ranges 30: the last CTA's merge grows with the ranges x heads)
+
+
 def splits_for(n_tokens: int, n_kv_heads: int, resident: int = RESIDENT_CTAS) -> int:
     """Ranges the keys of one (token, KV head) are cut into.  All CTAs do equal work, so what matters is
     how full the last wave is: with few rows the CTAs should fit one wave; with many, the count that

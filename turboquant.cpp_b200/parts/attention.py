@@ -110,6 +110,8 @@ class AttentionMixer(Mixer):
         elif KA.split_usable(self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size):
             n_splits = KA.splits_for(T, self.n_kv_heads * KA.head_chunks(self.n_heads, self.n_kv_heads),
                                      KA.split_resident(act, self.n_heads, self.n_kv_heads, self.head_dim, xn.device))
+            if KA.gqa_mma_usable(act, self.n_heads, self.n_kv_heads, self.head_dim):
+                n_splits = min(n_splits, KA.GQA_MAX_SPLITS)
             partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32,
                                   device=xn.device) if n_splits > 1 else None
             KA.attention_split(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
