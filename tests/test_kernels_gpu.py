@@ -472,6 +472,71 @@ def test_qkv_rope_cache(nh, nkv, hd, pairing, dtype, tol):
     assert np.all(c[~written] == 0)
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (2, 50, 40), (3, 133, 264), (4, 4096, 3584), (1, 7, 8)])
+def test_gemv(T, N, K):
+    """One to four tokens against bfloat16 weights: widths that are no multiple of the rows a warp or a block takes,
+    a K shorter than one pass of a warp."""
+    from turboquant_cpp_b200.kernels import gemv as KG
+    rng = np.random.default_rng(T + N + K)
+    x, w = bf16_values(rng.normal(size=(T, K))), bf16_values(rng.normal(size=(N, K)) / math.sqrt(K))
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    KG.gemv(dev(x, torch.bfloat16), dev(w, torch.bfloat16), out)
+    close(out, x @ w.T, 3e-6)
+    assert not KG.usable(torch.zeros((5, K), dtype=torch.bfloat16, device=DEV), dev(w, torch.bfloat16))       # five tokens
+    assert not KG.usable(dev(x, torch.float32), dev(w, torch.bfloat16))                                        # float32 rows
+    with pytest.raises(KG.KernelError):
+        KG.gemv(dev(x, torch.float32), dev(w, torch.bfloat16), out)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,H", [(4, 4, 16, 64), (6, 2, 32, 192), (5, 1, 48, 120), (16, 16, 128, 2048), (28, 4, 128, 3584)])
+@pytest.mark.parametrize("T", [1, 3, 4])
+@pytest.mark.parametrize("with_bias,with_rope,bias_dtype", [(True, True, torch.bfloat16), (True, True, torch.float32),
+                                                            (False, True, None), (True, False, torch.bfloat16)])
+def test_qkv_gemv_rope(nh, nkv, hd, H, T, with_bias, with_rope, bias_dtype):
+    """The fused projection of up to four tokens: product (rounded to bfloat16 as the library product's result is),
+    bias, rotation, queries out, keys and values at their positions' places in the pages and nowhere else; also
+    without a cache (a layer that reads another's)."""
+    from turboquant_cpp_b200.kernels import gemv as KG
+    from turboquant_cpp_b200.parts.rotary import RotaryEncoding
+    rng = np.random.default_rng(nh * 10 + hd + T)
+    seq_lens, q_lens, page = ([70, 130, 5, 64][:T] if T < 4 else [70, 130, 5, 64]), [1] * T, 64
+    if T == 3:
+        seq_lens, q_lens = [70, 131], [1, 2]                      # two tokens of one sequence in the step
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, torch.bfloat16)
+    width = (nh + 2 * nkv) * hd
+    x = bf16_values(rng.normal(size=(T, H)))
+    w = bf16_values(rng.normal(size=(width, H)) / math.sqrt(H))
+    bias = bf16_values(rng.normal(size=width)) if with_bias else None
+    theta = 12345.0
+    rot = RotaryEncoding(hd, theta, 256, "half")
+    rot.prepare(DEV)
+    cos, sin, _ = rot.tables() if with_rope else (None, None, None)
+    cache = torch.zeros((64, 2, nkv, page, hd), dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((T, nh, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    pos = d["positions"]
+    args = (dev(x, torch.bfloat16), dev(w, torch.bfloat16), None if bias is None else dev(bias, bias_dtype), cos, sin,
+            dev(pos, torch.int32), dev(d["seq_of"], torch.int32), dev(d["table"], torch.int32), page)
+    KG.qkv_gemv_rope(*args, q_out, cache, nh, nkv, hd)
+    y = P.round_bf16(x @ w.T) + (bias if bias is not None else 0.0)
+    turn = (lambda a: P.rotary(a, pos, theta, "half")) if with_rope else (lambda a: a)
+    q = turn(y[:, :nh * hd].reshape(T, nh, hd))
+    k = turn(y[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd))
+    v = y[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    tol = 6e-3
+    close(q_out, q, tol)
+    c = cache.float().cpu().numpy()
+    written = np.zeros(c.shape, dtype=bool)
+    for t in range(T):
+        pg = d["table"][d["seq_of"][t], pos[t] // page]
+        np.testing.assert_allclose(c[pg, 0, :, pos[t] % page], k[t], atol=tol * 8, rtol=0)
+        np.testing.assert_allclose(c[pg, 1, :, pos[t] % page], v[t], atol=tol * 8, rtol=0)
+        written[pg, :, :, pos[t] % page] = True
+    assert np.all(c[~written] == 0)
+    q_only = torch.full((T, nh, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KG.qkv_gemv_rope(*args, q_only, None, nh, nkv, hd)
+    assert torch.equal(q_only, q_out)
+
+
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("E,k,H,renorm,shared", [(8, 2, 64, False, True), (6, 3, 192, True, True), (5, 1, 120, False, False),
                                                   (60, 4, 200, False, True), (130, 8, 96, True, False)])

@@ -15,6 +15,7 @@ import torch
 
 from ..kernels import attention as KA
 from ..kernels import elementwise as KE
+from ..kernels import gemv as KG
 from ..kernels.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 from .base import KVNeed, LayerCache, Mixer, PositionEncoding, StepContext, register_mixer
@@ -62,6 +63,8 @@ class AttentionMixer(Mixer):
 
     def kernels(self) -> List[str]:
         names = ["attention", "elementwise"]
+        if getattr(self, "run_dtype", None) == torch.bfloat16:
+            names.append("gemv")
         if getattr(self, "run_dtype", None) == torch.bfloat16 and self.head_dim in (64, 128):
             names.append("attention_prefill")
         return names
@@ -80,9 +83,19 @@ class AttentionMixer(Mixer):
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         T = xn.shape[0]
         act = ctx.act_dtype
-        qkv = linear(xn, self.w_qkv, out_dtype=act)
         q = torch.empty((T, self.n_heads, self.head_dim), dtype=act, device=xn.device)
         tables = self.position.tables() if self.position is not None else None
+        fused = (KG.fused_pays(xn, self.w_qkv) and (self.position is None or (tables is not None and tables[2] == "half"))
+                 and (cache.kv is None or cache.kv.dtype == torch.bfloat16))
+        if fused:
+            # one or two tokens: the projection is a stream of its weights; bias, rotation and the cache write
+            # ride on the same launch instead of a library product and a kernel behind it
+            cos, sin = (tables[0], tables[1]) if tables is not None else (None, None)
+            KG.qkv_gemv_rope(xn, self.w_qkv, self.b_qkv, cos, sin, ctx.positions, ctx.seq_of_token, cache.page_table,
+                             cache.page_size, q, cache.kv if cache.writes else None, self.n_heads, self.n_kv_heads,
+                             self.head_dim)
+            return self._attend(q, T, act, ctx, cache)
+        qkv = linear(xn, self.w_qkv, out_dtype=act)
         bias = self.b_qkv
         if self.position is not None and tables is None:
             # an encoding that is not a table-driven rotation: the bias first, then the encoding's own pass over
@@ -96,6 +109,12 @@ class AttentionMixer(Mixer):
         KA.qkv_rope_cache(qkv, bias, cos, sin, pairing, ctx.positions, ctx.seq_of_token, cache.page_table,
                           cache.page_size, q, cache.kv if cache.writes else None,
                           self.n_heads, self.n_kv_heads, self.head_dim)
+        return self._attend(q, T, act, ctx, cache)
+
+    def _attend(self, q: torch.Tensor, T: int, act: torch.dtype, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        """Attention of the step's queries over the cache (the step's keys and values are in it), then the output
+        projection."""
+        xn = q
         o = torch.empty((T, self.q_size), dtype=act, device=xn.device)
         if ctx.max_q_len >= self.PREFILL_MIN_RUN and KA.prefill_usable(act, self.head_dim, cache.page_size):
             # long runs of new tokens (prompts): tensor cores
@@ -119,6 +138,8 @@ class AttentionMixer(Mixer):
         else:
             KA.attention(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
                          self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
+        if KG.pays(o, self.w_o):
+            return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=o.device))
         return linear(o, self.w_o, out_dtype=torch.float32)
 
 
