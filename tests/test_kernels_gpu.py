@@ -736,21 +736,28 @@ def test_sample_rows_distribution():
 @pytest.mark.parametrize("T,E,k,H,renorm,shared", [(1, 8, 2, 64, False, True), (8, 60, 4, 2048, False, True),
                                                     (64, 64, 8, 200, True, False), (33, 5, 1, 120, False, False),
                                                     (3, 1023, 40, 96, True, True), (128, 300, 4, 64, False, False),
-                                                    (5, 17, 3, 100, True, True), (7, 60, 4, 2048, False, True)])
+                                                    (5, 17, 3, 100, True, True), (7, 60, 4, 2048, False, True),
+                                                    (1, 60, 4, 2048, False, True), (2, 60, 4, 2048, True, True),
+                                                    (4, 64, 8, 3584, False, True), (3, 6, 3, 192, True, False),
+                                                    (4, 200, 16, 520, False, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("cluster", [True, False])
 def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dtype, cluster, monkeypatch):
     """The one-launch decode path gives exactly what the separate kernels give, call after call: a block per
     token for logits and selection; then, with up to 8 tokens, the blocks are a cluster that passes the choices
     round in shared memory and every block writes its own rows, else the block that finishes last (a counter)
-    does the layout and the gathered rows."""
+    does the layout and the gathered rows.  One to four bfloat16 tokens take a single block that lays the pairs out
+    by counting (with `cluster` off here, that form is switched off too, so the others see these sizes as well)."""
     from turboquant_cpp_b200.kernels import elementwise as KE, moe as KM
     if not cluster:
         if T > 8:
             pytest.skip("more than 8 tokens never form a cluster")
         monkeypatch.setenv("TQ_ROUTER_NO_CLUSTER", "1")
+        monkeypatch.setenv("TQ_ROUTER_NO_TINY", "1")
     rng = np.random.default_rng(T + E)
     x = dev(bf16_values(rng.normal(size=(T, H))), dtype)
+    if T > 1:
+        x[1] = x[0]                          # two tokens with the same choices: their pairs share experts
     wr = dev(bf16_values(rng.normal(size=(E, H)) * 0.3), dtype)
     wsg = dev(bf16_values(rng.normal(size=(1, H)) * 0.3), dtype) if shared else None
     assert KM.router_small_usable(T, k, E, H)

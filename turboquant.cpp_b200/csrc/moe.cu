@@ -622,6 +622,141 @@ router_cluster_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const
     }
 }
 
+// ---- the form for one to four tokens (bfloat16 rows and weights) ----
+// One block.  What such a step pays for is trips to memory one after another, not bytes, so: a warp takes rows of
+// the router matrix in pairs, its lanes ask for all their 16-byte pieces of the first pair at once and BEFORE the
+// kernel waits for the one ahead of it (weights do not depend on it); then the tokens' rows come into shared memory,
+// the dots, warp t chooses for token t, and the few pairs are laid out by counting (a pair's row = the pairs with a
+// smaller expert, or the same expert and an earlier place): two block barriers, no scan.  Every expert has at most
+// one tile (at most four rows, tiles hold at least as many).
+#define TINY_MAX_T 4
+#define TINY_MAX_PAIRS 64
+#define TINY_KI 8
+#define TINY_THREADS 512                 // 16 warps: 128 registers a thread, for the two rows a lane holds in flight
+__device__ __forceinline__ uint4 tiny_ld16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void tiny_widen(const uint4& v, float (&f)[8]) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+template <int T>
+__global__ void __launch_bounds__(TINY_THREADS)
+router_tiny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr, const __nv_bfloat16* __restrict__ wsg,
+                   int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ shared_scale, int H, int E, int k,
+                   int renorm, int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
+                   int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                   int* __restrict__ tile_count, int* __restrict__ n_tiles, __nv_bfloat16* __restrict__ x_rows) {
+    extern __shared__ __align__(16) unsigned char s_tiny[];
+    __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(s_tiny);                     // [T][H]
+    float* s_logit = reinterpret_cast<float*>(s_tiny + (size_t)T * H * 2);             // [T][E + 1]
+    __shared__ int s_ids[TINY_MAX_PAIRS], s_row[TINY_MAX_PAIRS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int rows = E + (wsg ? 1 : 0);
+    auto row_ptr = [&](int r) { return r < E ? wr + (size_t)r * H : wsg; };
+    // the first two rows of this warp, all pieces a lane has in them (up to TINY_KI each), before the wait
+    uint4 wa[TINY_KI], wb[TINY_KI];
+    auto ask = [&](int r0, int k0) {
+        const int r1 = r0 + nwarps;
+#pragma unroll
+        for (int it = 0; it < TINY_KI; ++it) {
+            const int kk = k0 + lane * 8 + it * 256;
+            wa[it] = (r0 < rows && kk < H) ? tiny_ld16(row_ptr(r0) + kk) : make_uint4(0u, 0u, 0u, 0u);
+            wb[it] = (r1 < rows && kk < H) ? tiny_ld16(row_ptr(r1) + kk) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    ask(warp, 0);
+    tq_grid_wait();
+    tq_grid_launch_dependents();
+    for (int i = threadIdx.x * 8; i < T * H; i += blockDim.x * 8)
+        *reinterpret_cast<uint4*>(s_x + i) = *reinterpret_cast<const uint4*>(x + i);
+    __syncthreads();
+    // ---- logits (fp32 sums of the bf16 products, a lane's pieces in order, then the lanes by shuffles) ----
+    for (int r0 = warp; r0 < rows; r0 += 2 * nwarps) {
+        const int r1 = r0 + nwarps;
+        float sa[T], sb[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) { sa[t] = 0.f; sb[t] = 0.f; }
+        for (int k0 = 0; k0 < H; k0 += TINY_KI * 256) {
+            if (r0 != warp || k0 != 0) ask(r0, k0);          // the first pieces were asked for before the wait
+#pragma unroll
+            for (int it = 0; it < TINY_KI; ++it) {
+                const int kk = k0 + lane * 8 + it * 256;
+                if (kk < H) {
+                    float fa[8], fb[8];
+                    tiny_widen(wa[it], fa);
+                    tiny_widen(wb[it], fb);
+#pragma unroll
+                    for (int t = 0; t < T; ++t) {
+                        float xf[8];
+                        tiny_widen(*reinterpret_cast<const uint4*>(s_x + (size_t)t * H + kk), xf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { sa[t] = fmaf(xf[i], fa[i], sa[t]); sb[t] = fmaf(xf[i], fb[i], sb[t]); }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            const float va = tq_warp_sum(sa[t]), vb = tq_warp_sum(sb[t]);
+            if (lane == 0) {
+                s_logit[t * (E + 1) + r0] = va;
+                if (r1 < rows) s_logit[t * (E + 1) + r1] = vb;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- warp t chooses for token t ----
+    if (warp < T) {
+        const float* row = s_logit + warp * (E + 1);
+        if (shared_scale && lane == 0) shared_scale[warp] = 1.0f / (1.0f + expf(-row[E]));
+        select_in_registers(row, E, k, renorm, lane, ids + (size_t)warp * k, wts + (size_t)warp * k, s_ids + warp * k);
+    }
+    __syncthreads();
+    // ---- layout by counting ----
+    const int P = T * k;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        int below = 0, own = 0, tiles_below = 0;
+        for (int q = 0; q < P; ++q) {
+            const int id = s_ids[q];
+            below += id < e;
+            own += id == e;
+            if (id < e) {                                   // count an expert once: at its first pair
+                bool firstq = true;
+                for (int q2 = 0; q2 < q; ++q2) firstq = firstq && s_ids[q2] != id;
+                tiles_below += firstq;
+            }
+        }
+        expert_offset[e] = below;
+        if (e < E) {
+            counts[e] = own;
+            if (own > 0) { tile_expert[tiles_below] = e; tile_row0[tiles_below] = below; tile_count[tiles_below] = own; }
+        } else {
+            n_tiles[0] = tiles_below;
+        }
+    }
+    if (threadIdx.x < P) {
+        const int p = threadIdx.x, id = s_ids[p];
+        int row = 0;
+        for (int q = 0; q < P; ++q) row += (s_ids[q] < id) || (s_ids[q] == id && q < p);
+        s_row[p] = row;
+        sorted_pair[row] = p;
+        row_of_pair[p] = row;
+    }
+    __syncthreads();
+    // ---- the tokens' rows, still in shared memory, to their pairs' places ----
+    const int n16 = H / 8;
+    for (int i = threadIdx.x; i < P * n16; i += blockDim.x) {
+        const int p = i / n16, c = i - p * n16;
+        reinterpret_cast<uint4*>(x_rows + (size_t)s_row[p] * H)[c] = reinterpret_cast<const uint4*>(s_x + (size_t)(p / k) * H)[c];
+    }
+}
+
 // ---- the counter form ----
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(SMALL_THREADS)
@@ -777,6 +912,22 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
     const int vec_w = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
     const int abytes = act_dtype == TQ_F32 ? 4 : 2;
     const int vec_x = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
+    // one to four tokens in bfloat16: the single-block form (TQ_ROUTER_NO_TINY=1: the others after all)
+    {
+        const char* tiny_env = getenv("TQ_ROUTER_NO_TINY");
+        const bool no_tiny = tiny_env && tiny_env[0] && tiny_env[0] != '0';
+        const size_t smem_tiny = (size_t)T_ * H * 2 + (size_t)T_ * (E + 1) * 4;
+        if (!no_tiny && T_ <= TINY_MAX_T && T_ * k <= TINY_MAX_PAIRS && T_ <= tile_rows && act_dtype == TQ_BF16 && w_dtype == TQ_BF16 &&
+            H % 8 == 0 && vec_w && vec_x && E <= 32 * SELECT_REGS && smem_tiny <= 40 * 1024) {
+#define TINY_CASE(TT) case TT: tq_launch(1, TINY_THREADS, smem_tiny, stream)(router_tiny_kernel<TT>, (const __nv_bfloat16*)x, \
+            (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, ids, wts, shared_scale, H, E, k, renorm, counts, sorted_pair,  \
+            row_of_pair, expert_offset, tile_expert, tile_row0, tile_count, n_tiles, (__nv_bfloat16*)x_rows); break;
+            switch (T_) { TINY_CASE(1) TINY_CASE(2) TINY_CASE(3) TINY_CASE(4) }
+#undef TINY_CASE
+            TQ_CHECK_LAUNCH("router_tiny");
+            return 0;
+        }
+    }
     // the cluster form (TQ_ROUTER_NO_CLUSTER=1: the counter form after all)
     const size_t smem_cluster = (((size_t)(E + 1) * 4 + 15) & ~(size_t)15) + (size_t)T_ * H * abytes;
     const char* no_cluster = getenv("TQ_ROUTER_NO_CLUSTER");
