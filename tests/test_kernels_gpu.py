@@ -754,6 +754,8 @@ def test_router_small_equals_the_separate_kernels(T, E, k, H, renorm, shared, dt
             pytest.skip("more than 8 tokens never form a cluster")
         monkeypatch.setenv("TQ_ROUTER_NO_CLUSTER", "1")
         monkeypatch.setenv("TQ_ROUTER_NO_TINY", "1")
+    else:
+        monkeypatch.setenv("TQ_ROUTER_NO_TINY", "0")      # "0": the single-block form wherever it can run, not only at one token
     rng = np.random.default_rng(T + E)
     x = dev(bf16_values(rng.normal(size=(T, H))), dtype)
     if T > 1:

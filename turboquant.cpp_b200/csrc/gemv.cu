@@ -40,16 +40,17 @@ __device__ __forceinline__ uint4 gemv_stream16(const void* p) {          // read
 template <int NR>
 struct GemvRows {
     const __nv_bfloat16* w[NR];
-    uint4 first[NR][GEMV_KI];
-    __device__ __forceinline__ void ask(int K, int lane) {                // the first trip
+    uint4 wv[NR][GEMV_KI];                                                // the pieces in flight (or just landed)
+    __device__ __forceinline__ void ask(int K, int lane, int k0) {        // one trip: GEMV_KI pieces of every row
 #pragma unroll
         for (int r = 0; r < NR; ++r)
 #pragma unroll
             for (int it = 0; it < GEMV_KI; ++it) {
-                const int k = lane * 8 + it * 256;
-                first[r][it] = k < K ? gemv_stream16(w[r] + k) : make_uint4(0u, 0u, 0u, 0u);
+                const int k = k0 + lane * 8 + it * 256;
+                wv[r][it] = k < K ? gemv_stream16(w[r] + k) : make_uint4(0u, 0u, 0u, 0u);
             }
     }
+    // after ask(K, lane, 0): the dots with the T rows of x in shared memory; every lane ends up with the full sums
     template <int T>
     __device__ __forceinline__ void dots(const __nv_bfloat16* __restrict__ s_x, int K, int lane, float (&acc)[NR][T]) {
 #pragma unroll
@@ -57,14 +58,7 @@ struct GemvRows {
 #pragma unroll
             for (int t = 0; t < T; ++t) acc[r][t] = 0.f;
         for (int k0 = 0; k0 < K; k0 += GEMV_KI * 256) {
-            uint4 wv[NR][GEMV_KI];
-#pragma unroll
-            for (int r = 0; r < NR; ++r)
-#pragma unroll
-                for (int it = 0; it < GEMV_KI; ++it) {
-                    const int k = k0 + lane * 8 + it * 256;
-                    wv[r][it] = k0 == 0 ? first[r][it] : (k < K ? gemv_stream16(w[r] + k) : make_uint4(0u, 0u, 0u, 0u));
-                }
+            if (k0 != 0) ask(K, lane, k0);                                // the first trip was started by the caller
 #pragma unroll
             for (int it = 0; it < GEMV_KI; ++it) {
                 const int k = k0 + lane * 8 + it * 256;
@@ -109,7 +103,7 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     const int n = blockIdx.x * GEMV_WARPS + warp;
     GemvRows<1> rows;
     rows.w[0] = w + (size_t)min(n, N - 1) * K;
-    rows.ask(K, lane);
+    rows.ask(K, lane, 0);
     gemv_stage_x<T>(x, s_gemv_x, K);
     float acc[1][T];
     rows.template dots<T>(s_gemv_x, K, lane, acc);
@@ -158,7 +152,7 @@ qkv_gemv_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     GemvRows<2> rows;
     rows.w[0] = w + ((size_t)h * hd + i) * K;
     rows.w[1] = w + ((size_t)h * hd + half + i) * K;
-    rows.ask(K, lane);
+    rows.ask(K, lane, 0);
     gemv_stage_x<T>(x, s_gemv_x, K);
     float acc[2][T];
     rows.template dots<T>(s_gemv_x, K, lane, acc);

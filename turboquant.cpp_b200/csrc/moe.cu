@@ -912,12 +912,14 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
     const int vec_w = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
     const int abytes = act_dtype == TQ_F32 ? 4 : 2;
     const int vec_x = ((size_t)H * abytes) % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)x_rows % 16) == 0;
-    // one to four tokens in bfloat16: the single-block form (TQ_ROUTER_NO_TINY=1: the others after all)
+    // one token in bfloat16: the single-block form (TQ_ROUTER_NO_TINY=1: the others after all).  The kernel takes up
+    // to four tokens, but inside a decode step it only wins with one (measured on B200, tokens/s of the step with
+    // this form / with the cluster: 538 / 518 at batch 1, 942 / 940 at batch 2, 1,380 / 1,455 at batch 4).
     {
         const char* tiny_env = getenv("TQ_ROUTER_NO_TINY");
         const bool no_tiny = tiny_env && tiny_env[0] && tiny_env[0] != '0';
         const size_t smem_tiny = (size_t)T_ * H * 2 + (size_t)T_ * (E + 1) * 4;
-        if (!no_tiny && T_ <= TINY_MAX_T && T_ * k <= TINY_MAX_PAIRS && T_ <= tile_rows && act_dtype == TQ_BF16 && w_dtype == TQ_BF16 &&
+        if (!no_tiny && (T_ == 1 || (tiny_env && tiny_env[0] == '0' && T_ <= TINY_MAX_T)) && T_ * k <= TINY_MAX_PAIRS && T_ <= tile_rows && act_dtype == TQ_BF16 && w_dtype == TQ_BF16 &&
             H % 8 == 0 && vec_w && vec_x && E <= 32 * SELECT_REGS && smem_tiny <= 40 * 1024) {
 #define TINY_CASE(TT) case TT: tq_launch(1, TINY_THREADS, smem_tiny, stream)(router_tiny_kernel<TT>, (const __nv_bfloat16*)x, \
             (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, ids, wts, shared_scale, H, E, k, renorm, counts, sorted_pair,  \
