@@ -118,7 +118,7 @@ def test_packing_layout():
     assert torch.equal(pp.data.view(2, 3, 2, 128, 64)[1, 2, 1, 3, :8], w[1, 259, 64:72])
 
 
-@pytest.mark.parametrize("R,N,K,bn,pair", [(1, 2048, 5632, 16, False), (8, 300, 1408, 16, False), (64, 3584, 2048, 128, True),
+@pytest.mark.parametrize("R,N,K,bn,pair", [(1, 2048, 5632, 16, False), (8, 300, 1408, 16, False), (64, 3584, 2048, 64, False),
                                            (40, 256, 4096, 64, False)])
 def test_k_shared_out_over_the_gpu(R, N, K, bn, pair):
     """A product with few tiles and a long K, its K cut into shares that write partial sums to slices of their own:
@@ -147,6 +147,8 @@ def test_k_shared_out_over_the_gpu(R, N, K, bn, pair):
         assert torch.equal(out, again)
     assert KT.k_splits_for(8, 2048, 5632, 16) > 4 and KT.k_splits_for(2048, 2048, 5632, 256) == 1
     assert KT.k_splits_for(8, 2048, 512, 16) == 1                       # a short K is not cut
+    with pytest.raises(KT.KernelError, match="single CTAs"):             # wide token tiles (pairs of CTAs) are never shared out
+        KT.gemm_tc(dev(a, torch.bfloat16), pw, torch.empty((2, R, N), dtype=torch.float32, device=DEV), None, 128, True, k_splits=2)
     with pytest.raises(KT.KernelError):                                  # the SwiGLU epilogue needs the whole sum
         KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w[:, :N // 2 * 2], torch.bfloat16), True),
                    torch.empty((2, R, N // 2), dtype=torch.float32, device=DEV), None, bn, pair, k_splits=2)

@@ -334,16 +334,15 @@ __device__ __noinline__ void split_merge_by_last(const float* __restrict__ parti
         const int h = idx / HD, d = idx % HD;
         const float* p = rows + (size_t)h * n_splits * (HD + 2);
         float M = -INFINITY;
-#pragma unroll 8
         for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(p + (size_t)sp * (HD + 2)));
         float L = 0.f, a = 0.f;
-#pragma unroll 8
-        for (int sp = 0; sp < n_splits; ++sp) {           // unrolled: the ranges' loads are in flight together
+        for (int sp = 0; sp < n_splits; ++sp) {
             const float ms = __ldcg(p + (size_t)sp * (HD + 2));
-            const float ls = __ldcg(p + (size_t)sp * (HD + 2) + 1), as = __ldcg(p + (size_t)sp * (HD + 2) + 2 + d);
-            const float f = ms != -INFINITY ? expf(ms - M) : 0.f;     // an empty range: l = 0 and sums of 0
-            L += ls * f;
-            a += as * f;
+            if (ms != -INFINITY) {
+                const float f = expf(ms - M);
+                L += __ldcg(p + (size_t)sp * (HD + 2) + 1) * f;
+                a += __ldcg(p + (size_t)sp * (HD + 2) + 2 + d) * f;
+            }
         }
         out_rows[(size_t)h * HD + d] = tq_from_float<TA>(a / L);
     }

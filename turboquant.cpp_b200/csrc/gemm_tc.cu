@@ -264,7 +264,9 @@ __device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int n_mx, int bn
     return t;
 }
 
-template <int BN, bool SWIGLU, typename TO, bool PAIR>
+// KSPLIT: the instantiation whose units of work are shares of a tile's K (see k_splits below); the others walk whole
+// tiles and carry none of that arithmetic in their loops.
+template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT>
 __global__ void __launch_bounds__((Tile<BN, PAIR>::THREADS), (Tile<BN, PAIR>::CTAS_PER_SM))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
@@ -288,11 +290,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // k_splits > 1: a tile's k-blocks are shared out over that many units of work, each writing its partial sums to
     // a slice of its own of `out` ([k_splits][R][N]; the caller adds the slices up in order).  For products with few
     // tiles and a long K (a down projection of a few tokens), which would otherwise keep a few SMs busy for long.
-    const int units = total * k_splits;
+    const int units = KSPLIT ? total * k_splits : total;
     if (worker >= units) return;                                         // both CTAs of a pair leave together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
-    const int kb_per = (num_kb + k_splits - 1) / k_splits;              // the host made sure every share holds a block
+    const int kb_per = KSPLIT ? (num_kb + k_splits - 1) / k_splits : num_kb;   // the host made sure every share holds a block
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
     constexpr int SA = T::A_SLOTS, SB = T::B_SLOTS;
@@ -346,7 +348,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t phase = 0;      // parity of the slot's current use
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers) {
-                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -380,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t freed_phase = 0;   // ... and the parity of that block's use of it
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers) {
-                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 const int n_mma = (t.count + 15) & ~15;                                   // N of the products
                 const int rows = PAIR ? n_mma / 2 : t.count;                              // token rows this CTA loads ...
@@ -423,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers, ++it) {
-                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
                 const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 // N of the products: this tile's rows; pairs: M = 256, 128 weight rows from each CTA
                 const uint32_t idesc = umma_idesc((t.count + 15) & ~15) + (PAIR ? ((uint32_t)(BM >> 4) << 24) : 0u);
@@ -465,11 +467,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int u = worker; u < units && ok; u += workers, ++it) {
-                const int id = u % total, kb0 = (u / total) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
             const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
             const int b = it & 1;
             const int n = (PAIR ? 2 * t.mx + (int)rank : t.mx) * COLS + r;           // output column
-            TO* out_u = out + (size_t)(u / total) * R * N;                           // this share's slice (kb0, kb1 unused here)
+            TO* out_u = KSPLIT ? out + (size_t)(u / total) * R * N : out;            // this share's slice (kb0, kb1 unused here)
             (void)kb0; (void)kb1;
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
@@ -570,12 +572,12 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
     return 0;
 }
 
-template <int BN, bool SWIGLU, typename TO, bool PAIR>
+template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
            const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, int sm_share_pct,
            int k_splits, cudaStream_t stream) {
     using T = Tile<BN, PAIR>;
-    auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR>;
+    auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR, KSPLIT>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
@@ -668,6 +670,12 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
         }                                                                                            \
         if (out_dtype == TQ_BF16) return launch<BN_, false, __nv_bfloat16, PAIR_>(TC_ARGS);           \
         return launch<BN_, false, float, PAIR_>(TC_ARGS);                                             \
+    }
+    if (k_splits > 1) {          // plain, float32 partial sums (checked above); narrow token tiles on single CTAs
+        TQ_REQUIRE(!pair && bn <= 64, "gemm_tc: K is shared out for token tiles of 16, 32 or 64 rows on single CTAs, not %d%s", bn, pair ? " on pairs" : "");
+        if (bn == 16) return launch<16, false, float, false, true>(TC_ARGS);
+        if (bn == 32) return launch<32, false, float, false, true>(TC_ARGS);
+        return launch<64, false, float, false, true>(TC_ARGS);
     }
     TC_CASE(16, false) TC_CASE(32, false) TC_CASE(64, false) TC_CASE(128, false) TC_CASE(256, false)
     TC_CASE(128, true) TC_CASE(256, true)

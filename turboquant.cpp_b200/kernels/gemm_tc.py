@@ -112,7 +112,7 @@ def k_splits_for(rows: int, n: int, k: int, token_tile: int, resident: int = 296
     or where the partial sums (rows x n floats per share) would weigh against the weights they save time on."""
     tiles = -(-n // BLOCK_ROWS) * -(-rows // max(1, token_tile))
     num_kb = -(-k // BLOCK_K)
-    if tiles * 2 > resident or num_kb < 16:
+    if tiles * 2 > resident or num_kb < 16 or token_tile > 64:       # the kernel shares K out for narrow token tiles only
         return 1
     want = min(resident // tiles, num_kb // 8, 32)
     while want > 1 and want * rows * n * 4 * 2 > n * k * 2 // 2:        # partial sums written and read vs. weight bytes
