@@ -32,6 +32,7 @@ def KA_resident(device) -> int:
 
 class MoEFeedForward(FeedForward):
     ROUTER_TC_MIN_TOKENS = 256     # steps with at least this many tokens compute router logits on tensor cores
+    SHARED_AFTER_ROUTER = {"": None, "0": False}.get(os.environ.get("TQ_SHARED_AFTER_ROUTER", ""), True)   # None: by the step's size
     SHARED_SM_SHARE = int(os.environ.get("TQ_SHARED_SM_SHARE", "0"))      # per cent of the SMs for the shared expert in long steps
 
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
@@ -135,9 +136,9 @@ class MoEFeedForward(FeedForward):
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
         act = ctx.act_dtype
-        # the shared expert does not depend on the routing: it starts first, on a second stream, and runs
-        # next to the router, the expert-sorted layout and the routed experts (its few CTAs would leave
-        # most of the GPU idle on their own, and the router's small kernels hide behind its weight stream)
+        # the shared expert does not depend on the routing: it runs on a second stream next to the routed experts
+        # (its few CTAs would leave most of the GPU idle on their own), and in most steps it starts first, so that
+        # the router's small kernels hide behind its weight stream
         y_shared = None
         side = None
         tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
@@ -148,7 +149,21 @@ class MoEFeedForward(FeedForward):
         if self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and isinstance(self.ws13, KT.PackedWeights):
             share_shared = self.SHARED_SM_SHARE
             share_routed = 100 - share_shared
-        if self.ws13 is not None:
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+        scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
+        layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
+        x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
+        small = KM.router_small_pays(T, k, self.n_experts, H)
+        # Decode steps whose pairs reach the number of experts (most experts are read: the routed products are several
+        # times the shared expert's): the router first, alone on the GPU, then the shared expert beside the routed
+        # ones with its down projection's K shared out.  With fewer pairs the shared expert starts first and the
+        # router runs beside it.  (Measured on B200, tokens/s with the router first / with the shared expert first:
+        # A2.7B sizes batch 8: 2,214 / 2,287, batch 16: 3,228 / 3,147; 57B-A14B sizes batch 1: 177 / 190, batch 8: 602 / 586.)
+        shared_after = small and (T * k >= self.n_experts if self.SHARED_AFTER_ROUTER is None else self.SHARED_AFTER_ROUTER)
+
+        def shared_expert():
+            nonlocal y_shared, side
             S = self.shared_intermediate
             stile = KT.token_tile_for(T, 1) if isinstance(self.ws13, KT.PackedWeights) else 0
             main = torch.cuda.current_stream()
@@ -164,7 +179,7 @@ class MoEFeedForward(FeedForward):
                 # Then its K is shared out over the GPU and the partial sums are added up where the experts'
                 # outputs are summed anyway (measured at the 57B-A14B sizes, batch 1: 144 -> 165 tokens/s; sharing
                 # it out at larger batches takes SMs from the routed experts and costs 3-10 %).
-                few = T * k * self.intermediate <= 2 * S
+                few = T * k * self.intermediate <= 2 * S or shared_after
                 splits = KT.k_splits_for(T, H, S, stile, 2 * KA_resident(dev)) if few and isinstance(self.ws2, KT.PackedWeights) else 1
                 y_shared = torch.empty((splits, T, H) if splits > 1 else (T, H), dtype=torch.float32, device=dev)
                 if splits > 1:
@@ -174,12 +189,10 @@ class MoEFeedForward(FeedForward):
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
-        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
-        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
-        scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
-        layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
-        x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
-        if KM.router_small_pays(T, k, self.n_experts, H):
+
+        if self.ws13 is not None and not shared_after:
+            shared_expert()
+        if small:
             # few tokens (decoding): router, layout and the sorted copies of the rows in one launch
             KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows)
         else:
@@ -193,6 +206,8 @@ class MoEFeedForward(FeedForward):
                 KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
             KM.moe_align(ids, layout)
             KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
+        if self.ws13 is not None and shared_after:
+            shared_expert()
         if ctx.debug is not None:
             # the tensors themselves: nothing below writes them, and inside a captured step a reference keeps their
             # memory from being reused, so that they hold every replay's choices
