@@ -152,3 +152,56 @@ def test_k_shared_out_over_the_gpu(R, N, K, bn, pair):
     with pytest.raises(KT.KernelError):                                  # the SwiGLU epilogue needs the whole sum
         KT.gemm_tc(dev(a, torch.bfloat16), KT.pack_weights(dev(w[:, :N // 2 * 2], torch.bfloat16), True),
                    torch.empty((2, R, N // 2), dtype=torch.float32, device=DEV), None, bn, pair, k_splits=2)
+
+
+@pytest.mark.parametrize("R,N,K,G,R2,N2,K2", [(300, 200, 136, 6, 130, 328, 136), (1100, 1408, 512, 8, 700, 1000, 256),
+                                               (40, 96, 72, 5, 513, 64, 2048), (600, 704, 256, 3, 1, 130, 64)])
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("second_first", [False, True])
+def test_two_products_in_one_launch(R, N, K, G, R2, N2, K2, swiglu, bn, second_first):
+    """The grouped product and a one-group product of other sizes walked by the same persistent CTAs: each output
+    has the bits of its own separate launch, and every element was written."""
+    from turboquant_cpp_b200.kernels import gemm_tc as KT, moe as KM
+    rng = np.random.default_rng(R + N2 + bn)
+    odtype = torch.bfloat16 if swiglu else torch.float32
+    a = dev(P.round_bf16(rng.normal(size=(R, K))), torch.bfloat16)
+    w = KT.pack_weights(dev(P.round_bf16(rng.normal(size=(G, 2 * N if swiglu else N, K)) / math.sqrt(K)), torch.bfloat16), swiglu)
+    a2 = dev(P.round_bf16(rng.normal(size=(R2, K2))), torch.bfloat16)
+    w2 = KT.pack_weights(dev(P.round_bf16(rng.normal(size=(1, 2 * N2 if swiglu else N2, K2)) / math.sqrt(K2)), torch.bfloat16), swiglu)
+    ids = np.sort(rng.integers(0, G, size=(R, 1)).astype(np.int32), axis=0)
+    if G > 2:
+        ids[ids == 1] = 2                                   # a group without rows
+    lay = KM.ExpertLayout(R, G, bn, DEV)
+    KM.moe_align(dev(ids, torch.int32), lay)
+    alone = torch.full((R, N), float("nan"), dtype=odtype, device=DEV)
+    alone2 = torch.full((R2, N2), float("nan"), dtype=odtype, device=DEV)
+    KT.gemm_tc(a, w, alone, lay, bn, True)
+    KT.gemm_tc(a2, w2, alone2, None, bn, True)
+    both = torch.full((R, N), float("nan"), dtype=odtype, device=DEV)
+    both2 = torch.full((R2, N2), float("nan"), dtype=odtype, device=DEV)
+    for _ in range(3):                                      # the same launch again: nothing left behind
+        KT.gemm_tc_dual(a, w, both, lay, a2, w2, both2, bn, second_first=second_first)
+    KT.check_status()
+    assert not torch.isnan(alone.float()).any() and not torch.isnan(alone2.float()).any()
+    assert torch.equal(both, alone) and torch.equal(both2, alone2)
+
+
+def test_two_products_refuse_what_they_cannot_do():
+    from turboquant_cpp_b200.kernels import gemm_tc as KT, moe as KM
+    from turboquant_cpp_b200.kernels._call import KernelError
+    a = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
+    w = KT.pack_weights(torch.zeros((2, 128, 64), dtype=torch.bfloat16, device=DEV), False)
+    ws = KT.pack_weights(torch.zeros((1, 256, 64), dtype=torch.bfloat16, device=DEV), True)
+    w1 = KT.pack_weights(torch.zeros((1, 128, 64), dtype=torch.bfloat16, device=DEV), False)
+    out = torch.zeros((64, 128), dtype=torch.float32, device=DEV)
+    lay = KM.ExpertLayout(64, 2, 64, DEV)
+    KM.moe_align(torch.zeros((64, 1), dtype=torch.int32, device=DEV), lay)
+    with pytest.raises(KernelError, match="128 or 256"):
+        KT.gemm_tc_dual(a, w, out, lay, a, w1, out.clone(), 64)
+    lay = KM.ExpertLayout(64, 2, 128, DEV)
+    KM.moe_align(torch.zeros((64, 1), dtype=torch.int32, device=DEV), lay)
+    with pytest.raises(KernelError, match="both plain"):
+        KT.gemm_tc_dual(a, w, out, lay, a, ws, out.clone(), 128)
+    with pytest.raises(KernelError, match="float32"):
+        KT.gemm_tc_dual(a, w, out.bfloat16(), lay, a, w1, out.bfloat16(), 128)

@@ -146,6 +146,36 @@ def test_float32_batch_of_16_unequal_prompts_then_64_tokens(folders):
     torch.cuda.empty_cache()
 
 
+def test_a_prompt_of_900_tokens_in_bfloat16_with_both_experts_products_in_one_launch(folders):
+    """At 900 tokens the routed experts' tiles are wide enough for pairs of CTAs and the shared expert's product has
+    few rounds of tiles: its tiles ride in the routed experts' launches (one launch for both gate/up products,
+    one for both down projections).  Whole, and in two pieces of 600 and 300 tokens (the second piece runs the
+    launches of their own), against the plain implementation."""
+    import torch
+    import turboquant_cpp_b200 as tq
+    from turboquant_cpp_b200.kernels import gemm_tc as KT
+    folder, plain = folders("A")
+    V = WIDTHS["A"]["vocab_size"]
+    eng = tq.Engine(tq.load_model(folder, "bfloat16", "cuda:0"), max_tokens=1024, record_routing=True)
+    toks = np.random.default_rng(77).integers(0, V, size=900).tolist()
+    keep = sampled(len(toks), 31, 4)
+    before = KT.DUAL_CALLS
+    logits, routing = run_schedule(eng, *whole("r", toks, keep))
+    assert KT.DUAL_CALLS == before + 2 * WIDTHS["A"]["num_hidden_layers"], "the step did not take the two-product launches"
+    report = {}
+    check_against_plain(plain, toks, logits["r"], routing["r"], "bfloat16", "A 900 whole", report)
+    steps = [[("r", toks[:600], sorted(p for p in keep if p < 600))],
+             [("r", toks[600:], sorted(p - 600 for p in keep if p >= 600))]]
+    pieces, routing = run_schedule(eng, steps, {1: ["r"]})
+    check_against_plain(plain, toks, pieces["r"], routing["r"], "bfloat16", "A 900 in pieces", report)
+    eng.check_kernels()
+    print(f"\n[A bfloat16, 900 tokens] worst logit error {report['worst']:.2e} of scale; smallest router margin "
+          f"{report['margin']:.2e}; flips {report['flips']}")
+    eng.release()
+    del eng
+    torch.cuda.empty_cache()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_three_schedules_at_the_widths_of_57b_a14b(folders, dtype):
     three_schedules(folders, "B", dtype)

@@ -35,6 +35,7 @@
 // role leaves its loop, copies in flight are waited for (bounded again), tensor memory is freed and
 // the kernel returns with *status != 0; nothing spins forever.
 #include <cuda.h>
+#include <type_traits>
 #include "common.cuh"
 
 TQ_DEFINE_LAST_ERROR
@@ -264,17 +265,50 @@ __device__ __forceinline__ TileInfo tile_info(int id, int n_ty, int n_mx, int bn
     return t;
 }
 
+// A second product in the same launch: one group, token tiles of BN consecutive rows, its own operands, output and
+// sizes.  The persistent CTAs walk the tiles of both products in one interleaved sequence, so that a product bound by
+// the tensor cores (a prompt's shared expert: every weight block is reused by all token tiles out of the L2) runs
+// on some SMs while a product bound by its weight stream (the prompt's routed experts: every block read once from
+// DRAM) runs on the others, and each SM alternates between the two; as two launches one would wait for the other,
+// since either fills the GPU with one CTA per SM.
+struct NoSecond {};
+struct Second {
+    CUtensorMap map_w, map_x, map_x_tail;
+    void* out;
+    int R, N, K;
+    int first;          // 0: the second product's tiles are spread evenly among the first's; 1: they all come first
+};
+
+// Which product and which of its tiles the u-th unit of work is: the second product's total2 tiles are spread evenly
+// over the total1 + total2 units (unit u is its c-th tile iff the count c = floor(u * total2 / all) grows at u + 1).
+struct Unit { int second, id; };
+__device__ __forceinline__ Unit unit_of(int u, int total1, int total2, int second_first) {
+    Unit w;
+    if (second_first) {
+        w.second = u < total2 ? 1 : 0;
+        w.id = w.second ? u : u - total2;
+        return w;
+    }
+    const long long all = (long long)total1 + total2;
+    const int c = (int)((long long)u * total2 / all), c_next = (int)((long long)(u + 1) * total2 / all);
+    w.second = c_next > c ? 1 : 0;
+    w.id = w.second ? c : u - c;
+    return w;
+}
+
 // KSPLIT: the instantiation whose units of work are shares of a tile's K (see k_splits below); the others walk whole
-// tiles and carry none of that arithmetic in their loops.
-template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT>
+// tiles and carry none of that arithmetic in their loops.  SECOND = Second: the instantiation that walks two products.
+template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT, typename SECOND>
 __global__ void __launch_bounds__((Tile<BN, PAIR>::THREADS), (Tile<BN, PAIR>::CTAS_PER_SM))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
-               int stream_weights, int* __restrict__ status, int k_splits) {
+               int stream_weights, int* __restrict__ status, int k_splits, const __grid_constant__ SECOND second) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     using T = Tile<BN, PAIR>;
+    constexpr bool DUAL = !std::is_same<SECOND, NoSecond>::value;
+    static_assert(!(DUAL && KSPLIT), "a launch either walks two products or shares K out");
     constexpr int COLS = SWIGLU ? BM / 2 : BM;         // output columns of a weight-row tile
     extern __shared__ uint8_t smem_raw[];
     __shared__ int s_abort;
@@ -290,7 +324,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // k_splits > 1: a tile's k-blocks are shared out over that many units of work, each writing its partial sums to
     // a slice of its own of `out` ([k_splits][R][N]; the caller adds the slices up in order).  For products with few
     // tiles and a long K (a down projection of a few tokens), which would otherwise keep a few SMs busy for long.
-    const int units = KSPLIT ? total * k_splits : total;
+    // the second product's sizes (DUAL only; the rest of the code reads them through `if constexpr`)
+    int R2 = 0, N2 = 0, n_ty2 = 0, n_m1_2 = 0, n_mx2 = 0, total2 = 0, num_kb2 = 0, second_first = 0;
+    if constexpr (DUAL) {
+        R2 = second.R; N2 = second.N; second_first = second.first;
+        n_ty2 = (R2 + BN - 1) / BN;
+        n_m1_2 = (N2 + COLS - 1) / COLS;
+        n_mx2 = PAIR ? (n_m1_2 + 1) / 2 : n_m1_2;
+        total2 = n_ty2 * n_mx2;
+        num_kb2 = (second.K + BK - 1) / BK;
+    }
+    const int units = KSPLIT ? total * k_splits : (DUAL ? total + total2 : total);
     if (worker >= units) return;                                         // both CTAs of a pair leave together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
@@ -344,23 +388,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // weights that only one token tile reads (a decode step, a short prompt) are streamed: first to leave
             // the L2; weights that several token tiles share stay
             const uint64_t policy = stream_weights ? policy_evict_first() : policy_evict_last();
+            const uint64_t keep = policy_evict_last();
+            (void)keep;
             int slot = 0, issued = 0;
             uint32_t phase = 0;      // parity of the slot's current use
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers) {
-                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
-                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
-                const int wt = t.expert * n_m1 + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
+                int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
+                bool is2 = false;                  // a tile of the second product
+                if constexpr (DUAL) {
+                    const Unit w = unit_of(u, total, total2, second_first);
+                    is2 = w.second != 0;
+                    id = w.id;
+                    if (is2) kb1 = num_kb2;
+                }
+                const TileInfo t = is2 ? tile_info(id, n_ty2, n_mx2, BN, nullptr, nullptr, nullptr, R2)
+                                       : tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                const int wt = t.expert * (is2 ? n_m1_2 : n_m1) + (PAIR ? 2 * t.mx + (int)rank : t.mx);    // packed weight tile
+                const CUtensorMap* mw = &map_w;
+                uint64_t pol = policy;
+                if constexpr (DUAL) if (is2) { mw = &second.map_w; pol = n_ty2 > 1 ? keep : policy_evict_first(); }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     // the slot is free once the products of the block SA before this one are done
                     if (!mbar_wait(done_bar(slot), phase ^ 1u, &s_abort)) { ok = false; break; }
                     if (PAIR) {
                         // the first CTA expects the bytes of both (the halves are equal); the second only loads
                         if (rank == 0) mbar_expect_tx(full_bar(slot), 2u * T::A_BYTES);
-                        tma_load_block_pair(a_tile(slot), &map_w, kb, wt, rank == 0 ? full_bar(slot) : map_to_cta(full_bar(slot), 0), policy);
+                        tma_load_block_pair(a_tile(slot), mw, kb, wt, rank == 0 ? full_bar(slot) : map_to_cta(full_bar(slot), 0), pol);
                     } else {
                         mbar_expect_tx(full_bar(slot), (uint32_t)T::A_BYTES);
-                        tma_load_block(a_tile(slot), &map_w, kb, wt, full_bar(slot), policy);
+                        tma_load_block(a_tile(slot), mw, kb, wt, full_bar(slot), pol);
                     }
                     ++issued;
                     if (++slot == SA) { slot = 0; phase ^= 1u; }
@@ -382,14 +439,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t freed_phase = 0;   // ... and the parity of that block's use of it
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers) {
-                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
-                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
+                bool is2 = false;                  // a tile of the second product
+                if constexpr (DUAL) {
+                    const Unit w = unit_of(u, total, total2, second_first);
+                    is2 = w.second != 0;
+                    id = w.id;
+                    if (is2) kb1 = num_kb2;
+                }
+                const TileInfo t = is2 ? tile_info(id, n_ty2, n_mx2, BN, nullptr, nullptr, nullptr, R2)
+                                       : tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 const int n_mma = (t.count + 15) & ~15;                                   // N of the products
                 const int rows = PAIR ? n_mma / 2 : t.count;                              // token rows this CTA loads ...
                 const int row0 = t.row0 + (PAIR ? (int)rank * (n_mma / 2) : 0);           // ... from here
                 const int boxes = rows / T::BOX_ROWS;
                 const int tails = (rows - boxes * T::BOX_ROWS + T::TAIL_ROWS - 1) / T::TAIL_ROWS;
                 const uint32_t bytes = (uint32_t)(boxes * T::BOX_BYTES + tails * T::TAIL_BYTES);
+                const CUtensorMap* mx = &map_x;
+                const CUtensorMap* mxt = &map_x_tail;
+                if constexpr (DUAL) if (is2) { mx = &second.map_x; mxt = &second.map_x_tail; }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (issued >= SB) {
                         if (!mbar_wait(done_bar(freed), freed_phase, &s_abort)) { ok = false; break; }
@@ -400,16 +468,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const uint32_t bar = rank == 0 ? full_bar(fb) : map_to_cta(full_bar(fb), 0);
                         if (rank == 0) mbar_expect_tx(full_bar(fb), 2u * bytes);
                         for (int bx = 0; bx < boxes; ++bx)
-                            tma_load_2d_pair(dst + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, bar, policy);
+                            tma_load_2d_pair(dst + bx * T::BOX_BYTES, mx, kb * BK, row0 + bx * T::BOX_ROWS, bar, policy);
                         for (int bx = 0; bx < tails; ++bx)
-                            tma_load_2d_pair(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                            tma_load_2d_pair(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, mxt, kb * BK,
                                              row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, bar, policy);
                     } else {
                         mbar_expect_tx(full_bar(fb), bytes);
                         for (int bx = 0; bx < boxes; ++bx)
-                            tma_load_2d(dst + bx * T::BOX_BYTES, &map_x, kb * BK, row0 + bx * T::BOX_ROWS, full_bar(fb), policy);
+                            tma_load_2d(dst + bx * T::BOX_BYTES, mx, kb * BK, row0 + bx * T::BOX_ROWS, full_bar(fb), policy);
                         for (int bx = 0; bx < tails; ++bx)
-                            tma_load_2d(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, &map_x_tail, kb * BK,
+                            tma_load_2d(dst + boxes * T::BOX_BYTES + bx * T::TAIL_BYTES, mxt, kb * BK,
                                         row0 + boxes * T::BOX_ROWS + bx * T::TAIL_ROWS, full_bar(fb), policy);
                     }
                     ++issued;
@@ -425,8 +493,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             for (int u = worker; u < units && ok; u += workers, ++it) {
-                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
-                const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+                int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
+                bool is2 = false;                  // a tile of the second product
+                if constexpr (DUAL) {
+                    const Unit w = unit_of(u, total, total2, second_first);
+                    is2 = w.second != 0;
+                    id = w.id;
+                    if (is2) kb1 = num_kb2;
+                }
+                const TileInfo t = is2 ? tile_info(id, n_ty2, n_mx2, BN, nullptr, nullptr, nullptr, R2)
+                                       : tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
                 // N of the products: this tile's rows; pairs: M = 256, 128 weight rows from each CTA
                 const uint32_t idesc = umma_idesc((t.count + 15) & ~15) + (PAIR ? ((uint32_t)(BM >> 4) << 24) : 0u);
                 const int b = it & 1;
@@ -467,11 +543,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int u = worker; u < units && ok; u += workers, ++it) {
-                const int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
-            const TileInfo t = tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
+            int id = KSPLIT ? u % total : u, kb0 = KSPLIT ? (u / total) * kb_per : 0, kb1 = KSPLIT ? min(num_kb, kb0 + kb_per) : num_kb;
+            bool is2 = false;                  // a tile of the second product
+            if constexpr (DUAL) {
+                const Unit w = unit_of(u, total, total2, second_first);
+                is2 = w.second != 0;
+                id = w.id;
+                if (is2) kb1 = num_kb2;
+            }
+            const TileInfo t = is2 ? tile_info(id, n_ty2, n_mx2, BN, nullptr, nullptr, nullptr, R2)
+                                   : tile_info(id, n_ty, n_mx, BN, tile_expert, tile_row0, tile_count, R);
             const int b = it & 1;
             const int n = (PAIR ? 2 * t.mx + (int)rank : t.mx) * COLS + r;           // output column
             TO* out_u = KSPLIT ? out + (size_t)(u / total) * R * N : out;            // this share's slice (kb0, kb1 unused here)
+            int Nn = N;                                                              // width of this product's output
+            if constexpr (DUAL) if (is2) { out_u = (TO*)second.out; Nn = N2; }
             (void)kb0; (void)kb1;
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
@@ -495,12 +581,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const float gate = __uint_as_float(high ? got : g[j]);
                         const float up = __uint_as_float(high ? g[8 + j] : got);
                         const int c = c0 + j + (high ? 8 : 0);
-                        if (n < N && c < t.count) out_u[(size_t)(t.row0 + c) * N + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
+                        if (n < Nn && c < t.count) out_u[(size_t)(t.row0 + c) * Nn + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
                     }
-                } else if (n < N) {
+                } else if (n < Nn) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c0 + j < t.count) out_u[(size_t)(t.row0 + c0 + j) * N + n] = tq_from_float<TO>(__uint_as_float(g[j]));
+                        if (c0 + j < t.count) out_u[(size_t)(t.row0 + c0 + j) * Nn + n] = tq_from_float<TO>(__uint_as_float(g[j]));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -572,12 +658,12 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
     return 0;
 }
 
-template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT = false>
+template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT = false, typename SECOND = NoSecond>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
            const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, int sm_share_pct,
-           int k_splits, cudaStream_t stream) {
+           int k_splits, cudaStream_t stream, const SECOND& second = SECOND(), long long tiles2 = 0) {
     using T = Tile<BN, PAIR>;
-    auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR, KSPLIT>;
+    auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR, KSPLIT, SECOND>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
@@ -604,7 +690,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     }
     constexpr int COLS = SWIGLU ? BM / 2 : BM;
     const long long n_m1 = (N + COLS - 1) / COLS;
-    const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y * k_splits;      // units of work
+    const long long tiles = (PAIR ? (n_m1 + 1) / 2 : n_m1) * grid_y * k_splits + tiles2;      // units of work
     const long long want = PAIR ? 2 * tiles : tiles;
     // sm_share_pct in 1..99: this launch takes only that share of the CTAs the GPU runs at once, so that another
     // launch on another stream runs beside it instead of behind it (a compute-bound product beside a memory-bound one)
@@ -617,7 +703,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     const int grid = (int)(want < room ? want : room);
     tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K,
         /* stream_weights: on average at most one token tile per group */ (te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0, status,
-        k_splits);
+        k_splits, second);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -682,4 +768,48 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
 #undef TC_CASE
 #undef TC_ARGS
     TQ_FAIL(-2, "gemm_tc: unreachable");
+}
+
+// Two products in one launch: the first as tq_gemm_tc computes it over the layout's groups (X, W, out, tile_*; G
+// groups), the second over one group with token tiles of `bn` consecutive rows (X2 [R2, K2], W2 packed for N2 x K2,
+// out2 [R2, N2]).  Both are plain or both SwiGLU, with the same output type; SwiGLU writes bf16 and a plain product
+// float32 (the experts' two steps); CTA pairs with token tiles of 128 or 256 rows.  second_first: 0 = the second
+// product's tiles are spread evenly among the first's, 1 = they come first.
+TQ_EXPORT int tq_gemm_tc_dual(const void* X, const void* W, void* out, const int* tile_expert, const int* tile_row0,
+                              const int* tile_count, const int* n_tiles, int max_tiles, int R, int N, int K, int G,
+                              const void* X2, const void* W2, void* out2, int R2, int N2, int K2, int out_dtype,
+                              int bn, int swiglu, int* status, int second_first, cudaStream_t stream) {
+    TQ_REQUIRE(tile_expert && tile_row0 && tile_count && n_tiles, "gemm_tc_dual: the first product needs a layout");
+    TQ_REQUIRE(R > 0 && N > 0 && K > 0 && G > 0 && R2 > 0 && N2 > 0 && K2 > 0, "gemm_tc_dual: bad sizes R=%d N=%d K=%d G=%d, R2=%d N2=%d K2=%d", R, N, K, G, R2, N2, K2);
+    TQ_REQUIRE(K % 8 == 0 && K2 % 8 == 0, "gemm_tc_dual: K=%d and K2=%d must be multiples of 8 (16-byte rows for TMA)", K, K2);
+    TQ_REQUIRE(((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)X2 % 16) == 0 && ((uintptr_t)W2 % 16) == 0,
+               "gemm_tc_dual: operands must be 16-byte aligned");
+    TQ_REQUIRE(bn == 128 || bn == 256, "gemm_tc_dual: token tiles of 128 or 256 rows (pairs of CTAs), not %d", bn);
+    TQ_REQUIRE((swiglu && out_dtype == TQ_BF16) || (!swiglu && out_dtype == TQ_F32),
+               "gemm_tc_dual: SwiGLU products write bfloat16 and plain products float32 (got swiglu=%d, type %d)", swiglu, out_dtype);
+    TQ_REQUIRE(status != nullptr, "gemm_tc_dual: a status word is required");
+    if (max_tiles == 0) return tq_gemm_tc(X2, W2, out2, out_dtype, nullptr, nullptr, nullptr, nullptr, 0, bn, R2, N2, K2, 1, swiglu, 1, status, 0, 1, stream);
+    const int cols = swiglu ? BM / 2 : BM;
+    const int n_m1 = (N + cols - 1) / cols, n_m1_2 = (N2 + cols - 1) / cols;
+    CUtensorMap mw, mx, mxt;
+    Second sec;
+    int rc = make_map_w(&mw, W, (uint64_t)((K + BK - 1) / BK), (uint64_t)G * n_m1);
+    if (rc) return rc;
+    if ((rc = make_map_x(&mx, X, (uint64_t)K, (uint64_t)R, 64u))) return rc;
+    if ((rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u))) return rc;
+    if ((rc = make_map_w(&sec.map_w, W2, (uint64_t)((K2 + BK - 1) / BK), (uint64_t)n_m1_2))) return rc;
+    if ((rc = make_map_x(&sec.map_x, X2, (uint64_t)K2, (uint64_t)R2, 64u))) return rc;
+    if ((rc = make_map_x(&sec.map_x_tail, X2, (uint64_t)K2, (uint64_t)R2, 16u))) return rc;
+    sec.out = out2; sec.R = R2; sec.N = N2; sec.K = K2; sec.first = second_first ? 1 : 0;
+    const long long tiles2 = (long long)((n_m1_2 + 1) / 2) * ((R2 + bn - 1) / bn);
+#define TC_DUAL(BN_)                                                                                                       \
+    if (bn == BN_) {                                                                                                       \
+        if (swiglu) return launch<BN_, true, __nv_bfloat16, true, false, Second>(mw, mx, mxt, out, tile_expert, tile_row0, \
+            tile_count, n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2);                                \
+        return launch<BN_, false, float, true, false, Second>(mw, mx, mxt, out, tile_expert, tile_row0, tile_count,        \
+            n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2);                                            \
+    }
+    TC_DUAL(128) TC_DUAL(256)
+#undef TC_DUAL
+    TQ_FAIL(-2, "gemm_tc_dual: unreachable");
 }

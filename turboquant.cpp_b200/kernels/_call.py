@@ -33,7 +33,15 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[ctypes.c_void_p]:
     return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream() -> ctypes.c_void_p:
+    """The current stream of the current device as the launchers take it.  Every launch asks, so this goes to
+    torch's C entry points where this build of torch has them (a tenth of the cost of building a Stream object)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -160,3 +160,35 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
         ptr(status if status is not None else status_word(x.device)), c_int(int(sm_share)), c_int(int(k_splits)), stream()))
     return out
+
+
+DUAL_CALLS = 0       # launches of two products so far (tests read it)
+
+
+def gemm_tc_dual(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: ExpertLayout,
+                 x2: torch.Tensor, w2: PackedWeights, out2: torch.Tensor, token_tile: int,
+                 status: Optional[torch.Tensor] = None, second_first: bool = False) -> None:
+    """Two products in one launch on pairs of CTAs: out = x . w over the layout's groups (as gemm_tc), and
+    out2 = x2 . w2 over one group with token tiles of `token_tile` (128 or 256) consecutive rows.  Both SwiGLU (bf16
+    results) or both plain (float32 results).  The persistent CTAs walk both products' tiles in one sequence, the
+    second product's spread evenly among the first's (or first, with second_first): a product bound by the tensor
+    cores beside one bound by its weight stream, where two launches would run one after the other.  The results
+    are those of two separate launches with the same token tile, bit for bit."""
+    if not (usable(x, w) and usable(x2, w2)):
+        raise KernelError("gemm_tc_dual: needs bfloat16 activations with K a multiple of 8 and weights packed for this K")
+    if w.swiglu != w2.swiglu or out.dtype != out2.dtype:
+        raise KernelError("gemm_tc_dual: both products are SwiGLU or both plain, with one output type")
+    if out.shape != (x.shape[0], w.n) or out2.shape != (x2.shape[0], w2.n) or w2.groups != 1:
+        raise KernelError(f"gemm_tc_dual: outputs {tuple(out.shape)}, {tuple(out2.shape)} do not fit {x.shape[0]} x {w.n} "
+                          f"and {x2.shape[0]} x {w2.n} (one group)")
+    if layout.tile_rows != token_tile:
+        raise KernelError(f"gemm_tc_dual: the layout has tiles of {layout.tile_rows} rows, the kernel was asked for {token_tile}")
+    global DUAL_CALLS
+    DUAL_CALLS += 1
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_gemm_tc_dual(
+        ptr(x), ptr(w.data), ptr(out), ptr(layout.tile_expert), ptr(layout.tile_row0), ptr(layout.tile_count),
+        ptr(layout.n_tiles), c_int(layout.max_tiles), c_int(x.shape[0]), c_int(w.n), c_int(w.k), c_int(w.groups),
+        ptr(x2), ptr(w2.data), ptr(out2), c_int(x2.shape[0]), c_int(w2.n), c_int(w2.k), c_int(code(out.dtype)),
+        c_int(token_tile), c_int(1 if w.swiglu else 0),
+        ptr(status if status is not None else status_word(x.device)), c_int(1 if second_first else 0), stream()))

@@ -36,6 +36,11 @@ class MoEFeedForward(FeedForward):
     ROUTER_TC_MIN_TOKENS = int(os.environ.get("TQ_ROUTER_TC_MIN", "64"))
     SHARED_AFTER_ROUTER = {"": None, "0": False}.get(os.environ.get("TQ_SHARED_AFTER_ROUTER", ""), True)   # None: by the step's size
     SHARED_SM_SHARE = int(os.environ.get("TQ_SHARED_SM_SHARE", "0"))      # per cent of the SMs for the shared expert in long steps
+    # long steps: the shared expert's products in the launches of the routed experts' ("": by the step's size,
+    # "0": never, "1": always, "spread": always, with the shared expert's tiles spread among the routed ones instead
+    # of ahead of them)
+    SHARED_IN_ROUTED_LAUNCH = os.environ.get("TQ_SHARED_DUAL", "")
+    SHARED_DOWN_SPLIT_RATIO = float(os.environ.get("TQ_SHARED_DOWN_SPLIT_RATIO", "14"))
 
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
                  norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True):
@@ -151,6 +156,24 @@ class MoEFeedForward(FeedForward):
         if self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and isinstance(self.ws13, KT.PackedWeights):
             share_shared = self.SHARED_SM_SHARE
             share_routed = 100 - share_shared
+        # Steps of some hundred to about 1,500 tokens: the shared expert's two products ride in the routed experts'
+        # launches, their tiles ahead of the routed ones.  Either product alone fills the GPU with one persistent CTA
+        # per SM, so as launches of their own they run one after the other, and at these sizes each has only two to
+        # four rounds of tiles per CTA: its last round leaves SMs idle, which the other product's tiles fill when
+        # the same CTAs walk both.  (Measured on B200 at the A2.7B sizes, ms per prompt apart / together: 768 tokens
+        # 7.88 / 7.40, 1,024: 9.29 / 8.51, 1,536: 10.54 / 10.35, 2,048: 12.34 / 12.44, 8,192: 44.9 / 45.8; at the
+        # 57B-A14B sizes 2,048 tokens: 16.5 / 16.8 over 8 layers.  Spreading the shared expert's tiles among the routed
+        # ones, a product bound by the tensor cores beside one bound by DRAM, is slower than either: both draw on
+        # the L2's bandwidth.)
+        dual = (self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and not KT._NO_PAIRS and self.SHARED_IN_ROUTED_LAUNCH != "0"
+                and act == torch.bfloat16 and all(isinstance(w, KT.PackedWeights) for w in (self.w13, self.w2, self.ws13, self.ws2)))
+        if dual and self.SHARED_IN_ROUTED_LAUNCH == "":
+            wide = KT.TOKEN_TILES[-1]
+            units = -(-T // wide) * -(-self.shared_intermediate // KT.BLOCK_ROWS)      # the shared gate/up product's tiles
+            dual = units < 4 * (KA_resident(dev) // 2)
+        if dual:
+            tile = KT.TOKEN_TILES[-1]        # one width for both products; a tile's MMA is as wide as its own rows
+            share_shared = share_routed = 0
         ids = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
@@ -183,6 +206,17 @@ class MoEFeedForward(FeedForward):
                 # it out at larger batches takes SMs from the routed experts and costs 3-10 %).
                 few = T * k * self.intermediate <= 2 * S or shared_after
                 splits = KT.k_splits_for(T, H, S, stile, 2 * KA_resident(dev)) if few and isinstance(self.ws2, KT.PackedWeights) else 1
+                # Between the two: while the routed experts of the step read less than about 14 times the shared down
+                # projection's bytes, the unsplit product (a CTA per 128 output columns, 50-150 us) outlasts the routed
+                # gate/up product beside it and holds SM slots that product's persistent CTAs were counted on; in two
+                # or four shares it is out of the way sooner.  Measured on B200, tokens/s without / with: A2.7B sizes
+                # batch 3: 1,246 / 1,277, 4: 1,423 / 1,481, 5: 1,666 / 1,708, 6: 1,900 / 1,897, 8: 2,283 / 2,272;
+                # 57B-A14B sizes batch 4: 400 / 427, 6: 506 / 524.
+                E = self.n_experts
+                touched = E * (1.0 - ((E - k) / E) ** T)          # distinct experts under uniform routing
+                if (splits == 1 and not few and stile <= 64 and isinstance(self.ws2, KT.PackedWeights)
+                        and touched * 3 * self.intermediate <= self.SHARED_DOWN_SPLIT_RATIO * S and S >= 32 * KT.BLOCK_K):
+                    splits = 2 if S < 128 * KT.BLOCK_K else 4
                 y_shared = torch.empty((splits, T, H) if splits > 1 else (T, H), dtype=torch.float32, device=dev)
                 if splits > 1:
                     KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits)
@@ -192,7 +226,7 @@ class MoEFeedForward(FeedForward):
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
 
-        if self.ws13 is not None and not shared_after:
+        if self.ws13 is not None and not shared_after and not dual:
             shared_expert()
         if small:
             # few tokens (decoding): router, layout and the sorted copies of the rows in one launch
@@ -208,7 +242,7 @@ class MoEFeedForward(FeedForward):
                 KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
             KM.moe_align(ids, layout)
             KE.gather_rows(xn, layout.sorted_pair, k, x_rows)
-        if self.ws13 is not None and shared_after:
+        if self.ws13 is not None and shared_after and not dual:
             shared_expert()
         if ctx.debug is not None:
             # the tensors themselves: nothing below writes them, and inside a captured step a reference keeps their
@@ -216,9 +250,16 @@ class MoEFeedForward(FeedForward):
             ctx.debug.setdefault("router_ids", []).append(ids)
             ctx.debug.setdefault("router_weights", []).append(wts)
         h_rows = torch.empty((T * k, self.intermediate), dtype=act, device=dev)
-        self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status, share_routed)
         y_rows = torch.empty((T * k, H), dtype=torch.float32, device=dev)
-        self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, share_routed)
+        if dual:
+            first = self.SHARED_IN_ROUTED_LAUNCH != "spread"
+            hs = torch.empty((T, self.shared_intermediate), dtype=act, device=dev)
+            y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
+            KT.gemm_tc_dual(x_rows, self.w13, h_rows, layout, xn, self.ws13, hs, tile, ctx.status, first)
+            KT.gemm_tc_dual(h_rows, self.w2, y_rows, layout, hs, self.ws2, y_shared, tile, ctx.status, first)
+        else:
+            self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status, share_routed)
+            self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, share_routed)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
