@@ -150,7 +150,14 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
             def so_far(rows):                            # what a penalizing sampler looks back at
                 return {"recent": [list(prompts[i]) + results[i].tokens for i in rows]} if penalizes else {}
             to_host = getattr(engine, "tokens_to_host", None) or (lambda t: t.tolist())
-            new_dev = sampler.sample(logits, order, [0] * len(order), **so_far(order))
+            into = getattr(engine, "sample_into", None)      # optional: the engine's own place for a step's samples
+
+            def sample(logits, rows, steps):
+                kw = so_far(rows)
+                if into is not None:
+                    kw["out"] = into(len(rows))
+                return sampler.sample(logits, rows, steps, **kw)
+            new_dev = sample(logits, order, [0] * len(order))
             new = to_host(new_dev)
             sync()
             stats.prefill_seconds += time.perf_counter() - t0
@@ -203,7 +210,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: GenParam
                             results[i].finish_reason = "context"
                             engine.close(live.pop(i))
                         break
-                new_dev = sampler.sample(logits, order, [len(results[i].tokens) for i in order], **so_far(order))
+                new_dev = sample(logits, order, [len(results[i].tokens) for i in order])
                 stats.steps += 1
                 # launch the step after this one now, unless a sequence is sure to end with this token
                 if can_ahead and all(len(results[i].tokens) + 1 < params.max_new_tokens

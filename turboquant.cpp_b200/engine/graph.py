@@ -37,7 +37,7 @@ class DecodeGraph:
         parts = [self.dev[self.offsets[i]:self.offsets[i + 1]] for i in range(len(sizes))]
         self.tables = [parts[7 + g].view(B, self.widths[g]) for g in range(len(self.widths))]
         self.ctx = StepContext(
-            n_tokens=B, n_seqs=B, tokens=parts[0], positions=parts[1], seq_of_token=parts[2], cu_seqlens=parts[3],
+            n_tokens=B, n_seqs=B, tokens=engine.sample_into(B), positions=parts[1], seq_of_token=parts[2], cu_seqlens=parts[3],
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=B, max_q_len=1,
             max_kv_len=engine.table_width * cache.page_size, act_dtype=engine.act_dtype, device=engine.device,
             host_q_lens=[1] * B, host_slots=[], debug={} if engine.record_routing else None, status=engine.status)
@@ -51,7 +51,7 @@ class DecodeGraph:
         self.logits = None
         self.first_debug = None
 
-    def fill(self, seqs, tokens: Sequence[int]) -> None:
+    def fill(self, seqs, tokens: Sequence[int], with_tokens: bool = True) -> None:
         self.turn ^= 1
         if self.copied[self.turn] is not None:
             self.copied[self.turn].synchronize()
@@ -70,17 +70,22 @@ class DecodeGraph:
                 n = len(pages)
                 row[:n] = [(-1 if p is None else p) for p in pages] if None in pages else pages
         self.dev.copy_(host, non_blocking=True)
+        if with_tokens:
+            self.engine.sample_into(B).copy_(host[o[0]:o[1]], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.copied[self.turn] = ev
 
-    def run(self, seqs, tokens: Sequence[int], tokens_dev: torch.Tensor = None) -> torch.Tensor:
-        """tokens_dev: the step's tokens as an int32 tensor on the device (the previous step's samples); they go
-        into the static buffer by a device copy, after the host's part of it."""
+    def run(self, seqs, tokens: Sequence[int], tokens_dev: torch.Tensor = None, own_logits: bool = True) -> torch.Tensor:
+        """The step reads its tokens in the engine's feed buffer.  tokens_dev: the step's tokens as an int32 tensor
+        on the device (the previous step's samples): nothing to do if they were sampled into the feed buffer, a
+        device copy otherwise; without it the host's tokens are copied there.  own_logits: a copy of the logits
+        (the captured step's buffer is written again by the next replay)."""
         eng = self.engine
-        self.fill(seqs, tokens)
-        if tokens_dev is not None:
-            self.dev[self.offsets[0]:self.offsets[1]].copy_(tokens_dev, non_blocking=True)
+        feed = eng.sample_into(self.batch)
+        self.fill(seqs, tokens, with_tokens=tokens_dev is None)
+        if tokens_dev is not None and tokens_dev.data_ptr() != feed.data_ptr():
+            feed.copy_(tokens_dev, non_blocking=True)
         caches = eng.cache.layer_caches(self.tables)
         if self.graph is None:
             # the first step of this batch size runs eagerly (it also loads kernels and lets libraries
@@ -113,7 +118,7 @@ class DecodeGraph:
         self.graph.replay()
         eng.graphs.replays += 1
         _call.LAUNCHES += self.kernels
-        return self.logits.clone()
+        return self.logits.clone() if own_logits else self.logits
 
 
 class DecodeGraphs:
@@ -153,4 +158,4 @@ class DecodeGraphs:
         g = self.graphs.get(B)
         if g is None:
             g = self.graphs[B] = DecodeGraph(self.engine, B)
-        return g.run(list(seqs), [0] * B, tokens_dev)
+        return g.run(list(seqs), [0] * B, tokens_dev, own_logits=False)

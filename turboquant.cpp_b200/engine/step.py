@@ -40,32 +40,59 @@ class StepEntry:
     want: Sequence[int] = ()      # places among `tokens` whose logits are asked for
 
 
+FEED_TOKENS = 4      # where the tokens begin in an engine's feed buffer (the status word is element 0)
+
+
 class TokenReader:
     """Brings a step's sampled tokens to the host without waiting for work queued behind them: two pinned
     buffers used in turn (allocated once: nothing is allocated or freed while steps are in flight), a copy and an
     event per step.  The engine's status word travels with the tokens: if a kernel gave up on a bounded wait,
     the tokens sampled from its output are never handed out."""
 
-    def __init__(self, n: int, status: Optional[torch.Tensor] = None):
-        self.bufs = [torch.empty(max(1, n) + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+    def __init__(self, n: int, status: Optional[torch.Tensor] = None, feed: Optional[torch.Tensor] = None):
+        """feed: the engine's [status, ..., tokens] buffer; samples that lie in it travel with the status word in
+        one copy, on a stream of the reader's own, so that the step queued behind them does not wait for the copy."""
+        self.bufs = [torch.empty(FEED_TOKENS + max(1, n) + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.turn = 0
         self.status = status
+        self.feed = feed
+        self.side = torch.cuda.Stream(device=feed.device) if feed is not None else None
+
+    def _withheld(self):
+        self.status.zero_()
+        raise KernelError("step: " + GAVE_UP + "; the tokens sampled from it are withheld")
 
     def start(self, tokens_dev):
+        """Starts the copy and returns the function that waits for it and gives the tokens.  Call that function
+        before the next sampling: samples in the engine's feed buffer are overwritten by it."""
         self.turn ^= 1
         n = tokens_dev.numel()
         host = self.bufs[self.turn]
+        done = torch.cuda.Event()
+        if (self.feed is not None and tokens_dev.dtype == torch.int32
+                and tokens_dev.data_ptr() == self.feed.data_ptr() + 4 * FEED_TOKENS):
+            sampled = torch.cuda.Event()
+            sampled.record()
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(sampled)
+                host[:FEED_TOKENS + n].copy_(self.feed[:FEED_TOKENS + n], non_blocking=True)
+                done.record()
+
+            def wait():
+                done.synchronize()
+                if int(host[0]) != 0:
+                    self._withheld()
+                return host[FEED_TOKENS:FEED_TOKENS + n].tolist()
+            return wait
         host[:n].copy_(tokens_dev, non_blocking=True)
         if self.status is not None:
             host[n:n + 1].copy_(self.status, non_blocking=True)
-        done = torch.cuda.Event()
         done.record()
 
         def wait():
             done.synchronize()
             if self.status is not None and int(host[n]) != 0:
-                self.status.zero_()
-                raise KernelError("step: " + GAVE_UP + "; the tokens sampled from it are withheld")
+                self._withheld()
             return host[:n].tolist()
         return wait
 
@@ -90,7 +117,12 @@ class Engine:
         self.debug: Optional[Dict[str, Any]] = None
         self.record_routing = bool(record_routing)
         # set by a kernel whose bounded wait ran out (one word per engine: a fault is seen by the engine it spoiled)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # The status word and the place where a step's sampled tokens are put share one buffer, [status, 3 unused,
+        # a token per slot]: the samples go to the host together with the word in one copy, and a decode graph reads
+        # its step's tokens there, so between two decode steps the stream carries the sampling kernel and one copy
+        # of the step's metadata, not six small operations with a gap of about ten microseconds before each.
+        self.feed = torch.zeros(FEED_TOKENS + self.cache.max_slots, dtype=torch.int32, device=self.device)
+        self.status = self.feed[0:1]
         self.steps_run = 0
         # widest page table a sequence can need; decode graphs keep tables of this width
         longest = min(self.model.max_position, max(self.capacity_tokens, self.cache.page_size))
@@ -261,7 +293,8 @@ class Engine:
         samples of the step before) and returns its logits, without advancing the sequences: the caller reads the
         samples on the host meanwhile and then either keeps the step (`commit_ahead`) or, if a sequence turned
         out to have ended, drops it (`drop_ahead`) and steps again.  A dropped step leaves nothing behind: what it
-        wrote into the cache lies beyond the sequences' lengths and is written again by the step that replaces it."""
+        wrote into the cache lies beyond the sequences' lengths and is written again by the step that replaces it.
+        The logits are the captured step's own buffer: they hold until the next decode step of this batch size."""
         if not self.can_step_ahead:
             raise StepError("this engine cannot launch a step ahead")
         if self._ahead is not None:
@@ -280,7 +313,12 @@ class Engine:
         return logits
 
     def token_reader(self, n: int) -> TokenReader:
-        return TokenReader(n, self.status)
+        return TokenReader(n, self.status, self.feed)
+
+    def sample_into(self, n: int) -> torch.Tensor:
+        """Where a sampler should put the tokens of a step's n sequences (int32 on the device): from there they
+        reach the host with the status word in one copy and the next decode step without one."""
+        return self.feed[FEED_TOKENS:FEED_TOKENS + n]
 
     def tokens_to_host(self, tokens_dev: torch.Tensor) -> List[int]:
         """A step's sampled tokens as a list, after a look at the status word (one synchronisation for both)."""

@@ -62,12 +62,15 @@ class Sampler:
         return self.rep_penalty > 1.0 and self.rep_window > 0
 
     def sample(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],
-               recent: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+               recent: Optional[Sequence[Sequence[int]]] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One token per row of float32 logits [R, V] (int32, on the device).  recent: for each row the tokens
         of its request so far (prompt, then generated); with a repetition penalty the last rep_window of them
-        lower their logits first, in place."""
+        lower their logits first, in place.  out: where to put the tokens (int32 [R] on the logits' device)."""
         R, V = logits.shape
-        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        if out is None:
+            out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        elif out.shape != (R,) or out.dtype != torch.int32 or out.device != logits.device or not out.is_contiguous():
+            raise ValueError(f"sample: out must be a contiguous int32 tensor of {R} elements on {logits.device}")
         if self.penalizes and recent is not None:
             W = self.rep_window
             table = np.full((R, W), -1, dtype=np.int32)
