@@ -134,3 +134,34 @@ def test_step_refuses_bad_input(engines):
     assert seq.length == 0
     eng.close(seq)
     eng.cache.book.check_invariants()
+
+
+def test_warm_up_captures_the_decode_graphs_ahead_of_the_first_batch(tiny_folders):
+    """After warm_up the first decode step of a batch size is already a replay, slots and pages are all back, and
+    the logits are those of an engine that was not warmed up, bit for bit."""
+    import turboquant_cpp_b200 as tq
+    model = tq.load_model(tiny_folders["A"], "bfloat16", "cuda:0")
+    warm = tq.Engine(model, max_tokens=1024, max_slots=4)
+    free = [p.n_free for p in warm.cache.book.pools]
+    assert warm.warm_up([1, 3]) == [1, 3]
+    assert warm.warm_up([3, 2]) == [2]                        # 3 has its graph already
+    assert [p.n_free for p in warm.cache.book.pools] == free
+    warm.cache.book.check_invariants()
+    assert warm.warm_up([9]) == []                            # more sequences than slots: nothing captured, nothing held
+    assert [p.n_free for p in warm.cache.book.pools] == free
+    cold = tq.Engine(model, max_tokens=1024, max_slots=4)
+    toks = tokens_for("A", 40, 5)
+    out = {}
+    for name, eng in (("warm", warm), ("cold", cold)):
+        before = eng.graphs.replays
+        seqs = [eng.open() for _ in range(3)]
+        eng.step([tq.StepEntry(s, toks[:20 + i], []) for i, s in enumerate(seqs)])
+        rows = [eng.step([tq.StepEntry(s, [toks[30 + j]], [0]) for s in seqs]).float().cpu().numpy() for j in range(3)]
+        out[name] = (rows, eng.graphs.replays - before)
+        for s in seqs:
+            eng.close(s)
+    assert out["warm"][1] == 3 and out["cold"][1] == 2         # the cold engine's first step of this size ran eagerly
+    for a, b in zip(out["warm"][0], out["cold"][0]):
+        assert np.array_equal(a, b)
+    warm.release()
+    cold.release()

@@ -90,6 +90,7 @@ def test_stop_tokens_and_streaming(tiny_folders, plain_models):
     first = want.index(stop)
     with tq.Model(tiny_folders["A"], temperature=0.0, max_tokens=12, dtype="float32", max_batch=2,
                   context_length=64) as m:
+        assert m.warm_up() == [1, 2] and m.warm_up() == []       # the decode steps of both batch sizes, captured once
         out = m.ask(p, stop_token_ids=[stop])
         assert out == want[:first + 1] and m.last_results[0].finish_reason == "stop"
         assert list(m.generate(p)) == want                       # the iterator yields the same tokens

@@ -175,6 +175,34 @@ class Engine:
         if self.graphs is not None:
             self.graphs.release()
 
+    def warm_up(self, batch_sizes) -> List[int]:
+        """Captures the decode graphs of these batch sizes now, with one step of one-token sequences that are
+        closed again, so that generation meets no new size in the middle of a batch (the first step of a new size
+        runs kernel by kernel, waits for the device and records the graph: tens of milliseconds).  Returns the
+        sizes captured by this call; sizes that have their graph already cost nothing.  It stops quietly at the
+        first size the free slots or pages do not hold."""
+        done: List[int] = []
+        if self.graphs is None or self.debug is not None or self.layer_dump:
+            return done
+        for B in sorted({int(b) for b in batch_sizes}):
+            if B < 1:
+                raise StepError(f"warm_up: batch size {B}")
+            g = self.graphs.graphs.get(B)
+            if g is not None and g.graph is not None:
+                continue
+            seqs: List[Sequence_] = []
+            try:
+                for _ in range(B):
+                    seqs.append(self.open())
+                self.step([StepEntry(s, [0], [0]) for s in seqs])
+                done.append(B)
+            except CacheFull:
+                break
+            finally:
+                for s in seqs:
+                    self.close(s)
+        return done
+
     # ---- sequences ------------------------------------------------------------------------------
     def open(self) -> Sequence_:
         return self.cache.open()

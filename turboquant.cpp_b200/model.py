@@ -82,6 +82,12 @@ class Model:
     def engine(self) -> Engine:
         return self._engine
 
+    def warm_up(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Captures the decode steps of these batch sizes (default: 1..max_batch) before the first request, so that
+        no request waits for a capture when its batch shrinks to a size not seen before.  Returns the sizes captured."""
+        self._check_open()
+        return self._engine.warm_up(range(1, self.max_batch + 1) if batch_sizes is None else batch_sizes)
+
     # ---- generation ---------------------------------------------------------------------------
     def _params(self, max_tokens, temperature, top_p, seed, stop_token_ids, rep_penalty=None, rep_window=None,
                 detect_loops=None) -> GenParams:
