@@ -139,6 +139,7 @@ class Engine:
         if self.layer_dump in ("0", ""):
             self.layer_dump = ""
         self._ahead = None                       # (sequences, tokens each) of a step launched ahead, if any
+        self._reader: Optional[TokenReader] = None
 
     # ---- what the generation loop asks -----------------------------------------------------------
     @property
@@ -341,7 +342,11 @@ class Engine:
         return logits
 
     def token_reader(self, n: int) -> TokenReader:
-        return TokenReader(n, self.status, self.feed)
+        """The engine's reader (pinned buffers for a token per slot, made once: pinning memory takes about a
+        millisecond, which a short generation would notice)."""
+        if self._reader is None:
+            self._reader = TokenReader(max(n, self.max_slots), self.status, self.feed)
+        return self._reader
 
     def sample_into(self, n: int) -> torch.Tensor:
         """Where a sampler should put the tokens of a step's n sequences (int32 on the device): from there they
