@@ -35,7 +35,6 @@ class MoEFeedForward(FeedForward):
     # tensor cores (measured on B200 at 64 tokens: +2.4 % on the step at the 57B-A14B sizes, +0.8 % at the A2.7B sizes)
     ROUTER_TC_MIN_TOKENS = int(os.environ.get("TQ_ROUTER_TC_MIN", "64"))
     SHARED_AFTER_ROUTER = {"": None, "0": False}.get(os.environ.get("TQ_SHARED_AFTER_ROUTER", ""), True)   # None: by the step's size
-    SHARED_SM_SHARE = int(os.environ.get("TQ_SHARED_SM_SHARE", "0"))      # per cent of the SMs for the shared expert in long steps
     # long steps: the shared expert's products in the launches of the routed experts' ("": by the step's size,
     # "0": never, "1": always, "spread": always, with the shared expert's tiles spread among the routed ones instead
     # of ahead of them)
@@ -133,12 +132,32 @@ class MoEFeedForward(FeedForward):
             cls._side_streams[key] = torch.cuda.Stream(device=device)
         return cls._side_streams[key]
 
-    def _product(self, x, w, out, layout, swiglu, token_tile, status=None, sm_share=0):
+    def _product(self, x, w, out, layout, swiglu, token_tile, status=None):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
         kernel otherwise."""
         if isinstance(w, KT.PackedWeights):
-            return KT.gemm_tc(x, w, out, layout, token_tile, status=status, sm_share=sm_share)
+            return KT.gemm_tc(x, w, out, layout, token_tile, status=status)
         return KM.grouped_gemm(x, w, out, layout, swiglu)
+
+    def _joint_launches(self, T: int, tile: int, act, dev) -> bool:
+        """Whether the shared expert's two products ride in the routed experts' launches, their tiles ahead of the
+        routed ones: steps of some hundred to about 1,500 tokens.  Either product alone fills the GPU with one
+        persistent CTA per SM, so as launches of their own they run one after the other, and at these sizes each
+        has only two to four rounds of tiles per CTA: its last round leaves SMs idle, which the other product's
+        tiles fill when the same CTAs walk both.  (Measured on B200 at the A2.7B sizes, ms per prompt apart /
+        together: 768 tokens 7.88 / 7.40, 1,024: 9.29 / 8.51, 1,536: 10.54 / 10.35, 2,048: 12.34 / 12.44, 8,192:
+        44.9 / 45.8; at the 57B-A14B sizes 2,048 tokens: 16.5 / 16.8 over 8 layers.  Spreading the shared expert's
+        tiles among the routed ones, a product bound by the tensor cores beside one bound by DRAM, is slower than
+        either: both draw on the L2's bandwidth.  Giving each product a share of the SMs instead, as launches of
+        their own on two streams, cost 25-60 %.)"""
+        how = self.SHARED_IN_ROUTED_LAUNCH
+        if (self.ws13 is None or tile < KT.PAIR_MIN_TILE or KT._NO_PAIRS or how == "0" or act != torch.bfloat16
+                or not all(isinstance(w, KT.PackedWeights) for w in (self.w13, self.w2, self.ws13, self.ws2))):
+            return False
+        if how != "":
+            return True
+        units = -(-T // KT.TOKEN_TILES[-1]) * -(-self.shared_intermediate // KT.BLOCK_ROWS)    # the shared gate/up product's tiles
+        return units < 4 * (KA_resident(dev) // 2)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
@@ -149,31 +168,9 @@ class MoEFeedForward(FeedForward):
         y_shared = None
         side = None
         tile = KT.token_tile_for(T * k, self.n_experts) if isinstance(self.w13, KT.PackedWeights) else 0
-        # long steps: both products fill the GPU with one persistent CTA per SM, so whichever starts first would
-        # keep the other waiting.  The shared expert's products are bound by the tensor cores, the routed experts'
-        # by the stream of their weights: each gets a share of the SMs and they run beside each other.
-        share_shared = share_routed = 0
-        if self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and isinstance(self.ws13, KT.PackedWeights):
-            share_shared = self.SHARED_SM_SHARE
-            share_routed = 100 - share_shared
-        # Steps of some hundred to about 1,500 tokens: the shared expert's two products ride in the routed experts'
-        # launches, their tiles ahead of the routed ones.  Either product alone fills the GPU with one persistent CTA
-        # per SM, so as launches of their own they run one after the other, and at these sizes each has only two to
-        # four rounds of tiles per CTA: its last round leaves SMs idle, which the other product's tiles fill when
-        # the same CTAs walk both.  (Measured on B200 at the A2.7B sizes, ms per prompt apart / together: 768 tokens
-        # 7.88 / 7.40, 1,024: 9.29 / 8.51, 1,536: 10.54 / 10.35, 2,048: 12.34 / 12.44, 8,192: 44.9 / 45.8; at the
-        # 57B-A14B sizes 2,048 tokens: 16.5 / 16.8 over 8 layers.  Spreading the shared expert's tiles among the routed
-        # ones, a product bound by the tensor cores beside one bound by DRAM, is slower than either: both draw on
-        # the L2's bandwidth.)
-        dual = (self.ws13 is not None and tile >= KT.PAIR_MIN_TILE and not KT._NO_PAIRS and self.SHARED_IN_ROUTED_LAUNCH != "0"
-                and act == torch.bfloat16 and all(isinstance(w, KT.PackedWeights) for w in (self.w13, self.w2, self.ws13, self.ws2)))
-        if dual and self.SHARED_IN_ROUTED_LAUNCH == "":
-            wide = KT.TOKEN_TILES[-1]
-            units = -(-T // wide) * -(-self.shared_intermediate // KT.BLOCK_ROWS)      # the shared gate/up product's tiles
-            dual = units < 4 * (KA_resident(dev) // 2)
+        dual = self._joint_launches(T, tile, act, dev)
         if dual:
             tile = KT.TOKEN_TILES[-1]        # one width for both products; a tile's MMA is as wide as its own rows
-            share_shared = share_routed = 0
         ids = torch.empty((T, k), dtype=torch.int32, device=dev)
         wts = torch.empty((T, k), dtype=torch.float32, device=dev)
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
@@ -196,7 +193,7 @@ class MoEFeedForward(FeedForward):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 hs = torch.empty((T, S), dtype=act, device=dev)
-                self._product(xn, self.ws13, hs, None, True, stile, ctx.status, share_shared)
+                self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
                 # The down projection has few tiles (rows of 128 output columns) and a long K: a handful of SMs stream
                 # all its weights (measured on B200: 0.8 TB/s at 2,048 x 5,632, 1.5 TB/s at 3,584 x 20,480).  While the
                 # routed experts read several times the shared expert's bytes on the main stream that does not
@@ -221,7 +218,7 @@ class MoEFeedForward(FeedForward):
                 if splits > 1:
                     KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits)
                 else:
-                    self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status, share_shared)
+                    self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status)
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
@@ -258,8 +255,8 @@ class MoEFeedForward(FeedForward):
             KT.gemm_tc_dual(x_rows, self.w13, h_rows, layout, xn, self.ws13, hs, tile, ctx.status, first)
             KT.gemm_tc_dual(h_rows, self.w2, y_rows, layout, hs, self.ws2, y_shared, tile, ctx.status, first)
         else:
-            self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status, share_routed)
-            self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, share_routed)
+            self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status)
+            self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
