@@ -305,7 +305,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
                int stream_weights, int* __restrict__ status, int k_splits, const __grid_constant__ SECOND second) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    // Bit 1 of stream_weights: the weights, the tile list and the sizes were final before the kernel ahead of this
+    // one in the stream started (a down projection behind its gate/up product; a product with one group), so the
+    // thread that streams the weights does not wait for that kernel: its loads are in flight while the kernel ahead
+    // still runs.  Everything else (the token rows above all) waits as usual.
+    const bool early_weights = (stream_weights & 2) != 0;
+    if (!early_weights) tq_grid_wait();      // everything below may read what the previous kernel wrote
     using T = Tile<BN, PAIR>;
     constexpr bool DUAL = !std::is_same<SECOND, NoSecond>::value;
     static_assert(!(DUAL && KSPLIT), "a launch either walks two products or shares K out");
@@ -379,6 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // had not allocated yet, and then wait forever for this grid to finish
     tq_grid_launch_dependents();
     const uint32_t tmem_base = s_tmem_base;
+    if (early_weights && warp != 0) tq_grid_wait();
 
     // The two producers are one thread each and their loops are kept to a few instructions per block: a single
     // thread runs one dependent instruction every few cycles, and a block lasts only some hundred cycles.
@@ -387,7 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             // weights that only one token tile reads (a decode step, a short prompt) are streamed: first to leave
             // the L2; weights that several token tiles share stay
-            const uint64_t policy = stream_weights ? policy_evict_first() : policy_evict_last();
+            const uint64_t policy = (stream_weights & 1) ? policy_evict_first() : policy_evict_last();
             const uint64_t keep = policy_evict_last();
             (void)keep;
             int slot = 0, issued = 0;
@@ -661,7 +667,7 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
 template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT = false, typename SECOND = NoSecond>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
            const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, int sm_share_pct,
-           int k_splits, cudaStream_t stream, const SECOND& second = SECOND(), long long tiles2 = 0) {
+           int k_splits, cudaStream_t stream, const SECOND& second = SECOND(), long long tiles2 = 0, int early_weights = 0) {
     using T = Tile<BN, PAIR>;
     auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR, KSPLIT, SECOND>;
     static bool configured = false;
@@ -702,7 +708,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     }
     const int grid = (int)(want < room ? want : room);
     tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K,
-        /* stream_weights: on average at most one token tile per group */ (te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0, status,
+        /* stream_weights: on average at most one token tile per group */ ((te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0) | (early_weights ? 2 : 0), status,
         k_splits, second);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
@@ -719,11 +725,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
 // CTA holds 128 weight rows and half of the token rows).  status: one int in device memory, set to 1 if
 // a bounded wait ran out.  sm_share_pct: 0 or 100 = the launch may fill the GPU; 1..99 = it takes that share of the
 // CTAs the GPU runs at once.  k_splits > 1 (plain products, fp32 out): out is [k_splits][R][N], slice s holding the
-// partial sums over the s-th share of K; the caller adds them up.
+// partial sums over the s-th share of K; the caller adds them up.  early_weights: the caller vouches that W, the
+// tile arrays and n_tiles were final before the kernel ahead of this one in the stream started; the weight stream then
+// starts without waiting for that kernel (programmatic dependent launch), the token rows wait for it as always.
 TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
                          const int* tile_row0, const int* tile_count, const int* n_tiles, int max_tiles, int bn,
                          int R, int N, int K, int G, int swiglu, int pair, int* status, int sm_share_pct,
-                         int k_splits, cudaStream_t stream) {
+                         int k_splits, int early_weights, cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
     TQ_REQUIRE(k_splits >= 1, "gemm_tc: %d shares of K", k_splits);
     if (k_splits > 1) {
@@ -747,7 +755,7 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     if (rc) return rc;
     rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u);
     if (rc) return rc;
-#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, sm_share_pct, k_splits, stream
+#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, sm_share_pct, k_splits, stream, NoSecond(), 0, early_weights
 #define TC_CASE(BN_, PAIR_)                                                                          \
     if (bn == BN_ && (pair != 0) == PAIR_) {                                                         \
         if (swiglu) {                                                                                \
@@ -788,7 +796,7 @@ TQ_EXPORT int tq_gemm_tc_dual(const void* X, const void* W, void* out, const int
     TQ_REQUIRE((swiglu && out_dtype == TQ_BF16) || (!swiglu && out_dtype == TQ_F32),
                "gemm_tc_dual: SwiGLU products write bfloat16 and plain products float32 (got swiglu=%d, type %d)", swiglu, out_dtype);
     TQ_REQUIRE(status != nullptr, "gemm_tc_dual: a status word is required");
-    if (max_tiles == 0) return tq_gemm_tc(X2, W2, out2, out_dtype, nullptr, nullptr, nullptr, nullptr, 0, bn, R2, N2, K2, 1, swiglu, 1, status, 0, 1, stream);
+    if (max_tiles == 0) return tq_gemm_tc(X2, W2, out2, out_dtype, nullptr, nullptr, nullptr, nullptr, 0, bn, R2, N2, K2, 1, swiglu, 1, status, 0, 1, 0, stream);
     const int cols = swiglu ? BM / 2 : BM;
     const int n_m1 = (N + cols - 1) / cols, n_m1_2 = (N2 + cols - 1) / cols;
     CUtensorMap mw, mx, mxt;

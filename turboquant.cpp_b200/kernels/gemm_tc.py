@@ -129,14 +129,16 @@ _NO_PAIRS = os.environ.get("TQ_NO_PAIRS", "") not in ("", "0")
 
 def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
             token_tile: int, pair: Optional[bool] = None, status: Optional[torch.Tensor] = None,
-            sm_share: int = 0, k_splits: int = 1) -> torch.Tensor:
+            sm_share: int = 0, k_splits: int = 1, early_weights: bool = False) -> torch.Tensor:
     """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
     silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group).
     pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1).  status: the int32 the
     kernel sets if a bounded wait runs out (default: the device's word).  sm_share: 1..99 = the launch takes only
     that percentage of the CTAs the GPU runs at once and leaves the rest to a launch on another stream.
     k_splits > 1: out is [k_splits, R, N] float32; slice s holds the partial sums over the s-th share of K (see
-    k_splits_for) and the caller adds the slices up in order."""
+    k_splits_for) and the caller adds the slices up in order.  early_weights: the caller vouches that the weights
+    and the layout were final before the kernel ahead of this one in the stream started (a down projection behind
+    its gate/up product); the kernel then starts streaming weights while that kernel still runs."""
     if pair is None:
         pair = token_tile >= PAIR_MIN_TILE and not _NO_PAIRS
     if not usable(x, w):
@@ -158,7 +160,8 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None, ptr(lo.tile_count) if lo else None,
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
         c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
-        ptr(status if status is not None else status_word(x.device)), c_int(int(sm_share)), c_int(int(k_splits)), stream()))
+        ptr(status if status is not None else status_word(x.device)), c_int(int(sm_share)), c_int(int(k_splits)),
+        c_int(1 if early_weights else 0), stream()))
     return out
 
 

@@ -132,11 +132,14 @@ class MoEFeedForward(FeedForward):
             cls._side_streams[key] = torch.cuda.Stream(device=device)
         return cls._side_streams[key]
 
-    def _product(self, x, w, out, layout, swiglu, token_tile, status=None):
+    EARLY_WEIGHTS = os.environ.get("TQ_EARLY_WEIGHTS", "1") not in ("", "0")
+
+    def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
-        kernel otherwise."""
+        kernel otherwise.  early: this is a down projection right behind its gate/up product in the stream: its
+        weights and the layout were there before that product started, so it may stream weights while that runs."""
         if isinstance(w, KT.PackedWeights):
-            return KT.gemm_tc(x, w, out, layout, token_tile, status=status)
+            return KT.gemm_tc(x, w, out, layout, token_tile, status=status, early_weights=early and self.EARLY_WEIGHTS)
         return KM.grouped_gemm(x, w, out, layout, swiglu)
 
     def _joint_launches(self, T: int, tile: int, act, dev) -> bool:
@@ -216,9 +219,9 @@ class MoEFeedForward(FeedForward):
                     splits = 2 if S < 128 * KT.BLOCK_K else 4
                 y_shared = torch.empty((splits, T, H) if splits > 1 else (T, H), dtype=torch.float32, device=dev)
                 if splits > 1:
-                    KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits)
+                    KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits, early_weights=self.EARLY_WEIGHTS)
                 else:
-                    self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status)
+                    self._product(hs, self.ws2, y_shared, None, False, stile, ctx.status, early=True)
             # hs and y_shared were allocated on the side stream; both live until this function returns,
             # after the main stream has joined the side stream again, and the side stream's next use
             # starts with a wait on the main stream: no cross-stream reuse hazard
@@ -256,7 +259,7 @@ class MoEFeedForward(FeedForward):
             KT.gemm_tc_dual(h_rows, self.w2, y_rows, layout, hs, self.ws2, y_shared, tile, ctx.status, first)
         else:
             self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status)
-            self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status)
+            self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, early=True)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
