@@ -191,6 +191,43 @@ def test_attention_split_merges_in_range_order_whoever_comes_last():
     assert int(KA.tickets(torch.device(DEV)).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,n_splits,ring", [(16, 16, 128, 4, "0"), (16, 16, 128, 3, "1"), (28, 4, 128, 8, "0"),
+                                                       (4, 2, 64, 1, "0"), (6, 1, 32, 16, "0")])
+def test_attention_split_asks_for_old_keys_before_the_wait_and_still_sees_the_new_ones(nh, nkv, hd, n_splits, ring, monkeypatch):
+    """A decode step: the kernel ahead writes each token's key and value at its own position, the attention kernel
+    behind it (launched early, its first groups of old keys asked for before it waits) must see them.  Twenty rounds
+    with fresh keys, values and queries each; the newest key is made the one that decides the result (its score
+    stands out), so a launch that missed it would differ; both ways of launching give the same bits."""
+    from turboquant_cpp_b200.kernels import attention as KA
+    monkeypatch.setenv("TQ_SPLIT_RING", ring)
+    rng = np.random.default_rng(nh + hd + n_splits)
+    seq_lens, page = [300, 17, 1, 130, 64, 2048, 9, 65], 64           # lengths after the step: the new token is the last
+    q_lens = [1] * len(seq_lens)
+    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, torch.bfloat16, n_pages=80)
+    T = len(seq_lens)
+    pos, seq_of, table = (dev(d[k], torch.int32) for k in ("positions", "seq_of", "table"))
+    cache = dev(d["cache"], torch.bfloat16)
+    width = (nh + 2 * nkv) * hd
+    for r in range(20):
+        qkv = bf16_values(rng.normal(size=(T, width)))
+        G = nh // nkv
+        qkv[:, nh * hd:(nh + nkv) * hd] = bf16_values(3.0 * qkv[:, :nh * hd].reshape(T, nkv, G, hd)[:, :, 0]).reshape(T, -1)   # the new key points along its group's first query
+        q = torch.empty((T, nh, hd), dtype=torch.bfloat16, device=DEV)
+        outs = []
+        for early in (True, False):
+            KA.qkv_rope_cache(dev(qkv, torch.bfloat16), None, None, None, "half", pos, seq_of, table, page, q, cache, nh, nkv, hd)
+            out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+            partial = torch.empty(T * nh * n_splits * (hd + 2), dtype=torch.float32, device=DEV) if n_splits > 1 else None
+            KA.attention_split(q, cache, pos, seq_of, table, page, 0, 1 / math.sqrt(hd), out, nh, nkv, hd, n_splits, partial,
+                               early_keys=early)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), f"round {r}"
+        # the new value carries weight in the result of the first head of each KV head: without it the output differs
+        v_new = torch.tensor(qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd), dtype=torch.float32, device=DEV)
+        got = outs[0].float().view(T, nkv, nh // nkv, hd)[:, :, 0]
+        assert (torch.nn.functional.cosine_similarity(got, v_new, dim=-1) > 0.5).all(), f"round {r}: the new key was not seen"
+
+
 @pytest.mark.parametrize("nh,hd", [(3, 128), (1, 128)])
 @pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 4), (900, 7)])
 def test_attention_split_ring_equals_registers(nh, hd, window, n_splits, monkeypatch):

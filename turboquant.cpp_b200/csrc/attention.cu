@@ -353,9 +353,16 @@ __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ page_table, int table_stride,
                        int page_size, int window, float scale, float* __restrict__ partial, int n_splits,
-                       int* __restrict__ arrived, TA* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+                       int* __restrict__ arrived, TA* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages,
+                       int early_keys) {
+    // early_keys: a decode step, in which the kernel ahead of this one wrote one thing into the cache, the keys and
+    // values at each token's own position (and the queries); positions, page table and every older key were there
+    // before that kernel started.  A warp whose first group of keys lies wholly below its token's position asks for
+    // that group before it waits for the kernel ahead: the first round trip to DRAM overlaps that kernel's end.
+    if (!early_keys) {
+        tq_grid_wait();                    // everything below may read what the previous kernel wrote
+        tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    }
     constexpr int HD = LPK * 8;
     constexpr int KPI = 32 / LPK;            // keys per load instruction of a warp
     constexpr int GS = KPI > 8 ? KPI : 8;    // keys per iteration of a warp (a group of absolute positions)
@@ -381,15 +388,6 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
     const int per = (groups + n_splits - 1) / n_splits;
     const int gb = first8 + split * per, ge = min(last8 + 1, gb + per);
 
-    float qv[GC][8], acc[GC][8], m[GC], l[GC];
-#pragma unroll
-    for (int h = 0; h < GC; ++h) {
-        m[h] = -INFINITY; l[h] = 0.f;
-        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (h < G) Vec8<TA>::load(q + ((size_t)t * nh + (size_t)g * G_all + h0 + h) * HD + sub * 8, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { qv[h][i] = f[i] * scale; acc[h][i] = 0.f; }
-    }
     using Raw = typename Vec8<TA>::Raw;
     static_assert(STAGES == 0 || sizeof(Raw) == 16, "the ring holds 16-byte loads");
     // the keys and values of a group of GS positions, as this lane reads them
@@ -419,6 +417,9 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
         for (int j = 0; j < LOADS; ++j) split_copy16(dst + (LOADS + j) * 32, vbase + (size_t)(j * KPI + part) * HD + sub * 8);
     };
     int next_grp = gb + warp, next_stage = 0, stage = 0;     // ring: the next group to copy and where; the stage to read
+    // the groups asked for ahead of the loop (one, or STAGES - 1 of the ring) end below the token's own position?
+    const bool ahead = early_keys && (gb + warp + (STAGES > 1 ? STAGES - 2 : 0) * SPLIT_WARPS) * GS + GS - 1 < pos;
+    if (early_keys && !ahead) { tq_grid_wait(); tq_grid_launch_dependents(); }
     if (STAGES > 0) {
 #pragma unroll
         for (int i = 0; i < STAGES - 1; ++i) {                // one commit per group, also past the end: the count is uniform
@@ -428,6 +429,16 @@ attention_split_kernel(const TA* __restrict__ q, const TA* __restrict__ cache, c
             next_stage = next_stage + 1 == STAGES ? 0 : next_stage + 1;
         }
     } else if (gb + warp < ge) fetch_group(gb + warp, kr, vr);
+    if (ahead) { tq_grid_wait(); tq_grid_launch_dependents(); }
+    float qv[GC][8], acc[GC][8], m[GC], l[GC];
+#pragma unroll
+    for (int h = 0; h < GC; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (h < G) Vec8<TA>::load(q + ((size_t)t * nh + (size_t)g * G_all + h0 + h) * HD + sub * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { qv[h][i] = f[i] * scale; acc[h][i] = 0.f; }
+    }
     for (int grp = gb + warp; grp < ge; grp += SPLIT_WARPS) {
         const int p0 = grp * GS;
         float kf[LOADS][8], vf[LOADS][8];
@@ -598,9 +609,13 @@ attention_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ page_table, int table_stride, int page_size, int window, float scale,
                      float* __restrict__ partial, int n_splits, int* __restrict__ arrived,
-                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_seqs, int n_pages, int early_keys) {
+    // early_keys: as in attention_split_kernel (a decode step: a warp's first group of keys, if it lies below the
+    // token's own position, is asked for before the wait on the kernel ahead)
+    if (!early_keys) {
+        tq_grid_wait();                    // everything below may read what the previous kernel wrote
+        tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    }
     constexpr int CPR = HD / 8;                          // 16-byte chunks per row
     constexpr int TILE = GQA_KEYS * HD;                  // elements of a K (or V) tile
     extern __shared__ __align__(128) unsigned char s_gqa[];
@@ -616,19 +631,6 @@ attention_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const int per = (groups + n_splits - 1) / n_splits;
     const int gb = first + split * per, ge = min(last + 1, gb + per);
 
-    // the queries as A fragments: rows gid and gid + 8 (heads), 16 head elements per k-step
-    uint32_t qa[HD / 16][4];
-    {
-        const __nv_bfloat16* q0 = q + ((size_t)t * nh + (size_t)g * G + gid) * HD + tig * 2;
-        const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            qa[ks][0] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16) : 0u;
-            qa[ks][1] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16) : 0u;
-            qa[ks][2] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8) : 0u;
-            qa[ks][3] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8) : 0u;
-        }
-    }
     float o[HD / 8][4];                                  // rows gid (0,1) and gid + 8 (2,3), head elements nd*8 + tig*2 + {0,1}
 #pragma unroll
     for (int nd = 0; nd < HD / 8; ++nd) { o[nd][0] = o[nd][1] = o[nd][2] = o[nd][3] = 0.f; }
@@ -651,10 +653,26 @@ attention_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         }
     };
     int next_grp = gb + warp, next_stage = 0, stage = 0;
+    const bool ahead = early_keys && next_grp * GQA_KEYS + GQA_KEYS - 1 < pos;    // the first group ends below the token's position
+    if (early_keys && !ahead) { tq_grid_wait(); tq_grid_launch_dependents(); }
     if (next_grp < ge) copy_group(next_grp, next_stage);
     split_commit();
     next_grp += GQA_WARPS;
     next_stage ^= 1;
+    if (ahead) { tq_grid_wait(); tq_grid_launch_dependents(); }
+    // the queries as A fragments: rows gid and gid + 8 (heads), 16 head elements per k-step
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* q0 = q + ((size_t)t * nh + (size_t)g * G + gid) * HD + tig * 2;
+        const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qa[ks][0] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16) : 0u;
+            qa[ks][1] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16) : 0u;
+            qa[ks][2] = gid < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8) : 0u;
+            qa[ks][3] = gid + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8) : 0u;
+        }
+    }
     for (int grp = gb + warp; grp < ge; grp += GQA_WARPS) {
         if (next_grp < ge) copy_group(next_grp, next_stage);          // the stage read one iteration ago
         split_commit();
@@ -771,11 +789,14 @@ attention_gqa_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 }
 
 // partial: T * nh * n_splits * (hd + 2) floats of scratch; arrived: T * nkv * ceil(G / 8) ints (G = nh / nkv) that are
-// zero before the launch and zero again after it (both unused, and may be null, with one range).
+// zero before the launch and zero again after it (both unused, and may be null, with one range).  early_keys: the
+// caller vouches that the kernel ahead of this one in the stream wrote nothing this launch reads but the queries and
+// the keys and values at the tokens' own positions (a decode step: one new token per sequence); older keys are then
+// asked for before the wait on that kernel.
 TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype, const int* positions,
                                  const int* seq_of_token, const int* page_table, int table_stride, int page_size,
                                  int window, float scale, float* partial, int n_splits, int* arrived, void* out, int T_,
-                                 int nh, int nkv, int hd, int n_seqs, int n_pages, cudaStream_t stream) {
+                                 int nh, int nkv, int hd, int n_seqs, int n_pages, int early_keys, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256,
                "attention_split: head size %d is not 16, 32, 64, 128 or 256", hd);
@@ -824,7 +845,7 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
             }                                                                                                   \
             tq_launch(dim3(T_, nkv, n_splits), GQA_WARPS * 32, smem, stream)(kern,                              \
                 (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, positions, seq_of_token, page_table, table_stride, \
-                page_size, window, scale, partial, n_splits, arrived, (__nv_bfloat16*)out, nh, nkv, n_seqs, n_pages); \
+                page_size, window, scale, partial, n_splits, arrived, (__nv_bfloat16*)out, nh, nkv, n_seqs, n_pages, early_keys); \
         } while (0)
         if (hd == 64) GQA_LAUNCH(64); else GQA_LAUNCH(128);
 #undef GQA_LAUNCH
@@ -847,7 +868,7 @@ TQ_EXPORT int tq_attention_split(const void* q, const void* cache, int act_dtype
         }                                                                                                       \
         tq_launch(grid, SPLIT_WARPS * 32, ring, stream)(kern,                                                   \
             (const TA*)q, (const TA*)cache, positions, seq_of_token, page_table, table_stride, page_size, window, \
-            scale, partial, n_splits, arrived, (TA*)out, nh, nkv, n_seqs, n_pages);                             \
+            scale, partial, n_splits, arrived, (TA*)out, nh, nkv, n_seqs, n_pages, early_keys);                 \
     } while (0)
 #define SPLIT_GC(TA, LPK)                                                                                       \
     do { if (G == 1) { if (ring && split_stages<TA, LPK>() > 0) SPLIT_LAUNCH(TA, LPK, 1, (split_stages<TA, LPK>()));   \
@@ -920,7 +941,7 @@ TQ_EXPORT int tq_attention_split_static(const void* q, const void* cache, int ac
     }
     return tq_attention_split(q, cache, act_dtype, positions, seq_of_token, page_table, table_stride, page_size, window,
                               scale, tq_static_partial_addr[device], n_splits, tq_static_arrived_addr[device], out, T_, nh,
-                              nkv, hd, 0x7fffffff, 0x7fffffff, stream);
+                              nkv, hd, 0x7fffffff, 0x7fffffff, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------

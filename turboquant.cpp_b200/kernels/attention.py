@@ -101,6 +101,7 @@ def split_resident(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: 
     return r * 3 // 4 if gqa_mma_usable(dtype, n_heads, n_kv_heads, head_dim) else r
 
 
+EARLY_KEYS = os.environ.get("TQ_EARLY_KEYS", "1") not in ("", "0")     # decode steps ask for old keys before the wait on the kernel ahead
 GQA_MAX_SPLITS = 8       # measured on B200 (7 heads per KV head, 2,048 keys): 1, 2 and 8 tokens all run fastest with 8 ranges
 #                          (18-20 us; 16 ranges 20, 32 ranges 30: the last CTA's merge grows with the ranges x heads)
 
@@ -138,9 +139,12 @@ def tickets(device: torch.device) -> torch.Tensor:
 def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                     page_table: torch.Tensor, page_size: int, window: int, scale: float, out: torch.Tensor,
                     n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int,
-                    partial: Optional[torch.Tensor]) -> torch.Tensor:
+                    partial: Optional[torch.Tensor], early_keys: bool = False) -> torch.Tensor:
     """Attention with the keys of each (token, KV head) cut into n_splits ranges and merged, in one launch;
-    `partial` holds T * n_heads * n_splits * (head_dim + 2) floats of scratch (not needed with one range)."""
+    `partial` holds T * n_heads * n_splits * (head_dim + 2) floats of scratch (not needed with one range).
+    early_keys: the caller vouches that the kernel ahead of this one in the stream wrote nothing this launch reads
+    but the queries and the keys and values at the tokens' own positions (a decode step: one new token per
+    sequence); the kernel then asks for older keys before it waits for that kernel."""
     T = q.shape[0]
     want_int32(positions, "positions")
     want_int32(page_table, "page table")
@@ -159,7 +163,8 @@ def attention_split(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch
                                        c_int(page_size), c_int(window), c_float(scale),
                                        ptr(partial) if n_splits > 1 else None, c_int(n_splits), ptr(arrived),
                                        ptr(out), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-                                       c_int(page_table.shape[0]), c_int(cache_layer.shape[0]), stream()),
+                                       c_int(page_table.shape[0]), c_int(cache_layer.shape[0]),
+                                       c_int(1 if early_keys else 0), stream()),
           kernels=2 if n_splits > 1 and (T * head_chunks(n_heads, n_kv_heads) * n_kv_heads * n_splits
                                          > 2 * resident_ctas(q.device) or os.environ.get("TQ_SPLIT_RING", "0") not in ("", "0"))
           else 1)      # many short CTAs: the launcher adds a merge launch of its own

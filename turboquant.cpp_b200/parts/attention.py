@@ -134,7 +134,8 @@ class AttentionMixer(Mixer):
             partial = torch.empty(T * self.n_heads * n_splits * (self.head_dim + 2), dtype=torch.float32,
                                   device=xn.device) if n_splits > 1 else None
             KA.attention_split(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
-                               self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim, n_splits, partial)
+                               self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim, n_splits, partial,
+                               early_keys=KA.EARLY_KEYS and ctx.max_q_len == 1)
         else:
             KA.attention(q, cache.kv, ctx.positions, ctx.seq_of_token, cache.page_table, cache.page_size,
                          self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
