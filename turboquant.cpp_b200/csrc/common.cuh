@@ -144,6 +144,14 @@ __device__ __forceinline__ float tq_block_max(float v, float* scratch) {
 // the many small kernels of a decode step, inside CUDA graphs too.  TQ_NO_PDL=1 switches it off.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tq_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A pointer for use after a tq_grid_wait() that is not the kernel's first statement.  The compiler takes data behind
+// a `const T* __restrict__` parameter to be read-only for the whole kernel and may move loads of it above the wait's
+// inline assembly, i.e. before the kernel ahead has written it; the value returned here is opaque to it, and its
+// definition (a volatile statement of its own) stays behind the wait, so loads through it do too.
+template <typename T> __device__ __forceinline__ T* tq_fresh(T* p) {
+    asm volatile("" : "+l"(p) : : "memory");
+    return p;
+}
 __device__ __forceinline__ void tq_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 struct TqLaunch {

@@ -89,8 +89,9 @@ template <int T>
 __device__ __forceinline__ void gemv_stage_x(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ s_x, int K) {
     tq_grid_wait();                    // x is what the previous kernel wrote; the weights were asked for before
     tq_grid_launch_dependents();
+    const __nv_bfloat16* xs = tq_fresh(x);                 // loads of x stay behind the wait
     for (int i = threadIdx.x * 8; i < T * K; i += blockDim.x * 8)
-        *reinterpret_cast<uint4*>(s_x + i) = *reinterpret_cast<const uint4*>(x + i);
+        *reinterpret_cast<uint4*>(s_x + i) = *reinterpret_cast<const uint4*>(xs + i);
     __syncthreads();
 }
 

@@ -555,11 +555,12 @@ router_cluster_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const
     float* s_logit = reinterpret_cast<float*>(s_raw);                         // [E + 1] the logits of this block's token
     TA* s_x = reinterpret_cast<TA*>(s_raw + (((size_t)(E + 1) * 4 + 15) & ~(size_t)15));   // [T][H] the step's rows
     __shared__ SmallShared S;
+    const TA* xs = tq_fresh(x);                                               // loads of x stay behind the wait
     if (vec_x) {
         const int n16 = (int)((size_t)T_ * H * sizeof(TA) / 16);
-        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(x)[i];
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(xs)[i];
     } else {
-        for (int i = threadIdx.x; i < T_ * H; i += blockDim.x) s_x[i] = x[i];
+        for (int i = threadIdx.x; i < T_ * H; i += blockDim.x) s_x[i] = xs[i];
     }
     __syncthreads();
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // all blocks of the cluster run
@@ -673,8 +674,9 @@ router_tiny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     ask(warp, 0);
     tq_grid_wait();
     tq_grid_launch_dependents();
+    const __nv_bfloat16* xs = tq_fresh(x);                 // loads of x stay behind the wait
     for (int i = threadIdx.x * 8; i < T * H; i += blockDim.x * 8)
-        *reinterpret_cast<uint4*>(s_x + i) = *reinterpret_cast<const uint4*>(x + i);
+        *reinterpret_cast<uint4*>(s_x + i) = *reinterpret_cast<const uint4*>(xs + i);
     __syncthreads();
     // ---- logits (fp32 sums of the bf16 products, a lane's pieces in order, then the lanes by shuffles) ----
     for (int r0 = warp; r0 < rows; r0 += 2 * nwarps) {
