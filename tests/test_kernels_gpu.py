@@ -512,62 +512,6 @@ def test_qkv_rope_cache(nh, nkv, hd, pairing, dtype, tol):
     assert np.all(c[~written] == 0)
 
 
-@pytest.mark.parametrize("H,R,P_", [(2048, 8, 4), (3584, 3, 8), (72, 5, 2), (256, 40, 1)])
-def test_rmsnorm_adds_up_partial_sums_in_order(H, R, P_):
-    """y as [P, R, H] partial sums (a projection whose K was shared out): the kernel adds them up in order, then adds
-    the sum to x; the bits are those of the parts added to x one launch after the other."""
-    from turboquant_cpp_b200.kernels import elementwise as K
-    rng = np.random.default_rng(H + R)
-    x = dev(rng.normal(size=(R, H)) * 3)
-    w = dev(bf16_values(1 + 0.1 * rng.normal(size=H)), torch.bfloat16)
-    parts = dev(rng.normal(size=(P_, R, H)))
-    x1, x2 = x.clone(), x.clone()
-    out1 = torch.empty((R, H), dtype=torch.bfloat16, device=DEV)
-    out2 = torch.empty((R, H), dtype=torch.bfloat16, device=DEV)
-    K.rmsnorm(x1, w, 1e-6, out1, add=parts)
-    for p in range(P_ - 1):                                  # ((x + y0) + y1) + ...: the same sums one launch at a time
-        K.rmsnorm(x2, w, 1e-6, out2, add=parts[p])
-    K.rmsnorm(x2, w, 1e-6, out2, add=parts[P_ - 1])
-    assert torch.equal(out1, out2) and torch.equal(x1, x2)
-    # many rows, or a row list: no kernel of ours sums the parts there, the wrapper does
-    rows = dev(np.array([R - 1, 0]), torch.int32)
-    out3 = torch.empty((2, H), dtype=torch.bfloat16, device=DEV)
-    out4 = torch.empty((2, H), dtype=torch.bfloat16, device=DEV)
-    K.rmsnorm(x1, w, 1e-6, out3, add=parts, rows=rows)
-    K.rmsnorm(x1, w, 1e-6, out4, add=parts.sum(0), rows=rows)
-    assert torch.equal(out3, out4)
-
-
-@pytest.mark.parametrize("nh,nkv,hd,pairing", [(4, 4, 16, "half"), (5, 1, 48, "interleaved"), (16, 16, 128, "half"), (28, 4, 128, "half")])
-@pytest.mark.parametrize("P_", [1, 4])
-def test_qkv_rope_cache_from_partial_sums(nh, nkv, hd, pairing, P_):
-    """The projection as [P, T, width] float32 partial sums: added up in order and rounded to bfloat16 before the
-    bias, which gives the bits of the same projection handed over in bfloat16."""
-    from turboquant_cpp_b200.kernels import attention as KA
-    from turboquant_cpp_b200.parts.rotary import RotaryEncoding
-    rng = np.random.default_rng(nh + hd)
-    seq_lens, q_lens, page = [70, 130, 5], [3, 2, 1], 64
-    d = paged_inputs(rng, seq_lens, q_lens, nkv, hd, page, torch.bfloat16)
-    T = sum(q_lens)
-    width = (nh + 2 * nkv) * hd
-    parts = dev(rng.normal(size=(P_, T, width)))
-    whole = parts[0].clone()
-    for p in range(1, P_):
-        whole += parts[p]
-    bias = dev(bf16_values(rng.normal(size=width)), torch.bfloat16)
-    rot = RotaryEncoding(hd, 12345.0, 256, pairing)
-    rot.prepare(DEV)
-    cos, sin, _ = rot.tables()
-    pos, seq_of, table = (dev(d[k], torch.int32) for k in ("positions", "seq_of", "table"))
-    outs = []
-    for qkv in (parts, whole.to(torch.bfloat16)):
-        cache = torch.zeros((64, 2, nkv, page, hd), dtype=torch.bfloat16, device=DEV)
-        q = torch.empty((T, nh, hd), dtype=torch.bfloat16, device=DEV)
-        KA.qkv_rope_cache(qkv, bias, cos, sin, pairing, pos, seq_of, table, page, q, cache, nh, nkv, hd)
-        outs.append((q, cache))
-    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
-
-
 @pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (2, 50, 40), (3, 133, 264), (4, 4096, 3584), (1, 7, 8)])
 def test_gemv(T, N, K):
     """One to four tokens against bfloat16 weights: widths that are no multiple of the rows a warp or a block takes,

@@ -59,40 +59,20 @@ template <> struct Vec8<float> {
 // ---------------------------------------------------------------------------------------
 // A block walks (head, pair) indices of one token's fused QKV row; with few tokens several blocks share a row.
 // ---------------------------------------------------------------------------------------
-template <typename TA, typename TB, bool PARTS>
+template <typename TA, typename TB>
 __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __restrict__ bias,
                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                       int pairing, const int* __restrict__ positions,
                                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
                                       int table_stride, int page_size, TA* __restrict__ q_out,
                                       TA* __restrict__ cache, int heads, int nh, int nkv, int hd, int vec8,
-                                      int n_seqs, int n_pages, const float* __restrict__ parts, int n_parts,
-                                      size_t part_stride) {
+                                      int n_seqs, int n_pages) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int width = (nh + 2 * nkv) * hd;
     const TA* row = qkv + (size_t)t * width;
-    // parts: the projection came as n_parts float32 partial sums over shares of its K ([n_parts][T][width]); they are
-    // added up in order and the sum is rounded to the activation type, as the product in one piece would have been
-    const float* prow = PARTS ? parts + (size_t)t * width : nullptr;
-    auto summed8 = [&](size_t at, float (&f)[8]) {
-        Vec8<float>::load(prow + at, f);
-        for (int p = 1; p < n_parts; ++p) {
-            float g[8];
-            Vec8<float>::load(prow + (size_t)p * part_stride + at, g);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += g[e];
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = tq_to_float(tq_from_float<TA>(f[e]));
-    };
-    auto summed1 = [&](size_t at) {
-        float f = prow[at];
-        for (int p = 1; p < n_parts; ++p) f += prow[(size_t)p * part_stride + at];
-        return tq_to_float(tq_from_float<TA>(f));
-    };
     const int pos = positions[t];
     const float* cs_row = cos_t ? cos_t + (size_t)pos * half : nullptr;
     const float* sn_row = sin_t ? sin_t + (size_t)pos * half : nullptr;
@@ -111,13 +91,8 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
             const int j = idx / groups, i = (idx - j * groups) * 8;
             const TA* src = row + (size_t)j * hd;
             float a[8], c[8];
-            if constexpr (PARTS) {
-                summed8((size_t)j * hd + i, a);
-                summed8((size_t)j * hd + half + i, c);
-            } else {
-                Vec8<TA>::load(src + i, a);
-                Vec8<TA>::load(src + half + i, c);
-            }
+            Vec8<TA>::load(src + i, a);
+            Vec8<TA>::load(src + half + i, c);
             if (bias) {
                 float ba[8], bc[8];
                 Vec8<TB>::load(bias + (size_t)j * hd + i, ba);
@@ -153,8 +128,7 @@ __global__ void qkv_rope_cache_kernel(const TA* __restrict__ qkv, const TB* __re
         const TA* src = row + (size_t)j * hd;
         int ia, ib;
         if (pairing == 0) { ia = i; ib = i + half; } else { ia = 2 * i; ib = 2 * i + 1; }
-        float a = PARTS ? summed1((size_t)j * hd + ia) : tq_to_float(src[ia]);
-        float c = PARTS ? summed1((size_t)j * hd + ib) : tq_to_float(src[ib]);
+        float a = tq_to_float(src[ia]), c = tq_to_float(src[ib]);
         if (bias) { a += tq_to_float(bias[(size_t)j * hd + ia]); c += tq_to_float(bias[(size_t)j * hd + ib]); }
         const bool is_v = j >= nh + nkv;
         if (!is_v && cs_row) {
@@ -178,18 +152,14 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
                                 const float* cos_t, const float* sin_t, int pairing,
                                 const int* positions, const int* seq_of_token, const int* page_table,
                                 int table_stride, int page_size, void* q_out, void* cache, int write_kv,
-                                int T_, int nh, int nkv, int hd, int n_seqs, int n_pages, const float* parts,
-                                int n_parts, cudaStream_t stream) {
-    // parts != null: qkv is not read; the projection is the sum of n_parts float32 slices [T, width] at `parts`
-    // (a product whose K was shared out), rounded to the activation type act_dtype
+                                int T_, int nh, int nkv, int hd, int n_seqs, int n_pages, cudaStream_t stream) {
     if (T_ == 0) return 0;
-    TQ_REQUIRE(parts == nullptr || (n_parts >= 1 && ((uintptr_t)parts % 16) == 0), "qkv_rope_cache: %d partial sums at %p", n_parts, (const void*)parts);
     TQ_REQUIRE(hd % 2 == 0 && hd >= 2 && hd <= 2048, "qkv_rope_cache: head size %d must be even and <= 2048", hd);
     TQ_REQUIRE(pairing == 0 || pairing == 1, "qkv_rope_cache: pairing %d is neither half (0) nor interleaved (1)", pairing);
     TQ_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_rope_cache: cos and sin tables must come together");
     const int heads = write_kv ? nh + 2 * nkv : nh;
     const int esize = act_dtype == TQ_F32 ? 4 : 2;
-    const int vec8 = pairing == 0 && hd % 16 == 0 && (parts != nullptr || ((uintptr_t)qkv % 16) == 0) && ((uintptr_t)q_out % 16) == 0 &&
+    const int vec8 = pairing == 0 && hd % 16 == 0 && ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
                      ((uintptr_t)cache % 16) == 0 && ((size_t)hd * esize) % 16 == 0 &&
                      ((uintptr_t)cos_t % 16) == 0 && ((uintptr_t)sin_t % 16) == 0 &&
                      ((uintptr_t)bias % 16) == 0 && ((size_t)hd * (bias_dtype == TQ_F32 ? 4 : 2)) % 16 == 0;
@@ -200,19 +170,10 @@ TQ_EXPORT int tq_qkv_rope_cache(const void* qkv, int act_dtype, const void* bias
     // few tokens: several blocks share a token's row, so that the step still fills the GPU
     int chunks = T_ >= 512 ? 1 : (pairs + threads - 1) / threads;
     if (chunks > 64) chunks = 64;
-    if (parts) {
     TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
-        (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB, true>, 
+        (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB>, 
             (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
-            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8, n_seqs, n_pages, parts, n_parts,
-            (size_t)T_ * (size_t)((nh + 2 * nkv) * hd)))));
-    } else {
-    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(bias_dtype, TB,
-        (tq_launch(dim3(T_, chunks), threads, 0, stream)(qkv_rope_cache_kernel<TA, TB, false>, 
-            (const TA*)qkv, (const TB*)bias, cos_t, sin_t, pairing, positions, seq_of_token, page_table,
-            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8, n_seqs, n_pages, parts, n_parts,
-            (size_t)T_ * (size_t)((nh + 2 * nkv) * hd)))));
-    }
+            table_stride, page_size, (TA*)q_out, (TA*)cache, heads, nh, nkv, hd, vec8, n_seqs, n_pages))));
     TQ_CHECK_LAUNCH("qkv_rope_cache");
     return 0;
 }

@@ -91,8 +91,7 @@ template <> __device__ __forceinline__ void tq_store4<__nv_bfloat16>(__nv_bfloat
 #define RMS_VEC_GROUPS 8
 template <typename TY, typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* __restrict__ rows,
-                                   const TW* __restrict__ w, TO* __restrict__ out, int H, float eps, int y_parts,
-                                   size_t y_part_stride) {
+                                   const TW* __restrict__ w, TO* __restrict__ out, int H, float eps) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
@@ -111,33 +110,9 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ x, const TY* __restrict__
             g[c] = tq_load4<TW>(w + 4 * i);                 // fetched now, so that it arrives during the reduction
             float4 a = tq_load4<float>(xr + 4 * i);
             if (yr) { const float4 b = tq_load4<TY>(yr + 4 * i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
-            if (y_parts <= 1) {
-                if (write_back) tq_store4<float>(xr + 4 * i, a);
-                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-            }
+            if (write_back) tq_store4<float>(xr + 4 * i, a);
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
             v[c] = a;
-        }
-    }
-    if (y_parts > 1) {
-        // y came as partial sums (a product whose K was shared out): the further parts are added in order,
-        // ((x + y0) + y1) + ..., in passes of their own so that the usual case above keeps all its loads in flight
-        for (int p = 1; p < y_parts; ++p) {
-#pragma unroll
-            for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
-                const int i = threadIdx.x + c * blockDim.x;
-                if (i < nvec) {
-                    const float4 b = tq_load4<TY>(yr + (size_t)p * y_part_stride + 4 * i);
-                    v[c].x += b.x; v[c].y += b.y; v[c].z += b.z; v[c].w += b.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < RMS_VEC_GROUPS; ++c) {
-            const int i = threadIdx.x + c * blockDim.x;
-            if (i < nvec) {
-                if (write_back) tq_store4<float>(xr + 4 * i, v[c]);
-                ss += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
-            }
         }
     }
     ss = tq_block_sum(ss, scratch);
@@ -205,15 +180,10 @@ rmsnorm_warp_kernel(float* __restrict__ x, const TY* __restrict__ y, const int* 
     }
 }
 
-// y_parts > 1: y is [y_parts][T][H], partial sums that are added up in order before they are added to x (rows of the
-// few-row kernel only: a decode step's projection whose K was shared out).
 TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, const void* w, int w_dtype,
-                         void* out, int out_dtype, int R, int H, float eps, int y_parts, long long y_part_stride,
-                         cudaStream_t stream) {
+                         void* out, int out_dtype, int R, int H, float eps, cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
-    TQ_REQUIRE(y_parts >= 1 && (y_parts == 1 || (y != nullptr && rows == nullptr && R < 512 && H % 4 == 0 && H / 4 <= 1024 * RMS_VEC_GROUPS)),
-               "rmsnorm: %d partial sums are taken for up to 511 rows of a width that is a multiple of 4, without a row list", y_parts);
     if (H % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
         ((uintptr_t)out % 16) == 0) {
         if (R >= 512 && H / 4 <= 32 * RMS_WARP_GROUPS) {
@@ -229,12 +199,11 @@ TQ_EXPORT int tq_rmsnorm(float* x, const void* y, int y_dtype, const int* rows, 
         if (H / 4 <= vthreads * RMS_VEC_GROUPS) {
             TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
                 (tq_launch(R, vthreads, 0, stream)(rmsnorm_vec_kernel<TY, TW, TO>, x, (const TY*)y, rows, (const TW*)w,
-                                                                            (TO*)out, H, eps, y_parts, (size_t)y_part_stride)))));
+                                                                            (TO*)out, H, eps)))));
             TQ_CHECK_LAUNCH("rmsnorm");
             return 0;
         }
     }
-    TQ_REQUIRE(y_parts == 1, "rmsnorm: %d partial sums need 16-byte aligned tensors", y_parts);
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
         (tq_launch(R, threads, 0, stream)(rmsnorm_kernel<TY, TW, TO>, x, (const TY*)y, rows, (const TW*)w,

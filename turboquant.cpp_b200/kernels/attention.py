@@ -27,25 +27,18 @@ def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optiona
                    n_heads: int, n_kv_heads: int, head_dim: int) -> None:
     """Bias and rotary encoding on the fused projection qkv [T, (nh+2nkv)*hd]; queries to q_out
     [T, nh, hd]; keys and values into cache_layer [pages, 2, nkv, page_size, hd] (None: the layer
-    reads another layer's cache, so only the queries are produced).  qkv may also be [P, T, width] float32: the
-    partial sums of a product whose K was shared out; they are added up in order and rounded to q_out's type
-    before the bias, as the product in one piece would have been."""
-    parts = None
-    if qkv.dim() == 3:
-        want_f32(qkv, "partial sums of the projection")
-        parts = qkv
-    T = qkv.shape[-2]
+    reads another layer's cache, so only the queries are produced)."""
+    T = qkv.shape[0]
     if cos is not None:
         want_f32(cos, "cos table")
         want_f32(sin, "sin table")
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_qkv_rope_cache(
-        ptr(qkv) if parts is None else None, c_int(code(q_out.dtype)), ptr(bias), c_int(code(bias.dtype) if bias is not None else 0),
+        ptr(qkv), c_int(code(qkv.dtype)), ptr(bias), c_int(code(bias.dtype) if bias is not None else 0),
         ptr(cos), ptr(sin), c_int(PAIRING[pairing]), ptr(positions), ptr(seq_of_token), ptr(page_table),
         c_int(page_table.shape[1]), c_int(page_size), ptr(q_out), ptr(cache_layer),
         c_int(0 if cache_layer is None else 1), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
-        c_int(page_table.shape[0]), c_int(0 if cache_layer is None else cache_layer.shape[0]),
-        ptr(parts), c_int(parts.shape[0] if parts is not None else 0), stream()))
+        c_int(page_table.shape[0]), c_int(0 if cache_layer is None else cache_layer.shape[0]), stream()))
 
 
 def attention(q: torch.Tensor, cache_layer: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,

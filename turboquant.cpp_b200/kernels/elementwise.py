@@ -27,24 +27,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             add: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """RMSNorm of rows of the float32 residual stream x [T, H] into out [R, H].
 
-    add:  the norm is taken of x + add (summed in float32); add may be [P, T, H] float32, the partial sums of a
-          product whose K was shared out (up to 511 rows): they are added up in order first.
+    add:  the norm is taken of x + add (summed in float32).
     rows: out[r] = norm of row rows[r] and x is left alone; without rows, R = T and the sum
           x + add is written back into x."""
     want_f32(x, "the residual stream")
     R, H = out.shape
     if rows is not None:
         want_int32(rows, "rows")
-    parts = 1
-    if add is not None and add.dim() == 3:
-        want_f32(add, "partial sums")
-        parts = add.shape[0]
-        if parts > 1 and (rows is not None or R >= 512):
-            add, parts = add.sum(0), 1          # not a decode step: no kernel of ours for it
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_rmsnorm(ptr(x), ptr(add), c_int(code(add.dtype) if add is not None else 0), ptr(rows),
                                ptr(weight), c_int(code(weight.dtype)), ptr(out), c_int(code(out.dtype)),
-                               c_int(R), c_int(H), c_float(eps), c_int(parts), c_longlong(x.shape[0] * H), stream()))
+                               c_int(R), c_int(H), c_float(eps), stream()))
     return out
 
 

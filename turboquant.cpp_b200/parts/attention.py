@@ -9,14 +9,12 @@ reference's Gemma branch :1646-1654."""
 from __future__ import annotations
 
 import math
-import os
 from typing import List, Optional
 
 import torch
 
 from ..kernels import attention as KA
 from ..kernels import elementwise as KE
-from ..kernels import gemm_tc as KT
 from ..kernels import gemv as KG
 from ..kernels.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
@@ -60,13 +58,6 @@ class AttentionMixer(Mixer):
             bdt = torch.float32 if any(b.dtype == torch.float32 for b in bs) else bs[0].dtype
             self.b_qkv = torch.cat([b.to(bdt) for b in bs], dim=0).contiguous()
         self.w_o = store.get(p + "o_proj.weight")
-        # bfloat16 runs keep a second copy of both projections in the tensor-core kernel's packed layout, for steps
-        # of a few tokens (see _tensor_core_projections)
-        self.w_qkv_packed = self.w_o_packed = None
-        if (store.run_dtype == torch.bfloat16 and self.TC_PROJECTION_MAX_TOKENS > 0 and KT.packable(self.w_qkv)
-                and KT.packable(self.w_o)):
-            self.w_qkv_packed = KT.pack_weights(self.w_qkv, False)
-            self.w_o_packed = KT.pack_weights(self.w_o, False)
         if self.position is not None:
             self.position.prepare(store.device)
 
@@ -74,8 +65,6 @@ class AttentionMixer(Mixer):
         names = ["attention", "elementwise"]
         if getattr(self, "run_dtype", None) == torch.bfloat16:
             names.append("gemv")
-            if self.TC_PROJECTION_MAX_TOKENS > 0:
-                names.append("gemm_tc")
         if getattr(self, "run_dtype", None) == torch.bfloat16 and self.head_dim in (64, 128):
             names.append("attention_prefill")
         return names
@@ -106,13 +95,7 @@ class AttentionMixer(Mixer):
                              cache.page_size, q, cache.kv if cache.writes else None, self.n_heads, self.n_kv_heads,
                              self.head_dim)
             return self._attend(q, T, act, ctx, cache)
-        tc = self._tensor_core_projections(T, xn, tables)
-        if tc:
-            qkv = self._project(xn, self.w_qkv_packed, ctx)
-            if qkv.dim() == 2:
-                qkv = qkv.unsqueeze(0)
-        else:
-            qkv = linear(xn, self.w_qkv, out_dtype=act)
+        qkv = linear(xn, self.w_qkv, out_dtype=act)
         bias = self.b_qkv
         if self.position is not None and tables is None:
             # an encoding that is not a table-driven rotation: the bias first, then the encoding's own pass over
@@ -126,29 +109,9 @@ class AttentionMixer(Mixer):
         KA.qkv_rope_cache(qkv, bias, cos, sin, pairing, ctx.positions, ctx.seq_of_token, cache.page_table,
                           cache.page_size, q, cache.kv if cache.writes else None,
                           self.n_heads, self.n_kv_heads, self.head_dim)
-        return self._attend(q, T, act, ctx, cache, tc)
+        return self._attend(q, T, act, ctx, cache)
 
-    # Steps of 3 to this many tokens compute both projections with the tensor-core kernel instead of the library's:
-    # that kernel starts streaming its weights while the kernel ahead of it still runs (programmatic dependent
-    # launch; the library's product starts its loads when the norm, or the attention, has finished), and with K
-    # in shares enough CTAs stream at once.  The partial sums are added up by the kernels that read them anyway.
-    TC_PROJECTION_MAX_TOKENS = int(os.environ.get("TQ_TC_PROJ_MAX", "48"))
-    partial_sums_ok = False      # set by a block whose norm adds up [P, T, hidden] partial sums
-
-    def _tensor_core_projections(self, T: int, xn: torch.Tensor, tables) -> bool:
-        return (self.w_qkv_packed is not None and KG.FUSED_MAX_TOKENS < T <= self.TC_PROJECTION_MAX_TOKENS
-                and (self.position is None or tables is not None) and KT.usable(xn, self.w_qkv_packed))
-
-    def _project(self, x: torch.Tensor, w: "KT.PackedWeights", ctx: StepContext) -> torch.Tensor:
-        """x . w^T in float32 on the tensor cores, as [T, N] or, with K in P shares, as [P, T, N] partial sums."""
-        T = x.shape[0]
-        tile = KT.token_tile_for(T, 1)
-        splits = KT.k_splits_for(T, w.n, w.k, tile, KA.resident_ctas(x.device) // 2)
-        out = torch.empty((splits, T, w.n) if splits > 1 else (T, w.n), dtype=torch.float32, device=x.device)
-        return KT.gemm_tc(x, w, out, None, tile, status=ctx.status, k_splits=splits, early_weights=True)
-
-    def _attend(self, q: torch.Tensor, T: int, act: torch.dtype, ctx: StepContext, cache: LayerCache,
-                tc: bool = False) -> torch.Tensor:
+    def _attend(self, q: torch.Tensor, T: int, act: torch.dtype, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         """Attention of the step's queries over the cache (the step's keys and values are in it), then the output
         projection."""
         xn = q
@@ -178,9 +141,6 @@ class AttentionMixer(Mixer):
                          self.window, self.scale, o, self.n_heads, self.n_kv_heads, self.head_dim)
         if KG.pays(o, self.w_o):
             return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=o.device))
-        if tc and KT.usable(o, self.w_o_packed):
-            y = self._project(o, self.w_o_packed, ctx)
-            return y if y.dim() == 2 or self.partial_sums_ok else y.sum(0)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
 

@@ -112,8 +112,6 @@ class Part:
 
 
 class Norm(Part):
-    sums_parts = False       # add_forward also takes y as [P, T, size] float32 partial sums (a product whose K was shared out)
-
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
                 add: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Norm of the rows of x (of x + add if add is given); with `rows`, of those rows only.
@@ -152,8 +150,6 @@ class Mixer(Part):
         return True
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
-        """-> [T, hidden].  A mixer with an attribute `partial_sums_ok` that a block has set to True may instead
-        return [P, T, hidden] float32 partial sums, which the block's norm adds up (Norm.sums_parts)."""
         raise NotImplementedError
 
 

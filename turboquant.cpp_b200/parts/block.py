@@ -17,10 +17,6 @@ from .base import Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, StateNeed
 class PreNormBlock(Block):
     def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
-        # a mixer that can hand its output on as partial sums ([P, T, hidden]) may do so if the norm behind it adds
-        # them up while it adds them to the residual stream
-        if getattr(ffn_norm, "sums_parts", False) and hasattr(mixer, "partial_sums_ok"):
-            mixer.partial_sums_ok = True
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]

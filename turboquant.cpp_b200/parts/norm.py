@@ -27,8 +27,6 @@ class RMSNorm(Norm):
     def kernels(self) -> List[str]:
         return ["elementwise"]
 
-    sums_parts = True      # add_forward takes y as [P, T, size] float32 partial sums and adds them up in order
-
     def forward(self, x, out_dtype, rows=None, add=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=out_dtype, device=x.device)
