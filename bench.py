@@ -144,6 +144,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="float32: the true 32-bit path of the whole model (exact kernels, SGEMM without TF32)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
                     "prefill to this file (torch profiler; not part of any timed number)")
@@ -175,7 +177,8 @@ def main() -> int:
     n = model_numbers(cfg, args.layers)
     torch.cuda.set_device(0)
     t_load = time.time()
-    model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    EL = 2 if args.dtype == "bfloat16" else 4                 # bytes per weight and per cached value
+    model = tq.random_model(cfg, seed=0, dtype=args.dtype, device="cuda:0")
     torch.cuda.synchronize()
     print(f"[bench] model with {args.layers} layers ready in {time.time() - t_load:.1f} s", file=sys.stderr, flush=True)
     rng = np.random.default_rng(0)
@@ -229,7 +232,7 @@ def main() -> int:
     clocks.start()
     main_run = run_decode(args.batch, args.steps, args.warmup, want_experts=True)
     clock_rec = clocks.stop()
-    dbytes = decode_bytes(n, main_run["distinct"], args.batch, main_run["ctx_tokens"])
+    dbytes = decode_bytes(n, main_run["distinct"], args.batch, main_run["ctx_tokens"], EL)
     achieved = dbytes / (main_run["ms_per_step"] * 1e-3) / 1e9
 
     # ---- end to end through the Python entry point ---------------------------------------------------
@@ -254,7 +257,7 @@ def main() -> int:
                       "this architecture; timed on 1 and 2 layers of these sizes and scaled to this run's layers "
                       "(tests/golden/reference_cpu_timing.txt); other hardware, so context, not a race",
                       "ms_per_token_1_layer": ref_ms.get(1), "ms_per_token_2_layers": ref_ms.get(2)} if ref_rate else None),
-        "dtype": "bf16", "data": "synthetic token ids, seeded random weights", "impl": "ours",
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic token ids, seeded random weights", "impl": "ours",
         "config": {"model": model_name, "layers": args.layers, "layers_of_model": FULL_LAYERS,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "experts": cfg["num_experts"],
@@ -289,7 +292,8 @@ def main() -> int:
         torch.cuda.empty_cache()
         fl = prefill_flops(n, PROMPT)
         out["prefill"] = {"value": round(PROMPT / best * 1e3, 1), "tokens": PROMPT, "ms": round(best, 3),
-                          "frac": round(fl / (best * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                          # (no measured peak for float32 products without TF32: no fraction there)
+                          "frac": round(fl / (best * 1e-3) / (pk["bf16_tflops"] * 1e12), 4) if EL == 2 else None}
         k_pts = max(8, min(args.steps, 32))
         out["points"], out["points_frac"] = {}, {}
         # from 2,048-token prompts, and with the context at 4,096 by the last timed step
@@ -297,7 +301,7 @@ def main() -> int:
                                     ("decode_b1_ctx4096", 1, CONTEXT - k_pts - 3), ("decode_b8_ctx4096", 8, CONTEXT - k_pts - 3),
                                     ("decode_b64_ctx4096", 64, CONTEXT - k_pts - 3)):
             r = run_decode(batch, k_pts, 3, want_experts=True, prompt=prompt)
-            by = decode_bytes(n, r["distinct"], batch, r["ctx_tokens"])
+            by = decode_bytes(n, r["distinct"], batch, r["ctx_tokens"], EL)
             out["points"][name] = round(r["tok_s"], 1)
             out["points_frac"][name] = round(by / (r["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     if args.kernel_table:
