@@ -641,10 +641,13 @@ def test_moe_align(T, E, k):
     assert np.all(covered == 1)
 
 
-@pytest.mark.parametrize("R,N,K,G", [(1, 32, 64, 8), (130, 48, 192, 6), (77, 100, 50, 3), (200, 70, 130, 5)])
+@pytest.mark.parametrize("R,N,K,G", [(1, 32, 64, 8), (130, 48, 192, 6), (77, 100, 50, 3), (200, 70, 130, 5), (9, 24, 4100, 2)])
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-def test_grouped_gemm(R, N, K, G, swiglu, dtype, tol):
+@pytest.mark.parametrize("few_rows", [False, True])
+def test_grouped_gemm(R, N, K, G, swiglu, dtype, tol, few_rows):
+    """few_rows: the kernel of decode steps (a stream of the weights for up to eight rows of a tile at a time); it
+    takes any number of rows per tile, so the same cases hold for it."""
     from turboquant_cpp_b200.kernels import moe as KM
     rng = np.random.default_rng(R + N)
     a = bf16_values(rng.normal(size=(R, K)))
@@ -657,7 +660,7 @@ def test_grouped_gemm(R, N, K, G, swiglu, dtype, tol):
     order = lay.sorted_pair.cpu().numpy()[:R]
     a_sorted = a[order]
     out = torch.full((R, N), float("nan"), dtype=dtype, device=DEV)
-    KM.grouped_gemm(dev(a_sorted, dtype), dev(w, dtype), out, lay, swiglu)
+    KM.grouped_gemm(dev(a_sorted, dtype), dev(w, dtype), out, lay, swiglu, few_rows=few_rows)
     want = np.zeros((R, N))
     for r in range(R):
         e = ids[order[r], 0]
@@ -668,7 +671,7 @@ def test_grouped_gemm(R, N, K, G, swiglu, dtype, tol):
     close(out, want, tol)
     # one group, no layout (the shared expert's products)
     out1 = torch.full((R, N), float("nan"), dtype=dtype, device=DEV)
-    KM.grouped_gemm(dev(a, dtype), dev(w[:1], dtype), out1, None, swiglu)
+    KM.grouped_gemm(dev(a, dtype), dev(w[:1], dtype), out1, None, swiglu, few_rows=few_rows)
     w0 = w[0]
     want1 = P.silu(a @ w0[:N].T) * (a @ w0[N:].T) if swiglu else a @ w0.T
     close(out1, want1, tol)

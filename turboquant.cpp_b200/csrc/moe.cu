@@ -1056,14 +1056,181 @@ grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same product for tiles of a few rows (decode steps), as a stream of the weights: a block stages up to
+// GV_ROWS rows of its tile in shared memory (in pieces of GV_KC values of K) and each warp computes four output
+// columns (two with SwiGLU: a gate and an up row each) for all of them, a lane taking every 32nd group of four values of K, the lanes' sums added by shuffles.
+// The tiled kernel above reads a 64-row tile's worth of weights for however few rows the tile holds and keeps few
+// loads in flight; this one keeps several 16-byte pieces of a weight row in flight per lane (measured on B200 in
+// float32 at 60 experts of 1408 x 2048 with a shared expert of 5632: a decode step of 8 tokens 39.0 -> 18.8 ms, of one
+// token 18.8 -> 6.1 ms).  fp32 multiply-adds in a fixed order that
+// depends on K alone: a row's result does not depend on the tile it falls in or on the rest of the batch.
+// ---------------------------------------------------------------------------------------
+#define GV_ROWS 8
+#define GV_WARPS 8
+#define GV_KC 2048                 // values of K per piece: 8 rows x 2048 floats = 64 KiB of shared memory
+#define GV_FLY 4                   // 16-byte pieces of a weight row a lane has in flight
+
+// four weights at p as floats (16-byte or 8-byte load; the caller made sure of the alignment)
+template <typename T> __device__ __forceinline__ float4 gv_load4(const T* p);
+template <> __device__ __forceinline__ float4 gv_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 gv_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename TA, typename TW, typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ C,
+                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ tile_count, const int* __restrict__ n_tiles,
+                    int R, int N, int K, int tile_rows, int vec) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ __align__(16) float s_rows[];          // [GV_ROWS][GV_KC]
+    int expert = 0, row0, rows;
+    if (tile_expert) {
+        if ((int)blockIdx.y >= n_tiles[0]) return;
+        expert = tile_expert[blockIdx.y];
+        row0 = tile_row0[blockIdx.y];
+        rows = tile_count[blockIdx.y];
+    } else {
+        row0 = blockIdx.y * tile_rows;
+        if (row0 >= R) return;
+        rows = min(tile_rows, R - row0);
+    }
+    constexpr int S = SWIGLU ? 2 : 1;
+    constexpr int COLS = SWIGLU ? 2 : 4;                               // output columns of a warp: 32 sums per lane either way
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int Nw = SWIGLU ? 2 * N : N;
+    const TW* Wg = W + (size_t)expert * Nw * K;
+    const int n_first = (blockIdx.x * GV_WARPS + warp) * COLS;         // this warp's columns
+    for (int rb = 0; rb < rows; rb += GV_ROWS) {                       // usually one trip: a tile of a decode step is short
+        const int nr = min(GV_ROWS, rows - rb);
+        float acc[COLS][S][GV_ROWS];
+#pragma unroll
+        for (int c = 0; c < COLS; ++c)
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r) acc[c][s][r] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += GV_KC) {
+            const int kc = min(GV_KC, K - k0);
+            __syncthreads();                                           // the piece before this one has been used
+            for (int i = threadIdx.x; i < nr * kc; i += blockDim.x) {
+                const int r = i / kc, kk = i - r * kc;
+                s_rows[r * GV_KC + kk] = tq_to_float(A[(size_t)(row0 + rb + r) * K + k0 + kk]);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int c = 0; c < COLS; ++c) {
+                const int n = n_first + c;
+                if (n < N) {                                           // uniform across the warp
+#pragma unroll
+                    for (int s = 0; s < S; ++s) {
+                        const TW* wrow = Wg + (size_t)(s * N + n) * K + k0;
+                        // a lane takes every 32nd group of four values; GV_FLY groups are asked for before the first is used
+                        for (int kb = lane * 4; kb < kc; kb += 128 * GV_FLY) {
+                            float4 w4[GV_FLY];
+#pragma unroll
+                            for (int f = 0; f < GV_FLY; ++f) {
+                                const int kk = kb + 128 * f;
+                                if (vec) {
+                                    w4[f] = kk < kc ? gv_load4<TW>(wrow + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                } else {
+                                    w4[f].x = kk < kc ? tq_to_float(wrow[kk]) : 0.f;
+                                    w4[f].y = kk + 1 < kc ? tq_to_float(wrow[kk + 1]) : 0.f;
+                                    w4[f].z = kk + 2 < kc ? tq_to_float(wrow[kk + 2]) : 0.f;
+                                    w4[f].w = kk + 3 < kc ? tq_to_float(wrow[kk + 3]) : 0.f;
+                                }
+                            }
+#pragma unroll
+                            for (int f = 0; f < GV_FLY; ++f) {
+                                const int kk = kb + 128 * f;
+                                if (kk < kc) {
+#pragma unroll
+                                    for (int r = 0; r < GV_ROWS; ++r) {
+                                        if (r < nr) {
+                                            // values of the row past the piece's end are not read: their weights are zero
+                                            const float* a = s_rows + r * GV_KC + kk;
+                                            float t = acc[c][s][r];
+                                            t = fmaf(a[0], w4[f].x, t);
+                                            if (kk + 1 < kc) t = fmaf(a[1], w4[f].y, t);
+                                            if (kk + 2 < kc) t = fmaf(a[2], w4[f].z, t);
+                                            if (kk + 3 < kc) t = fmaf(a[3], w4[f].w, t);
+                                            acc[c][s][r] = t;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+            const int n = n_first + c;
+            if (n < N) {
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r) {
+                    if (r < nr) {
+                        float v = tq_warp_sum(acc[c][0][r]);
+                        if (SWIGLU) {
+                            const float u = tq_warp_sum(acc[c][S - 1][r]);
+                            v = v / (1.0f + expf(-v)) * u;
+                        }
+                        if (lane == 0) C[(size_t)(row0 + rb + r) * N + n] = tq_from_float<TO>(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// tile_rows: the rows of a tile when there is no tile list (one group); few_rows != 0 selects this kernel in
+// tq_grouped_gemm.
+template <typename TA, typename TW, typename TO, bool SWIGLU>
+int launch_grouped_gemv(const void* A, const void* W, void* C, const int* te, const int* tr, const int* tc, const int* nt,
+                        int by, int R, int N, int K, int tile_rows, cudaStream_t stream) {
+    auto kern = grouped_gemv_kernel<TA, TW, TO, SWIGLU>;
+    const int smem = GV_ROWS * GV_KC * (int)sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) TQ_FAIL(-1, "grouped_gemm: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    constexpr int cols = GV_WARPS * (SWIGLU ? 2 : 4);
+    dim3 grid((N + cols - 1) / cols, by);
+    // 16-byte (8-byte) loads of four weights: rows of K values that start on such a boundary
+    const int vec = K % 4 == 0 && ((uintptr_t)W % (4 * sizeof(TW))) == 0;
+    tq_launch(grid, GV_WARPS * 32, smem, stream)(kern, (const TA*)A, (const TW*)W, (TO*)C, te, tr, tc, nt, R, N, K, tile_rows, vec);
+    return 0;
+}
+
 TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
                               const int* tile_expert, const int* tile_row0, const int* tile_count,
-                              const int* n_tiles, int max_tiles, int R, int N, int K, int swiglu,
+                              const int* n_tiles, int max_tiles, int R, int N, int K, int swiglu, int few_rows,
                               cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
     TQ_REQUIRE(R > 0 && N > 0 && K > 0, "grouped_gemm: bad sizes R=%d N=%d K=%d", R, N, K);
     const int by = tile_expert ? max_tiles : (R + GG_BM - 1) / GG_BM;
     TQ_REQUIRE(by <= 65535, "grouped_gemm: %d row tiles exceed the grid limit", by);
+    if (few_rows) {
+        // tiles of a few rows each (a decode step): the weight-stream form
+        int rc = 0;
+#define GV_LAUNCH(SW)                                                                                   \
+        TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                      \
+            (rc = launch_grouped_gemv<TA, TW, TO, SW>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream)))))
+        if (swiglu) { GV_LAUNCH(true); } else { GV_LAUNCH(false); }
+#undef GV_LAUNCH
+        if (rc) return rc;
+        TQ_CHECK_LAUNCH("grouped_gemv");
+        return 0;
+    }
     dim3 grid((N + GG_BN - 1) / GG_BN, by);
 #define GG_LAUNCH(SW)                                                                                   \
     TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                          \

@@ -130,9 +130,11 @@ def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Optional[ExpertLayout],
-                 swiglu: bool) -> torch.Tensor:
+                 swiglu: bool, few_rows: bool = False) -> torch.Tensor:
     """Exact (CUDA-core, fp32 accumulation) grouped product.  a [R, K]; w [G, Nw, K] with Nw = N,
-    or 2N when swiglu (gate rows, then up rows); out [R, N].  layout None: one group (G = 1)."""
+    or 2N when swiglu (gate rows, then up rows); out [R, N].  layout None: one group (G = 1).
+    few_rows: the tiles hold a few rows each (a decode step): the kernel that streams the weights once per eight
+    rows of a tile instead of the tiled one (any number of rows is right, many are slow)."""
     R, K = a.shape
     N = out.shape[1]
     if w.dim() == 2:
@@ -145,7 +147,8 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Op
         ptr(a), c_int(code(a.dtype)), ptr(w), c_int(code(w.dtype)), ptr(out), c_int(code(out.dtype)),
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None,
         ptr(lo.tile_count) if lo else None, ptr(lo.n_tiles) if lo else None,
-        c_int(lo.max_tiles if lo else 0), c_int(R), c_int(N), c_int(K), c_int(1 if swiglu else 0), stream()))
+        c_int(lo.max_tiles if lo else 0), c_int(R), c_int(N), c_int(K), c_int(1 if swiglu else 0),
+        c_int(1 if few_rows else 0), stream()))
     return out
 
 

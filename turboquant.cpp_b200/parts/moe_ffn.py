@@ -133,6 +133,7 @@ class MoEFeedForward(FeedForward):
         return cls._side_streams[key]
 
     EARLY_WEIGHTS = os.environ.get("TQ_EARLY_WEIGHTS", "1") not in ("", "0")
+    EXACT_FEW_ROWS = int(os.environ.get("TQ_EXACT_FEW_ROWS", "16"))      # steps of up to this many tokens take the exact kernels' weight-stream form
 
     def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
@@ -140,7 +141,11 @@ class MoEFeedForward(FeedForward):
         weights and the layout were there before that product started, so it may stream weights while that runs."""
         if isinstance(w, KT.PackedWeights):
             return KT.gemm_tc(x, w, out, layout, token_tile, status=status, early_weights=early and self.EARLY_WEIGHTS)
-        return KM.grouped_gemm(x, w, out, layout, swiglu)
+        # the exact kernels: tiles of a few rows (decode steps) stream the weights; a group's tile holds at most the
+        # step's tokens, and the one-group product (the shared expert) all of them
+        rows = x.shape[0]
+        few = rows <= self.EXACT_FEW_ROWS if layout is None else rows <= self.EXACT_FEW_ROWS * self.top_k
+        return KM.grouped_gemm(x, w, out, layout, swiglu, few_rows=few)
 
     def _joint_launches(self, T: int, tile: int, act, dev) -> bool:
         """Whether the shared expert's two products ride in the routed experts' launches, their tiles ahead of the
