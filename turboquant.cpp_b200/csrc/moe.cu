@@ -1058,12 +1058,12 @@ grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
 
 // ---------------------------------------------------------------------------------------
 // The same product for tiles of a few rows (decode steps), as a stream of the weights: a block stages up to
-// GV_ROWS rows of its tile in shared memory (in pieces of GV_KC values of K) and each warp computes four output
-// columns (two with SwiGLU: a gate and an up row each) for all of them, a lane taking every 32nd group of four values of K, the lanes' sums added by shuffles.
+// GV_ROWS rows of its tile in shared memory (in pieces of GV_KC values of K) and each warp computes one output
+// column (with SwiGLU: from a gate and an up row) for all of them, a lane taking every 32nd group of four values of K, the lanes' sums added by shuffles.
 // The tiled kernel above reads a 64-row tile's worth of weights for however few rows the tile holds and keeps few
 // loads in flight; this one keeps several 16-byte pieces of a weight row in flight per lane (measured on B200 in
-// float32 at 60 experts of 1408 x 2048 with a shared expert of 5632: a decode step of 8 tokens 39.0 -> 18.8 ms, of one
-// token 18.8 -> 6.1 ms).  fp32 multiply-adds in a fixed order that
+// float32 at 60 experts of 1408 x 2048 with a shared expert of 5632: a decode step of 8 tokens 39.0 -> 21 ms, of one
+// token 18.8 -> 5.6 ms; four columns per warp were 10 % faster at 8 tokens and took six times as long to compile).  fp32 multiply-adds in a fixed order that
 // depends on K alone: a row's result does not depend on the tile it falls in or on the rest of the batch.
 // ---------------------------------------------------------------------------------------
 #define GV_ROWS 8
@@ -1102,7 +1102,7 @@ grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
         rows = min(tile_rows, R - row0);
     }
     constexpr int S = SWIGLU ? 2 : 1;
-    constexpr int COLS = SWIGLU ? 2 : 4;                               // output columns of a warp: 32 sums per lane either way
+    constexpr int COLS = 1;                                            // output columns of a warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int Nw = SWIGLU ? 2 * N : N;
     const TW* Wg = W + (size_t)expert * Nw * K;
@@ -1119,9 +1119,12 @@ grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
         for (int k0 = 0; k0 < K; k0 += GV_KC) {
             const int kc = min(GV_KC, K - k0);
             __syncthreads();                                           // the piece before this one has been used
-            for (int i = threadIdx.x; i < nr * kc; i += blockDim.x) {
-                const int r = i / kc, kk = i - r * kc;
-                s_rows[r * GV_KC + kk] = tq_to_float(A[(size_t)(row0 + rb + r) * K + k0 + kk]);
+            // all GV_ROWS rows of the piece, rows the tile does not have and values past the piece's end as zeros: the
+            // sums below then need no conditions
+            const int kc4 = (kc + 3) & ~3;
+            for (int i = threadIdx.x; i < GV_ROWS * kc4; i += blockDim.x) {
+                const int r = i / kc4, kk = i - r * kc4;
+                s_rows[r * GV_KC + kk] = (r < nr && kk < kc) ? tq_to_float(A[(size_t)(row0 + rb + r) * K + k0 + kk]) : 0.f;
             }
             __syncthreads();
 #pragma unroll
@@ -1148,21 +1151,16 @@ grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
                             }
 #pragma unroll
                             for (int f = 0; f < GV_FLY; ++f) {
-                                const int kk = kb + 128 * f;
-                                if (kk < kc) {
+                                const int kk = kb + 128 * f < kc ? kb + 128 * f : 0;   // a group past the end has zero weights: any staged values do
 #pragma unroll
-                                    for (int r = 0; r < GV_ROWS; ++r) {
-                                        if (r < nr) {
-                                            // values of the row past the piece's end are not read: their weights are zero
-                                            const float* a = s_rows + r * GV_KC + kk;
-                                            float t = acc[c][s][r];
-                                            t = fmaf(a[0], w4[f].x, t);
-                                            if (kk + 1 < kc) t = fmaf(a[1], w4[f].y, t);
-                                            if (kk + 2 < kc) t = fmaf(a[2], w4[f].z, t);
-                                            if (kk + 3 < kc) t = fmaf(a[3], w4[f].w, t);
-                                            acc[c][s][r] = t;
-                                        }
-                                    }
+                                for (int r = 0; r < GV_ROWS; ++r) {
+                                    const float4 a = *reinterpret_cast<const float4*>(s_rows + r * GV_KC + kk);
+                                    float t = acc[c][s][r];
+                                    t = fmaf(a.x, w4[f].x, t);
+                                    t = fmaf(a.y, w4[f].y, t);
+                                    t = fmaf(a.z, w4[f].z, t);
+                                    t = fmaf(a.w, w4[f].w, t);
+                                    acc[c][s][r] = t;
                                 }
                             }
                         }
@@ -1203,7 +1201,7 @@ int launch_grouped_gemv(const void* A, const void* W, void* C, const int* te, co
         if (e != cudaSuccess) TQ_FAIL(-1, "grouped_gemm: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    constexpr int cols = GV_WARPS * (SWIGLU ? 2 : 4);
+    constexpr int cols = GV_WARPS;
     dim3 grid((N + cols - 1) / cols, by);
     // 16-byte (8-byte) loads of four weights: rows of K values that start on such a boundary
     const int vec = K % 4 == 0 && ((uintptr_t)W % (4 * sizeof(TW))) == 0;
@@ -1219,13 +1217,18 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
     TQ_REQUIRE(R > 0 && N > 0 && K > 0, "grouped_gemm: bad sizes R=%d N=%d K=%d", R, N, K);
     const int by = tile_expert ? max_tiles : (R + GG_BM - 1) / GG_BM;
     TQ_REQUIRE(by <= 65535, "grouped_gemm: %d row tiles exceed the grid limit", by);
-    if (few_rows) {
-        // tiles of a few rows each (a decode step): the weight-stream form
+    // tiles of a few rows each (a decode step): the weight-stream form, for the type combinations the parts use
+    // (all float32; bfloat16 in and out; bfloat16 in, float32 out); others take the tiled kernel
+    const bool gv_types = (a_dtype == TQ_F32 && w_dtype == TQ_F32 && c_dtype == TQ_F32) ||
+                          (a_dtype == TQ_BF16 && w_dtype == TQ_BF16);
+    if (few_rows && gv_types) {
         int rc = 0;
-#define GV_LAUNCH(SW)                                                                                   \
-        TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                      \
-            (rc = launch_grouped_gemv<TA, TW, TO, SW>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream)))))
-        if (swiglu) { GV_LAUNCH(true); } else { GV_LAUNCH(false); }
+#define GV_LAUNCH(TA, TW, TO)                                                                                     \
+        rc = swiglu ? launch_grouped_gemv<TA, TW, TO, true>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream) \
+                    : launch_grouped_gemv<TA, TW, TO, false>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream)
+        if (a_dtype == TQ_F32) GV_LAUNCH(float, float, float);
+        else if (c_dtype == TQ_F32) GV_LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+        else GV_LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
 #undef GV_LAUNCH
         if (rc) return rc;
         TQ_CHECK_LAUNCH("grouped_gemv");
