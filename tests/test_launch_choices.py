@@ -65,3 +65,27 @@ def test_attention_head_sizes():
     assert KA.split_usable(16, 1, 128, 64)             # 16 query heads per KV head: shared out over two CTAs
     assert not KA.split_usable(4, 4, 48, 64)           # head size 48: the exact kernel takes it
     assert KA.prefill_usable(__import__("torch").bfloat16, 128, 64) and not KA.prefill_usable(__import__("torch").float32, 128, 64)
+
+
+def test_shares_of_the_shared_down_projection():
+    """The sizes of the two real models: whole from the batch on where sharing it out was measured to cost, in shares
+    below; prompts (wide token tiles) never."""
+    from turboquant_cpp_b200.parts.moe_ffn import experts_touched, shared_down_shares
+    a = dict(n_experts=60, top_k=4, intermediate=1408, shared_intermediate=5632, hidden=2048, sms=148)
+    b = dict(n_experts=64, top_k=8, intermediate=2560, shared_intermediate=20480, hidden=3584, sms=148)
+    shares = lambda m, T, first=False: shared_down_shares(T, token_tile=KT.token_tile_for(T, 1), router_first=first, **m)
+    assert shares(a, 1) > 4 and shares(a, 2) > 4                    # the longer chain of the layer: over the whole GPU
+    assert [shares(a, T) for T in (3, 4, 5)] == [2, 2, 2]
+    assert [shares(a, T) for T in (6, 8, 12)] == [1, 1, 1]
+    assert shares(a, 16, first=True) > 1                            # the router ran first: beside the routed experts, shared out
+    assert shares(b, 1) > 8 and [shares(b, T) for T in (3, 4, 6)] == [4, 4, 4] and shares(b, 7) == 1
+    assert shares(a, 2048) == 1 and shares(b, 300) == 1
+    assert shared_down_shares(4, 8, 2, 64, 128, 64, 16, 148, False) == 1        # a tiny model: too short a K to share out
+    assert abs(experts_touched(1, 60, 4) - 4) < 1e-9 and 25 < experts_touched(8, 60, 4) < 26
+    assert experts_touched(10 ** 6, 60, 4) <= 60
+
+
+def test_when_the_shared_expert_rides_in_the_routed_launches():
+    from turboquant_cpp_b200.parts.moe_ffn import shared_rides_with_routed
+    assert [shared_rides_with_routed(T, 5632, 148) for T in (768, 1024, 1536, 2048, 8192)] == [True, True, True, False, False]
+    assert not shared_rides_with_routed(512, 20480, 148)            # the larger model's shared expert fills the GPU sooner

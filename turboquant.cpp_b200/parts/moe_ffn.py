@@ -30,6 +30,40 @@ def KA_resident(device) -> int:
     return resident_ctas(device) // 4
 
 
+def experts_touched(n_tokens: int, n_experts: int, top_k: int) -> float:
+    """Distinct experts a step of n_tokens tokens reads under uniform routing."""
+    return n_experts * (1.0 - ((n_experts - top_k) / n_experts) ** n_tokens)
+
+
+def shared_down_shares(n_tokens: int, n_experts: int, top_k: int, intermediate: int, shared_intermediate: int,
+                       hidden: int, token_tile: int, sms: int, router_first: bool, ratio: float = 14.0) -> int:
+    """Into how many shares of K the shared expert's down projection (hidden x shared_intermediate, a CTA per 128
+    output columns when whole) is cut in a decode step.
+      * one or two tokens, or the router runs ahead of the shared expert: as many shares as fill the GPU
+        (`k_splits_for`): the product is the longer of the layer's two chains;
+      * while the routed experts of the step read less than about `ratio` times this product's bytes: two shares (four
+        from 8,192 values of K on), so that it does not outlast the routed gate/up product beside it, whose persistent
+        CTAs were counted on the SM slots it holds;
+      * else one: shared out it would take SMs from the routed experts (3-10 % of the step).
+    Measured on B200, tokens/s whole / in shares: A2.7B sizes batch 3: 1,246 / 1,277, 4: 1,423 / 1,481, 5: 1,666 /
+    1,708, 6: 1,900 / 1,897, 8: 2,283 / 2,272; 57B-A14B sizes batch 1: 144 / 165, 3: 330 / 368, 4: 400 / 427, 6: 506 / 524."""
+    S = shared_intermediate
+    if token_tile > 64:
+        return 1                                   # wide token tiles (prompts) fill the GPU as they are
+    if n_tokens * top_k * intermediate <= 2 * S or router_first:
+        return KT.k_splits_for(n_tokens, hidden, S, token_tile, 2 * sms)
+    if experts_touched(n_tokens, n_experts, top_k) * 3 * intermediate <= ratio * S and S >= 32 * KT.BLOCK_K:
+        return 2 if S < 128 * KT.BLOCK_K else 4
+    return 1
+
+
+def shared_rides_with_routed(n_tokens: int, shared_intermediate: int, sms: int) -> bool:
+    """Whether a long step's shared expert has so few rounds of tiles (fewer than four per CTA pair in its gate/up
+    product, at the widest token tile) that its tiles ride in the routed experts' launches."""
+    units = -(-n_tokens // KT.TOKEN_TILES[-1]) * -(-shared_intermediate // KT.BLOCK_ROWS)
+    return units < 4 * (sms // 2)
+
+
 class MoEFeedForward(FeedForward):
     # steps with at least this many tokens (and too many pairs for the one-launch router) compute router logits on
     # tensor cores (measured on B200 at 64 tokens: +2.4 % on the step at the 57B-A14B sizes, +0.8 % at the A2.7B sizes)
@@ -119,7 +153,7 @@ class MoEFeedForward(FeedForward):
     def step_work(self, n_tokens, kv_tokens):
         E, k, H, I, S = self.n_experts, self.top_k, self.hidden, self.intermediate, self.shared_intermediate
         el = 4 if getattr(self, "run_dtype", None) == torch.float32 else 2
-        touched = E * (1.0 - ((E - k) / E) ** n_tokens)          # distinct experts under uniform routing
+        touched = experts_touched(n_tokens, E, k)
         byt = el * (touched * 3 * H * I + 3 * H * S + (E + 1) * H)
         return {"moe": (byt, 2.0 * n_tokens * (k * 3 * H * I + 3 * H * S + (E + 1) * H))}
 
@@ -164,8 +198,7 @@ class MoEFeedForward(FeedForward):
             return False
         if how != "":
             return True
-        units = -(-T // KT.TOKEN_TILES[-1]) * -(-self.shared_intermediate // KT.BLOCK_ROWS)    # the shared gate/up product's tiles
-        return units < 4 * (KA_resident(dev) // 2)
+        return shared_rides_with_routed(T, self.shared_intermediate, KA_resident(dev))
 
     def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H, k, dev = xn.shape[0], self.hidden, self.top_k, xn.device
@@ -202,26 +235,10 @@ class MoEFeedForward(FeedForward):
             with torch.cuda.stream(side):
                 hs = torch.empty((T, S), dtype=act, device=dev)
                 self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
-                # The down projection has few tiles (rows of 128 output columns) and a long K: a handful of SMs stream
-                # all its weights (measured on B200: 0.8 TB/s at 2,048 x 5,632, 1.5 TB/s at 3,584 x 20,480).  While the
-                # routed experts read several times the shared expert's bytes on the main stream that does not
-                # matter, the shared expert ends first either way; with one or two tokens it is the longer chain.
-                # Then its K is shared out over the GPU and the partial sums are added up where the experts'
-                # outputs are summed anyway (measured at the 57B-A14B sizes, batch 1: 144 -> 165 tokens/s; sharing
-                # it out at larger batches takes SMs from the routed experts and costs 3-10 %).
-                few = T * k * self.intermediate <= 2 * S or shared_after
-                splits = KT.k_splits_for(T, H, S, stile, 2 * KA_resident(dev)) if few and isinstance(self.ws2, KT.PackedWeights) else 1
-                # Between the two: while the routed experts of the step read less than about 14 times the shared down
-                # projection's bytes, the unsplit product (a CTA per 128 output columns, 50-150 us) outlasts the routed
-                # gate/up product beside it and holds SM slots that product's persistent CTAs were counted on; in two
-                # or four shares it is out of the way sooner.  Measured on B200, tokens/s without / with: A2.7B sizes
-                # batch 3: 1,246 / 1,277, 4: 1,423 / 1,481, 5: 1,666 / 1,708, 6: 1,900 / 1,897, 8: 2,283 / 2,272;
-                # 57B-A14B sizes batch 4: 400 / 427, 6: 506 / 524.
-                E = self.n_experts
-                touched = E * (1.0 - ((E - k) / E) ** T)          # distinct experts under uniform routing
-                if (splits == 1 and not few and stile <= 64 and isinstance(self.ws2, KT.PackedWeights)
-                        and touched * 3 * self.intermediate <= self.SHARED_DOWN_SPLIT_RATIO * S and S >= 32 * KT.BLOCK_K):
-                    splits = 2 if S < 128 * KT.BLOCK_K else 4
+                splits = 1
+                if isinstance(self.ws2, KT.PackedWeights):
+                    splits = shared_down_shares(T, self.n_experts, k, self.intermediate, S, H, stile, KA_resident(dev),
+                                                shared_after, self.SHARED_DOWN_SPLIT_RATIO)
                 y_shared = torch.empty((splits, T, H) if splits > 1 else (T, H), dtype=torch.float32, device=dev)
                 if splits > 1:
                     KT.gemm_tc(hs, self.ws2, y_shared, None, stile, status=ctx.status, k_splits=splits, early_weights=self.EARLY_WEIGHTS)
