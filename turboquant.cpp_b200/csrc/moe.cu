@@ -1057,19 +1057,20 @@ grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
 }
 
 // ---------------------------------------------------------------------------------------
-// The same product for tiles of a few rows (decode steps), as a stream of the weights: a block stages up to
+// The same product for tiles of a few rows (decode steps), as a stream of the weights: a block stages
 // GV_ROWS rows of its tile in shared memory (in pieces of GV_KC values of K) and each warp computes one output
 // column (with SwiGLU: from a gate and an up row) for all of them, a lane taking every 32nd group of four values of K, the lanes' sums added by shuffles.
 // The tiled kernel above reads a 64-row tile's worth of weights for however few rows the tile holds and keeps few
 // loads in flight; this one keeps several 16-byte pieces of a weight row in flight per lane (measured on B200 in
-// float32 at 60 experts of 1408 x 2048 with a shared expert of 5632: a decode step of 8 tokens 39.0 -> 21 ms, of one
-// token 18.8 -> 5.6 ms; four columns per warp were 10 % faster at 8 tokens and took six times as long to compile).  fp32 multiply-adds in a fixed order that
+// float32 at 60 experts of 1408 x 2048: a decode step of 8 tokens 39.0 -> 14.5 ms, of one token 18.8 -> 3.0 ms with
+// two rows per pass and eight pieces in flight; eight rows and four pieces: 21 and 5.6 ms; four output columns per warp
+// were 10 % faster than one at 8 tokens and took six times as long to compile).  fp32 multiply-adds in a fixed order that
 // depends on K alone: a row's result does not depend on the tile it falls in or on the rest of the batch.
 // ---------------------------------------------------------------------------------------
-#define GV_ROWS 8
+#define GV_ROWS 2
 #define GV_WARPS 8
-#define GV_KC 2048                 // values of K per piece: 8 rows x 2048 floats = 64 KiB of shared memory
-#define GV_FLY 4                   // 16-byte pieces of a weight row a lane has in flight
+#define GV_KC 2048                 // values of K per piece: 4 rows x 2048 floats = 32 KiB of shared memory
+#define GV_FLY 8                   // 16-byte pieces of a weight row a lane has in flight
 
 // four weights at p as floats (16-byte or 8-byte load; the caller made sure of the alignment)
 template <typename T> __device__ __forceinline__ float4 gv_load4(const T* p);

@@ -20,6 +20,7 @@ import torch
 from ..kernels import elementwise as KE
 from ..kernels import gemm_tc as KT
 from ..kernels import moe as KM
+from ..kernels.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 from .base import FeedForward, StepContext, register_feed_forward
 
@@ -167,6 +168,7 @@ class MoEFeedForward(FeedForward):
         return cls._side_streams[key]
 
     EARLY_WEIGHTS = os.environ.get("TQ_EARLY_WEIGHTS", "1") not in ("", "0")
+    EXACT_SHARED_ROWS = 2        # rows of the shared expert that the exact weight-stream kernel takes in one pass
     EXACT_FEW_ROWS = int(os.environ.get("TQ_EXACT_FEW_ROWS", "16"))      # steps of up to this many tokens take the exact kernels' weight-stream form
 
     def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False):
@@ -234,6 +236,14 @@ class MoEFeedForward(FeedForward):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 hs = torch.empty((T, S), dtype=act, device=dev)
+                if not isinstance(self.ws13, KT.PackedWeights) and T > self.EXACT_SHARED_ROWS:
+                    # unpacked weights (float32 runs, sizes the tensor-core kernel does not take) and more rows than
+                    # one pass of the exact weight-stream kernel holds: the shared expert is a dense feed-forward, and
+                    # the library's products serve it as they serve the dense layers
+                    gu = linear(xn, self.ws13[0], out_dtype=torch.float32)
+                    KE.silu_mul(gu, hs)
+                    y_shared = linear(hs, self.ws2[0], out_dtype=torch.float32)
+                    return
                 self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
                 splits = 1
                 if isinstance(self.ws2, KT.PackedWeights):
