@@ -23,6 +23,7 @@ Only one GPU is supported: for --gpus N > 1 a line says so and the exit code is 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -222,7 +223,9 @@ def main() -> int:
         ctx_mid = ctx_tokens + batch * steps // 2
         for s in seqs:
             eng.close(s)
+        eng.release()             # the engine's graphs point back at it: without this its cache would stay until a collection
         del eng
+        gc.collect()
         torch.cuda.empty_cache()
         return dict(ms_per_step=ms / steps, tok_s=batch * steps / ms * 1e3, launches=launches, distinct=distinct,
                     ctx_tokens=ctx_mid)
@@ -288,7 +291,9 @@ def main() -> int:
             if i > 0:
                 best = min(best, a.elapsed_time(b))
             eng.close(s)
+        eng.release()
         del eng
+        gc.collect()
         torch.cuda.empty_cache()
         fl = prefill_flops(n, PROMPT)
         out["prefill"] = {"value": round(PROMPT / best * 1e3, 1), "tokens": PROMPT, "ms": round(best, 3),
