@@ -169,7 +169,7 @@ class MoEFeedForward(FeedForward):
 
     EARLY_WEIGHTS = os.environ.get("TQ_EARLY_WEIGHTS", "1") not in ("", "0")
     EXACT_SHARED_ROWS = 2        # rows of the shared expert that the exact weight-stream kernel takes in one pass
-    EXACT_FEW_ROWS = int(os.environ.get("TQ_EXACT_FEW_ROWS", "16"))      # steps of up to this many tokens take the exact kernels' weight-stream form
+    EXACT_FEW_ROWS = int(os.environ.get("TQ_EXACT_FEW_ROWS", "64"))      # steps of up to this many tokens take the exact kernels' weight-stream form
 
     def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
